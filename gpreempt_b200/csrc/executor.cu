@@ -1,0 +1,210 @@
+// Executors: replay a model's kernel list on a stream, optionally with block-level preemption.
+// Counterpart of src/executor.cpp in the reference: Executor::execute (:119-134),
+// launch_kernel (:136-164), capture_graph (:176-196), BLPExecutor::execute (:211-232),
+// getStopPoint (:269-278), resume (:280-298), init (:300-342).
+#include "executor.h"
+
+#include <vector>
+
+using namespace gpx;
+
+namespace gpx {
+
+BlpArgs exec_blp_args(gpx_exec *e, size_t idx) {
+    BlpArgs b{};
+    const Kernel &k = e->model->kernels[idx];
+    b.total_tiles = k.total_tiles;
+    b.kernel_id = (int)idx;
+    if (e->kind == GPX_EXEC_BLP) {
+        b.preempted = e->word_dptr;
+        b.stop_index = e->d_stop_index;
+        b.executed = e->d_executed + idx;
+    }
+    if (e->trace_on) b.trace = e->d_trace + 4 * idx;
+    return b;
+}
+
+int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
+    const Kernel &k = e->model->kernels[idx];
+    BlpArgs b = exec_blp_args(e, idx);
+    cudaError_t err = k.is_conv ? conv_launch(k.conv, k.tile, k.grid, b, s)
+                                : pool_launch(k.pool, k.grid, b, s);
+    if (err != cudaSuccess) {
+        set_error("launch of kernel %zu (%s) failed: %s", idx, k.name.c_str(),
+                  cudaGetErrorString(err));
+        return GPX_FAIL;
+    }
+    return GPX_SUCC;
+}
+
+}  // namespace gpx
+
+extern "C" {
+
+int gpx_exec_create(gpx_model *m, int kind, gpx_exec **out) {
+    GPX_REQUIRE(m && out, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(kind == GPX_EXEC_BASE || kind == GPX_EXEC_BLP, GPX_OUT_OF_RANGE,
+                "unknown executor kind %d", kind);
+    gpx_exec *e = new gpx_exec();
+    e->model = m;
+    e->kind = kind;
+    size_t nk = m->kernels.size();
+    // dpStopIndex and executed[] are owned by the executor (src/executor.cpp:329-333).
+    GPX_CUDA(cudaMalloc((void **)&e->d_stop_index, 256));
+    GPX_CUDA(cudaMalloc((void **)&e->d_executed, sizeof(int) * (nk + 1)));
+    GPX_CUDA(cudaMalloc((void **)&e->d_trace, sizeof(uint64_t) * 4 * (nk + 1)));
+    GPX_CUDA(cudaHostAlloc((void **)&e->h_stop_index, 64, cudaHostAllocPortable));
+    GPX_CUDA(cudaHostAlloc((void **)&e->h_minus_one, 64, cudaHostAllocPortable));
+    GPX_CUDA(cudaHostAlloc((void **)&e->h_trace_init, sizeof(uint64_t) * 4 * (nk + 1),
+                           cudaHostAllocPortable));
+    *e->h_stop_index = -1;
+    *e->h_minus_one = -1;
+    for (size_t i = 0; i < nk + 1; ++i) {
+        e->h_trace_init[4 * i + 0] = ~0ull;
+        e->h_trace_init[4 * i + 1] = 0;
+        e->h_trace_init[4 * i + 2] = ~0ull;
+        e->h_trace_init[4 * i + 3] = 0;
+    }
+    GPX_CUDA(cudaMemcpy(e->d_stop_index, e->h_minus_one, sizeof(int), cudaMemcpyHostToDevice));
+    GPX_CUDA(cudaMemset(e->d_executed, 0, sizeof(int) * (nk + 1)));
+    GPX_CUDA(cudaMemcpy(e->d_trace, e->h_trace_init, sizeof(uint64_t) * 4 * (nk + 1),
+                        cudaMemcpyHostToDevice));
+    *out = e;
+    return GPX_SUCC;
+}
+
+int gpx_exec_destroy(gpx_exec *e) {
+    if (!e) return GPX_SUCC;
+    if (e->graph_exec) cudaGraphExecDestroy(e->graph_exec);
+    if (e->graph) cudaGraphDestroy(e->graph);
+    cudaFree(e->d_stop_index);
+    cudaFree(e->d_executed);
+    cudaFree(e->d_trace);
+    cudaFreeHost(e->h_stop_index);
+    cudaFreeHost(e->h_minus_one);
+    cudaFreeHost(e->h_trace_init);
+    delete e;
+    return GPX_SUCC;
+}
+
+int gpx_exec_set_word(gpx_exec *e, gpx_word *w) {
+    GPX_REQUIRE(e && w, GPX_FAIL, "NULL argument");
+    void *d = nullptr;
+    GPX_TRY(gpx_word_dptr(w, &d));
+    GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "set the preempt word before capturing the graph");
+    e->word_dptr = (const int *)d;
+    return GPX_SUCC;
+}
+
+int gpx_exec_enable_trace(gpx_exec *e, int on) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "enable tracing before capturing the graph");
+    e->trace_on = on != 0;
+    return GPX_SUCC;
+}
+
+static int exec_prologue(gpx_exec *e, cudaStream_t s) {
+    size_t nk = e->model->kernels.size();
+    if (e->kind == GPX_EXEC_BLP) {
+        GPX_REQUIRE(e->word_dptr, GPX_FAIL, "BLP executor has no preempt word (gpx_exec_set_word)");
+        // BLPExecutor::execute zeroes executed[] first (src/executor.cpp:212-214).
+        GPX_CUDA(cudaMemsetAsync(e->d_executed, 0, sizeof(int) * nk, s));
+    }
+    if (e->trace_on)
+        GPX_CUDA(cudaMemcpyAsync(e->d_trace, e->h_trace_init, sizeof(uint64_t) * 4 * nk,
+                                 cudaMemcpyHostToDevice, s));
+    return GPX_SUCC;
+}
+
+int gpx_exec_execute(gpx_exec *e, gpx_stream stream) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    cudaStream_t s = as_stream(stream);
+    if (e->graph_exec) {
+        GPX_CUDA(cudaGraphLaunch(e->graph_exec, s));
+        return GPX_SUCC;
+    }
+    GPX_TRY(exec_prologue(e, s));
+    size_t nk = e->model->kernels.size();
+    for (size_t i = 0; i < nk; ++i) GPX_TRY(exec_launch(e, i, s));
+    return GPX_SUCC;
+}
+
+int gpx_exec_launch_kernel(gpx_exec *e, size_t idx, gpx_stream s) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    GPX_REQUIRE(idx < e->model->kernels.size(), GPX_OUT_OF_RANGE, "kernel index %zu out of range",
+                idx);
+    if (e->kind == GPX_EXEC_BLP)
+        GPX_REQUIRE(e->word_dptr, GPX_FAIL, "BLP executor has no preempt word");
+    return exec_launch(e, idx, as_stream(s));
+}
+
+int gpx_exec_capture_graph(gpx_exec *e, gpx_stream stream) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    GPX_REQUIRE(stream, GPX_FAIL, "graph capture needs a non-default stream");
+    GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "graph already captured");
+    cudaStream_t s = as_stream(stream);
+    GPX_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int st = exec_prologue(e, s);
+    size_t nk = e->model->kernels.size();
+    for (size_t i = 0; st == GPX_SUCC && i < nk; ++i) st = exec_launch(e, i, s);
+    cudaError_t err = cudaStreamEndCapture(s, &e->graph);
+    if (st != GPX_SUCC) return st;
+    GPX_CUDA(err);
+    GPX_CUDA(cudaGraphInstantiate(&e->graph_exec, e->graph, 0));
+    return GPX_SUCC;
+}
+
+int gpx_exec_stop_point(gpx_exec *e, gpx_stream stream, int *stop_index) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    cudaStream_t s = as_stream(stream);
+    if (e->kind != GPX_EXEC_BLP) {
+        GPX_CUDA(cudaStreamSynchronize(s));
+        if (stop_index) *stop_index = -1;
+        return GPX_SUCC;
+    }
+    GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
+                             cudaMemcpyDeviceToHost, s));
+    GPX_CUDA(cudaStreamSynchronize(s));
+    int v = *e->h_stop_index;
+    if (v != -1)
+        GPX_CUDA(cudaMemcpyAsync(e->d_stop_index, e->h_minus_one, sizeof(int),
+                                 cudaMemcpyHostToDevice, s));
+    e->stop_index = v;
+    if (stop_index) *stop_index = v;
+    return GPX_SUCC;
+}
+
+int gpx_exec_resume(gpx_exec *e, gpx_stream stream, int *resumed_from) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    int v = -1;
+    GPX_TRY(gpx_exec_stop_point(e, stream, &v));
+    if (resumed_from) *resumed_from = v;
+    if (v < 0) return GPX_SUCC;
+    size_t nk = e->model->kernels.size();
+    GPX_REQUIRE((size_t)v < nk, GPX_FAIL, "stop index %d outside the kernel list", v);
+    cudaStream_t s = as_stream(stream);
+    for (size_t i = (size_t)v; i < nk; ++i) GPX_TRY(exec_launch(e, i, s));
+    return GPX_SUCC;
+}
+
+int gpx_exec_read_trace(gpx_exec *e, uint64_t *out, size_t cap_u64, size_t *n_u64) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    size_t n = 4 * e->model->kernels.size();
+    if (n_u64) *n_u64 = n;
+    if (!out) return GPX_SUCC;
+    GPX_REQUIRE(cap_u64 >= n, GPX_OUT_OF_RANGE, "trace needs %zu slots, %zu given", n, cap_u64);
+    GPX_CUDA(cudaMemcpy(out, e->d_trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    return GPX_SUCC;
+}
+
+int gpx_exec_read_cursors(gpx_exec *e, int *out, size_t cap, size_t *n_out) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    size_t n = e->model->kernels.size();
+    if (n_out) *n_out = n;
+    if (!out) return GPX_SUCC;
+    GPX_REQUIRE(cap >= n, GPX_OUT_OF_RANGE, "cursors need %zu slots, %zu given", n, cap);
+    GPX_CUDA(cudaMemcpy(out, e->d_executed, n * sizeof(int), cudaMemcpyDeviceToHost));
+    return GPX_SUCC;
+}
+
+}  // extern "C"

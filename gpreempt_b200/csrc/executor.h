@@ -1,0 +1,26 @@
+// Executor state: the native counterpart of foo::Executor / foo::BLPExecutor
+// (include/executor.h:14-84 in the reference).
+#pragma once
+
+#include "model.h"
+
+struct gpx_exec {
+    gpx_model *model = nullptr;
+    int kind = GPX_EXEC_BASE;
+    const int *word_dptr = nullptr;   // BLPExecutor::dpStop, owned by the caller
+    int *d_stop_index = nullptr;      // BLPExecutor::dpStopIndex
+    int *d_executed = nullptr;        // BLPExecutor::executed, one cursor per kernel
+    unsigned long long *d_trace = nullptr;
+    int *h_stop_index = nullptr;      // pinned landing slot of the stop index
+    int *h_minus_one = nullptr;       // pinned -1 used to re-arm the stop index
+    unsigned long long *h_trace_init = nullptr;
+    int stop_index = -1;
+    bool trace_on = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+};
+
+namespace gpx {
+BlpArgs exec_blp_args(gpx_exec *e, size_t idx);
+int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s);
+}  // namespace gpx

@@ -1,0 +1,740 @@
+// Model runtime: built-in graphs, storages, parameter files, name-addressed tensor I/O and
+// the kernel list.  Counterpart of src/model.cpp in the reference (Model::load_model :79-125,
+// load_from_json :128-235, load_param :263-282, get/set :288-321, ModelParamParser :15-55).
+#include "model.h"
+#include "json.h"
+
+#include <algorithm>
+#include <cmath>
+#include <memory>
+
+using namespace gpx;
+
+int gpx_model::add_storage(const Storage &s) {
+    storage_idx[s.name] = storages.size();
+    storages.push_back(s);
+    return (int)storages.size() - 1;
+}
+
+int gpx_model::find(const std::string &n) const {
+    auto it = storage_idx.find(n);
+    return it == storage_idx.end() ? -1 : (int)it->second;
+}
+
+namespace gpx {
+
+// ---- seeded synthetic data ------------------------------------------------------------------
+// Counter-based generator: element i of stream t under seed s is a pure function of (s, t, i),
+// so tensors can be produced in any order and on any number of threads.
+
+static inline uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+static inline uint64_t counter_bits(uint64_t seed, uint64_t stream, uint64_t i) {
+    return mix64(mix64(seed * 0xD1342543DE82EF95ull + stream) ^ (i * 0x2545F4914F6CDD1Dull + 1));
+}
+
+void normal_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std) {
+    const double two_pi = 6.283185307179586476925286766559;
+    for (size_t i = 0; i < n; ++i) {
+        uint64_t h = counter_bits(seed, stream, i);
+        double u1 = ((double)(uint32_t)(h >> 32) + 1.0) * (1.0 / 4294967296.0);  // (0, 1]
+        double u2 = (double)(uint32_t)h * (1.0 / 4294967296.0);                  // [0, 1)
+        double z = std::sqrt(-2.0 * std::log(u1)) * std::cos(two_pi * u2);
+        dst[i] = (float)(mean + std * z);
+    }
+}
+
+void uniform_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float lo, float hi) {
+    for (size_t i = 0; i < n; ++i) {
+        uint64_t h = counter_bits(seed, stream, i);
+        double u = (double)(h >> 11) * (1.0 / 9007199254740992.0);  // [0, 1)
+        dst[i] = (float)(lo + (hi - lo) * u);
+    }
+}
+
+// ---- graph construction ---------------------------------------------------------------------
+
+struct GraphBuilder {
+    gpx_model &m;
+    explicit GraphBuilder(gpx_model &model) : m(model) {}
+
+    int add_act(const std::string &name, int N, int C, int H, int W, Storage::Kind kind) {
+        Storage s;
+        s.name = name;
+        s.kind = kind;
+        if (H == 1 && W == 1 && kind != Storage::ActCanonical) {
+            // [N][C] is the same in NHWC and NCHW.
+            s.kind = Storage::ActCanonical;
+        }
+        if (H == 1 && W == 1) {
+            s.rank = 2;
+            s.dims[0] = N;
+            s.dims[1] = C;
+        } else {
+            s.rank = 4;
+            s.dims[0] = N;
+            s.dims[1] = C;
+            s.dims[2] = H;
+            s.dims[3] = W;
+        }
+        s.bytes = (size_t)N * C * H * W * sizeof(float);
+        return m.add_storage(s);
+    }
+
+    int input(const std::string &name, int N, int C, int H, int W) {
+        Node n;
+        n.name = name;
+        n.op = Op::Input;
+        n.N = N;
+        n.H = H;
+        n.W = W;
+        n.C = C;
+        n.storage = add_act(name, N, C, H, W, Storage::ActCanonical);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    int conv(const std::string &name, int in, int cout, int k, int stride, int pad, bool relu,
+             int residual = -1, const std::string &param_prefix = "") {
+        const Node &src = m.nodes[in];
+        Node n;
+        n.name = name;
+        n.op = Op::Conv;
+        n.inputs.push_back(in);
+        if (residual >= 0) n.inputs.push_back(residual);
+        n.residual = residual;
+        n.k = k;
+        n.stride = stride;
+        n.pad = pad;
+        n.relu = relu;
+        n.N = src.N;
+        n.H = (src.H + 2 * pad - k) / stride + 1;
+        n.W = (src.W + 2 * pad - k) / stride + 1;
+        n.C = cout;
+        const std::string pp = param_prefix.empty() ? name : param_prefix;
+        Storage w;
+        w.name = pp + ".weight";
+        w.kind = Storage::Weight;
+        w.is_param = true;
+        w.rank = 4;
+        w.dims[0] = cout;
+        w.dims[1] = src.C;
+        w.dims[2] = k;
+        w.dims[3] = k;
+        w.bytes = (size_t)cout * src.C * k * k * sizeof(float);
+        w.fan_in = src.C * k * k;
+        n.weight = m.add_storage(w);
+        Storage b;
+        b.name = pp + ".bias";
+        b.kind = Storage::Vec;
+        b.is_param = true;
+        b.rank = 1;
+        b.dims[0] = cout;
+        b.bytes = (size_t)cout * sizeof(float);
+        n.bias = m.add_storage(b);
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActNHWC);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    // Fully connected layer over the flattened (C, H, W) input: a convolution whose filter
+    // covers the whole feature map, so the canonical weight [out][C*H*W] is its OIHW filter.
+    int dense(const std::string &name, int in, int cout, bool relu) {
+        const Node &src = m.nodes[in];
+        return conv(name, in, cout, src.H, 1, 0, relu);
+    }
+
+    int pool(const std::string &name, int in, Op op, int k, int stride, int pad) {
+        const Node &src = m.nodes[in];
+        Node n;
+        n.name = name;
+        n.op = op;
+        n.inputs.push_back(in);
+        n.k = k;
+        n.stride = stride;
+        n.pad = pad;
+        n.N = src.N;
+        n.C = src.C;
+        n.H = (src.H + 2 * pad - k) / stride + 1;
+        n.W = (src.W + 2 * pad - k) / stride + 1;
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActNHWC);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+};
+
+// ResNet v1.5 with bottleneck blocks (stride on the 3x3 convolution), batch norm folded into
+// each convolution's bias.  layers = {3,4,6,3} gives ResNet-50, {3,8,36,3} ResNet-152.
+static void build_resnet(gpx_model &m, int batch, const int layers[4]) {
+    GraphBuilder g(m);
+    int x = g.input("data", batch, 3, 224, 224);
+    x = g.conv("conv1", x, 64, 7, 2, 3, true);
+    x = g.pool("maxpool", x, Op::MaxPool, 3, 2, 1);
+    int planes = 64;
+    for (int l = 0; l < 4; ++l) {
+        for (int b = 0; b < layers[l]; ++b) {
+            std::string p = "layer" + std::to_string(l + 1) + "." + std::to_string(b);
+            int stride = (b == 0 && l > 0) ? 2 : 1;
+            int identity = x;
+            if (b == 0) identity = g.conv(p + ".downsample", x, planes * 4, 1, stride, 0, false);
+            int y = g.conv(p + ".conv1", x, planes, 1, 1, 0, true);
+            y = g.conv(p + ".conv2", y, planes, 3, stride, 1, true);
+            x = g.conv(p + ".conv3", y, planes * 4, 1, 1, 0, true, identity);
+        }
+        planes *= 2;
+    }
+    x = g.pool("avgpool", x, Op::AvgPool, 7, 1, 0);
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "fc");
+    m.head_node = x;
+}
+
+// VGG configuration D/E: 3x3 convolutions + ReLU, 2x2 max pooling, three dense layers.
+static void build_vgg(gpx_model &m, int batch, const int *cfg, int ncfg) {
+    GraphBuilder g(m);
+    int x = g.input("data", batch, 3, 224, 224);
+    int ci = 0, pi = 0;
+    for (int i = 0; i < ncfg; ++i) {
+        if (cfg[i] == 0) {
+            x = g.pool("pool" + std::to_string(pi++), x, Op::MaxPool, 2, 2, 0);
+        } else {
+            x = g.conv("features." + std::to_string(ci++), x, cfg[i], 3, 1, 1, true);
+        }
+    }
+    x = g.dense("classifier.0", x, 4096, true);
+    x = g.dense("classifier.3", x, 4096, true);
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "classifier.6");
+    m.head_node = x;
+}
+
+int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts) {
+    int batch = opts.batch > 0 ? opts.batch : 1;
+    m.batch = batch;
+    if (opts.dtype && opts.dtype[0] && std::string(opts.dtype) != "float32") {
+        set_error("dtype '%s' is not available for model '%s' (float32 only)", opts.dtype,
+                  name.c_str());
+        return GPX_NOT_FOUND;
+    }
+    if (name == "resnet50") {
+        const int l[4] = {3, 4, 6, 3};
+        build_resnet(m, batch, l);
+    } else if (name == "resnet152") {
+        const int l[4] = {3, 8, 36, 3};
+        build_resnet(m, batch, l);
+    } else if (name == "resnet_tiny") {
+        // Two-stage miniature with the same block structure, for fast tests.
+        const int l[4] = {1, 1, 1, 1};
+        build_resnet(m, batch, l);
+    } else if (name == "vgg16") {
+        const int cfg[] = {64, 64, 0, 128, 128, 0, 256, 256, 256, 0, 512, 512, 512, 0, 512, 512, 512, 0};
+        build_vgg(m, batch, cfg, (int)(sizeof(cfg) / sizeof(int)));
+    } else if (name == "vgg" || name == "vgg19") {
+        const int cfg[] = {64, 64, 0, 128, 128, 0, 256, 256, 256, 256, 0, 512, 512, 512, 512, 0,
+                           512, 512, 512, 512, 0};
+        build_vgg(m, batch, cfg, (int)(sizeof(cfg) / sizeof(int)));
+    } else {
+        set_error("unknown model '%s'", name.c_str());
+        return GPX_NOT_FOUND;
+    }
+    m.name = name;
+    return GPX_SUCC;
+}
+
+// ---- storages and kernel list ---------------------------------------------------------------
+
+int finalize_model(gpx_model &m) {
+    const DeviceInfo &d = device_info();
+    GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
+    m.device = d.device;
+    m.sm_count = d.sm_count;
+    // One device buffer per storage, zero-filled, no sharing (src/model.cpp:101-113).
+    for (auto &s : m.storages) {
+        GPX_CUDA(cudaMalloc((void **)&s.dptr, s.bytes));
+        GPX_CUDA(cudaMemset(s.dptr, 0, s.bytes));
+    }
+    for (size_t ni = 0; ni < m.nodes.size(); ++ni) {
+        const Node &n = m.nodes[ni];
+        if (n.op == Op::Input) continue;
+        const Node &src = m.nodes[n.inputs[0]];
+        Kernel k;
+        k.name = n.name;
+        k.node = (int)ni;
+        if (n.op == Op::Conv) {
+            GPX_REQUIRE(n.C % 4 == 0, GPX_FAIL, "%s: Cout %d not a multiple of 4", n.name.c_str(),
+                        n.C);
+            ConvParams &p = k.conv;
+            p.in = m.storages[src.storage].dptr;
+            p.w = m.storages[n.weight].dptr;
+            p.bias = m.storages[n.bias].dptr;
+            p.res = n.residual >= 0 ? m.storages[m.nodes[n.residual].storage].dptr : nullptr;
+            p.out = m.storages[n.storage].dptr;
+            p.N = src.N;
+            p.H = src.H;
+            p.W = src.W;
+            p.Cin = src.C;
+            p.Ho = n.H;
+            p.Wo = n.W;
+            p.Cout = n.C;
+            p.kh = p.kw = n.k;
+            p.stride = n.stride;
+            p.pad = n.pad;
+            p.M = n.N * n.H * n.W;
+            p.K = n.k * n.k * src.C;
+            p.relu = n.relu ? 1 : 0;
+            p.in_nchw = (src.op == Op::Input && (src.H > 1 || src.W > 1)) ? 1 : 0;
+            k.is_conv = true;
+            k.tile = conv_pick_tile(p, m.sm_count);
+            conv_set_tiles(p, k.tile);
+            k.total_tiles = p.tiles_m * p.tiles_n;
+            k.grid = conv_grid(p, k.tile, m.sm_count, true);
+            k.flops = 2.0 * p.M * (double)p.K * p.Cout;
+            k.bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)p.K * p.Cout +
+                             (double)p.M * p.Cout * (p.res ? 2 : 1));
+        } else {
+            GPX_REQUIRE(n.C % 4 == 0, GPX_FAIL, "%s: C %d not a multiple of 4", n.name.c_str(), n.C);
+            PoolParams &p = k.pool;
+            p.in = m.storages[src.storage].dptr;
+            p.out = m.storages[n.storage].dptr;
+            p.N = src.N;
+            p.H = src.H;
+            p.W = src.W;
+            p.C = src.C;
+            p.Ho = n.H;
+            p.Wo = n.W;
+            p.k = n.k;
+            p.stride = n.stride;
+            p.pad = n.pad;
+            p.mode = n.op == Op::MaxPool ? 0 : 1;
+            p.tile_elems = 2048;
+            long long total = (long long)n.N * n.H * n.W * (n.C / 4);
+            p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
+            k.is_conv = false;
+            k.total_tiles = p.total_tiles;
+            k.grid = pool_grid(p, m.sm_count);
+            k.flops = (double)total * 4 * n.k * n.k;
+            k.bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)total * 4);
+        }
+        m.kernels.push_back(k);
+    }
+    return GPX_SUCC;
+}
+
+// ---- layout transforms between canonical (NCHW / OIHW) and device layouts -------------------
+
+static void nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W) {
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c)
+            for (int h = 0; h < H; ++h)
+                for (int w = 0; w < W; ++w)
+                    dst[(((size_t)n * H + h) * W + w) * C + c] =
+                        src[(((size_t)n * C + c) * H + h) * W + w];
+}
+static void nhwc_to_nchw(const float *src, float *dst, int N, int C, int H, int W) {
+    for (int n = 0; n < N; ++n)
+        for (int h = 0; h < H; ++h)
+            for (int w = 0; w < W; ++w)
+                for (int c = 0; c < C; ++c)
+                    dst[(((size_t)n * C + c) * H + h) * W + w] =
+                        src[(((size_t)n * H + h) * W + w) * C + c];
+}
+static void oihw_to_khwc_o(const float *src, float *dst, int O, int I, int KH, int KW) {
+    for (int o = 0; o < O; ++o)
+        for (int i = 0; i < I; ++i)
+            for (int h = 0; h < KH; ++h)
+                for (int w = 0; w < KW; ++w)
+                    dst[(((size_t)h * KW + w) * I + i) * O + o] =
+                        src[(((size_t)o * I + i) * KH + h) * KW + w];
+}
+static void khwc_o_to_oihw(const float *src, float *dst, int O, int I, int KH, int KW) {
+    for (int o = 0; o < O; ++o)
+        for (int i = 0; i < I; ++i)
+            for (int h = 0; h < KH; ++h)
+                for (int w = 0; w < KW; ++w)
+                    dst[(((size_t)o * I + i) * KH + h) * KW + w] =
+                        src[(((size_t)h * KW + w) * I + i) * O + o];
+}
+
+static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, cudaStream_t st) {
+    // Model::set, src/model.cpp:313-321: `len < size` is rejected.
+    GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "set %s: %zu bytes given, %zu needed",
+                s.name.c_str(), len, s.bytes);
+    (void)m;
+    if (s.kind == Storage::ActCanonical || s.kind == Storage::Vec) {
+        GPX_CUDA(cudaMemcpyAsync(s.dptr, host, s.bytes, cudaMemcpyHostToDevice, st));
+        return GPX_SUCC;
+    }
+    std::vector<float> tmp(s.bytes / sizeof(float));
+    if (s.kind == Storage::ActNHWC)
+        nchw_to_nhwc((const float *)host, tmp.data(), (int)s.dims[0], (int)s.dims[1],
+                     (int)s.dims[2], (int)s.dims[3]);
+    else
+        oihw_to_khwc_o((const float *)host, tmp.data(), (int)s.dims[0], (int)s.dims[1],
+                       (int)s.dims[2], (int)s.dims[3]);
+    // The staging vector dies at return, so this copy completes before returning.
+    GPX_CUDA(cudaMemcpyAsync(s.dptr, tmp.data(), s.bytes, cudaMemcpyHostToDevice, st));
+    GPX_CUDA(cudaStreamSynchronize(st));
+    return GPX_SUCC;
+}
+
+static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStream_t st) {
+    // Model::get, src/model.cpp:296-305.
+    GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "get %s: %zu bytes given, %zu needed",
+                s.name.c_str(), len, s.bytes);
+    (void)m;
+    if (s.kind == Storage::ActCanonical || s.kind == Storage::Vec) {
+        GPX_CUDA(cudaMemcpyAsync(host, s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
+        return GPX_SUCC;
+    }
+    std::vector<float> tmp(s.bytes / sizeof(float));
+    GPX_CUDA(cudaMemcpyAsync(tmp.data(), s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
+    GPX_CUDA(cudaStreamSynchronize(st));
+    if (s.kind == Storage::ActNHWC)
+        nhwc_to_nchw(tmp.data(), (float *)host, (int)s.dims[0], (int)s.dims[1], (int)s.dims[2],
+                     (int)s.dims[3]);
+    else
+        khwc_o_to_oihw(tmp.data(), (float *)host, (int)s.dims[0], (int)s.dims[1], (int)s.dims[2],
+                       (int)s.dims[3]);
+    return GPX_SUCC;
+}
+
+static const char kParamMagic[] = "TVM_MODEL_PARAMS";  // 17 bytes with the NUL, as the reference reads
+
+}  // namespace gpx
+
+extern "C" {
+
+int gpx_synth_normal(float *host, size_t n, uint64_t seed, uint64_t stream, float mean,
+                     float std) {
+    GPX_REQUIRE(host || n == 0, GPX_FAIL, "host is NULL");
+    normal_fill(host, n, seed, stream, mean, std);
+    return GPX_SUCC;
+}
+
+int gpx_synth_uniform(float *host, size_t n, uint64_t seed, uint64_t stream, float lo, float hi) {
+    GPX_REQUIRE(host || n == 0, GPX_FAIL, "host is NULL");
+    uniform_fill(host, n, seed, stream, lo, hi);
+    return GPX_SUCC;
+}
+
+int gpx_model_open(const char *name, const gpx_model_opts *opts, gpx_model **out) {
+    GPX_REQUIRE(name && out, GPX_FAIL, "NULL argument");
+    gpx_model_opts o{};
+    if (opts) o = *opts;
+    std::unique_ptr<gpx_model> m(new gpx_model());
+    std::string nm(name);
+    // Aliases for the model names the reference's task configs use (config/A.json, C.json).
+    if (nm == "resnet") nm = "resnet152";
+    GPX_TRY(build_builtin_graph(*m, nm, o));
+    int st = finalize_model(*m);
+    if (st != GPX_SUCC) {
+        gpx_model_close(m.release());
+        return st;
+    }
+    *out = m.release();
+    return GPX_SUCC;
+}
+
+int gpx_model_close(gpx_model *m) {
+    if (!m) return GPX_SUCC;
+    for (auto &s : m->storages)
+        if (s.dptr) cudaFree(s.dptr);
+    delete m;
+    return GPX_SUCC;
+}
+
+int gpx_model_storage_num(gpx_model *m, size_t *n) {
+    GPX_REQUIRE(m && n, GPX_FAIL, "NULL argument");
+    *n = m->storages.size();
+    return GPX_SUCC;
+}
+
+int gpx_model_storage_info(gpx_model *m, size_t idx, char *name, size_t name_cap, size_t *bytes,
+                           char *stype, size_t stype_cap, int *is_param) {
+    GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    GPX_REQUIRE(idx < m->storages.size(), GPX_OUT_OF_RANGE, "storage index %zu out of range", idx);
+    const Storage &s = m->storages[idx];
+    if (name && name_cap) snprintf(name, name_cap, "%s", s.name.c_str());
+    if (bytes) *bytes = s.bytes;
+    if (stype && stype_cap) snprintf(stype, stype_cap, "%s", s.stype.c_str());
+    if (is_param) *is_param = s.is_param ? 1 : 0;
+    return GPX_SUCC;
+}
+
+int gpx_model_find(gpx_model *m, const char *name, size_t *idx) {
+    GPX_REQUIRE(m && name && idx, GPX_FAIL, "NULL argument");
+    int i = m->find(name);
+    if (i < 0) {
+        set_error("storage '%s' not found", name);
+        return GPX_NOT_FOUND;
+    }
+    *idx = (size_t)i;
+    return GPX_SUCC;
+}
+
+int gpx_model_set(gpx_model *m, const char *name, const void *host, size_t len, gpx_stream s) {
+    GPX_REQUIRE(m && name && host, GPX_FAIL, "NULL argument");
+    int i = m->find(name);
+    if (i < 0) {
+        set_error("storage '%s' not found", name);
+        return GPX_NOT_FOUND;
+    }
+    return storage_set(m, m->storages[i], host, len, as_stream(s));
+}
+
+int gpx_model_get(gpx_model *m, const char *name, void *host, size_t len, gpx_stream s) {
+    GPX_REQUIRE(m && name && host, GPX_FAIL, "NULL argument");
+    int i = m->find(name);
+    if (i < 0) {
+        set_error("storage '%s' not found", name);
+        return GPX_NOT_FOUND;
+    }
+    return storage_get(m, m->storages[i], host, len, as_stream(s));
+}
+
+int gpx_model_shape(gpx_model *m, const char *name, int64_t dims[4], int *rank) {
+    GPX_REQUIRE(m && name && dims && rank, GPX_FAIL, "NULL argument");
+    int i = m->find(name);
+    if (i < 0) {
+        set_error("storage '%s' not found", name);
+        return GPX_NOT_FOUND;
+    }
+    const Storage &s = m->storages[i];
+    *rank = s.rank;
+    for (int d = 0; d < 4; ++d) dims[d] = d < s.rank ? s.dims[d] : 1;
+    return GPX_SUCC;
+}
+
+int gpx_model_init_random(gpx_model *m, uint64_t seed) {
+    GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    std::vector<float> tmp;
+    uint64_t stream = 0;
+    for (auto &s : m->storages) {
+        if (!s.is_param) continue;
+        size_t n = s.bytes / sizeof(float);
+        tmp.resize(n);
+        if (s.kind == Storage::Weight)
+            normal_fill(tmp.data(), n, seed, stream, 0.f, std::sqrt(2.0f / (float)s.fan_in));
+        else
+            normal_fill(tmp.data(), n, seed, stream, 0.f, 0.01f);
+        ++stream;
+        GPX_TRY(storage_set(m, s, tmp.data(), s.bytes, nullptr));
+    }
+    GPX_CUDA(cudaStreamSynchronize(nullptr));
+    return GPX_SUCC;
+}
+
+int gpx_model_load_params(gpx_model *m, const char *path) {
+    GPX_REQUIRE(m && path, GPX_FAIL, "NULL argument");
+    FILE *fp = fopen(path, "rb");
+    GPX_REQUIRE(fp, GPX_NOT_FOUND, "cannot open %s", path);
+    struct Closer {
+        FILE *f;
+        ~Closer() { fclose(f); }
+    } closer{fp};
+    char magic[sizeof(kParamMagic)];
+    GPX_REQUIRE(fread(magic, 1, sizeof(magic), fp) == sizeof(magic) &&
+                    memcmp(magic, kParamMagic, sizeof(magic)) == 0,
+                GPX_FAIL, "%s: bad magic", path);
+    uint64_t count = 0;
+    GPX_REQUIRE(fread(&count, sizeof(count), 1, fp) == 1 && count != 0, GPX_FAIL,
+                "%s: bad parameter count", path);
+    std::vector<float> data;
+    size_t loaded = 0;
+    for (uint64_t i = 0; i < count; ++i) {
+        std::string key;
+        for (;;) {
+            int c = fgetc(fp);
+            GPX_REQUIRE(c != EOF && key.size() < 255, GPX_FAIL, "%s: truncated name", path);
+            if (c == 0) break;
+            key.push_back((char)c);
+        }
+        uint64_t n = 0;
+        GPX_REQUIRE(fread(&n, sizeof(n), 1, fp) == 1 && n != 0, GPX_FAIL, "%s: bad size for %s",
+                    path, key.c_str());
+        GPX_REQUIRE(n <= (1ull << 34), GPX_FAIL, "%s: implausible size for %s", path, key.c_str());
+        data.resize(n);
+        GPX_REQUIRE(fread(data.data(), sizeof(float), n, fp) == n, GPX_FAIL,
+                    "%s: truncated data for %s", path, key.c_str());
+        int idx = m->find(key);
+        // Names absent from the graph are skipped, as Model::load_param does
+        // (src/model.cpp:270-276 looks names up and copies the ones it finds).
+        if (idx < 0) continue;
+        Storage &s = m->storages[idx];
+        GPX_REQUIRE(n * sizeof(float) == s.bytes, GPX_OUT_OF_RANGE,
+                    "%s: %s has %llu elements, model expects %zu", path, key.c_str(),
+                    (unsigned long long)n, s.bytes / sizeof(float));
+        GPX_TRY(storage_set(m, s, data.data(), s.bytes, nullptr));
+        ++loaded;
+    }
+    GPX_CUDA(cudaStreamSynchronize(nullptr));
+    GPX_REQUIRE(loaded > 0, GPX_NOT_FOUND, "%s: no parameter matched the model", path);
+    return GPX_SUCC;
+}
+
+int gpx_model_save_params(gpx_model *m, const char *path) {
+    GPX_REQUIRE(m && path, GPX_FAIL, "NULL argument");
+    FILE *fp = fopen(path, "wb");
+    GPX_REQUIRE(fp, GPX_FAIL, "cannot create %s", path);
+    struct Closer {
+        FILE *f;
+        ~Closer() { fclose(f); }
+    } closer{fp};
+    uint64_t count = 0;
+    for (auto &s : m->storages) count += s.is_param ? 1 : 0;
+    fwrite(kParamMagic, 1, sizeof(kParamMagic), fp);
+    fwrite(&count, sizeof(count), 1, fp);
+    std::vector<float> data;
+    for (auto &s : m->storages) {
+        if (!s.is_param) continue;
+        uint64_t n = s.bytes / sizeof(float);
+        data.resize(n);
+        GPX_TRY(storage_get(m, s, data.data(), s.bytes, nullptr));
+        GPX_CUDA(cudaStreamSynchronize(nullptr));
+        fwrite(s.name.c_str(), 1, s.name.size() + 1, fp);
+        fwrite(&n, sizeof(n), 1, fp);
+        GPX_REQUIRE(fwrite(data.data(), sizeof(float), n, fp) == n, GPX_FAIL, "short write to %s",
+                    path);
+    }
+    return GPX_SUCC;
+}
+
+int gpx_model_kernel_num(gpx_model *m, size_t *n) {
+    GPX_REQUIRE(m && n, GPX_FAIL, "NULL argument");
+    *n = m->kernels.size();
+    return GPX_SUCC;
+}
+
+int gpx_model_kernel_info(gpx_model *m, size_t idx, char *name, size_t name_cap,
+                          uint32_t launch_params[6], int *total_tiles, double *flops,
+                          double *bytes) {
+    GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    GPX_REQUIRE(idx < m->kernels.size(), GPX_OUT_OF_RANGE, "kernel index %zu out of range", idx);
+    const Kernel &k = m->kernels[idx];
+    if (name && name_cap) snprintf(name, name_cap, "%s", k.name.c_str());
+    if (launch_params) {
+        launch_params[0] = (uint32_t)k.grid;
+        launch_params[1] = launch_params[2] = 1;
+        launch_params[3] = 256;
+        launch_params[4] = launch_params[5] = 1;
+    }
+    if (total_tiles) *total_tiles = k.total_tiles;
+    if (flops) *flops = k.flops;
+    if (bytes) *bytes = k.bytes;
+    return GPX_SUCC;
+}
+
+int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
+    GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    // Same skeleton as the TVM graph JSON Model::load_from_json walks (src/model.cpp:157-197):
+    // parameters and inputs are "null" nodes listed in arg_nodes; compute nodes are "tvm_op"
+    // with attrs.func_name; attrs.dltype / attrs.shape hold one entry per node; heads names
+    // the output.  Layer hyper-parameters ride in each node's attrs.
+    Json nodes = Json::array(), arg_nodes = Json::array(), dltype = Json::array(),
+         shapes = Json::array(), row_ptr = Json::array();
+    std::unordered_map<int, int> storage_to_json;  // storage index -> json node id
+    int jid = 0;
+    auto shape_of = [&](const Storage &s) {
+        Json sh = Json::array();
+        for (int d = 0; d < s.rank; ++d) sh.push(Json((long long)s.dims[d]));
+        return sh;
+    };
+    auto add_null = [&](int storage) {
+        const Storage &s = m->storages[storage];
+        Json n = Json::object();
+        n.set("op", "null");
+        n.set("name", s.name);
+        n.set("inputs", Json::array());
+        nodes.push(n);
+        arg_nodes.push(Json(jid));
+        dltype.push(Json(s.stype));
+        shapes.push(shape_of(s));
+        row_ptr.push(Json(jid));
+        storage_to_json[storage] = jid++;
+    };
+    int head_json = -1;
+    for (size_t ni = 0; ni < m->nodes.size(); ++ni) {
+        const Node &n = m->nodes[ni];
+        if (n.op == Op::Input) {
+            add_null(n.storage);
+            continue;
+        }
+        if (n.weight >= 0) add_null(n.weight);
+        if (n.bias >= 0) add_null(n.bias);
+        Json jn = Json::object();
+        jn.set("op", "tvm_op");
+        jn.set("name", n.name);
+        Json attrs = Json::object();
+        const char *fn = n.op == Op::Conv      ? "gpx_conv2d"
+                         : n.op == Op::MaxPool ? "gpx_max_pool2d"
+                                               : "gpx_avg_pool2d";
+        attrs.set("func_name", fn);
+        attrs.set("flatten_data", "0");
+        attrs.set("num_outputs", "1");
+        attrs.set("kernel", Json(n.k));
+        attrs.set("stride", Json(n.stride));
+        attrs.set("padding", Json(n.pad));
+        attrs.set("relu", Json(n.relu));
+        attrs.set("channels", Json(n.C));
+        Json inputs = Json::array();
+        auto ref = [&](int storage) {
+            Json r = Json::array();
+            r.push(Json(storage_to_json[storage]));
+            r.push(Json(0));
+            r.push(Json(0));
+            inputs.push(r);
+        };
+        ref(m->nodes[n.inputs[0]].storage);
+        if (n.weight >= 0) ref(n.weight);
+        if (n.bias >= 0) ref(n.bias);
+        if (n.residual >= 0) {
+            ref(m->nodes[n.residual].storage);
+            attrs.set("residual", Json(true));
+        }
+        attrs.set("num_inputs", std::to_string(inputs.size()));
+        jn.set("attrs", attrs);
+        jn.set("inputs", inputs);
+        nodes.push(jn);
+        const Storage &s = m->storages[n.storage];
+        dltype.push(Json(s.stype));
+        shapes.push(shape_of(s));
+        row_ptr.push(Json(jid));
+        if ((int)ni == m->head_node) head_json = jid;
+        storage_to_json[n.storage] = jid++;
+    }
+    row_ptr.push(Json(jid));
+    Json root = Json::object();
+    root.set("nodes", nodes);
+    root.set("arg_nodes", arg_nodes);
+    Json heads = Json::array(), h = Json::array();
+    h.push(Json(head_json));
+    h.push(Json(0));
+    h.push(Json(0));
+    heads.push(h);
+    root.set("heads", heads);
+    Json attrs = Json::object();
+    Json dl = Json::array();
+    dl.push("list_str");
+    dl.push(dltype);
+    attrs.set("dltype", dl);
+    Json sh = Json::array();
+    sh.push("list_shape");
+    sh.push(shapes);
+    attrs.set("shape", sh);
+    root.set("attrs", attrs);
+    root.set("node_row_ptr", row_ptr);
+    Json meta = Json::object();
+    meta.set("model", m->name);
+    meta.set("batch", Json(m->batch));
+    root.set("gpx", meta);
+    std::string text = root.dump(1);
+    if (needed) *needed = text.size() + 1;
+    if (!buf || cap < text.size() + 1) return buf ? GPX_OUT_OF_RANGE : GPX_SUCC;
+    memcpy(buf, text.c_str(), text.size() + 1);
+    return GPX_SUCC;
+}
+
+}  // extern "C"

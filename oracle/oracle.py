@@ -1,0 +1,279 @@
+"""CPU oracle for libgpx — TEST INFRASTRUCTURE ONLY (see gpx_oracle.c for the full header).
+
+Only tests/, the smoke check and the CPU-baseline leg of bench.py may import this module.
+PARITY UNPINNED: the reference stores no expected outputs and its arithmetic (TVM-generated
+kernels, apache/tvm @ 513c2be0c3b853) is not in its tree; the layer functions here are checked
+against PyTorch CPU operators by tests/test_oracle.py instead.
+
+The model definitions below restate the published architectures independently of the
+product's graph builder: ResNet v1.5 bottleneck networks and VGG, with batch norm folded into
+a per-convolution bias, NCHW activations and OIHW filters as the reference's graphs use
+(scripts/compile/compile.py:27-44).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libgpx_oracle.so")
+_lib = None
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_f64p = ctypes.POINTER(ctypes.c_double)
+_i32p = ctypes.POINTER(ctypes.c_int)
+
+
+def build() -> str:
+    """Compiles gpx_oracle.c when the shared object is missing or stale."""
+    src = os.path.join(_HERE, "gpx_oracle.c")
+    if not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(_LIB_PATH)
+        conv_args = [_f32p, _f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 10
+        _lib.orc_conv2d_nchw.argtypes = conv_args
+        _lib.orc_conv2d_nchw_fast.argtypes = conv_args
+        _lib.orc_pool2d_nchw.argtypes = [_f32p, _f32p] + [ctypes.c_int] * 8
+        _lib.orc_axpy_f32.argtypes = [ctypes.c_float, _f32p, _f32p, ctypes.c_size_t]
+        _lib.orc_f32_to_bf16.argtypes = [_f32p, _u16p, ctypes.c_size_t]
+        _lib.orc_bf16_to_f32.argtypes = [_u16p, _f32p, ctypes.c_size_t]
+        _lib.orc_gemm_bf16_nt.argtypes = [_u16p, _u16p, _f64p] + [ctypes.c_int] * 3
+        _lib.orc_gemm_bf16_nt_fast.argtypes = [_u16p, _u16p, _f32p] + [ctypes.c_int] * 3
+        _lib.orc_gemm_bf16_nt_samples.argtypes = [_u16p, _u16p, _i32p, _i32p, ctypes.c_int,
+                                                  _f64p, ctypes.c_int]
+    return _lib
+
+
+def _p(a: np.ndarray | None, typ):
+    if a is None:
+        return ctypes.cast(None, typ)
+    return a.ctypes.data_as(typ)
+
+
+def _c(a, dtype=np.float32) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+# ---- layer functions ---------------------------------------------------------------------------
+
+def conv2d(x, w, bias=None, stride=1, pad=0, relu=False, residual=None, fast=False):
+    """Fused conv2d + bias + residual + ReLU.  x NCHW, w OIHW."""
+    x, w = _c(x), _c(w)
+    n, cin, h, wd = x.shape
+    cout, cin2, kh, kw = w.shape
+    assert cin == cin2
+    ho = (h + 2 * pad - kh) // stride + 1
+    wo = (wd + 2 * pad - kw) // stride + 1
+    out = np.empty((n, cout, ho, wo), np.float32)
+    b = _c(bias) if bias is not None else None
+    r = _c(residual) if residual is not None else None
+    if r is not None:
+        assert r.shape == out.shape
+    fn = lib().orc_conv2d_nchw_fast if fast else lib().orc_conv2d_nchw
+    fn(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(r, _f32p), _p(out, _f32p), n, cin, h, wd,
+       cout, kh, kw, stride, pad, int(relu))
+    return out
+
+
+def pool2d(x, k, stride, pad, mode):
+    x = _c(x)
+    n, c, h, w = x.shape
+    ho = (h + 2 * pad - k) // stride + 1
+    wo = (w + 2 * pad - k) // stride + 1
+    out = np.empty((n, c, ho, wo), np.float32)
+    lib().orc_pool2d_nchw(_p(x, _f32p), _p(out, _f32p), n, c, h, w, k, stride, pad,
+                          0 if mode == "max" else 1)
+    return out
+
+
+def axpy(a, x, y):
+    """Returns fma(a, x, y) element-wise in fp32 (y is not modified)."""
+    x = _c(x)
+    out = _c(y).copy()
+    lib().orc_axpy_f32(np.float32(a), _p(x, _f32p), _p(out, _f32p), x.size)
+    return out
+
+
+def f32_to_bf16(x):
+    x = _c(x)
+    out = np.empty(x.shape, np.uint16)
+    lib().orc_f32_to_bf16(_p(x, _f32p), _p(out, _u16p), x.size)
+    return out
+
+
+def bf16_to_f32(x):
+    x = _c(x, np.uint16)
+    out = np.empty(x.shape, np.float32)
+    lib().orc_bf16_to_f32(_p(x, _u16p), _p(out, _f32p), x.size)
+    return out
+
+
+def gemm_bf16_nt(a_bits, b_bits):
+    """Exact (fp64) A[M][K] x B[N][K]^T for bf16 bit patterns; returns float64 [M][N]."""
+    a, b = _c(a_bits, np.uint16), _c(b_bits, np.uint16)
+    m, k = a.shape
+    n, k2 = b.shape
+    assert k == k2
+    out = np.empty((m, n), np.float64)
+    lib().orc_gemm_bf16_nt(_p(a, _u16p), _p(b, _u16p), _p(out, _f64p), m, n, k)
+    return out
+
+
+def gemm_bf16_nt_fast(a_bits, b_bits):
+    a, b = _c(a_bits, np.uint16), _c(b_bits, np.uint16)
+    m, k = a.shape
+    n, _ = b.shape
+    out = np.empty((m, n), np.float32)
+    lib().orc_gemm_bf16_nt_fast(_p(a, _u16p), _p(b, _u16p), _p(out, _f32p), m, n, k)
+    return out
+
+
+def gemm_bf16_nt_samples(a_bits, b_bits, rows, cols):
+    a, b = _c(a_bits, np.uint16), _c(b_bits, np.uint16)
+    rows, cols = _c(rows, np.int32), _c(cols, np.int32)
+    out = np.empty(rows.size, np.float64)
+    lib().orc_gemm_bf16_nt_samples(_p(a, _u16p), _p(b, _u16p), _p(rows, _i32p), _p(cols, _i32p),
+                                   rows.size, _p(out, _f64p), a.shape[1])
+    return out
+
+
+# ---- model definitions -------------------------------------------------------------------------
+
+def resnet_param_shapes(layers=(3, 4, 6, 3), num_classes=1000):
+    """Ordered {name: shape} of a bottleneck ResNet with folded batch norm."""
+    shapes = {"conv1.weight": (64, 3, 7, 7), "conv1.bias": (64,)}
+    inplanes, planes = 64, 64
+    for li, nblocks in enumerate(layers):
+        for b in range(nblocks):
+            p = f"layer{li + 1}.{b}"
+            if b == 0:
+                shapes[f"{p}.downsample.weight"] = (planes * 4, inplanes, 1, 1)
+                shapes[f"{p}.downsample.bias"] = (planes * 4,)
+            shapes[f"{p}.conv1.weight"] = (planes, inplanes, 1, 1)
+            shapes[f"{p}.conv1.bias"] = (planes,)
+            shapes[f"{p}.conv2.weight"] = (planes, planes, 3, 3)
+            shapes[f"{p}.conv2.bias"] = (planes,)
+            shapes[f"{p}.conv3.weight"] = (planes * 4, planes, 1, 1)
+            shapes[f"{p}.conv3.bias"] = (planes * 4,)
+            inplanes = planes * 4
+        planes *= 2
+    shapes["fc.weight"] = (num_classes, inplanes, 1, 1)
+    shapes["fc.bias"] = (num_classes,)
+    return shapes
+
+
+def resnet_forward(params, data, layers=(3, 4, 6, 3), fast=False, taps=None):
+    """ResNet v1.5 forward.  `taps`, when a dict, receives every intermediate by node name."""
+    def keep(name, v):
+        if taps is not None:
+            taps[name] = v
+        return v
+
+    x = keep("conv1", conv2d(data, params["conv1.weight"], params["conv1.bias"], 2, 3, True,
+                             fast=fast))
+    x = keep("maxpool", pool2d(x, 3, 2, 1, "max"))
+    for li, nblocks in enumerate(layers):
+        for b in range(nblocks):
+            p = f"layer{li + 1}.{b}"
+            stride = 2 if (b == 0 and li > 0) else 1
+            identity = x
+            if b == 0:
+                identity = keep(f"{p}.downsample",
+                                conv2d(x, params[f"{p}.downsample.weight"],
+                                       params[f"{p}.downsample.bias"], stride, 0, False, fast=fast))
+            y = keep(f"{p}.conv1", conv2d(x, params[f"{p}.conv1.weight"], params[f"{p}.conv1.bias"],
+                                          1, 0, True, fast=fast))
+            y = keep(f"{p}.conv2", conv2d(y, params[f"{p}.conv2.weight"], params[f"{p}.conv2.bias"],
+                                          stride, 1, True, fast=fast))
+            x = keep(f"{p}.conv3", conv2d(y, params[f"{p}.conv3.weight"], params[f"{p}.conv3.bias"],
+                                          1, 0, True, residual=identity, fast=fast))
+    x = keep("avgpool", pool2d(x, x.shape[2], 1, 0, "avg"))
+    x = conv2d(x, params["fc.weight"], params["fc.bias"], 1, 0, False, fast=fast)
+    return keep("heads", x.reshape(x.shape[0], -1))
+
+
+VGG_CFG = {
+    "vgg16": (64, 64, 0, 128, 128, 0, 256, 256, 256, 0, 512, 512, 512, 0, 512, 512, 512, 0),
+    "vgg19": (64, 64, 0, 128, 128, 0, 256, 256, 256, 256, 0, 512, 512, 512, 512, 0,
+              512, 512, 512, 512, 0),
+}
+
+
+def vgg_forward(params, data, cfg="vgg16", fast=False, taps=None):
+    x = data
+    ci = 0
+    for c in VGG_CFG[cfg]:
+        if c == 0:
+            x = pool2d(x, 2, 2, 0, "max")
+        else:
+            x = conv2d(x, params[f"features.{ci}.weight"], params[f"features.{ci}.bias"], 1, 1,
+                       True, fast=fast)
+            ci += 1
+    # The first dense layer sees the (C, H, W)-flattened feature map: a 7x7 "valid" convolution.
+    x = conv2d(x, params["classifier.0.weight"], params["classifier.0.bias"], 1, 0, True, fast=fast)
+    x = conv2d(x, params["classifier.3.weight"], params["classifier.3.bias"], 1, 0, True, fast=fast)
+    x = conv2d(x, params["classifier.6.weight"], params["classifier.6.bias"], 1, 0, False,
+               fast=fast)
+    out = x.reshape(x.shape[0], -1)
+    if taps is not None:
+        taps["heads"] = out
+    return out
+
+
+MODELS = {
+    "resnet50": lambda p, d, **kw: resnet_forward(p, d, (3, 4, 6, 3), **kw),
+    "resnet152": lambda p, d, **kw: resnet_forward(p, d, (3, 8, 36, 3), **kw),
+    "resnet_tiny": lambda p, d, **kw: resnet_forward(p, d, (1, 1, 1, 1), **kw),
+    "vgg16": lambda p, d, **kw: vgg_forward(p, d, "vgg16", **kw),
+    "vgg19": lambda p, d, **kw: vgg_forward(p, d, "vgg19", **kw),
+}
+
+
+def forward(model, params, data, **kw):
+    return MODELS[model](params, data, **kw)
+
+
+# ---- block-level preemption protocol (scripts/compile/convert_to_blp.py:39-70) -----------------
+
+def blp_simulate(total_tiles, n_ctas, tile_cost, raise_at, cursor=0, stop_index=-1, kernel_id=0):
+    """Discrete-event restatement of the persistent-CTA loop.
+
+    Every CTA repeats: read the flag; if clear, claim tile `cursor++` (tiles >= total end the
+    CTA) and spend tile_cost(tile) time units on it; if raised, record kernel_id into the stop
+    index when that is still -1, and return.  `raise_at` is the time the flag flips to 1 (None =
+    never).  Returns (tiles in completion order, cursor, stop_index, drain_time).
+    """
+    import heapq
+
+    ready = [(0.0, c) for c in range(n_ctas)]
+    heapq.heapify(ready)
+    done = []
+    last_exit = 0.0
+    while ready:
+        t, c = heapq.heappop(ready)
+        if raise_at is not None and t >= raise_at:
+            if stop_index == -1:
+                stop_index = kernel_id
+            last_exit = max(last_exit, t)
+            continue
+        idx = cursor
+        cursor += 1
+        if idx >= total_tiles:
+            last_exit = max(last_exit, t)
+            continue
+        t_end = t + tile_cost(idx)
+        done.append(idx)
+        heapq.heappush(ready, (t_end, c))
+    return done, cursor, stop_index, last_exit

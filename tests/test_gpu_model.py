@@ -1,0 +1,259 @@
+"""Model-level parity (GPU forward vs the CPU oracle) and preempt/resume bit-exactness."""
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+RTOL_FP32 = 1e-4  # max|gpu - oracle| / max|oracle|, the fp32 tolerance of the parity contract
+
+
+def _rel(a, b):
+    return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))) /
+                 max(float(np.max(np.abs(b))), 1e-30))
+
+
+def _data(gpx, batch, seed=0):
+    return gpx.synth_normal(batch * 3 * 224 * 224, seed, 0).reshape(batch, 3, 224, 224)
+
+
+@pytest.mark.parametrize("model,batch", [("resnet_tiny", 1), ("resnet_tiny", 3), ("resnet50", 1),
+                                         ("resnet50", 2)])
+def test_forward_matches_oracle_layer_by_layer(gpx, oracle, model, batch):
+    ex = gpx.BaseExecutor()
+    ex.init(model, batch=batch, seed=1)
+    data = _data(gpx, batch)
+    ex.set_input("data", data)
+    ex.execute()
+    heads = ex.get_output("heads")
+    params = ex.model.params()
+    taps = {}
+    want = oracle.forward(model, params, data, taps=taps)
+    assert heads.shape == want.shape == (batch, 1000)
+    for name, ref in taps.items():
+        got = ex.model.get(name).reshape(ref.shape)
+        assert _rel(got, ref) <= RTOL_FP32, f"{model} b{batch} node {name}"
+    assert _rel(heads, want) <= RTOL_FP32
+    ex.clear()
+
+
+def test_all_ten_input_fixture(gpx, oracle):
+    """The reference's DNN smoke input: every element 10.0 (src/tests/test-dnn.cpp:25-29)."""
+    ex = gpx.BaseExecutor()
+    ex.init("resnet_tiny", batch=1, seed=5)
+    data = np.full((1, 3, 224, 224), 10.0, np.float32)
+    ex.set_input("data", data)
+    ex.execute()
+    got = ex.get_output("heads")
+    want = oracle.forward("resnet_tiny", ex.model.params(), data)
+    assert _rel(got, want) <= RTOL_FP32
+    ex.clear()
+
+
+def test_vgg16_matches_oracle(gpx, oracle):
+    ex = gpx.BaseExecutor()
+    ex.init("vgg16", batch=1, seed=7)
+    data = _data(gpx, 1, seed=8)
+    ex.set_input("data", data)
+    ex.execute()
+    got = ex.get_output("heads")
+    want = oracle.forward("vgg16", ex.model.params(), data)
+    assert _rel(got, want) <= RTOL_FP32
+    ex.clear()
+
+
+def test_set_get_size_checks_and_names(gpx):
+    from gpreempt_b200 import binding as B
+
+    ex = gpx.BaseExecutor()
+    ex.init("resnet_tiny", batch=1, seed=1)
+    assert ex.get_data_size("data") == 3 * 224 * 224 * 4
+    assert ex.get_data_size("heads") == 4000
+    with pytest.raises(gpx.GpxError) as e:
+        ex.set_input("data", np.zeros(10, np.float32))
+    assert e.value.status == B.OUT_OF_RANGE  # `len < size` is rejected, src/model.cpp:317
+    with pytest.raises(gpx.GpxError) as e:
+        ex.model.find_storage_idx("no_such_tensor")
+    assert e.value.status == B.NOT_FOUND
+    with pytest.raises(gpx.GpxError) as e:
+        ex.launch_kernel(10_000)
+    assert e.value.status == B.OUT_OF_RANGE
+    w = ex.model.get("conv1.weight")
+    assert w.shape == (64, 3, 7, 7)
+    ex.model.set("conv1.weight", w * 2)
+    assert np.array_equal(ex.model.get("conv1.weight"), w * 2)
+    ex.clear()
+
+
+def test_params_file_round_trip(gpx, tmp_path):
+    """mod.params format of ModelParamParser::parse_from_file (src/model.cpp:15-55)."""
+    a = gpx.Model("resnet_tiny")
+    a.init_random(3)
+    path = str(tmp_path / "mod.params")
+    a.save_param(path)
+    raw = open(path, "rb").read()
+    assert raw[:17] == b"TVM_MODEL_PARAMS\x00"
+    count = int(np.frombuffer(raw[17:25], np.uint64)[0])
+    pa = a.params()
+    assert count == len(pa)
+    b = gpx.Model("resnet_tiny")
+    b.load_param(path)
+    pb = b.params()
+    for k in pa:
+        assert np.array_equal(pa[k], pb[k]), k
+    a.clear(), b.clear()
+
+
+def test_graph_capture_matches_eager(gpx):
+    ex = gpx.BaseExecutor()
+    ex.init("resnet_tiny", batch=2, seed=1)
+    data = _data(gpx, 2)
+    ex.set_input("data", data)
+    ex.execute()
+    eager = ex.get_output("heads")
+    s = gpx.Stream(0)
+    ex.capture_graph(s)
+    ex.set_input("data", data * 0.5)
+    ex.execute(s)
+    s.sync()
+    ex.set_input("data", data)
+    ex.execute(s)
+    s.sync()
+    assert np.array_equal(ex.get_output("heads"), eager)
+    ex.clear()
+    s.destroy()
+
+
+def _all_activations(ex):
+    out = {}
+    for i in range(ex.model.get_storage_num()):
+        info = ex.model.get_storage_info(i)
+        if not info["is_param"] and info["name"] != "data":
+            out[info["name"]] = ex.model.get(info["name"])
+    return out
+
+
+@pytest.mark.parametrize("model,batch,transport", [("resnet_tiny", 8, 0), ("resnet50", 8, 0),
+                                                   ("resnet50", 8, 1)])
+def test_model_preempt_resume_bit_identical(gpx, model, batch, transport):
+    """Asserted form of src/tests/test-dnn-blp.cpp:36-43: execute, raise the word, drain, clear,
+    resume; every activation equals the uninterrupted run bit for bit."""
+    base = gpx.BaseExecutor()
+    base.init(model, batch=batch, seed=1)
+    data = _data(gpx, batch)
+    base.set_input("data", data)
+    base.execute()
+    want = _all_activations(base)
+    params = base.model.params()
+
+    word = gpx.PreemptWord(transport)
+    ex = gpx.BLPExecutor()
+    ex.init(model, batch=batch)
+    for k, v in params.items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.enable_trace(True)
+    s = gpx.Stream(1)
+    ex.set_input("data", data)
+
+    # uninterrupted BLP run == static-schedule run
+    ex.execute(s)
+    assert ex.getStopPoint(s) == -1
+    got = _all_activations(ex)
+    for k in want:
+        assert np.array_equal(got[k], want[k]), f"uninterrupted {k}"
+    nk = ex.get_kernel_num()
+    tiles = np.array([ex.model.get_kernel_info(i)["total_tiles"] for i in range(nk)])
+    trace = ex.read_trace()
+    assert np.array_equal(trace[:, 3].astype(np.int64), tiles)
+    # kernels of one stream run in order: start times are non-decreasing
+    assert np.all(np.diff(trace[:, 0].astype(np.int64)) >= 0)
+
+    # time one uninterrupted run to place the triggers
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+
+    rng = np.random.default_rng(17)
+    stops_seen = 0
+    for trial in range(10):
+        ex.set_input("data", data * 0.0)
+        ex.execute(s)
+        s.sync()  # scrub every activation so stale results cannot pass
+        ex.set_input("data", data)
+        word.clear()
+        time.sleep(0.001)
+        ex.execute(s)
+        rounds = 0
+        while True:
+            if rounds < 4:
+                delay = float(rng.uniform(0, run_us / 2))
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < delay:
+                    pass
+                word.raise_()
+            s.sync()           # BE drained
+            word.clear()       # only now may later kernels run again
+            time.sleep(0.0005)
+            stop = ex.resume(s)
+            rounds += 1
+            if stop == -1:
+                break
+            stops_seen += 1
+            assert 0 <= stop < nk
+            assert rounds < 60
+        s.sync()
+        got = _all_activations(ex)
+        for k in want:
+            assert np.array_equal(got[k], want[k]), f"trial {trial}: {k} differs after resume"
+        cursors = ex.read_cursors()
+        assert np.all(cursors >= tiles), "a kernel finished with unclaimed tiles"
+    assert stops_seen > 0, "no run was ever preempted"
+    base.clear(), ex.clear(), word.destroy(), s.destroy()
+
+
+def test_execute_with_word_raised_runs_nothing_then_resumes(gpx):
+    """The reference's manual test raises the flag right after execute
+    (src/tests/test-dnn-blp.cpp:36-43); kernels that start with the word raised retire with zero
+    work and the stop point is the first of them."""
+    base = gpx.BaseExecutor()
+    base.init("resnet_tiny", batch=2, seed=2)
+    data = _data(gpx, 2)
+    base.set_input("data", data)
+    base.execute()
+    want = base.get_output("heads")
+    word = gpx.PreemptWord(0)
+    ex = gpx.BLPExecutor()
+    ex.init("resnet_tiny", batch=2)
+    for k, v in base.model.params().items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.set_input("data", data)
+    s = gpx.Stream(1)
+    word.raise_()
+    ex.execute(s)
+    assert ex.getStopPoint(s) == 0
+    assert np.all(ex.read_cursors() == 0)
+    word.clear()
+    # getStopPoint re-armed the index; a plain relaunch from 0 is what resume would do
+    for i in range(ex.get_kernel_num()):
+        ex.launch_kernel(i, s)
+    assert ex.getStopPoint(s) == -1
+    assert np.array_equal(ex.get_output("heads"), want)
+    base.clear(), ex.clear(), word.destroy(), s.destroy()
+
+
+def test_export_json_has_the_tvm_graph_skeleton(gpx):
+    import json
+
+    m = gpx.Model("resnet_tiny")
+    g = json.loads(m.export_json())
+    assert set(["nodes", "arg_nodes", "heads", "attrs", "node_row_ptr"]) <= set(g)
+    names = [n["name"] for n in g["nodes"]]
+    assert names[0] == "data" and "heads" in names
+    assert g["nodes"][g["heads"][0][0]]["name"] == "heads"
+    assert g["attrs"]["dltype"][0] == "list_str" and len(g["attrs"]["dltype"][1]) == len(names)
+    assert g["attrs"]["shape"][1][0] == [1, 3, 224, 224]
+    m.clear()
