@@ -208,6 +208,41 @@ def axpy_tiles(n: int, tile_elems: int = 0) -> int:
     return t.value
 
 
+class GemmContext:
+    """Progress slots and accumulator spill area of the preemptible GEMM (zeroed = fresh)."""
+
+    def __init__(self):
+        n = ctypes.c_size_t()
+        check(B.load().gpx_gemm_ctx_bytes(ctypes.byref(n)))
+        self.buf = DeviceBuffer(n.value)
+        self.buf.zero()
+
+    def reset(self) -> None:
+        self.buf.zero()
+
+    def status(self) -> tuple[int, int]:
+        err, cta = ctypes.c_int(), ctypes.c_int()
+        check(B.load().gpx_gemm_status(self.buf.ptr, ctypes.byref(err), ctypes.byref(cta)))
+        return err.value, cta.value
+
+    def free(self) -> None:
+        self.buf.free()
+
+
+def gemm_bf16(a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, m: int, n: int, k: int,
+              ctx: GemmContext, blp: BlpContext | None = None, stream=None) -> None:
+    """C[m][n] = A[m][k] x B[n][k]^T, bf16 in/out, fp32 accumulation on tcgen05."""
+    s = blp.struct() if blp is not None else None
+    check(B.load().gpx_gemm_bf16(a.ptr, b.ptr, c.ptr, m, n, k, ctx.buf.ptr,
+                                 ctypes.byref(s) if s is not None else None, _h(stream)))
+
+
+def gemm_tiles(m: int, n: int) -> int:
+    t = ctypes.c_int()
+    check(B.load().gpx_gemm_tiles(m, n, ctypes.byref(t)))
+    return t.value
+
+
 def synth_normal(n: int, seed: int, stream: int = 0, mean: float = 0.0, std: float = 1.0):
     out = np.empty(n, np.float32)
     check(B.load().gpx_synth_normal(out.ctypes.data_as(ctypes.c_void_p), n, seed, stream, mean, std))

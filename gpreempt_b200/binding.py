@@ -85,6 +85,7 @@ _SIGS = {
     "gpx_gemm_bf16": [vp, vp, vp, ci, ci, ci, vp, P(Blp), vp],
     "gpx_gemm_ctx_bytes": [P(sz)],
     "gpx_gemm_tiles": [ci, ci, P(ci)],
+    "gpx_gemm_status": [vp, P(ci), P(ci)],
     "gpx_synth_normal": [vp, sz, u64, u64, ctypes.c_float, ctypes.c_float],
     "gpx_synth_uniform": [vp, sz, u64, u64, ctypes.c_float, ctypes.c_float],
     "gpx_model_open": [ctypes.c_char_p, P(ModelOpts), P(vp)],

@@ -4,6 +4,7 @@
 // src/cuda-clients/blpclient.cpp:30-76 in the reference.
 #include "common.h"
 #include "blp.cuh"
+#include "word.h"
 
 #include <atomic>
 #include <mutex>
@@ -94,14 +95,6 @@ __global__ void gpx_ping_kernel(const int *flag, unsigned long long *seen,
     }
     *seen = t;
 }
-
-struct gpx_word {
-    int transport;
-    int *host_alias;   // pinned host word (MAPPED) or host shadow of the value (DEVICE)
-    int *dptr;         // address kernels poll
-    cudaStream_t wstream;  // DEVICE transport: dedicated highest-priority stream
-    int device;
-};
 
 extern "C" {
 

@@ -1,0 +1,837 @@
+// Workload driver and per-GPU dispatch loop.
+//
+// Replaces, for this path, the DISB harness the reference vendors (BenchmarkSuite,
+// BenchmarkTask, Load, BasicAnalyzer: third_party/disb/src/{benchmark,load,analyzer}.cpp), the
+// per-policy clients (src/cuda-clients/{gpreemptclient,blpclient}.cpp,
+// src/common-clients/{baseclient,seqclient,rtonlyclient}.cpp) and the REEF scheduler thread
+// (src/reef-client/reef_scheduler.cpp:246-510).
+//
+// One dispatcher thread per GPU owns the preempt word and every launch.  Client threads hand
+// requests over through a per-client atomic state word (no mutex, no condition variable) and
+// spin until it flips to DONE.  Latency-critical requests are launched the moment they are
+// seen; best-effort executors are launched only while the word is clear, drain inside their
+// kernels when it is raised, and are resumed from their stop point once the last
+// latency-critical request has completed and every best-effort stream has quiesced.
+#include "executor.h"
+#include "json.h"
+#include "word.h"
+
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <memory>
+#include <random>
+#include <thread>
+#include <unistd.h>
+
+namespace gpx {
+
+enum Policy { POLICY_BASE, POLICY_SEQ, POLICY_BLP_WAIT, POLICY_YIELD };
+
+// ---- loads (third_party/disb/src/load.cpp) ----------------------------------------------------
+
+struct Load {
+    enum Type { Continuous, Periodic, Poisson, Trace, Burst } type = Continuous;
+    double frequency = 0;
+    std::vector<double> trace_ms;
+    double on_s = 1.0, off_s = 1.0;  // burst: Poisson arrivals during `on`, silence during `off`
+    long long max_requests = -1;
+    uint64_t begin_ns = 0, end_ns = 0, next_ns = 0;
+    uint64_t interval_ns = 0;
+    size_t next_trace = 0;
+    long long issued = 0;
+    std::mt19937_64 rng;
+    std::uniform_real_distribution<double> uni{0.0, 1.0};
+
+    void start(uint64_t begin, uint64_t end, uint64_t seed) {
+        begin_ns = begin;
+        end_ns = end;
+        next_ns = begin;
+        rng.seed(seed);
+        if (type == Periodic && frequency > 0) interval_ns = (uint64_t)(1e9 / frequency);
+        if (type == Burst) next_ns = begin + exp_interval();
+    }
+    uint64_t exp_interval() {
+        // Exponential inter-arrival gap, load.cpp:229-237, truncated to whole microseconds.
+        double u = uni(rng);
+        if (u <= 0) u = 1e-12;
+        double s = (-1.0 / frequency) * std::log(u);
+        return (uint64_t)(s * 1e6) * 1000ull;
+    }
+    uint64_t burst_next(uint64_t t) {
+        // Arrivals only inside the `on` part of each on+off period.
+        uint64_t period = (uint64_t)((on_s + off_s) * 1e9), on = (uint64_t)(on_s * 1e9);
+        uint64_t cand = t + exp_interval();
+        uint64_t rel = (cand - begin_ns) % period;
+        if (rel >= on) cand += period - rel;  // jump to the start of the next `on` window
+        return cand;
+    }
+    static void sleep_until(uint64_t t) {
+        for (;;) {
+            uint64_t now = now_ns();
+            if (now >= t) return;
+            uint64_t left = t - now;
+            if (left > 200000) {
+                timespec ts{(time_t)((left - 100000) / 1000000000ull),
+                            (long)((left - 100000) % 1000000000ull)};
+                nanosleep(&ts, nullptr);
+            }  // the last 200 us are spun for a precise launch time
+        }
+    }
+    // Returns false when the run is over.  An arrival whose successor has already arrived is
+    // dropped, as in the reference (load.cpp:164-176, 216-227, 279-296).
+    bool wait_next(std::atomic<bool> &stop) {
+        if (stop.load(std::memory_order_relaxed)) return false;
+        if (max_requests >= 0 && issued >= max_requests) return false;
+        uint64_t now = now_ns();
+        switch (type) {
+            case Continuous:
+                if (now < begin_ns) sleep_until(begin_ns);
+                if (now >= end_ns) return false;
+                break;
+            case Periodic: {
+                if (frequency <= 0) return false;
+                uint64_t nn = next_ns + interval_ns;
+                while (nn < now) {
+                    next_ns = nn;
+                    nn = next_ns + interval_ns;
+                }
+                if (next_ns >= end_ns) return false;
+                sleep_until(next_ns);
+                next_ns = nn;
+                break;
+            }
+            case Poisson: {
+                if (frequency <= 0) return false;
+                uint64_t nn = next_ns + exp_interval();
+                while (nn < now) {
+                    next_ns = nn;
+                    nn = next_ns + exp_interval();
+                }
+                if (next_ns >= end_ns) return false;
+                sleep_until(next_ns);
+                next_ns = nn;
+                break;
+            }
+            case Burst: {
+                if (frequency <= 0) return false;
+                uint64_t nn = burst_next(next_ns);
+                while (nn < now) {
+                    next_ns = nn;
+                    nn = burst_next(next_ns);
+                }
+                if (next_ns >= end_ns) return false;
+                sleep_until(next_ns);
+                next_ns = nn;
+                break;
+            }
+            case Trace: {
+                if (next_trace >= trace_ms.size()) return false;
+                size_t nn = next_trace + 1;
+                uint64_t launch = begin_ns + (uint64_t)(trace_ms[next_trace] * 1e6);
+                while (nn < trace_ms.size()) {
+                    uint64_t t = begin_ns + (uint64_t)(trace_ms[nn] * 1e6);
+                    if (t >= now) break;
+                    launch = t;
+                    ++nn;
+                }
+                next_trace = nn;
+                if (launch >= end_ns) return false;
+                sleep_until(launch);
+                break;
+            }
+        }
+        if (stop.load(std::memory_order_relaxed)) return false;
+        ++issued;
+        return true;
+    }
+};
+
+// ---- tenants ----------------------------------------------------------------------------------
+
+enum ReqState : int { ST_IDLE = 0, ST_HINTED, ST_SUBMITTED, ST_RUNNING, ST_SUSPENDED, ST_DONE };
+
+struct Record {
+    uint64_t arrive, prepare, preprocess, copy_in, infer, copy_out, postprocess;  // ns
+    uint64_t total() const { return prepare + preprocess + copy_in + infer + copy_out + postprocess; }
+};
+
+struct Tenant {
+    std::string id, name, model_name;
+    int priority = 1;
+    int batch = 1;
+    bool use_graph = false;
+    uint64_t preprocess_us = 0;
+    int gpu = 0;
+    uint64_t seed = 0;
+    Load load;
+    gpx_model *model = nullptr;
+    gpx_exec *exec = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done = nullptr;
+    void *h_in = nullptr, *h_out = nullptr;
+    size_t in_bytes = 0, out_bytes = 0;
+    std::atomic<int> state{ST_IDLE};
+    std::atomic<uint64_t> ticket{0};
+    uint64_t submit_ns = 0;
+    int stop_index = -1;
+    int resumes = 0;
+    std::vector<Record> records;
+    Record standalone{};
+    uint64_t first_ns = 0, last_ns = 0;
+    cudaEvent_t ev_first = nullptr, ev_last = nullptr;
+    bool ev_first_recorded = false;
+};
+
+struct Stats {
+    std::vector<double> drain_us;      // word raised -> every best-effort stream idle (host-observed)
+    std::vector<double> hp_queue_us;   // request seen by the dispatcher -> launched
+    long long raises = 0;
+    long long be_resumes = 0;
+    long long be_launches = 0;
+};
+
+// ---- dispatcher -------------------------------------------------------------------------------
+
+struct Dispatcher {
+    int device = 0;
+    Policy policy = POLICY_YIELD;
+    bool hint = true;
+    std::vector<Tenant *> hp, be;
+    gpx_word *word = nullptr;
+    cudaEvent_t clear_event = nullptr;
+    std::atomic<bool> stop{false};
+    std::atomic<bool> failed{false};
+    std::thread thread;
+    Stats stats;
+    std::string error;
+
+    bool word_raised = false;
+    uint64_t t_raise = 0;
+    bool drain_pending = false;
+
+    int fail(const char *what) {
+        error = std::string(what) + ": " + last_error();
+        failed.store(true);
+        return GPX_FAIL;
+    }
+
+    int launch_full(Tenant *t) {
+        gpx_exec *e = t->exec;
+        if (e->kind == GPX_EXEC_BLP && word && word->transport == GPX_WORD_DEVICE && clear_event)
+            GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
+        GPX_TRY(gpx_exec_execute(e, t->stream));
+        if (e->kind == GPX_EXEC_BLP)
+            GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
+                                     cudaMemcpyDeviceToHost, t->stream));
+        GPX_CUDA(cudaEventRecord(t->done, t->stream));
+        return GPX_SUCC;
+    }
+
+    int launch_resume(Tenant *t) {
+        gpx_exec *e = t->exec;
+        if (word && word->transport == GPX_WORD_DEVICE && clear_event)
+            GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
+        // Re-arm the stop index, then replay kernels stop..N-1 with the saved cursors
+        // (BLPExecutor::resume, src/executor.cpp:280-298).
+        GPX_CUDA(cudaMemcpyAsync(e->d_stop_index, e->h_minus_one, sizeof(int),
+                                 cudaMemcpyHostToDevice, t->stream));
+        size_t nk = e->model->kernels.size();
+        for (size_t i = (size_t)t->stop_index; i < nk; ++i) GPX_TRY(exec_launch(e, i, t->stream));
+        GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
+                                 cudaMemcpyDeviceToHost, t->stream));
+        GPX_CUDA(cudaEventRecord(t->done, t->stream));
+        return GPX_SUCC;
+    }
+
+    int raise() {
+        if (!word || word_raised) return GPX_SUCC;
+        GPX_TRY(gpx_word_raise(word));
+        word_raised = true;
+        t_raise = now_ns();
+        ++stats.raises;
+        drain_pending = false;
+        for (Tenant *t : be)
+            if (t->state.load(std::memory_order_relaxed) == ST_RUNNING) drain_pending = true;
+        return GPX_SUCC;
+    }
+
+    int clear() {
+        if (!word || !word_raised) return GPX_SUCC;
+        GPX_TRY(gpx_word_clear(word));
+        if (word->transport == GPX_WORD_DEVICE) GPX_CUDA(cudaEventRecord(clear_event, word->wstream));
+        word_raised = false;
+        return GPX_SUCC;
+    }
+
+    int step() {
+        // 1. latency-critical: hints raise the word early, submissions are launched at once.
+        int hp_active = 0;
+        bool hp_launched_this_step = false;
+        for (Tenant *t : hp) {
+            int st = t->state.load(std::memory_order_acquire);
+            if (st == ST_HINTED) {
+                ++hp_active;
+                if (policy == POLICY_YIELD || policy == POLICY_BLP_WAIT) GPX_TRY(raise());
+            } else if (st == ST_SUBMITTED) {
+                ++hp_active;
+                if (policy == POLICY_YIELD || policy == POLICY_BLP_WAIT) GPX_TRY(raise());
+                bool may_launch = true;
+                if (policy == POLICY_BLP_WAIT) {
+                    // Wait-based: the latency-critical kernels are only launched once every
+                    // best-effort executor has drained (blpclient.cpp:185-191).
+                    for (Tenant *b : be)
+                        if (b->state.load(std::memory_order_relaxed) == ST_RUNNING) may_launch = false;
+                } else if (policy == POLICY_SEQ) {
+                    may_launch = seq_turn(t);
+                }
+                if (may_launch) {
+                    stats.hp_queue_us.push_back((now_ns() - t->submit_ns) / 1e3);
+                    GPX_TRY(launch_full(t));
+                    t->state.store(ST_RUNNING, std::memory_order_release);
+                    hp_launched_this_step = true;
+                }
+            } else if (st == ST_RUNNING) {
+                cudaError_t q = cudaEventQuery(t->done);
+                if (q == cudaSuccess) {
+                    t->state.store(ST_DONE, std::memory_order_release);
+                    seq_release(t);
+                } else if (q != cudaErrorNotReady) {
+                    set_error("event query failed: %s", cudaGetErrorString(q));
+                    return GPX_FAIL;
+                } else {
+                    ++hp_active;
+                }
+            }
+        }
+        (void)hp_launched_this_step;
+        // 2. best-effort progress.
+        int be_running = 0;
+        for (Tenant *t : be) {
+            int st = t->state.load(std::memory_order_acquire);
+            if (st == ST_RUNNING) {
+                cudaError_t q = cudaEventQuery(t->done);
+                if (q == cudaSuccess) {
+                    int stop = t->exec->kind == GPX_EXEC_BLP ? *t->exec->h_stop_index : -1;
+                    if (stop == -1) {
+                        t->state.store(ST_DONE, std::memory_order_release);
+                        seq_release(t);
+                    } else {
+                        t->stop_index = stop;
+                        t->state.store(ST_SUSPENDED, std::memory_order_release);
+                    }
+                } else if (q != cudaErrorNotReady) {
+                    set_error("event query failed: %s", cudaGetErrorString(q));
+                    return GPX_FAIL;
+                } else {
+                    ++be_running;
+                }
+            }
+        }
+        if (word_raised && drain_pending && be_running == 0) {
+            stats.drain_us.push_back((now_ns() - t_raise) / 1e3);
+            drain_pending = false;
+        }
+        // 3. the word is cleared only when no latency-critical request is in the system and
+        //    every best-effort stream has quiesced, so no kernel can run ahead of an incomplete
+        //    predecessor.
+        if (word_raised && hp_active == 0 && be_running == 0) GPX_TRY(clear());
+        // 4. best-effort launches and resumes while the word is clear.
+        if (!word_raised) {
+            for (Tenant *t : be) {
+                int st = t->state.load(std::memory_order_acquire);
+                if (st == ST_SUBMITTED) {
+                    if (policy == POLICY_SEQ && !seq_turn(t)) continue;
+                    GPX_TRY(launch_full(t));
+                    ++stats.be_launches;
+                    t->state.store(ST_RUNNING, std::memory_order_release);
+                } else if (st == ST_SUSPENDED) {
+                    GPX_TRY(launch_resume(t));
+                    ++stats.be_resumes;
+                    ++t->resumes;
+                    t->state.store(ST_RUNNING, std::memory_order_release);
+                }
+            }
+        }
+        return GPX_SUCC;
+    }
+
+    // Strict serialisation (src/common-clients/seqclient.cpp:82-102): one request on the GPU
+    // at a time, in submission order.
+    Tenant *seq_owner = nullptr;
+    bool seq_turn(Tenant *t) {
+        if (seq_owner && seq_owner != t) return false;
+        if (!seq_owner) {
+            uint64_t mine = t->ticket.load(std::memory_order_relaxed);
+            for (Tenant *o : hp)
+                if (o != t && o->state.load(std::memory_order_relaxed) == ST_SUBMITTED &&
+                    o->ticket.load(std::memory_order_relaxed) < mine)
+                    return false;
+            for (Tenant *o : be)
+                if (o != t && o->state.load(std::memory_order_relaxed) == ST_SUBMITTED &&
+                    o->ticket.load(std::memory_order_relaxed) < mine)
+                    return false;
+            seq_owner = t;
+        }
+        return true;
+    }
+    void seq_release(Tenant *t) {
+        if (seq_owner == t) seq_owner = nullptr;
+    }
+
+    void run() {
+        if (gpx_init(device) != GPX_SUCC) {
+            fail("dispatcher gpx_init");
+            return;
+        }
+        while (!stop.load(std::memory_order_relaxed)) {
+            if (step() != GPX_SUCC) {
+                fail("dispatcher step");
+                return;
+            }
+        }
+    }
+};
+
+// ---- the benchmark suite ----------------------------------------------------------------------
+
+static std::atomic<uint64_t> g_ticket{1};
+
+struct Suite {
+    std::vector<std::unique_ptr<Tenant>> tenants;
+    std::vector<std::unique_ptr<Dispatcher>> dispatchers;  // one per GPU
+    Policy policy = POLICY_YIELD;
+    double time_s = 1.0;
+    int warmup = 5, standalone = 20;
+    uint64_t seed = 0;
+    bool hint = true;
+    int word_transport = GPX_WORD_DEVICE;
+    std::string end_when;  // "" = time; otherwise run ends when this task hits max_requests
+    std::atomic<bool> stop{false};
+    uint64_t run_begin = 0, run_end = 0;
+
+    Dispatcher *dispatcher_for(int gpu) {
+        for (auto &d : dispatchers)
+            if (d->device == gpu) return d.get();
+        return nullptr;
+    }
+
+    // One request through the six phases of BenchmarkTask::inferOnce (benchmark.cpp:66-135).
+    int infer_once(Tenant *t, Dispatcher *d, Record *rec) {
+        uint64_t t0 = now_ns();
+        rec->arrive = t0;
+        uint64_t t1 = now_ns();  // prepareInput: inputs are pre-generated
+        bool hinting = d->hint && t->priority == 0 && d->policy == POLICY_YIELD;
+        if (t->preprocess_us) {
+            // The pre-preemption hint of the reference fires ~100 us before the data-prepare
+            // phase ends (gpreemptclient.cpp:203-219); here the word is raised when copyInput
+            // begins, which hides the drain behind the input copy.
+            usleep((useconds_t)t->preprocess_us);
+        }
+        uint64_t t2 = now_ns();
+        if (hinting) t->state.store(ST_HINTED, std::memory_order_release);
+        GPX_CUDA(cudaMemcpyAsync(t->model->storages[0].dptr, t->h_in, t->in_bytes,
+                                 cudaMemcpyHostToDevice, t->stream));
+        GPX_CUDA(cudaStreamSynchronize(t->stream));
+        uint64_t t3 = now_ns();
+        t->submit_ns = t3;
+        t->ticket.store(g_ticket.fetch_add(1), std::memory_order_relaxed);
+        t->state.store(ST_SUBMITTED, std::memory_order_release);
+        // Spin for the dispatcher's DONE; best-effort clients back off between polls.
+        for (uint32_t spin = 0;; ++spin) {
+            if (t->state.load(std::memory_order_acquire) == ST_DONE) break;
+            if (d->failed.load(std::memory_order_relaxed)) {
+                set_error("dispatcher failed: %s", d->error.c_str());
+                return GPX_FAIL;
+            }
+            if (t->priority != 0 && (spin & 15) == 15) usleep(20);
+        }
+        t->state.store(ST_IDLE, std::memory_order_release);
+        uint64_t t4 = now_ns();
+        int head = t->model->nodes[t->model->head_node].storage;
+        GPX_CUDA(cudaMemcpyAsync(t->h_out, t->model->storages[head].dptr, t->out_bytes,
+                                 cudaMemcpyDeviceToHost, t->stream));
+        GPX_CUDA(cudaStreamSynchronize(t->stream));
+        uint64_t t5 = now_ns();
+        rec->prepare = t1 - t0;
+        rec->preprocess = t2 - t1;
+        rec->copy_in = t3 - t2;
+        rec->infer = t4 - t3;
+        rec->copy_out = t5 - t4;
+        rec->postprocess = 0;
+        return GPX_SUCC;
+    }
+};
+
+static double percentile(std::vector<double> v, double p) {
+    if (v.empty()) return 0;
+    std::sort(v.begin(), v.end());
+    double pos = p * (v.size() - 1);
+    size_t lo = (size_t)pos;
+    size_t hi = std::min(lo + 1, v.size() - 1);
+    return v[lo] + (v[hi] - v[lo]) * (pos - lo);
+}
+
+static Json summarize(const std::vector<double> &v) {
+    Json j = Json::object();
+    j.set("count", Json((long long)v.size()));
+    if (v.empty()) return j;
+    double sum = 0, mx = 0;
+    for (double x : v) {
+        sum += x;
+        mx = std::max(mx, x);
+    }
+    j.set("mean", Json(sum / v.size()));
+    j.set("p50", Json(percentile(v, 0.5)));
+    j.set("p90", Json(percentile(v, 0.9)));
+    j.set("p99", Json(percentile(v, 0.99)));
+    j.set("max", Json(mx));
+    return j;
+}
+
+static int parse_policy(const std::string &client, Policy *p, bool *rt_only, bool *hint) {
+    *rt_only = false;
+    *hint = true;
+    if (client == "gpreemptclient") *p = POLICY_YIELD;
+    else if (client == "gpreemptclient_wo") { *p = POLICY_YIELD; *hint = false; }
+    else if (client == "blpclient") *p = POLICY_BLP_WAIT;
+    else if (client == "baseclient") *p = POLICY_BASE;
+    else if (client == "seqclient") *p = POLICY_SEQ;
+    else if (client == "rtonlyclient") { *p = POLICY_BASE; *rt_only = true; }
+    else {
+        set_error("unknown client '%s'", client.c_str());
+        return GPX_NOT_FOUND;
+    }
+    return GPX_SUCC;
+}
+
+static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
+    bool rt_only = false, hint = true;
+    GPX_TRY(parse_policy(client, &s.policy, &rt_only, &hint));
+    s.hint = cfg.has("preempt_hint") ? cfg["preempt_hint"].as_bool() : hint;
+    s.time_s = cfg["time"].as_double(1.0);
+    if (cfg.has("warmup")) s.warmup = (int)cfg["warmup"].as_int();
+    if (cfg.has("standalone")) s.standalone = (int)cfg["standalone"].as_int();
+    s.seed = (uint64_t)cfg["seed"].as_int(0);
+    if (cfg.has("word_transport"))
+        s.word_transport = cfg["word_transport"].as_string() == "mapped" ? GPX_WORD_MAPPED : GPX_WORD_DEVICE;
+    s.end_when = cfg["end_when"].as_string();
+    int default_gpu = (int)cfg["device"].as_int(0);
+    const Json &tasks = cfg["tasks"];
+    GPX_REQUIRE(tasks.is_array() && tasks.size() > 0, GPX_FAIL, "config has no tasks");
+    for (size_t i = 0; i < tasks.size(); ++i) {
+        const Json &jt = tasks[i];
+        std::string id = jt["id"].as_string();
+        // rtonlyclient keeps only tasks whose id contains "_rt" (rtonlyclient.cpp:132-139).
+        if (rt_only && id.find("_rt") == std::string::npos) continue;
+        std::unique_ptr<Tenant> t(new Tenant());
+        t->id = id;
+        const Json &jc = jt["client"], &jl = jt["load"];
+        t->name = jc["name"].as_string();
+        t->model_name = jc["model_name"].as_string();
+        t->priority = (int)jc["priority"].as_int(1);
+        t->batch = (int)jc["batch_size"].as_int(1);
+        t->use_graph = jc["use_cuda_graph"].as_bool(false);
+        t->preprocess_us = (uint64_t)jc["preprocess_time"].as_int(0);
+        t->gpu = jc.has("gpu") ? (int)jc["gpu"].as_int() : default_gpu;
+        t->seed = jc.has("seed") ? (uint64_t)jc["seed"].as_int() : s.seed + 100 + i;
+        std::string lt = jl["type"].as_string();
+        if (lt == "continuous") t->load.type = Load::Continuous;
+        else if (lt == "periodic") t->load.type = Load::Periodic;
+        else if (lt == "poisson") t->load.type = Load::Poisson;
+        else if (lt == "trace") t->load.type = Load::Trace;
+        else if (lt == "burst") t->load.type = Load::Burst;
+        else {
+            set_error("task %s: unknown load type '%s'", id.c_str(), lt.c_str());
+            return GPX_NOT_FOUND;
+        }
+        t->load.frequency = jl["frequency"].as_double(0);
+        if (jl.has("on")) t->load.on_s = jl["on"].as_double(1.0);
+        if (jl.has("off")) t->load.off_s = jl["off"].as_double(1.0);
+        if (jl.has("max_requests")) t->load.max_requests = jl["max_requests"].as_int(-1);
+        const Json &tr = jl["trace"];
+        for (size_t k = 0; k < tr.size(); ++k) t->load.trace_ms.push_back(tr[k].as_double());
+        s.tenants.push_back(std::move(t));
+    }
+    GPX_REQUIRE(!s.tenants.empty(), GPX_FAIL, "no task left after filtering");
+    return GPX_SUCC;
+}
+
+static int init_tenant(Suite &s, Tenant *t) {
+    GPX_TRY(gpx_init(t->gpu));
+    gpx_model_opts o{};
+    o.batch = t->batch;
+    GPX_TRY(gpx_model_open(t->model_name.c_str(), &o, &t->model));
+    GPX_TRY(gpx_model_init_random(t->model, 1));
+    bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);
+    GPX_TRY(gpx_exec_create(t->model, blp ? GPX_EXEC_BLP : GPX_EXEC_BASE, &t->exec));
+    Dispatcher *d = s.dispatcher_for(t->gpu);
+    if (blp) GPX_TRY(gpx_exec_set_word(t->exec, d->word));
+    gpx_stream st;
+    GPX_TRY(gpx_stream_create(&st, t->priority == 0 ? 0 : 1));
+    t->stream = as_stream(st);
+    GPX_CUDA(cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming));
+    GPX_CUDA(cudaEventCreate(&t->ev_first));
+    GPX_CUDA(cudaEventCreate(&t->ev_last));
+    const Storage &in = t->model->storages[0];
+    const Storage &out = t->model->storages[t->model->nodes[t->model->head_node].storage];
+    t->in_bytes = in.bytes;
+    t->out_bytes = out.bytes;
+    GPX_CUDA(cudaHostAlloc(&t->h_in, t->in_bytes, cudaHostAllocPortable));
+    GPX_CUDA(cudaHostAlloc(&t->h_out, t->out_bytes, cudaHostAllocPortable));
+    normal_fill((float *)t->h_in, t->in_bytes / sizeof(float), t->seed, 0, 0.f, 1.f);
+    if (t->use_graph) GPX_TRY(gpx_exec_capture_graph(t->exec, t->stream));
+    return GPX_SUCC;
+}
+
+static void destroy_suite(Suite &s) {
+    for (auto &d : s.dispatchers) {
+        d->stop.store(true);
+        if (d->thread.joinable()) d->thread.join();
+    }
+    for (auto &tp : s.tenants) {
+        Tenant *t = tp.get();
+        if (t->model) cudaSetDevice(t->gpu);
+        if (t->stream) cudaStreamSynchronize(t->stream);
+        if (t->exec) gpx_exec_destroy(t->exec);
+        if (t->model) gpx_model_close(t->model);
+        if (t->done) cudaEventDestroy(t->done);
+        if (t->ev_first) cudaEventDestroy(t->ev_first);
+        if (t->ev_last) cudaEventDestroy(t->ev_last);
+        if (t->stream) cudaStreamDestroy(t->stream);
+        if (t->h_in) cudaFreeHost(t->h_in);
+        if (t->h_out) cudaFreeHost(t->h_out);
+    }
+    for (auto &d : s.dispatchers) {
+        cudaSetDevice(d->device);
+        if (d->clear_event) cudaEventDestroy(d->clear_event);
+        if (d->word) gpx_word_destroy(d->word);
+    }
+}
+
+static int run_suite(Suite &s, Json *report) {
+    // Dispatchers, one per GPU in use.
+    for (auto &tp : s.tenants) {
+        if (s.dispatcher_for(tp->gpu)) continue;
+        std::unique_ptr<Dispatcher> d(new Dispatcher());
+        d->device = tp->gpu;
+        d->policy = s.policy;
+        d->hint = s.hint;
+        GPX_TRY(gpx_init(d->device));
+        if (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT) {
+            GPX_TRY(gpx_word_create(&d->word, s.word_transport));
+            GPX_CUDA(cudaEventCreateWithFlags(&d->clear_event, cudaEventDisableTiming));
+            GPX_CUDA(cudaEventRecord(d->clear_event, d->word->wstream));
+        }
+        s.dispatchers.push_back(std::move(d));
+    }
+    // client->init() for every task on the calling thread (benchmark.cpp:187-199).
+    for (auto &tp : s.tenants) {
+        GPX_TRY(init_tenant(s, tp.get()));
+        Dispatcher *d = s.dispatcher_for(tp->gpu);
+        (tp->priority == 0 ? d->hp : d->be).push_back(tp.get());
+    }
+    for (auto &d : s.dispatchers) d->thread = std::thread([dp = d.get()] { dp->run(); });
+
+    // Warm-up, then stand-alone latency of each client (benchmark.cpp:221-299).
+    for (auto &tp : s.tenants) {
+        Tenant *t = tp.get();
+        GPX_TRY(gpx_init(t->gpu));
+        Dispatcher *d = s.dispatcher_for(t->gpu);
+        Record r{};
+        for (int i = 0; i < s.warmup; ++i) GPX_TRY(s.infer_once(t, d, &r));
+        Record sum{};
+        int n = std::max(1, s.standalone);
+        for (int i = 0; i < n; ++i) {
+            GPX_TRY(s.infer_once(t, d, &r));
+            sum.prepare += r.prepare;
+            sum.preprocess += r.preprocess;
+            sum.copy_in += r.copy_in;
+            sum.infer += r.infer;
+            sum.copy_out += r.copy_out;
+            sum.postprocess += r.postprocess;
+        }
+        t->standalone.prepare = sum.prepare / n;
+        t->standalone.preprocess = sum.preprocess / n;
+        t->standalone.copy_in = sum.copy_in / n;
+        t->standalone.infer = sum.infer / n;
+        t->standalone.copy_out = sum.copy_out / n;
+        t->standalone.postprocess = sum.postprocess / n;
+    }
+    for (auto &d : s.dispatchers) {
+        d->stats = Stats();
+    }
+
+    // One thread per task (benchmark.cpp:325-328).
+    s.run_begin = now_ns() + 50000000ull;
+    s.run_end = s.run_begin + (uint64_t)(s.time_s * 1e9);
+    std::atomic<int> core{0};
+    std::atomic<int> errors{0};
+    std::string first_error;
+    std::vector<std::thread> threads;
+    for (size_t i = 0; i < s.tenants.size(); ++i) {
+        Tenant *t = s.tenants[i].get();
+        t->load.start(s.run_begin, s.run_end, s.seed * 7919 + 2 + i);
+        t->records.reserve(1 << 16);
+        threads.emplace_back([&, t] {
+            gpx_bind_core(core.fetch_add(1) + 1);
+            if (gpx_init(t->gpu) != GPX_SUCC) {
+                errors.fetch_add(1);
+                return;
+            }
+            Dispatcher *d = s.dispatcher_for(t->gpu);
+            while (t->load.wait_next(s.stop)) {
+                Record r{};
+                if (!t->ev_first_recorded) {
+                    cudaEventRecord(t->ev_first, t->stream);
+                    t->ev_first_recorded = true;
+                    t->first_ns = now_ns();
+                }
+                if (s.infer_once(t, d, &r) != GPX_SUCC) {
+                    if (errors.fetch_add(1) == 0) first_error = last_error();
+                    s.stop.store(true);
+                    return;
+                }
+                t->last_ns = now_ns();
+                t->records.push_back(r);
+            }
+            cudaEventRecord(t->ev_last, t->stream);
+            cudaStreamSynchronize(t->stream);
+            if (!s.end_when.empty() && t->id == s.end_when) s.stop.store(true);
+        });
+    }
+    for (auto &th : threads) th.join();
+    uint64_t t_end = now_ns();
+    for (auto &d : s.dispatchers) {
+        d->stop.store(true);
+        if (d->thread.joinable()) d->thread.join();
+        if (d->failed.load()) {
+            set_error("%s", d->error.c_str());
+            return GPX_FAIL;
+        }
+    }
+    if (errors.load()) {
+        set_error("client thread failed: %s", first_error.c_str());
+        return GPX_FAIL;
+    }
+
+    // Report: the keys of BasicAnalyzer::generateReport (analyzer.cpp:154-168) plus percentiles.
+    Json root = Json::object();
+    Json jt = Json::array();
+    for (auto &tp : s.tenants) {
+        Tenant *t = tp.get();
+        Json j = Json::object();
+        j.set("id", t->id);
+        j.set("type", "basic");
+        j.set("model", t->model_name);
+        j.set("priority", Json(t->priority));
+        j.set("batch_size", Json(t->batch));
+        j.set("gpu", Json(t->gpu));
+        size_t n = t->records.size();
+        j.set("requests", Json((long long)n));
+        double span_s = n ? (t->last_ns - s.run_begin) / 1e9 : 0;
+        if (t->load.type == Load::Continuous && !s.end_when.empty() && n)
+            span_s = (t->last_ns - t->first_ns) / 1e9;
+        double wall_s = (std::min(t_end, s.run_end) - s.run_begin) / 1e9;
+        if (!s.end_when.empty() || wall_s <= 0) wall_s = span_s;
+        j.set("avgThroughput(req/s)", Json(wall_s > 0 ? n / wall_s : 0.0));
+        j.set("throughput(inf/s)", Json(wall_s > 0 ? n * (double)t->batch / wall_s : 0.0));
+        float dev_ms = 0;
+        if (n && t->ev_first_recorded) {
+            cudaSetDevice(t->gpu);
+            if (cudaEventElapsedTime(&dev_ms, t->ev_first, t->ev_last) != cudaSuccess) dev_ms = 0;
+        }
+        j.set("deviceSpan(ms)", Json((double)dev_ms));
+        Record sum{};
+        std::vector<double> total_us, infer_us;
+        for (const Record &r : t->records) {
+            sum.prepare += r.prepare;
+            sum.preprocess += r.preprocess;
+            sum.copy_in += r.copy_in;
+            sum.infer += r.infer;
+            sum.copy_out += r.copy_out;
+            sum.postprocess += r.postprocess;
+            total_us.push_back(r.total() / 1e3);
+            infer_us.push_back(r.infer / 1e3);
+        }
+        auto avg = [&](uint64_t v) { return Json((long long)(n ? v / n / 1000 : 0)); };
+        long long sa = (long long)(t->standalone.total() / 1000);
+        long long av = (long long)(n ? sum.total() / n / 1000 : 0);
+        j.set("standAloneTotalLatency(us)", Json(sa));
+        j.set("standAloneInferLatency(us)", Json((long long)(t->standalone.infer / 1000)));
+        j.set("avgPrepareInputLatency(us)", avg(sum.prepare));
+        j.set("avgPreprocessLatency(us)", avg(sum.preprocess));
+        j.set("avgCopyInputLatency(us)", avg(sum.copy_in));
+        j.set("avgInferLatency(us)", avg(sum.infer));
+        j.set("avgCopyOutputLatency(us)", avg(sum.copy_out));
+        j.set("avgPostprocessLatency(us)", avg(sum.postprocess));
+        j.set("avgTotalLatency(us)", Json(av));
+        j.set("avgTotalLatencyIncrease(us)", Json(av - sa));
+        j.set("totalLatency(us)", summarize(total_us));
+        j.set("inferLatency(us)", summarize(infer_us));
+        j.set("resumes", Json(t->resumes));
+        j.set("in_bytes", Json((long long)t->in_bytes));
+        j.set("out_bytes", Json((long long)t->out_bytes));
+        size_t nk = 0;
+        gpx_model_kernel_num(t->model, &nk);
+        j.set("kernels", Json((long long)nk));
+        jt.push(j);
+    }
+    root.set("tasks", jt);
+    Json jd = Json::array();
+    for (auto &d : s.dispatchers) {
+        Json j = Json::object();
+        j.set("gpu", Json(d->device));
+        j.set("wordRaises", Json(d->stats.raises));
+        j.set("beLaunches", Json(d->stats.be_launches));
+        j.set("beResumes", Json(d->stats.be_resumes));
+        j.set("preemptLatency(us)", summarize(d->stats.drain_us));
+        j.set("hpDispatchDelay(us)", summarize(d->stats.hp_queue_us));
+        jd.push(j);
+    }
+    root.set("gpus", jd);
+    root.set("elapsed(s)", Json((t_end - s.run_begin) / 1e9));
+    const char *pn = s.policy == POLICY_YIELD      ? "yield"
+                     : s.policy == POLICY_BLP_WAIT ? "blp-wait"
+                     : s.policy == POLICY_SEQ      ? "seq"
+                                                   : "base";
+    root.set("policy", pn);
+    root.set("preempt_hint", Json(s.hint));
+    *report = root;
+    return GPX_SUCC;
+}
+
+}  // namespace gpx
+
+using namespace gpx;
+
+extern "C" int gpx_run_workload(const char *client, const char *config_json, char *report,
+                                size_t cap, size_t *needed) {
+    GPX_REQUIRE(client && config_json, GPX_FAIL, "NULL argument");
+    Json cfg;
+    std::string err;
+    if (!Json::parse(config_json, &cfg, &err)) {
+        set_error("config is not valid JSON: %s", err.c_str());
+        return GPX_FAIL;
+    }
+    Suite s;
+    int st = build_suite(s, client, cfg);
+    Json rep;
+    if (st == GPX_SUCC) st = run_suite(s, &rep);
+    std::string saved = last_error();
+    s.stop.store(true);
+    destroy_suite(s);
+    if (st != GPX_SUCC) {
+        set_error("%s", saved.c_str());
+        return st;
+    }
+    std::string text = rep.dump(1);
+    if (needed) *needed = text.size() + 1;
+    if (!report || cap < text.size() + 1) {
+        set_error("report needs %zu bytes", text.size() + 1);
+        return report ? GPX_OUT_OF_RANGE : GPX_SUCC;
+    }
+    memcpy(report, text.c_str(), text.size() + 1);
+    return GPX_SUCC;
+}

@@ -159,6 +159,9 @@ int gpx_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, vo
                   const gpx_blp *blp, gpx_stream s);
 int gpx_gemm_ctx_bytes(size_t *bytes);
 int gpx_gemm_tiles(int M, int N, int *tiles);
+/* Blocking read of the context header: *error is 0, or the code of the bounded wait that
+ * gave up inside the kernel (the kernel then returned early and C is incomplete). */
+int gpx_gemm_status(const void *ctx, int *error, int *error_cta);
 
 /* ---- seeded synthetic data ---------------------------------------------------------- */
 
