@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Headline benchmark: two tenants on one GPU (per rank).
+
+Workload (the reference's A-type contention config, config/A.json, at the sizes the baseline
+names): a latency-critical ResNet-50 batch-1 fp32 client with Poisson arrivals at 100 req/s and
+a best-effort ResNet-50 batch-32 fp32 client that resubmits continuously.  A "step" is one
+best-effort batch (32 inferences) executed while the latency-critical load keeps arriving.
+
+    python bench.py --gpus N --steps K --warmup W          # this library, one rank per GPU
+    python bench.py --impl reference --steps K --warmup W  # CPU port of the same forward
+
+Rank 0 prints ONE JSON line.  `value` is the whole-job best-effort throughput (inf/s) under
+contention with inputs resident in HBM; `e2e` is the same with every request's input copied
+from pinned host memory and its result copied back inside the timed region; `hp` carries the
+latency-critical p50/p99 under contention and solo, `preempt_us` the word-raise -> drained
+latency.  No number here is produced on the CPU oracle except the `cpu_baseline` object.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BE_BATCH = 32
+HP_RATE = 100.0
+
+
+def workload_config(device: int, steps: int, warmup: int, resident: bool, hp: bool = True,
+                    be: bool = True, seconds: float = 600.0) -> dict:
+    tasks = []
+    if hp:
+        tasks.append({
+            "id": "resnet50_rt",
+            "load": {"type": "poisson", "priority": 0, "frequency": HP_RATE},
+            "client": {"name": "resnet50_rt", "model_name": "resnet50", "priority": 0,
+                       "batch_size": 1, "use_cuda_graph": True, "preprocess_time": 0},
+        })
+    if be:
+        tasks.append({
+            "id": "resnet50_be",
+            "load": {"type": "continuous", "priority": 1, "max_requests": steps},
+            "client": {"name": "resnet50_be", "model_name": "resnet50", "priority": 1,
+                       "batch_size": BE_BATCH, "use_cuda_graph": True, "preprocess_time": 0},
+        })
+    cfg = {"time": seconds, "device": device, "seed": 2, "warmup": warmup, "standalone": 5,
+           "resident_inputs": resident, "tasks": tasks}
+    if be:
+        cfg["end_when"] = "resnet50_be"
+    return cfg
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.device)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fp:
+            return json.load(fp), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def conv_roofline(api, device: int) -> dict:
+    """Per-layer device time of one best-effort forward, measured with CUDA events on the
+    launching stream, and the algorithmic FLOP rate of the convolution kernels."""
+    ex = api.BLPExecutor()
+    ex.init("resnet50", batch=BE_BATCH, seed=1)
+    word = api.PreemptWord(1)
+    ex.set_word(word)
+    s = api.Stream(1)
+    data = api.synth_normal(BE_BATCH * 3 * 224 * 224, 0).reshape(BE_BATCH, 3, 224, 224)
+    ex.set_input("data", data)
+    nk = ex.get_kernel_num()
+    infos = [ex.model.get_kernel_info(i) for i in range(nk)]
+    for _ in range(3):
+        ex.execute(s)
+    s.sync()
+    events = [api.Event() for _ in range(nk + 1)]
+    reps = 5
+    per_kernel = [0.0] * nk
+    for _ in range(reps):
+        ex.execute(s)  # zeroes the tile cursors; its own kernels are not the timed ones
+        s.sync()
+        # relaunch every kernel with fresh cursors, an event between each pair
+        import ctypes
+        from gpreempt_b200 import binding as B
+        B.check(B.load().gpx_memset(ctypes.c_void_p(_cursor_ptr(ex)), 0, 4 * nk, s.handle))
+        events[0].record(s)
+        for i in range(nk):
+            ex.launch_kernel(i, s)
+            events[i + 1].record(s)
+        events[nk].sync()
+        for i in range(nk):
+            per_kernel[i] += events[i].elapsed_ms(events[i + 1]) / reps
+    conv = [(infos[i], per_kernel[i]) for i in range(nk) if "pool" not in infos[i]["name"]]
+    flops = sum(k["flops"] for k, _ in conv)
+    ms = sum(t for _, t in conv)
+    total_ms = sum(per_kernel)
+    top = sorted(((per_kernel[i], infos[i]["name"]) for i in range(nk)), reverse=True)[:3]
+    ex.clear(), word.destroy(), s.destroy()
+    for e in events:
+        e.destroy()
+    return {"conv_flops_per_step": flops, "conv_ms_per_step": ms, "all_kernels_ms_per_step": total_ms,
+            "conv_launches_per_step": len(conv), "top": [[round(t, 4), n] for t, n in top]}
+
+
+def _cursor_ptr(ex) -> int:
+    """Device address of the executor's executed[] array (read back through the C ABI)."""
+    import ctypes
+    from gpreempt_b200 import binding as B
+    p = ctypes.c_void_p()
+    B.check(B.load().gpx_exec_cursor_dptr(ex.handle, ctypes.byref(p)))
+    return p.value
+
+
+def cpu_baseline(images: int = 4) -> dict:
+    """The oracle's fp32 forward (a port, not the reference's TVM build) timed on host cores."""
+    import numpy as np
+    from oracle import oracle as orc
+
+    orc.build()
+    rng = np.random.default_rng(1)
+    params = {}
+    for name, shape in orc.resnet_param_shapes().items():
+        if name.endswith("weight"):
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
+    orc.forward("resnet50", params, data, fast=True)  # warm-up
+    t0 = time.perf_counter()
+    for _ in range(images):
+        orc.forward("resnet50", params, data, fast=True)
+    dt = time.perf_counter() - t0
+    return {"value": images / dt, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{images} ResNet-50 fp32 batch-1 forwards of the CPU oracle "
+                      f"(fp32 accumulate, OpenMP), {dt:.1f} s"}
+
+
+def run_reference(args, rank: int) -> None:
+    """Reference arm: the reference's arithmetic cannot be built here (TVM-generated kernels are
+    absent from its tree), so the CPU port of the same forward is timed, one image per step."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+
+    orc.build()
+    rng = np.random.default_rng(1)
+    params = {}
+    for name, shape in orc.resnet_param_shapes().items():
+        if name.endswith("weight"):
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
+    for _ in range(max(1, min(args.warmup, 3))):
+        orc.forward("resnet50", params, data, fast=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.forward("resnet50", params, data, fast=True)
+    dt = time.perf_counter() - t0
+    value = args.steps / dt
+    sample = "each step = 1 of the 32 images of a best-effort batch (ResNet-50 fp32 forward on the CPU)"
+    line = {
+        "impl": "reference", "metric": "be_throughput_under_hp_contention", "value": value,
+        "unit": "inf/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: HP ResNet-50 b1 Poisson 100 req/s vs BE ResNet-50 b32 "
+                               "closed loop, fp32", "note": sample},
+        "cpu_baseline": {"value": value, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "inf/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="gpx", choices=["gpx", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    from gpreempt_b200 import api, dist
+    from gpreempt_b200 import binding as B
+    import ctypes
+
+    group = dist.init(world, rank)
+    device = local_rank if world > 1 else 0
+    api.init_cuda(device)
+
+    def launches() -> int:
+        c = ctypes.c_uint64()
+        B.check(B.load().gpx_launch_count(ctypes.byref(c)))
+        return c.value
+
+    # solo runs: latency-critical alone (rtonlyclient) and best-effort alone
+    hp_solo = json.loads(api.run_workload(
+        "rtonlyclient", json.dumps(workload_config(device, 0, args.warmup, False, be=False, seconds=2.0))))
+    be_solo = json.loads(api.run_workload(
+        "baseclient", json.dumps(workload_config(device, max(20, args.steps // 4), args.warmup, True, hp=False))))
+
+    sampler = ClockSampler(device)
+    dist.barrier(group)
+    api.device_sync()
+    sampler.start()
+    l0 = launches()
+    t0 = time.perf_counter()
+    resident = json.loads(api.run_workload(
+        "gpreemptclient", json.dumps(workload_config(device, args.steps, args.warmup, True))))
+    api.device_sync()
+    t1 = time.perf_counter()
+    l1 = launches()
+    e2e = json.loads(api.run_workload(
+        "gpreemptclient", json.dumps(workload_config(device, args.steps, args.warmup, False))))
+    api.device_sync()
+    dist.barrier(group)
+    clocks = sampler.stop()
+
+    def task(rep, tid):
+        return next(t for t in rep["tasks"] if t["id"] == tid)
+
+    be_r, be_e = task(resident, "resnet50_be"), task(e2e, "resnet50_be")
+    hp_r, hp_e = task(resident, "resnet50_rt"), task(e2e, "resnet50_rt")
+    # device-timed span of exactly K best-effort steps (CUDA events on the best-effort stream)
+    ms_resident = be_r["deviceSpan(ms)"]
+    ms_e2e = be_e["deviceSpan(ms)"]
+    worst_resident = dist.max_over_ranks(group, ms_resident)
+    worst_e2e = dist.max_over_ranks(group, ms_e2e)
+    total_inf = world * args.steps * BE_BATCH
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        roof = conv_roofline(api, device)
+        tflops = roof["conv_flops_per_step"] / (roof["conv_ms_per_step"] * 1e-3) / 1e12
+        peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        line = {
+            "metric": "be_throughput_under_hp_contention",
+            "value": total_inf / (worst_resident * 1e-3),
+            "unit": "inf/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": worst_resident / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32",
+            "data": "synthetic",
+            "config": {
+                "workload": "configs[1]: HP ResNet-50 b1 fp32 Poisson 100 req/s vs BE ResNet-50 b32 "
+                            "fp32 closed loop, one scheduler per GPU (replicas)",
+                "be_batch": BE_BATCH, "hp_rate_hz": HP_RATE, "policy": "gpreemptclient (in-kernel yield)",
+                "l2": "every step streams 3 GB of layer traffic (weights + activations), larger than L2",
+                "step": "one best-effort batch under latency-critical load",
+            },
+            "e2e": {"value": total_inf / (worst_e2e * 1e-3), "unit": "inf/s",
+                    "h2d_bytes_per_step": be_e["in_bytes"], "d2h_bytes_per_step": be_e["out_bytes"],
+                    "ms_per_step": worst_e2e / args.steps},
+            "hp": {
+                "p50_ms": hp_e["totalLatency(us)"].get("p50", 0) / 1e3,
+                "p99_ms": hp_e["totalLatency(us)"].get("p99", 0) / 1e3,
+                "requests": hp_e["requests"],
+                "solo_p50_ms": task(hp_solo, "resnet50_rt")["totalLatency(us)"].get("p50", 0) / 1e3,
+                "solo_p99_ms": task(hp_solo, "resnet50_rt")["totalLatency(us)"].get("p99", 0) / 1e3,
+                "resident_p99_ms": hp_r["totalLatency(us)"].get("p99", 0) / 1e3,
+            },
+            "be_solo_inf_s": task(be_solo, "resnet50_be")["throughput(inf/s)"],
+            "preempt_us": e2e["gpus"][0]["preemptLatency(us)"],
+            "be_resumes": e2e["gpus"][0]["beResumes"],
+            "gpu_launches": l1 - l0,
+            "wall_s_resident_run": t1 - t0,
+            "roofline": {
+                "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
+                "frac": tflops / peak, "traffic": None,
+                "kernel": "conv_simt_kernel (fp32 implicit-GEMM convolution, best-effort batch 32)",
+                "peak_source": f"bf16_tflops_sustained of {peak_kind} peaks",
+                "launches_per_step": roof["conv_launches_per_step"],
+                "ms_per_step_all_kernels": roof["all_kernels_ms_per_step"],
+                "top_kernels_ms": roof["top"],
+            },
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    dist.finish(group)
+
+
+if __name__ == "__main__":
+    main()

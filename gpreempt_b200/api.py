@@ -24,6 +24,10 @@ def init_cuda(device: int = 0) -> None:
     _initialised.add(device)
 
 
+def device_sync() -> None:
+    check(B.load().gpx_device_sync())
+
+
 def device_info() -> dict:
     sm, mem = ctypes.c_int(), ctypes.c_size_t()
     name = ctypes.create_string_buffer(128)
@@ -448,6 +452,33 @@ def run_workload(client: str, config_json: str) -> str:
     check(B.load().gpx_run_workload(client.encode(), config_json.encode(), buf, cap,
                                     ctypes.byref(need)))
     return buf.value.decode()
+
+
+def fill_uniform(buf: DeviceBuffer, n: int, bf16: bool, seed: int, stream_id: int = 0,
+                 stream=None, lo: float = -1.0, hi: float = 1.0) -> None:
+    """Fills a device buffer with the counter-based uniform generator (fp32 or bf16)."""
+    check(B.load().gpx_fill_uniform(buf.ptr, n, int(bf16), seed, stream_id, lo, hi, _h(stream)))
+    check(B.load().gpx_stream_sync(_h(stream)))
+
+
+def count_diff(a: DeviceBuffer, b: DeviceBuffer, nbytes: int, stream=None) -> int:
+    d = ctypes.c_uint64()
+    check(B.load().gpx_count_diff(a.ptr, b.ptr, nbytes, ctypes.byref(d), _h(stream)))
+    return d.value
+
+
+def preempt_microbench(kind: str, size: int, triggers: int, seed: int = 5,
+                       transport: int = B.WORD_DEVICE) -> dict:
+    """Runs gpx_preempt_microbench; kind is "axpy" (size = elements) or "gemm" (size = M=N=K)."""
+    summary = B.MicrobenchSummary()
+    drain = (ctypes.c_double * max(triggers, 1))()
+    seen = (ctypes.c_double * max(triggers, 1))()
+    check(B.load().gpx_preempt_microbench(0 if kind == "axpy" else 1, size, triggers, seed,
+                                          transport, drain, seen, ctypes.byref(summary)))
+    out = {name: getattr(summary, name) for name, _ in B.MicrobenchSummary._fields_}
+    out["drain_us"] = list(drain[:summary.preempted])
+    out["seen_us"] = list(seen[:summary.preempted])
+    return out
 
 
 def clock_offset_ns() -> tuple[int, int]:

@@ -30,6 +30,17 @@ class Blp(ctypes.Structure):
     ]
 
 
+class MicrobenchSummary(ctypes.Structure):
+    _fields_ = [
+        ("triggers", ctypes.c_int), ("preempted", ctypes.c_int), ("resumes", ctypes.c_int),
+        ("mismatches", ctypes.c_int), ("kernel_ms", ctypes.c_double),
+        ("drain_us_p50", ctypes.c_double), ("drain_us_p99", ctypes.c_double),
+        ("drain_us_max", ctypes.c_double), ("drain_us_mean", ctypes.c_double),
+        ("seen_us_p50", ctypes.c_double), ("seen_us_p99", ctypes.c_double),
+        ("clock_uncertainty_ns", ctypes.c_double),
+    ]
+
+
 class ModelOpts(ctypes.Structure):
     _fields_ = [("batch", ctypes.c_int), ("dtype", ctypes.c_char_p), ("seq_len", ctypes.c_int)]
 
@@ -86,6 +97,10 @@ _SIGS = {
     "gpx_gemm_ctx_bytes": [P(sz)],
     "gpx_gemm_tiles": [ci, ci, P(ci)],
     "gpx_gemm_status": [vp, P(ci), P(ci)],
+    "gpx_preempt_microbench": [ci, sz, ci, u64, ci, P(ctypes.c_double), P(ctypes.c_double),
+                               P(MicrobenchSummary)],
+    "gpx_fill_uniform": [vp, sz, ci, u64, u64, ctypes.c_float, ctypes.c_float, vp],
+    "gpx_count_diff": [vp, vp, sz, P(u64), vp],
     "gpx_synth_normal": [vp, sz, u64, u64, ctypes.c_float, ctypes.c_float],
     "gpx_synth_uniform": [vp, sz, u64, u64, ctypes.c_float, ctypes.c_float],
     "gpx_model_open": [ctypes.c_char_p, P(ModelOpts), P(vp)],
@@ -113,6 +128,8 @@ _SIGS = {
     "gpx_exec_resume": [vp, vp, P(ci)],
     "gpx_exec_enable_trace": [vp, ci],
     "gpx_exec_read_trace": [vp, P(u64), sz, P(sz)],
+    "gpx_launch_count": [P(u64)],
+    "gpx_exec_cursor_dptr": [vp, P(vp)],
     "gpx_exec_read_cursors": [vp, P(ci), sz, P(sz)],
     "gpx_run_workload": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, sz, P(sz)],
     "gpx_clock_offset_ns": [P(i64), P(i64)],

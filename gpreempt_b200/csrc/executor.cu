@@ -4,11 +4,14 @@
 // getStopPoint (:269-278), resume (:280-298), init (:300-342).
 #include "executor.h"
 
+#include <atomic>
 #include <vector>
 
 using namespace gpx;
 
 namespace gpx {
+
+std::atomic<unsigned long long> g_kernel_launches{0};
 
 BlpArgs exec_blp_args(gpx_exec *e, size_t idx) {
     BlpArgs b{};
@@ -34,6 +37,7 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
                   cudaGetErrorString(err));
         return GPX_FAIL;
     }
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     return GPX_SUCC;
 }
 
@@ -121,6 +125,7 @@ int gpx_exec_execute(gpx_exec *e, gpx_stream stream) {
     cudaStream_t s = as_stream(stream);
     if (e->graph_exec) {
         GPX_CUDA(cudaGraphLaunch(e->graph_exec, s));
+        g_kernel_launches.fetch_add(e->model->kernels.size(), std::memory_order_relaxed);
         return GPX_SUCC;
     }
     GPX_TRY(exec_prologue(e, s));
@@ -147,6 +152,7 @@ int gpx_exec_capture_graph(gpx_exec *e, gpx_stream stream) {
     int st = exec_prologue(e, s);
     size_t nk = e->model->kernels.size();
     for (size_t i = 0; st == GPX_SUCC && i < nk; ++i) st = exec_launch(e, i, s);
+    g_kernel_launches.fetch_sub(st == GPX_SUCC ? nk : 0, std::memory_order_relaxed);  // captured, not run
     cudaError_t err = cudaStreamEndCapture(s, &e->graph);
     if (st != GPX_SUCC) return st;
     GPX_CUDA(err);
@@ -184,6 +190,18 @@ int gpx_exec_resume(gpx_exec *e, gpx_stream stream, int *resumed_from) {
     GPX_REQUIRE((size_t)v < nk, GPX_FAIL, "stop index %d outside the kernel list", v);
     cudaStream_t s = as_stream(stream);
     for (size_t i = (size_t)v; i < nk; ++i) GPX_TRY(exec_launch(e, i, s));
+    return GPX_SUCC;
+}
+
+int gpx_exec_cursor_dptr(gpx_exec *e, void **dptr) {
+    GPX_REQUIRE(e && dptr, GPX_FAIL, "NULL argument");
+    *dptr = e->d_executed;
+    return GPX_SUCC;
+}
+
+int gpx_launch_count(uint64_t *count) {
+    GPX_REQUIRE(count, GPX_FAIL, "count is NULL");
+    *count = g_kernel_launches.load(std::memory_order_relaxed);
     return GPX_SUCC;
 }
 

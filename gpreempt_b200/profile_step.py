@@ -1,0 +1,65 @@
+"""Small, self-terminating workloads for `ncu` captures of the hot kernels.
+
+    python -m gpreempt_b200.profile_step gemm  [--size 8192] [--iters 2]
+    python -m gpreempt_b200.profile_step axpy  [--size 268435456] [--iters 2]
+    python -m gpreempt_b200.profile_step model [--model resnet50] [--batch 32] [--iters 2]
+
+Each run launches the kernels of interest `iters` times with preemption armed (the word stays
+clear) and exits; inputs are larger than L2 so DRAM counters are meaningful, and at most a few
+GB are held on the device.
+"""
+from __future__ import annotations
+
+import argparse
+
+from . import api
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "axpy", "model"])
+    ap.add_argument("--size", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--batch", type=int, default=32)
+    a = ap.parse_args()
+    api.init_cuda(0)
+    s = api.Stream(1)
+    word = api.PreemptWord(1)
+    if a.what == "gemm":
+        n = a.size or 8192
+        da, db = api.DeviceBuffer(n * n * 2), api.DeviceBuffer(n * n * 2)
+        dc = api.DeviceBuffer(n * n * 2)
+        api.fill_uniform(da, n * n, True, 3, 0, s)
+        api.fill_uniform(db, n * n, True, 3, 1, s)
+        ctx = api.GemmContext()
+        blp = api.BlpContext(word, trace=False)
+        for _ in range(a.iters):
+            ctx.reset(), blp.reset()
+            api.gemm_bf16(da, db, dc, n, n, n, ctx, blp, s)
+            s.sync()
+        assert ctx.status() == (0, 0)
+    elif a.what == "axpy":
+        n = a.size or (1 << 28)
+        dx, dy = api.DeviceBuffer(n * 4), api.DeviceBuffer(n * 4)
+        api.fill_uniform(dx, n, False, 4, 0, s)
+        api.fill_uniform(dy, n, False, 4, 1, s)
+        blp = api.BlpContext(word, trace=False)
+        for _ in range(a.iters):
+            blp.reset()
+            api.axpy(1.0009765625, dx, dy, n, blp, s)
+            s.sync()
+    else:
+        ex = api.BLPExecutor()
+        ex.init(a.model, batch=a.batch, seed=1)
+        ex.set_word(word)
+        data = api.synth_normal(a.batch * 3 * 224 * 224, 0).reshape(a.batch, 3, 224, 224)
+        ex.set_input("data", data)
+        for _ in range(a.iters):
+            ex.execute(s)
+            assert ex.getStopPoint(s) == -1
+    print("done")
+
+
+if __name__ == "__main__":
+    main()

@@ -163,6 +163,31 @@ int gpx_gemm_tiles(int M, int N, int *tiles);
  * gave up inside the kernel (the kernel then returned early and C is incomplete). */
 int gpx_gemm_status(const void *ctx, int *error, int *error_cta);
 
+/* Preemption microbenchmark: `triggers` times, launch the best-effort kernel (kind 0 = fp32
+ * axpy over `size` elements, kind 1 = bf16 GEMM with M = N = K = `size`), raise the preempt
+ * word after a uniformly random delay in [0, kernel time), wait for the drain, clear, resume
+ * until complete, and compare the result with an uninterrupted run bit for bit.  Asserted,
+ * repeated form of src/tests/test-dnn-blp.cpp:36-43.  Flag-to-drain latency = %globaltimer of
+ * the last CTA exit (moved to the host clock with gpx_clock_offset_ns) minus the host time just
+ * before the raise.  drain_us / seen_us (may be NULL) receive one sample per preempted launch. */
+typedef struct gpx_microbench_summary {
+    int triggers;     /* launches attempted */
+    int preempted;    /* launches that drained before completing */
+    int resumes;      /* relaunches needed to complete them */
+    int mismatches;   /* runs whose result differed from the uninterrupted run (must be 0) */
+    double kernel_ms; /* uninterrupted kernel time (CUDA events) */
+    double drain_us_p50, drain_us_p99, drain_us_max, drain_us_mean;
+    double seen_us_p50, seen_us_p99; /* raise -> first CTA observed the word */
+    double clock_uncertainty_ns;
+} gpx_microbench_summary;
+int gpx_preempt_microbench(int kind, size_t size, int triggers, uint64_t seed, int transport,
+                           double *drain_us, double *seen_us, gpx_microbench_summary *out);
+/* Device-side fill with the counter-based generator (fp32, or bf16 when is_bf16) and a
+ * bit-wise comparison of two device buffers; helpers of the microbenchmark and the tests. */
+int gpx_fill_uniform(void *dptr, size_t n, int is_bf16, uint64_t seed, uint64_t stream, float lo,
+                     float hi, gpx_stream s);
+int gpx_count_diff(const void *a, const void *b, size_t bytes, uint64_t *diff, gpx_stream s);
+
 /* ---- seeded synthetic data ---------------------------------------------------------- */
 
 /* Counter-based generator: element i of `stream` under `seed` is a pure function of
@@ -240,6 +265,12 @@ int gpx_exec_resume(gpx_exec *e, gpx_stream s, int *resumed_from);
 /* Device %globaltimer trace of the last run: per kernel 4 uint64 (see gpx_blp.trace). */
 int gpx_exec_enable_trace(gpx_exec *e, int on);
 int gpx_exec_read_trace(gpx_exec *e, uint64_t *out, size_t cap_u64, size_t *n_u64);
+/* Device address of the executed[] cursor array (one int per kernel); zeroing it re-arms every
+ * kernel for a full run, as BLPExecutor::execute does (src/executor.cpp:212-214). */
+int gpx_exec_cursor_dptr(gpx_exec *e, void **dptr);
+/* Number of layer kernels this library has launched in this process so far (kernels replayed
+ * by a CUDA graph launch are counted per graph node). */
+int gpx_launch_count(uint64_t *count);
 /* executed[] cursors (tiles claimed per kernel) of the last run. */
 int gpx_exec_read_cursors(gpx_exec *e, int *out, size_t cap, size_t *n);
 
