@@ -12,7 +12,10 @@
 namespace gpx {
 
 constexpr int kAxpyThreads = 256;
-constexpr size_t kAxpyDefaultTile = 4096;  // elements; 48 KB of traffic per tile
+// Elements per tile.  24 KB of traffic per tile: with 8 resident CTAs per SM sharing ~46 GB/s a
+// tile lasts about 4 us, which bounds the drain after the word is seen; bandwidth is unchanged
+// against larger tiles because the poll and the claim of one CTA overlap the copies of the others.
+constexpr size_t kAxpyDefaultTile = 2048;
 
 // VEC float4 loads of x and of y are issued before the first use so each thread keeps
 // 2*VEC 16-byte requests in flight.

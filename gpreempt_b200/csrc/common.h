@@ -69,4 +69,16 @@ typedef int (*cuStreamWriteValue32_t)(cudaStream_t, unsigned long long, uint32_t
 cuStreamWriteValue32_t driver_stream_write32();
 void *driver_entry(const char *name);
 
+// Host-clock / device-%globaltimer correlation by bounded ping kernels.
+struct ClockProbe {
+    int *flag = nullptr;
+    unsigned long long *seen = nullptr;
+    int *dflag = nullptr;
+    unsigned long long *dseen = nullptr;
+    cudaStream_t stream = nullptr;
+    int init();
+    void destroy();
+    int measure(int pings, uint64_t settle_ns, int64_t *host_minus_device, int64_t *spread);
+};
+
 }  // namespace gpx

@@ -218,9 +218,13 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
     GPX_CUDA(cudaStreamSynchronize(st));
     out->kernel_ms = kernel_ms;
 
+    // The host clock and %globaltimer drift apart by tens of ppm, so the offset is re-measured
+    // right before every trigger.
+    ClockProbe probe;
+    GPX_TRY(probe.init());
     int64_t offset = 0, unc = 0;
-    GPX_TRY(gpx_clock_offset_ns(&offset, &unc));
-    out->clock_uncertainty_ns = (double)unc;
+    GPX_TRY(probe.measure(8, 100000, &offset, &unc));
+    double unc_sum = 0;
 
     std::mt19937_64 rng(seed * 31 + 5);
     std::uniform_real_distribution<double> uni(0.0, 1.0);
@@ -231,6 +235,8 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
         GPX_TRY(gpx_word_clear(word));
         if (transport == GPX_WORD_DEVICE) GPX_CUDA(cudaStreamSynchronize(word->wstream));
         uint64_t delay_ns = (uint64_t)(uni(rng) * kernel_ms * 1e6);
+        GPX_TRY(probe.measure(3, 40000, &offset, &unc));
+        unc_sum += (double)unc;
         GPX_TRY(launch());
         spin_ns(delay_ns);
         uint64_t t_raise = now_ns();
@@ -275,6 +281,8 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
         size_t lo = (size_t)pos, hi = std::min(lo + 1, v.size() - 1);
         return v[lo] + (v[hi] - v[lo]) * (pos - lo);
     };
+    out->clock_uncertainty_ns = triggers ? unc_sum / triggers : (double)unc;
+    probe.destroy();
     out->triggers = triggers;
     out->preempted = preempted;
     out->resumes = resumes_total;

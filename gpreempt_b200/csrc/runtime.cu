@@ -60,6 +60,9 @@ cuStreamWriteValue32_t driver_stream_write32() {
 
 using namespace gpx;
 
+__global__ void gpx_ping_kernel(const int *flag, unsigned long long *seen,
+                                unsigned long long timeout_ns);
+
 // ---- wait / no-op kernels -------------------------------------------------------------------
 
 // One thread waits for *flag != 0, at most timeout_ns of %globaltimer; the outcome goes to
@@ -95,6 +98,60 @@ __global__ void gpx_ping_kernel(const int *flag, unsigned long long *seen,
     }
     *seen = t;
 }
+
+namespace gpx {
+
+int ClockProbe::init() {
+    GPX_CUDA(cudaHostAlloc((void **)&flag, 64, cudaHostAllocMapped));
+    GPX_CUDA(cudaHostAlloc((void **)&seen, 64, cudaHostAllocMapped));
+    GPX_CUDA(cudaHostGetDevicePointer((void **)&dflag, flag, 0));
+    GPX_CUDA(cudaHostGetDevicePointer((void **)&dseen, seen, 0));
+    GPX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    return GPX_SUCC;
+}
+
+void ClockProbe::destroy() {
+    if (stream) cudaStreamDestroy(stream);
+    if (flag) cudaFreeHost(flag);
+    if (seen) cudaFreeHost(seen);
+    stream = nullptr;
+    flag = nullptr;
+    seen = nullptr;
+}
+
+// Each ping launches a one-thread kernel that polls a mapped host flag (bounded), lets it
+// settle, stores the flag at host time th and reads back the device time at which the kernel
+// saw it.  th - seen = (host - device) - transport latency, so the largest sample is the one
+// with the least latency and under-estimates the true offset by that latency (about 1 us).
+// The two clocks drift against each other by tens of ppm, so callers re-measure close to the
+// events they want to place on the other clock.
+int ClockProbe::measure(int pings, uint64_t settle_ns, int64_t *host_minus_device, int64_t *spread) {
+    int64_t lo = INT64_MAX, hi = INT64_MIN;
+    int good = 0;
+    for (int i = 0; i < pings; ++i) {
+        *flag = 0;
+        *seen = 0;
+        gpx_ping_kernel<<<1, 1, 0, stream>>>(dflag, dseen, 200000000ull);
+        GPX_CUDA(cudaGetLastError());
+        uint64_t t_wait = now_ns();
+        while (now_ns() - t_wait < settle_ns) {
+        }
+        uint64_t th = now_ns();
+        __atomic_store_n(flag, 1, __ATOMIC_SEQ_CST);
+        GPX_CUDA(cudaStreamSynchronize(stream));
+        if (*seen == 0) continue;
+        int64_t off = (int64_t)th - (int64_t)*seen;
+        if (off > hi) hi = off;
+        if (off < lo) lo = off;
+        ++good;
+    }
+    GPX_REQUIRE(good > 0, GPX_TIMEOUT, "clock ping never completed");
+    *host_minus_device = hi;
+    if (spread) *spread = hi - lo;
+    return GPX_SUCC;
+}
+
+}  // namespace gpx
 
 extern "C" {
 
@@ -357,46 +414,11 @@ int gpx_noop_launch(gpx_stream s) {
 
 int gpx_clock_offset_ns(int64_t *host_minus_device, int64_t *uncertainty_ns) {
     GPX_REQUIRE(host_minus_device, GPX_FAIL, "NULL argument");
-    int *flag = nullptr;
-    unsigned long long *seen = nullptr;
-    GPX_CUDA(cudaHostAlloc((void **)&flag, 64, cudaHostAllocMapped));
-    GPX_CUDA(cudaHostAlloc((void **)&seen, 64, cudaHostAllocMapped));
-    int *dflag = nullptr;
-    unsigned long long *dseen = nullptr;
-    GPX_CUDA(cudaHostGetDevicePointer((void **)&dflag, flag, 0));
-    GPX_CUDA(cudaHostGetDevicePointer((void **)&dseen, seen, 0));
-    cudaStream_t st;
-    GPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    int64_t best = INT64_MAX, worst = INT64_MIN;
-    int good = 0;
-    for (int i = 0; i < 16; ++i) {
-        *flag = 0;
-        *seen = 0;
-        gpx_ping_kernel<<<1, 1, 0, st>>>(dflag, dseen, 200000000ull);
-        GPX_CUDA(cudaGetLastError());
-        // Let the kernel start polling, then store the flag and note the host time of the store.
-        uint64_t t_wait = now_ns();
-        while (now_ns() - t_wait < 200000) {
-        }
-        uint64_t th = now_ns();
-        __atomic_store_n(flag, 1, __ATOMIC_SEQ_CST);
-        GPX_CUDA(cudaStreamSynchronize(st));
-        if (*seen == 0) continue;
-        // seen = device time at which the store became visible = th + transport latency, so
-        // host - device is over-estimated by at most that latency; the minimum is closest.
-        int64_t off = (int64_t)th - (int64_t)*seen;
-        // off = host - device - latency  =>  the largest value has the smallest latency
-        if (off > worst) worst = off;
-        if (off < best) best = off;
-        ++good;
-    }
-    cudaStreamDestroy(st);
-    cudaFreeHost(flag);
-    cudaFreeHost(seen);
-    GPX_REQUIRE(good > 0, GPX_TIMEOUT, "clock ping never completed");
-    *host_minus_device = worst;
-    if (uncertainty_ns) *uncertainty_ns = worst - best;
-    return GPX_SUCC;
+    ClockProbe probe;
+    GPX_TRY(probe.init());
+    int st = probe.measure(16, 200000, host_minus_device, uncertainty_ns);
+    probe.destroy();
+    return st;
 }
 
 }  // extern "C"
