@@ -241,6 +241,21 @@ def gemm_bf16(a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, m: int, n: int,
                                  ctypes.byref(s) if s is not None else None, _h(stream)))
 
 
+def gemm_bf16_static(a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, m: int, n: int, k: int,
+                     resume: bool = False, blp: BlpContext | None = None, stream=None) -> None:
+    """The same GEMM with its scratch in the library's static device array: nothing is allocated
+    by the call.  For callers that cannot allocate device memory; at most 64 output tiles."""
+    s = blp.struct() if blp is not None else None
+    check(B.load().gpx_gemm_bf16_static(a.ptr, b.ptr, c.ptr, m, n, k, int(resume),
+                                        ctypes.byref(s) if s is not None else None, _h(stream)))
+
+
+def gemm_static_status() -> tuple[int, int]:
+    err, cta = ctypes.c_int(), ctypes.c_int()
+    check(B.load().gpx_gemm_static_status(ctypes.byref(err), ctypes.byref(cta)))
+    return err.value, cta.value
+
+
 def gemm_tiles(m: int, n: int) -> int:
     t = ctypes.c_int()
     check(B.load().gpx_gemm_tiles(m, n, ctypes.byref(t)))

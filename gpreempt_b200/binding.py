@@ -97,6 +97,8 @@ _SIGS = {
     "gpx_gemm_ctx_bytes": [P(sz)],
     "gpx_gemm_tiles": [ci, ci, P(ci)],
     "gpx_gemm_status": [vp, P(ci), P(ci)],
+    "gpx_gemm_bf16_static": [vp, vp, vp, ci, ci, ci, ci, P(Blp), vp],
+    "gpx_gemm_static_status": [P(ci), P(ci)],
     "gpx_preempt_microbench": [ci, sz, ci, u64, ci, P(ctypes.c_double), P(ctypes.c_double),
                                P(MicrobenchSummary)],
     "gpx_fill_uniform": [vp, sz, ci, u64, u64, ctypes.c_float, ctypes.c_float, vp],

@@ -486,3 +486,99 @@ int gpx_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, vo
 }
 
 }  // extern "C"
+
+// ---- variant that allocates nothing ------------------------------------------------------------
+//
+// Some callers of this GEMM cannot allocate device memory: a client whose device memory is
+// handed out once by an external pool or a memory-capped container, a latency-critical thread
+// that must not enter the allocator (cudaMalloc can synchronise the whole device), or code that
+// runs where allocation is simply not permitted.  For them the progress slots and the
+// accumulator spill area live in the file-scope array below instead of a caller-allocated
+// context.  The array is sized for kStaticMaxTiles output tiles (one CTA per tile), is part of
+// the library image and is held by every GPU that loads the library until the process exits.
+namespace gpx {
+
+constexpr int kStaticMaxTiles = 64;
+constexpr size_t kStaticCtxBytes = kSpillOffset + (size_t)kStaticMaxTiles * kSpillBytesPerCta;
+
+static __device__ __align__(256) unsigned char g_gemm_static_ctx[kStaticCtxBytes];
+
+// Device address of g_gemm_static_ctx on each device.  In host code the array's name is only a
+// host-side stand-in for the symbol, never a device address, so the address is looked up once
+// per device (with that device current) and cached.
+static unsigned char *g_static_ctx_addr[64] = {nullptr};
+
+static int static_ctx_address(int device, unsigned char **out) {
+    if (!g_static_ctx_addr[device]) {
+        void *p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, g_gemm_static_ctx);
+        if (err != cudaSuccess || !p) {
+            set_error("cudaGetSymbolAddress(g_gemm_static_ctx) failed on device %d: %s", device,
+                      cudaGetErrorString(err));
+            return GPX_FAIL;
+        }
+        g_static_ctx_addr[device] = (unsigned char *)p;
+    }
+    *out = g_static_ctx_addr[device];
+    return GPX_SUCC;
+}
+
+}  // namespace gpx
+
+extern "C" int gpx_gemm_bf16_static(const void *A, const void *B, void *C, int M, int N, int K,
+                                    int resume, const gpx_blp *blp, gpx_stream s) {
+    GPX_REQUIRE(A && B && C, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(M > 0 && N > 0 && K > 0 && M % kBM == 0 && N % kBN == 0 && K % kBK == 0,
+                GPX_OUT_OF_RANGE, "M, N, K must be multiples of %d, %d, %d", kBM, kBN, kBK);
+    GPX_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)B % 16) == 0 && ((uintptr_t)C % 16) == 0,
+                GPX_FAIL, "A, B and C must be 16-byte aligned");
+    const int tiles = (M / kBM) * (N / kBN);
+    GPX_REQUIRE(tiles <= kStaticMaxTiles, GPX_OUT_OF_RANGE,
+                "gpx_gemm_bf16_static handles at most %d output tiles of %dx%d (M/%d * N/%d = %d "
+                "here); use gpx_gemm_bf16 with a caller-allocated context for larger products",
+                kStaticMaxTiles, kBM, kBN, kBM, kBN, tiles);
+    const DeviceInfo &d = device_info();
+    GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
+    unsigned char *ctx = nullptr;
+    GPX_TRY(static_ctx_address(d.device, &ctx));
+    CUtensorMap ta, tb;
+    GPX_TRY(make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, kBM, kBK));
+    GPX_TRY(make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, kBN, kBK));
+    static bool attr_set[64] = {false};
+    if (!attr_set[d.device]) {
+        GPX_CUDA(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+        attr_set[d.device] = true;
+    }
+    BlpArgs b{};
+    b.total_tiles = tiles;
+    if (blp) {
+        b.preempted = (const int *)blp->preempted;
+        b.stop_index = (int *)blp->stop_index;
+        b.executed = (int *)blp->executed;
+        b.kernel_id = blp->kernel_id;
+        b.trace = (unsigned long long *)blp->trace;
+        GPX_REQUIRE(!b.preempted || b.stop_index, GPX_FAIL, "preemptible launch needs stop_index");
+    }
+    // The array keeps the previous call's contents.  A fresh product must start from zeroed
+    // progress slots and error header; a resume must find them as the drained launch left them.
+    if (!resume) GPX_CUDA(cudaMemsetAsync(ctx, 0, kSpillOffset, as_stream(s)));
+    int grid = tiles < d.sm_count ? tiles : d.sm_count;
+    gemm_bf16_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, as_stream(s)>>>(
+        ta, tb, (__nv_bfloat16 *)C, M, N, K, ctx, b);
+    GPX_CUDA(cudaGetLastError());
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_gemm_static_status(int *error, int *error_cta) {
+    GPX_REQUIRE(error, GPX_FAIL, "NULL argument");
+    const DeviceInfo &d = device_info();
+    GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
+    unsigned char *ctx = nullptr;
+    GPX_TRY(static_ctx_address(d.device, &ctx));
+    GemmHeader h;
+    GPX_CUDA(cudaMemcpy(&h, ctx, sizeof(h), cudaMemcpyDeviceToHost));
+    *error = h.error;
+    if (error_cta) *error_cta = h.error_cta;
+    return GPX_SUCC;
+}

@@ -163,6 +163,27 @@ int gpx_gemm_tiles(int M, int N, int *tiles);
  * gave up inside the kernel (the kernel then returned early and C is incomplete). */
 int gpx_gemm_status(const void *ctx, int *error, int *error_cta);
 
+/* Has no counterpart in the reference.  The same GEMM for callers that cannot allocate device
+ * memory — a client whose device memory is handed out once by an external pool or a capped
+ * container, a latency-critical thread that must stay out of the allocator (cudaMalloc may
+ * synchronise the device), or code running where allocation is not permitted.  The progress
+ * slots and the accumulator spill area live in a static device array inside the library
+ * (8 KiB + 64 x 128 KiB = 8 396 800 bytes, held by every GPU that loads the library until the
+ * process exits), so no context is passed and the call performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine.  Limit: at most 64 output tiles, i.e.
+ * (M / 128) * (N / 256) <= 64 (for example 2048 x 1024), any K that is a multiple of 64; larger
+ * products are rejected with GPX_OUT_OF_RANGE and a message naming the limit.
+ *   resume = 0  start a new product: the slots and the error header are cleared on `s` first
+ *               (the array keeps whatever the previous call left);
+ *   resume = 1  continue a product whose previous launch drained on the preempt word.
+ * The first call on a device looks up the array's device address (a one-time set-up with that
+ * device current); make that first call outside any stream capture.  All calls on a device share
+ * the one array: two calls whose kernels overlap on the GPU race on it, so issue them on one
+ * stream or order them with events.  gpx_gemm_static_status reads the error header (blocking). */
+int gpx_gemm_bf16_static(const void *A, const void *B, void *C, int M, int N, int K, int resume,
+                         const gpx_blp *blp, gpx_stream s);
+int gpx_gemm_static_status(int *error, int *error_cta);
+
 /* Preemption microbenchmark: `triggers` times, launch the best-effort kernel (kind 0 = fp32
  * axpy over `size` elements, kind 1 = bf16 GEMM with M = N = K = `size`), raise the preempt
  * word after a uniformly random delay in [0, kernel time), wait for the drain, clear, resume
