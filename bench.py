@@ -136,12 +136,8 @@ def conv_roofline(api, device: int) -> dict:
     reps = 5
     per_kernel = [0.0] * nk
     for _ in range(reps):
-        ex.execute(s)  # zeroes the tile cursors; its own kernels are not the timed ones
-        s.sync()
         # relaunch every kernel with fresh cursors, an event between each pair
-        import ctypes
-        from gpreempt_b200 import binding as B
-        B.check(B.load().gpx_memset(ctypes.c_void_p(_cursor_ptr(ex)), 0, 4 * nk, s.handle))
+        ex.reset_cursors(s)
         events[0].record(s)
         for i in range(nk):
             ex.launch_kernel(i, s)
@@ -149,28 +145,24 @@ def conv_roofline(api, device: int) -> dict:
         events[nk].sync()
         for i in range(nk):
             per_kernel[i] += events[i].elapsed_ms(events[i + 1]) / reps
-    conv = [(infos[i], per_kernel[i]) for i in range(nk) if "pool" not in infos[i]["name"]]
-    flops = sum(k["flops"] for k, _ in conv)
-    ms = sum(t for _, t in conv)
+    assert ex.error() == (0, 0), ex.error()
+    # tensor-core convolutions run 192-thread CTAs; everything else is a CUDA-core kernel
+    tc = [i for i in range(nk) if infos[i]["launch_params"][3] == 192]
+    dominant = tc if tc else [i for i in range(nk) if "pool" not in infos[i]["name"]]
+    flops = sum(infos[i]["flops"] for i in dominant)
+    ms = sum(per_kernel[i] for i in dominant)
     total_ms = sum(per_kernel)
     top = sorted(((per_kernel[i], infos[i]["name"]) for i in range(nk)), reverse=True)[:3]
     ex.clear(), word.destroy(), s.destroy()
     for e in events:
         e.destroy()
     return {"conv_flops_per_step": flops, "conv_ms_per_step": ms, "all_kernels_ms_per_step": total_ms,
-            "conv_launches_per_step": len(conv), "top": [[round(t, 4), n] for t, n in top]}
+            "conv_launches_per_step": len(dominant), "tensor_core": bool(tc),
+            "share_of_step": ms / total_ms if total_ms else 0.0,
+            "top": [[round(t, 4), n] for t, n in top]}
 
 
-def _cursor_ptr(ex) -> int:
-    """Device address of the executor's executed[] array (read back through the C ABI)."""
-    import ctypes
-    from gpreempt_b200 import binding as B
-    p = ctypes.c_void_p()
-    B.check(B.load().gpx_exec_cursor_dptr(ex.handle, ctypes.byref(p)))
-    return p.value
-
-
-def cpu_baseline(images: int = 4) -> dict:
+def cpu_baseline(images: int = 100) -> dict:
     """The oracle's fp32 forward (a port, not the reference's TVM build) timed on host cores."""
     import numpy as np
     from oracle import oracle as orc
@@ -346,7 +338,10 @@ def main() -> None:
             "roofline": {
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": tflops / peak, "traffic": None,
-                "kernel": "conv_simt_kernel (fp32 implicit-GEMM convolution, best-effort batch 32)",
+                "kernel": ("cgemm_tcgen05_kernel (split-bf16 tensor-core convolution, 3 bf16 MMAs per "
+                           "fp32 MAC, best-effort batch 32)") if roof["tensor_core"] else
+                          "conv_simt_kernel (fp32 FFMA convolution, best-effort batch 32)",
+                "share_of_step": roof["share_of_step"],
                 "peak_source": f"bf16_tflops_sustained of {peak_kind} peaks",
                 "launches_per_step": roof["conv_launches_per_step"],
                 "ms_per_step_all_kernels": roof["all_kernels_ms_per_step"],

@@ -419,6 +419,15 @@ class Executor:
                                            n.value, ctypes.byref(n)))
         return out.reshape(-1, 4)
 
+    def error(self) -> tuple[int, int]:
+        """(code, kernel*1000+cta) of a tensor-core kernel whose bounded wait gave up; (0, 0) = none."""
+        code, where = ctypes.c_int(), ctypes.c_int()
+        check(B.load().gpx_exec_error(self.handle, ctypes.byref(code), ctypes.byref(where)))
+        return code.value, where.value
+
+    def reset_cursors(self, stream=None) -> None:
+        check(B.load().gpx_exec_reset_cursors(self.handle, _h(stream)))
+
     def read_cursors(self) -> np.ndarray:
         n = ctypes.c_size_t()
         check(B.load().gpx_exec_read_cursors(self.handle, None, 0, ctypes.byref(n)))

@@ -1,0 +1,466 @@
+// Convolution as a row-shifted GEMM on the tcgen05 tensor cores, fp32 accuracy from split-bf16
+// operands, K-block-granular preemption.
+//
+// Stands in for the TVM-generated fused conv2d(+bias)(+add)(+relu) kernels the reference
+// replays (src/executor.cpp:157-162).  Activations and weights are stored as two bf16 planes
+// (x ~= hi + lo); one fp32 product is three tensor-core products hi*hi + hi*lo + lo*hi
+// accumulated in fp32 in tensor memory, which keeps 16 mantissa bits per operand and meets the
+// 1e-4 parity bound of the fp32 configuration at a third of the bf16 tensor rate.
+//
+// GEMM view: rows are stored pixels of the input (see act_layout.h), a filter tap is a constant
+// row shift, so the A operand of every K block is a plain 2-D TMA tile [128 rows][64 channels]
+// at row (m0 + shift[tap]); rows outside the tensor are zero-filled by TMA.  B is the weight
+// matrix [Cout][taps*Cin].  Rows that are not real output pixels (image borders of the padded
+// layouts) are computed and dropped by the epilogue.
+//
+// CTA roles, ring, messages and the preempt / spill / resume protocol are those of
+// gemm_tcgen05.cu; the epilogue additionally adds the bias and the residual, applies ReLU,
+// splits the fp32 result into hi/lo planes and scatters rows into the consumer's layout.
+#include "layers.cuh"
+#include "sm100.cuh"
+
+#include <cuda_bf16.h>
+
+namespace gpx {
+
+using namespace sm100;
+
+constexpr int kCBM = 128, kCBK = 64, kCUmmaK = 16;
+constexpr int kCgemmThreads = 192;
+constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
+constexpr int kCPollEvery = 2;
+
+template <int BN>
+struct CgemmCfg {
+    static constexpr uint32_t kABytes = kCBM * kCBK * 2;        // one plane of A: 16 KiB
+    static constexpr uint32_t kWBytes = BN * kCBK * 2;          // one plane of W
+    static constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kWBytes;
+    static constexpr int kStages = BN == 128 ? 3 : 4;
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + 256;
+    // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
+    // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
+    static constexpr int kAccs = 4;
+    static constexpr int kTmemCols = kAccs * BN;
+};
+
+enum : int { CMSG_DATA = 0, CMSG_STOP = 1, CMSG_EXIT = 2 };
+enum : int { CEPI_COMPLETE = 0, CEPI_PARTIAL = 1, CEPI_EXIT = 2 };
+
+struct CgemmControl {
+    unsigned long long full[4];
+    unsigned long long empty[4];
+    unsigned long long tmem_full;
+    unsigned long long tmem_empty;
+    uint32_t tmem_base;
+    int stage_msg[4];
+    int epi_kind;
+    int epi_k_done;
+    int epi_go;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&p);
+}
+__device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi_to_f32(uint32_t packed) {
+    return __uint_as_float(packed & 0xffff0000u);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kCgemmThreads, 1)
+cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
+    using Cfg = CgemmCfg<BN>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ unsigned char smem_raw[];
+    uint32_t raw_addr = smem_u32(smem_raw);
+    uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    unsigned char *smem = smem_raw + pad;
+    CgemmControl *ctl = reinterpret_cast<CgemmControl *>(smem + (size_t)kStages * Cfg::kStageBytes);
+    const uint32_t smem_base = smem_u32(smem);
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = p.taps * p.cin_blocks;
+    const bool resumable = blp.preempted != nullptr;
+
+    CgemmSlot *slot = p.slots + blockIdx.x;
+    float *spill = p.spill + (size_t)blockIdx.x * (kCBM * Cfg::kTmemCols);
+    // A non-preemptible launch never stops early, so it neither reads nor writes the cursor.
+    const int first_iter = resumable ? slot->next_iter : 0;
+    const int first_k = resumable ? slot->k_done : 0;
+    const int slot_grid = resumable ? slot->grid : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl->tmem_full), 2);
+        mbar_init(smem_u32(&ctl->tmem_empty), 1);
+        ctl->abort_flag = 0;
+        ctl->epi_kind = CEPI_EXIT;
+        ctl->epi_k_done = 0;
+        ctl->epi_go = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        trace_begin(blp);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&ctl->tmem_base), Cfg::kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const bool grid_ok = slot_grid == 0 || slot_grid == (int)gridDim.x;
+    auto fail = [&](int code) {
+        ctl->abort_flag = 1;
+        if (atomicCAS(p.error, 0, code) == 0) p.error[1] = blp.kernel_id * 1000 + (int)blockIdx.x;
+    };
+
+    if (!grid_ok) {
+        if (threadIdx.x == 0) fail(900);
+    } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int flag = resumable ? load_word(blp.preempted) : 0;
+            int msg = CMSG_EXIT;
+            bool ok = true;
+            for (int it = first_iter; ok; ++it) {
+                int tile = blockIdx.x + it * gridDim.x;
+                if (tile >= total_tiles) break;
+                // Column tiles vary fastest: CTAs that run together share the same A rows.
+                const int n_blk = tile % p.tiles_n;
+                const int m_blk = tile / p.tiles_n;
+                const int kb0 = it == first_iter ? first_k : 0;
+                for (int kb = kb0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs)) {
+                        fail(101);
+                        ok = false;
+                        break;
+                    }
+                    if (resumable && ((kb - kb0) % kCPollEvery) == 0) {
+                        if (flag != 0) {
+                            msg = CMSG_STOP;
+                            ok = false;
+                            break;
+                        }
+                        flag = load_word(blp.preempted);
+                    }
+                    const int tap = kb / p.cin_blocks;
+                    const int cb = kb - tap * p.cin_blocks;
+                    ctl->stage_msg[stage] = CMSG_DATA;
+                    const uint32_t bar = smem_u32(&ctl->full[stage]);
+                    mbar_arrive_expect_tx(bar, Cfg::kStageBytes);
+                    const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
+                    const int a_row = m_blk * kCBM + p.tap_shift[tap];
+                    const int w_col = tap * p.cin + cb * kCBK;
+                    tma_load_2d(dst, &p.a_hi, bar, cb * kCBK, a_row);
+                    tma_load_2d(dst + Cfg::kABytes, &p.a_lo, bar, cb * kCBK, a_row);
+                    tma_load_2d(dst + 2 * Cfg::kABytes, &p.w_hi, bar, w_col, n_blk * BN);
+                    tma_load_2d(dst + 2 * Cfg::kABytes + Cfg::kWBytes, &p.w_lo, bar, w_col, n_blk * BN);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!*abort_flag) {
+                bool have_slot = msg == CMSG_STOP;
+                if (!have_slot)
+                    have_slot = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs);
+                if (have_slot) {
+                    ctl->stage_msg[stage] = msg;
+                    mbar_arrive(smem_u32(&ctl->full[stage]));
+                } else {
+                    fail(102);
+                }
+                if (msg == CMSG_STOP && blp.trace) atomicMin(blp.trace + 2, globaltimer_ns());
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16_f32(kCBM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t seg = 0;
+            int kb = first_k;
+            bool seg_open = false;
+            for (;;) {
+                if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, kCWaitLimitNs)) {
+                    fail(201);
+                    break;
+                }
+                tc_fence_after_sync();
+                const int msg = ctl->stage_msg[stage];
+                if (!seg_open) {
+                    if (!mbar_wait(smem_u32(&ctl->tmem_empty), seg & 1, abort_flag, kCWaitLimitNs)) {
+                        fail(202);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    seg_open = true;
+                }
+                if (msg != CMSG_DATA) {
+                    ctl->epi_kind = msg == CMSG_STOP ? CEPI_PARTIAL : CEPI_EXIT;
+                    ctl->epi_k_done = kb;
+                    mma_commit(smem_u32(&ctl->tmem_full));
+                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                    break;
+                }
+                const uint32_t base = smem_base + stage * Cfg::kStageBytes;
+                const uint64_t a_hi = make_smem_desc_sw128(base);
+                const uint64_t a_lo = make_smem_desc_sw128(base + Cfg::kABytes);
+                const uint64_t w_hi = make_smem_desc_sw128(base + 2 * Cfg::kABytes);
+                const uint64_t w_lo = make_smem_desc_sw128(base + 2 * Cfg::kABytes + Cfg::kWBytes);
+#pragma unroll
+                for (int k = 0; k < kCBK / kCUmmaK; ++k) {
+                    // fp32 product from three bf16 products.  The tensor core truncates when it
+                    // adds into the fp32 accumulator, a bias that grows with the length of the
+                    // accumulation chain, so the chain is split over four accumulators that the
+                    // epilogue adds with round-to-nearest: the dominant hi*hi terms alternate
+                    // between two of them, the small hi*lo and lo*hi terms get one each.  The
+                    // order is fixed, so a resumed tile replays exactly the instruction sequence
+                    // of an uninterrupted one.
+                    const uint32_t first = kb > 0 ? 1u : 0u;
+                    mma_f16_ss(tmem_base + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc,
+                               (first || k > 1) ? 1u : 0u);
+                    mma_f16_ss(tmem_base + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                    mma_f16_ss(tmem_base + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                }
+                mma_commit(smem_u32(&ctl->empty[stage]));
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                if (++kb == num_kb) {
+                    ctl->epi_kind = CEPI_COMPLETE;
+                    ctl->epi_k_done = num_kb;
+                    mma_commit(smem_u32(&ctl->tmem_full));
+                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                    ++seg;
+                    kb = 0;
+                    seg_open = false;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const bool leader = threadIdx.x == 64;
+        uint32_t v[32];
+        if (first_k > 0) {
+            for (int c = 0; c < Cfg::kTmemCols; c += 32) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint4 q = src[j];
+                    v[4 * j + 0] = q.x;
+                    v[4 * j + 1] = q.y;
+                    v[4 * j + 2] = q.z;
+                    v[4 * j + 3] = q.w;
+                }
+                tmem_st_32x32(t_lane + c, v);
+            }
+            tmem_st_wait();
+        }
+        tc_fence_before_sync();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (leader) mbar_arrive(smem_u32(&ctl->tmem_empty));
+
+        int it = first_iter;
+        int seg_k0 = first_k;
+        int tiles_done = 0;
+        const int img = p.in_hs * p.in_ws;
+        for (uint32_t seg = 0;; ++seg) {
+            if (leader) {
+                bool ok = mbar_wait(smem_u32(&ctl->tmem_full), seg & 1, abort_flag, kCWaitLimitNs);
+                if (!ok) fail(301);
+                ctl->epi_go = ok ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!ctl->epi_go) break;
+            tc_fence_after_sync();
+            const int kind = ctl->epi_kind;
+            const int k_done = ctl->epi_k_done;
+            if (kind == CEPI_EXIT) {
+                if (leader && resumable) {
+                    slot->next_iter = it;
+                    slot->k_done = 0;
+                    slot->grid = gridDim.x;
+                }
+                break;
+            }
+            if (kind == CEPI_COMPLETE) {
+                const int tile = blockIdx.x + it * gridDim.x;
+                const int n_blk = tile % p.tiles_n;
+                const int m_blk = tile / p.tiles_n;
+                // Which output pixel, if any, does this GEMM row stand for?
+                const int vrow = m_blk * kCBM + row;
+                bool valid = vrow < p.m_rows;
+                int n_img = 0, h = 0, w = 0;
+                if (valid) {
+                    n_img = vrow / img;
+                    int r = vrow - n_img * img;
+                    int hs = r / p.in_ws;
+                    int ws = r - hs * p.in_ws;
+                    h = hs - p.in_off;
+                    w = ws - p.in_off;
+                    valid = h >= 0 && h < p.out.H && w >= 0 && w < p.out.W;
+                }
+                size_t out_off = 0, res_off = 0;
+                if (valid) {
+                    out_off = p.out_f32 ? ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid
+                                        : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
+                    if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
+                }
+                for (int c = 0; c < BN; c += 32) {
+                    float f[32], g[32];
+                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    tmem_ld_32x32(t_lane + BN + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
+                    tmem_ld_32x32(t_lane + 2 * BN + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(v[j]);
+                    tmem_ld_32x32(t_lane + 3 * BN + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] += g[j] + __uint_as_float(v[j]);
+                    if (!valid) continue;
+                    if (p.bias) {
+                        const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + n_blk * BN + c);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 b = __ldg(b4 + j);
+                            f[4 * j + 0] += b.x;
+                            f[4 * j + 1] += b.y;
+                            f[4 * j + 2] += b.z;
+                            f[4 * j + 3] += b.w;
+                        }
+                    }
+                    if (p.res_hi) {
+                        const uint4 *rh = reinterpret_cast<const uint4 *>(p.res_hi + res_off + c);
+                        const uint4 *rl = reinterpret_cast<const uint4 *>(p.res_lo + res_off + c);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 a = rh[j], b = rl[j];
+                            const uint32_t ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                f[8 * j + 2 * q + 0] += bf16_lo_to_f32(ah[q]) + bf16_lo_to_f32(bl[q]);
+                                f[8 * j + 2 * q + 1] += bf16_hi_to_f32(ah[q]) + bf16_hi_to_f32(bl[q]);
+                            }
+                        }
+                    }
+                    if (p.relu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+                    }
+                    if (p.out_f32) {
+                        const int col0 = n_blk * BN + c;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.cout_valid) p.out_f32[out_off + col0 + j] = f[j];
+                        continue;
+                    }
+                    uint4 *oh = reinterpret_cast<uint4 *>(p.out_hi + out_off + c);
+                    uint4 *ol = reinterpret_cast<uint4 *>(p.out_lo + out_off + c);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t hi[4], lo[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float x0 = f[8 * j + 2 * q], x1 = f[8 * j + 2 * q + 1];
+                            uint32_t ph = pack_bf16(x0, x1);
+                            hi[q] = ph;
+                            lo[q] = pack_bf16(x0 - bf16_lo_to_f32(ph), x1 - bf16_hi_to_f32(ph));
+                        }
+                        oh[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        ol[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    }
+                }
+                ++it;
+                ++tiles_done;
+                seg_k0 = 0;
+                tc_fence_before_sync();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (leader) {
+                    mbar_arrive(smem_u32(&ctl->tmem_empty));
+                    if (blp.executed) atomicAdd(blp.executed, 1);
+                }
+                continue;
+            }
+            // CEPI_PARTIAL
+            if (k_done > seg_k0) {
+                for (int c = 0; c < Cfg::kTmemCols; c += 32) {
+                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_wait();
+                    uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        dst[j] = make_uint4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+            if (leader) {
+                slot->next_iter = it;
+                slot->k_done = k_done;
+                slot->grid = gridDim.x;
+                if (blp.stop_index) atomicCAS(blp.stop_index, -1, blp.kernel_id);
+            }
+            break;
+        }
+        if (leader && blp.trace && tiles_done) atomicAdd(blp.trace + 3, (unsigned long long)tiles_done);
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0 && lane == 0 && *abort_flag) {
+        for (int spin = 0; spin < 64; ++spin) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+    if (threadIdx.x == 0 && blp.trace) atomicMax(blp.trace + 1, globaltimer_ns());
+}
+
+cudaError_t cgemm_prepare(int device) {
+    static bool done[64] = {false};
+    if (device < 0 || device >= 64 || done[device]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(cgemm_tcgen05_kernel<128>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)CgemmCfg<128>::kSmem);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(cgemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)CgemmCfg<64>::kSmem);
+    if (e != cudaSuccess) return e;
+    done[device] = true;
+    return cudaSuccess;
+}
+
+cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s) {
+    if (bn == 128)
+        cgemm_tcgen05_kernel<128><<<grid, kCgemmThreads, CgemmCfg<128>::kSmem, s>>>(p, blp);
+    else
+        cgemm_tcgen05_kernel<64><<<grid, kCgemmThreads, CgemmCfg<64>::kSmem, s>>>(p, blp);
+    return cudaGetLastError();
+}
+
+size_t cgemm_spill_floats_per_cta() { return (size_t)kCBM * CgemmCfg<128>::kTmemCols; }
+
+}  // namespace gpx

@@ -1,12 +1,13 @@
-// fp32 convolution / dense layer as an implicit GEMM on the CUDA cores (FFMA), with the
-// bias + residual + ReLU epilogue fused and block-level preemption at output-tile granularity.
-// It stands in for the TVM-generated fused conv2d / dense kernels the reference replays
-// (src/executor.cpp:157-162); the preemption loop is the native form of
-// scripts/compile/convert_to_blp.py:39-70.
+// Convolution / dense layer as an implicit GEMM on the CUDA cores (fp32 FFMA), pooling and
+// sub-sampling; block-level preemption at output-tile granularity.
 //
-// Exact fp32 arithmetic (one FFMA per multiply-add, K walked in increasing order inside one
-// thread), so the result does not depend on which CTA runs a tile: preempt + resume is
-// bit-identical to an uninterrupted run.
+// These kernels cover what the tensor-core convolution does not: the stem (fp32 NCHW input with
+// three channels), dense layers with a handful of rows, and the memory-bound layers.  They stand
+// in for TVM-generated fused kernels the reference replays (src/executor.cpp:157-162); the
+// preemption loop is the native form of scripts/compile/convert_to_blp.py:39-70.
+//
+// One FFMA per multiply-add with K walked in increasing order inside one thread, so the result
+// does not depend on which CTA runs a tile: preempt + resume is bit-identical.
 #include "layers.cuh"
 
 namespace gpx {
@@ -14,15 +15,28 @@ namespace gpx {
 constexpr int kConvThreads = 256;
 constexpr int kConvBK = 16;
 
+__device__ __forceinline__ float bf16_bits_to_f32(bf16_bits v) {
+    return __uint_as_float((unsigned)v << 16);
+}
+__device__ __forceinline__ bf16_bits f32_to_bf16_bits(float f) {
+    unsigned u = __float_as_uint(f);
+    u += 0x7fffu + ((u >> 16) & 1u);  // round to nearest even (finite inputs)
+    return (bf16_bits)(u >> 16);
+}
+
+__device__ __forceinline__ float view_load(const ActView &v, int n, int h, int w, int c) {
+    if (v.f32) return v.f32[(((size_t)n * v.l.C + c) * v.l.H + h) * v.l.W + w];
+    size_t off = (size_t)layout_row(v.l, n, h, w) * v.l.C + c;
+    return bf16_bits_to_f32(v.hi[off]) + bf16_bits_to_f32(v.lo[off]);
+}
+
 template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__(kConvThreads)
-conv_simt_kernel(ConvParams p, BlpArgs blp) {
+conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
     constexpr int BK = kConvBK;
     static_assert((BM / TM) * (BN / TN) == kConvThreads, "thread layout");
-    constexpr int SA = (BM * 4 + kConvThreads - 1) / kConvThreads;  // float4 slots of A per thread
     constexpr int SB = (BN * 4 + kConvThreads - 1) / kConvThreads;  // float4 slots of B per thread
-    constexpr int EA = BM / 16;  // scalar A elements per thread on the generic path
-    static_assert(EA <= SA * 4, "register staging too small");
+    constexpr int EA = BM / 16;                                      // A elements per thread
 
     __shared__ __align__(16) float As[2][BK][BM + 4];
     __shared__ __align__(16) float Bs[2][BK][BN + 4];
@@ -31,9 +45,9 @@ conv_simt_kernel(ConvParams p, BlpArgs blp) {
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN);
     const int ty = tid / (BN / TN);
-    const bool vecA = (p.Cin % BK == 0) && !p.in_nchw;
     const int nchunks = (p.K + BK - 1) / BK;
     const bool dynamic = blp.preempted != nullptr;
+    const int H = p.in.l.H, W = p.in.l.W;
 
     if (tid == 0) trace_begin(blp);
     int iter = 0;
@@ -50,72 +64,39 @@ conv_simt_kernel(ConvParams p, BlpArgs blp) {
         const int m0 = (tile % p.tiles_m) * BM;
         const int n0 = (tile / p.tiles_m) * BN;
 
-        // Pixel coordinates of the A rows this thread stages; fixed for the whole tile.
-        int row_n[SA], row_h[SA], row_w[SA];
-#pragma unroll
-        for (int j = 0; j < SA; ++j) {
-            int r = vecA ? (tid + j * kConvThreads) / 4 : (tid % BM);
-            int m = m0 + r;
-            bool ok = (r < BM) && (m < p.M);
+        // Output pixel of the A row this thread stages; fixed for the whole tile.
+        int row_n, row_h, row_w;
+        {
+            int m = m0 + tid % BM;
+            bool ok = m < p.M;
             int mm = ok ? m : 0;
             int wo = mm % p.Wo;
             int t = mm / p.Wo;
             int ho = t % p.Ho;
-            row_n[j] = ok ? t / p.Ho : -1;
-            row_h[j] = ho * p.stride - p.pad;
-            row_w[j] = wo * p.stride - p.pad;
+            row_n = ok ? t / p.Ho : -1;
+            row_h = ho * p.stride - p.pad;
+            row_w = wo * p.stride - p.pad;
         }
 
-        float ra[SA * 4];
+        float ra[EA];
         float4 rb[SB];
 
         auto load_chunk = [&](int c) {
             const int k0 = c * BK;
-            if (vecA) {
-                // A BK-wide chunk lies inside one filter tap because Cin % BK == 0.
-                const int tap = k0 / p.Cin;
-                const int ci0 = k0 - tap * p.Cin;
-                const int fh = tap / p.kw;
-                const int fw = tap - fh * p.kw;
 #pragma unroll
-                for (int j = 0; j < SA; ++j) {
-                    int i = tid + j * kConvThreads;
-                    int q = i & 3;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    int hi = row_h[j] + fh, wi = row_w[j] + fw;
-                    if (i < BM * 4 && row_n[j] >= 0 && hi >= 0 && hi < p.H && wi >= 0 &&
-                        wi < p.W) {
-                        size_t off = (((size_t)row_n[j] * p.H + hi) * p.W + wi) * p.Cin + ci0 +
-                                     q * 4;
-                        v = *reinterpret_cast<const float4 *>(p.in + off);
-                    }
-                    ra[j * 4 + 0] = v.x;
-                    ra[j * 4 + 1] = v.y;
-                    ra[j * 4 + 2] = v.z;
-                    ra[j * 4 + 3] = v.w;
+            for (int e = 0; e < EA; ++e) {
+                int kk = tid / BM + e * (kConvThreads / BM);
+                int k = k0 + kk;
+                float v = 0.f;
+                if (k < p.K && row_n >= 0) {
+                    int tap = k / p.Cin;
+                    int ci = k - tap * p.Cin;
+                    int fh = tap / p.kw;
+                    int fw = tap - fh * p.kw;
+                    int hi = row_h + fh, wi = row_w + fw;
+                    if (hi >= 0 && hi < H && wi >= 0 && wi < W) v = view_load(p.in, row_n, hi, wi, ci);
                 }
-            } else {
-#pragma unroll
-                for (int e = 0; e < EA; ++e) {
-                    int kk = tid / BM + e * (kConvThreads / BM);
-                    int k = k0 + kk;
-                    float v = 0.f;
-                    if (k < p.K && row_n[0] >= 0) {
-                        int tap = k / p.Cin;
-                        int ci = k - tap * p.Cin;
-                        int fh = tap / p.kw;
-                        int fw = tap - fh * p.kw;
-                        int hi = row_h[0] + fh, wi = row_w[0] + fw;
-                        if (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) {
-                            size_t off =
-                                p.in_nchw
-                                    ? (((size_t)row_n[0] * p.Cin + ci) * p.H + hi) * p.W + wi
-                                    : (((size_t)row_n[0] * p.H + hi) * p.W + wi) * p.Cin + ci;
-                            v = p.in[off];
-                        }
-                    }
-                    ra[e] = v;
-                }
+                ra[e] = v;
             }
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
@@ -132,24 +113,10 @@ conv_simt_kernel(ConvParams p, BlpArgs blp) {
         };
 
         auto store_chunk = [&](int buf) {
-            if (vecA) {
 #pragma unroll
-                for (int j = 0; j < SA; ++j) {
-                    int i = tid + j * kConvThreads;
-                    if (i < BM * 4) {
-                        int r = i >> 2, q = i & 3;
-                        As[buf][q * 4 + 0][r] = ra[j * 4 + 0];
-                        As[buf][q * 4 + 1][r] = ra[j * 4 + 1];
-                        As[buf][q * 4 + 2][r] = ra[j * 4 + 2];
-                        As[buf][q * 4 + 3][r] = ra[j * 4 + 3];
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < EA; ++e) {
-                    int kk = tid / BM + e * (kConvThreads / BM);
-                    As[buf][kk][tid % BM] = ra[e];
-                }
+            for (int e = 0; e < EA; ++e) {
+                int kk = tid / BM + e * (kConvThreads / BM);
+                As[buf][kk][tid % BM] = ra[e];
             }
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
@@ -190,20 +157,31 @@ conv_simt_kernel(ConvParams p, BlpArgs blp) {
             __syncthreads();
         }
 
-        // Epilogue: + bias, + residual, ReLU; NHWC rows are GEMM rows.
+        // Epilogue: + bias, + residual, ReLU; rows go to the consumer's layout.
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             int m = m0 + ty * TM + i;
             if (m >= p.M) continue;
+            int wo = m % p.Wo;
+            int t = m / p.Wo;
+            int ho = t % p.Ho;
+            int n_img = t / p.Ho;
+            size_t out_row = p.out_f32 ? (size_t)m : (size_t)layout_row(p.out, n_img, ho, wo);
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 int n = n0 + tx * TN + j;
                 if (n >= p.Cout) continue;
                 float v = acc[i][j];
                 if (p.bias) v += p.bias[n];
-                if (p.res) v += p.res[(size_t)m * p.Cout + n];
+                if (p.res.hi || p.res.f32) v += view_load(p.res, n_img, ho, wo, n);
                 if (p.relu) v = fmaxf(v, 0.f);
-                p.out[(size_t)m * p.Cout + n] = v;
+                if (p.out_f32) {
+                    p.out_f32[out_row * p.Cout + n] = v;
+                } else {
+                    bf16_bits h = f32_to_bf16_bits(v);
+                    p.out_hi[out_row * p.Cout + n] = h;
+                    p.out_lo[out_row * p.Cout + n] = f32_to_bf16_bits(v - bf16_bits_to_f32(h));
+                }
             }
         }
         ++iter;
@@ -227,8 +205,8 @@ void conv_set_tiles(ConvParams &p, int tile) {
 }
 
 int conv_pick_tile(const ConvParams &p, int sm_count) {
-    // Largest tile that still yields about two waves of CTAs; small-M layers (batch 1, late
-    // stages) fall through to the smallest tile to expose parallelism.
+    // Largest tile that still yields about two waves of CTAs; small-M layers fall through to
+    // the smallest tile to expose parallelism.
     for (int tile = CONV_TILE_128; tile <= CONV_TILE_32; ++tile) {
         int bm, bn;
         tile_dims(tile, bm, bn);
@@ -250,8 +228,7 @@ static int occupancy() {
     return v;
 }
 
-int conv_grid(const ConvParams &p, int tile, int sm_count, bool preemptible) {
-    (void)preemptible;
+int conv_grid(const ConvParams &p, int tile, int sm_count) {
     long long tiles = (long long)p.tiles_m * p.tiles_n;
     int occ = tile == CONV_TILE_128   ? occupancy<128, 128, 8, 8>()
               : tile == CONV_TILE_64 ? occupancy<64, 64, 4, 4>()
@@ -280,18 +257,23 @@ cudaError_t conv_launch(const ConvParams &p, int tile, int grid, const BlpArgs &
     return cudaGetLastError();
 }
 
-// ---- pooling ------------------------------------------------------------------------------
+// ---- pooling / sub-sampling ---------------------------------------------------------------
 
 constexpr int kPoolThreads = 256;
 
-// Max / average pooling over NHWC, one float4 of channels per thread-iteration.  A tile is
-// tile_elems consecutive output float4 vectors.
-__global__ void __launch_bounds__(kPoolThreads) pool_kernel(PoolParams p, BlpArgs blp) {
+// Max / average pooling, or a strided copy, over split-plane activations; eight channels (one
+// 16-byte vector per plane) per thread-iteration.  A tile is tile_elems consecutive output
+// vectors in (n, ho, wo, c/8) order.
+__global__ void __launch_bounds__(kPoolThreads)
+pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
-    const int C4 = p.C / 4;
-    const long long total = (long long)p.N * p.Ho * p.Wo * C4;
+    const int C = p.out.C;
+    const int C8 = C / 8;
+    const int Ho = p.out.H, Wo = p.out.W;
+    const int H = p.in.l.H, W = p.in.l.W;
+    const long long total = (long long)p.out.N * Ho * Wo * C8;
     int iter = 0;
     for (;;) {
         int tile;
@@ -306,50 +288,133 @@ __global__ void __launch_bounds__(kPoolThreads) pool_kernel(PoolParams p, BlpArg
         long long begin = (long long)tile * p.tile_elems;
         long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
         for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
-            int c4 = (int)(e % C4);
-            long long t = e / C4;
-            int wo = (int)(t % p.Wo);
-            t /= p.Wo;
-            int ho = (int)(t % p.Ho);
-            int n = (int)(t / p.Ho);
-            float4 acc = p.mode == 0 ? make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY)
-                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+            int c8 = (int)(e % C8);
+            long long t = e / C8;
+            int wo = (int)(t % Wo);
+            t /= Wo;
+            int ho = (int)(t % Ho);
+            int n = (int)(t / Ho);
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = p.mode == 0 ? -INFINITY : 0.f;
             int cnt = 0;
-            for (int fh = 0; fh < p.k; ++fh) {
+            const int kk = p.mode == 2 ? 1 : p.k;
+            for (int fh = 0; fh < kk; ++fh) {
                 int hi = ho * p.stride - p.pad + fh;
-                if (hi < 0 || hi >= p.H) continue;
-                for (int fw = 0; fw < p.k; ++fw) {
+                if (hi < 0 || hi >= H) continue;
+                for (int fw = 0; fw < kk; ++fw) {
                     int wi = wo * p.stride - p.pad + fw;
-                    if (wi < 0 || wi >= p.W) continue;
-                    float4 v = *reinterpret_cast<const float4 *>(
-                        p.in + (((size_t)n * p.H + hi) * p.W + wi) * p.C + c4 * 4);
-                    if (p.mode == 0) {
-                        acc.x = fmaxf(acc.x, v.x);
-                        acc.y = fmaxf(acc.y, v.y);
-                        acc.z = fmaxf(acc.z, v.z);
-                        acc.w = fmaxf(acc.w, v.w);
-                    } else {
-                        acc.x += v.x;
-                        acc.y += v.y;
-                        acc.z += v.z;
-                        acc.w += v.w;
+                    if (wi < 0 || wi >= W) continue;
+                    size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * C + c8 * 8;
+                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
+                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
+                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float x0 = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
+                        float x1 = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+                        if (p.mode == 0) {
+                            acc[2 * q] = fmaxf(acc[2 * q], x0);
+                            acc[2 * q + 1] = fmaxf(acc[2 * q + 1], x1);
+                        } else {
+                            acc[2 * q] += x0;
+                            acc[2 * q + 1] += x1;
+                        }
                     }
                     ++cnt;
                 }
             }
             if (p.mode == 1) {
                 float inv = 1.0f / (float)cnt;
-                acc.x *= inv;
-                acc.y *= inv;
-                acc.z *= inv;
-                acc.w *= inv;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] *= inv;
             }
-            *reinterpret_cast<float4 *>(p.out + (size_t)e * 4) = acc;
+            unsigned hi4[4], lo4[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                bf16_bits h0 = f32_to_bf16_bits(acc[2 * q]), h1 = f32_to_bf16_bits(acc[2 * q + 1]);
+                bf16_bits l0 = f32_to_bf16_bits(acc[2 * q] - bf16_bits_to_f32(h0));
+                bf16_bits l1 = f32_to_bf16_bits(acc[2 * q + 1] - bf16_bits_to_f32(h1));
+                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+            }
+            size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
+            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
         }
         ++iter;
         if (dynamic) __syncthreads();
     }
     if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+// Patch matrix for the tensor-core GEMM: one thread-iteration writes eight consecutive columns
+// (one 16-byte vector per plane) of one row.
+__global__ void __launch_bounds__(kPoolThreads)
+im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
+    __shared__ int s_tile;
+    const bool dynamic = blp.preempted != nullptr;
+    if (threadIdx.x == 0) trace_begin(blp);
+    const int K8 = p.Kp / 8;
+    const long long total = (long long)p.M * K8;
+    const int H = p.in.l.H, W = p.in.l.W;
+    int iter = 0;
+    for (;;) {
+        int tile;
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = blp_claim(blp, iter);
+        }
+        if (tile < 0) break;
+        long long begin = (long long)tile * p.tile_elems;
+        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+            int k8 = (int)(e % K8);
+            int m = (int)(e / K8);
+            int wo = m % p.Wo;
+            int t = m / p.Wo;
+            int ho = t % p.Ho;
+            int n = t / p.Ho;
+            unsigned hi4[4], lo4[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float x[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    int k = k8 * 8 + q * 2 + u;
+                    float v = 0.f;
+                    if (k < p.K) {
+                        int tap = k / p.Cin;
+                        int ci = k - tap * p.Cin;
+                        int fh = tap / p.kw;
+                        int fw = tap - fh * p.kw;
+                        int hi = ho * p.stride - p.pad + fh, wi = wo * p.stride - p.pad + fw;
+                        if (hi >= 0 && hi < H && wi >= 0 && wi < W) v = view_load(p.in, n, hi, wi, ci);
+                    }
+                    x[u] = v;
+                }
+                bf16_bits h0 = f32_to_bf16_bits(x[0]), h1 = f32_to_bf16_bits(x[1]);
+                bf16_bits l0 = f32_to_bf16_bits(x[0] - bf16_bits_to_f32(h0));
+                bf16_bits l1 = f32_to_bf16_bits(x[1] - bf16_bits_to_f32(h1));
+                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+            }
+            size_t off = (size_t)m * p.Kp + k8 * 8;
+            *reinterpret_cast<uint4 *>(p.out_hi + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+            *reinterpret_cast<uint4 *>(p.out_lo + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+        }
+        ++iter;
+        if (dynamic) __syncthreads();
+    }
+    if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    im2col_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    return cudaGetLastError();
 }
 
 int pool_grid(const PoolParams &p, int sm_count) {

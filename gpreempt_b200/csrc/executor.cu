@@ -30,8 +30,22 @@ BlpArgs exec_blp_args(gpx_exec *e, size_t idx) {
 int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
     const Kernel &k = e->model->kernels[idx];
     BlpArgs b = exec_blp_args(e, idx);
-    cudaError_t err = k.is_conv ? conv_launch(k.conv, k.tile, k.grid, b, s)
-                                : pool_launch(k.pool, k.grid, b, s);
+    cudaError_t err;
+    if (k.type == KernelType::Cgemm) {
+        // The descriptor is the model's; progress slots, spill area and error word are this
+        // executor's.
+        CgemmParams p = k.cgemm;
+        p.slots = e->d_slots + idx * kSlotsPerKernel;
+        p.spill = e->d_spill;
+        p.error = e->d_error;
+        err = cgemm_launch(p, k.tile, k.grid, b, s);
+    } else if (k.type == KernelType::Im2col) {
+        err = im2col_launch(k.im2col, k.grid, b, s);
+    } else if (k.type == KernelType::ConvSimt) {
+        err = conv_launch(k.conv, k.tile, k.grid, b, s);
+    } else {
+        err = pool_launch(k.pool, k.grid, b, s);
+    }
     if (err != cudaSuccess) {
         set_error("launch of kernel %zu (%s) failed: %s", idx, k.name.c_str(),
                   cudaGetErrorString(err));
@@ -57,6 +71,14 @@ int gpx_exec_create(gpx_model *m, int kind, gpx_exec **out) {
     GPX_CUDA(cudaMalloc((void **)&e->d_stop_index, 256));
     GPX_CUDA(cudaMalloc((void **)&e->d_executed, sizeof(int) * (nk + 1)));
     GPX_CUDA(cudaMalloc((void **)&e->d_trace, sizeof(uint64_t) * 4 * (nk + 1)));
+    // Tensor-core convolutions: per-kernel progress slots, one spill area (only one kernel of an
+    // executor can hold partial tiles at a time) and an error word.
+    GPX_CUDA(cudaMalloc((void **)&e->d_slots, sizeof(CgemmSlot) * kSlotsPerKernel * (nk + 1)));
+    GPX_CUDA(cudaMemset(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * (nk + 1)));
+    size_t spill_bytes = sizeof(float) * cgemm_spill_floats_per_cta() * (size_t)(m->max_cgemm_grid + 1);
+    GPX_CUDA(cudaMalloc((void **)&e->d_spill, spill_bytes));
+    GPX_CUDA(cudaMalloc((void **)&e->d_error, 64));
+    GPX_CUDA(cudaMemset(e->d_error, 0, 64));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_stop_index, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_minus_one, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_trace_init, sizeof(uint64_t) * 4 * (nk + 1),
@@ -84,6 +106,9 @@ int gpx_exec_destroy(gpx_exec *e) {
     cudaFree(e->d_stop_index);
     cudaFree(e->d_executed);
     cudaFree(e->d_trace);
+    cudaFree(e->d_slots);
+    cudaFree(e->d_spill);
+    cudaFree(e->d_error);
     cudaFreeHost(e->h_stop_index);
     cudaFreeHost(e->h_minus_one);
     cudaFreeHost(e->h_trace_init);
@@ -113,6 +138,7 @@ static int exec_prologue(gpx_exec *e, cudaStream_t s) {
         GPX_REQUIRE(e->word_dptr, GPX_FAIL, "BLP executor has no preempt word (gpx_exec_set_word)");
         // BLPExecutor::execute zeroes executed[] first (src/executor.cpp:212-214).
         GPX_CUDA(cudaMemsetAsync(e->d_executed, 0, sizeof(int) * nk, s));
+        GPX_CUDA(cudaMemsetAsync(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * nk, s));
     }
     if (e->trace_on)
         GPX_CUDA(cudaMemcpyAsync(e->d_trace, e->h_trace_init, sizeof(uint64_t) * 4 * nk,
@@ -190,6 +216,23 @@ int gpx_exec_resume(gpx_exec *e, gpx_stream stream, int *resumed_from) {
     GPX_REQUIRE((size_t)v < nk, GPX_FAIL, "stop index %d outside the kernel list", v);
     cudaStream_t s = as_stream(stream);
     for (size_t i = (size_t)v; i < nk; ++i) GPX_TRY(exec_launch(e, i, s));
+    return GPX_SUCC;
+}
+
+int gpx_exec_error(gpx_exec *e, int *code, int *where) {
+    GPX_REQUIRE(e && code, GPX_FAIL, "NULL argument");
+    int h[2] = {0, 0};
+    GPX_CUDA(cudaMemcpy(h, e->d_error, sizeof(h), cudaMemcpyDeviceToHost));
+    *code = h[0];
+    if (where) *where = h[1];
+    return GPX_SUCC;
+}
+
+int gpx_exec_reset_cursors(gpx_exec *e, gpx_stream stream) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    size_t nk = e->model->kernels.size();
+    GPX_CUDA(cudaMemsetAsync(e->d_executed, 0, sizeof(int) * nk, as_stream(stream)));
+    GPX_CUDA(cudaMemsetAsync(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * nk, as_stream(stream)));
     return GPX_SUCC;
 }
 

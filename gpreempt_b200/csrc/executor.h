@@ -11,6 +11,9 @@ struct gpx_exec {
     int *d_stop_index = nullptr;      // BLPExecutor::dpStopIndex
     int *d_executed = nullptr;        // BLPExecutor::executed, one cursor per kernel
     unsigned long long *d_trace = nullptr;
+    gpx::CgemmSlot *d_slots = nullptr;  // [kernel][kSlotsPerKernel] progress of tensor-core kernels
+    float *d_spill = nullptr;           // accumulator spill area shared by this executor's kernels
+    int *d_error = nullptr;             // {code, where} written by a kernel whose bounded wait gave up
     int *h_stop_index = nullptr;      // pinned landing slot of the stop index
     int *h_minus_one = nullptr;       // pinned -1 used to re-arm the stop index
     unsigned long long *h_trace_init = nullptr;
@@ -21,6 +24,7 @@ struct gpx_exec {
 };
 
 namespace gpx {
+constexpr size_t kSlotsPerKernel = 256;
 BlpArgs exec_blp_args(gpx_exec *e, size_t idx);
 int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s);
 }  // namespace gpx

@@ -2,47 +2,113 @@
 // list (KernelInfo in the reference, include/model.h:22-30).
 #pragma once
 
+#include "act_layout.h"
 #include "blp.cuh"
+
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace gpx {
 
-// Convolution / dense layer as an implicit GEMM: out[M = N*Ho*Wo][Cout] = im2col(in)[M][K] *
-// w[K][Cout], K = kh*kw*Cin ordered (kh, kw, ci), followed by + bias, + residual, ReLU.
+typedef unsigned short bf16_bits;
+
+// A tensor as a layer kernel sees it: fp32 in canonical order (the graph input "data" is NCHW,
+// "heads" is [N][C]) or two bf16 planes in one of the row orders of act_layout.h.
+struct ActView {
+    const float *f32;      // non-null: fp32 NCHW tensor (planes unused)
+    const bf16_bits *hi;   // split planes
+    const bf16_bits *lo;
+    ActLayout l;
+};
+
+// ---- tensor-core convolution (cgemm_tcgen05.cu) ----------------------------------------------
+
+struct CgemmSlot {
+    int next_iter;  // first iteration of this CTA's static schedule that is not complete
+    int k_done;     // K blocks already accumulated for it (spill area valid if > 0)
+    int grid;       // grid size the schedule was started with (0 = fresh)
+    int pad;
+};
+
+struct CgemmParams {
+    CUtensorMap a_hi, a_lo;  // activation planes [in.rows][Cin], box 128 rows x 64 channels
+    CUtensorMap w_hi, w_lo;  // weight planes [Cout][taps*Cin], box BN rows x 64
+    int taps;                // 1 or 9
+    int cin;                 // input channels (multiple of 64)
+    int cin_blocks;          // cin / 64
+    int tap_shift[9];        // row shift of each tap
+    int m_rows;              // GEMM rows to cover (stored rows of one input plane)
+    int in_hs, in_ws;        // stored image dims of the input (decode of a GEMM row)
+    int in_off;              // 1 when the input rows include a zero border, else 0
+    int tiles_m, tiles_n;
+    int relu;
+    const float *bias;       // [Cout] or null
+    const bf16_bits *res_hi, *res_lo;  // residual planes or null
+    ActLayout res;
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
+    float *out_f32;          // non-null: fp32 [pixel][cout_valid] output (graph heads) instead of planes
+    int cout_valid;          // real output channels (the last column tile may be partly padding)
+    CgemmSlot *slots;        // one per CTA of this kernel
+    float *spill;            // [grid][128*BN] fp32, shared by the kernels of one executor
+    int *error;              // {code, kernel*1000+cta}
+};
+
+cudaError_t cgemm_prepare(int device);
+cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s);
+size_t cgemm_spill_floats_per_cta();
+
+// ---- CUDA-core convolution / dense (conv_simt.cu) --------------------------------------------
+
+// out[M = N*Ho*Wo][Cout] = im2col(in)[M][K] * w[K][Cout], K = kh*kw*Cin ordered (kh, kw, ci),
+// then + bias, + residual, ReLU.  Used where the tensor-core kernel does not apply: the stem
+// (3 input channels, fp32 NCHW input), dense layers with a handful of rows, odd channel counts.
 struct ConvParams {
-    const float *in;    // NHWC, or NCHW when in_nchw (the graph input "data")
-    const float *w;     // [K][Cout]
+    ActView in;
+    const float *w;     // [K][Cout] fp32
     const float *bias;  // [Cout] or null
-    const float *res;   // NHWC residual with the output's shape, or null
-    float *out;         // NHWC
-    int N, H, W, Cin;
-    int Ho, Wo, Cout;
+    ActView res;        // residual (hi == null && f32 == null: none)
+    float *out_f32;     // fp32 [M][Cout] output (graph heads), or null
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
+    int Cin, Ho, Wo, Cout;
     int kh, kw, stride, pad;
     int M, K;
     int relu;
-    int in_nchw;
     int tiles_m, tiles_n;
 };
 
 struct PoolParams {
-    const float *in;  // NHWC
-    float *out;       // NHWC
-    int N, H, W, C;
-    int Ho, Wo;
+    ActView in;
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
     int k, stride, pad;
-    int mode;         // 0 = max, 1 = average over valid taps (global average uses k = H)
+    int mode;         // 0 = max, 1 = average over valid taps, 2 = copy of the tap (0,0) (subsample)
     int total_tiles;
-    int tile_elems;   // output float4 vectors per tile
+    int tile_elems;   // output 8-channel vectors per tile
 };
 
-// Tile shapes the SIMT convolution is instantiated for.
+// Patch matrix of a convolution whose input has too few channels for the tensor-core kernel
+// (the stem): row m = output pixel, column k = (fh, fw, ci), zero-padded to a multiple of 64
+// columns, written as hi/lo planes so a 1x1 tensor-core GEMM can consume it.
+struct Im2colParams {
+    ActView in;             // fp32 NCHW or split planes
+    bf16_bits *out_hi, *out_lo;
+    int Cin, Ho, Wo;
+    int kh, kw, stride, pad;
+    int K, Kp;              // real and padded row length
+    int M;
+    int total_tiles;
+    int tile_elems;         // 8-column vectors per tile
+};
+cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+
 enum ConvTile { CONV_TILE_128 = 0, CONV_TILE_64 = 1, CONV_TILE_32 = 2 };
 
 int conv_pick_tile(const ConvParams &p, int sm_count);
 void conv_set_tiles(ConvParams &p, int tile);
-int conv_grid(const ConvParams &p, int tile, int sm_count, bool preemptible);
-cudaError_t conv_launch(const ConvParams &p, int tile, int grid, const BlpArgs &blp,
-                        cudaStream_t s);
+int conv_grid(const ConvParams &p, int tile, int sm_count);
+cudaError_t conv_launch(const ConvParams &p, int tile, int grid, const BlpArgs &blp, cudaStream_t s);
 cudaError_t pool_launch(const PoolParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 int pool_grid(const PoolParams &p, int sm_count);
 

@@ -67,10 +67,6 @@ struct GraphBuilder {
         Storage s;
         s.name = name;
         s.kind = kind;
-        if (H == 1 && W == 1 && kind != Storage::ActCanonical) {
-            // [N][C] is the same in NHWC and NCHW.
-            s.kind = Storage::ActCanonical;
-        }
         if (H == 1 && W == 1) {
             s.rank = 2;
             s.dims[0] = N;
@@ -94,13 +90,13 @@ struct GraphBuilder {
         n.H = H;
         n.W = W;
         n.C = C;
-        n.storage = add_act(name, N, C, H, W, Storage::ActCanonical);
+        n.storage = add_act(name, N, C, H, W, Storage::InputF32);
         m.nodes.push_back(n);
         return (int)m.nodes.size() - 1;
     }
 
     int conv(const std::string &name, int in, int cout, int k, int stride, int pad, bool relu,
-             int residual = -1, const std::string &param_prefix = "") {
+             int residual = -1, const std::string &param_prefix = "", bool is_head = false) {
         const Node &src = m.nodes[in];
         Node n;
         n.name = name;
@@ -137,7 +133,7 @@ struct GraphBuilder {
         b.dims[0] = cout;
         b.bytes = (size_t)cout * sizeof(float);
         n.bias = m.add_storage(b);
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActNHWC);
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, is_head ? Storage::OutputF32 : Storage::ActSplit);
         m.nodes.push_back(n);
         return (int)m.nodes.size() - 1;
     }
@@ -162,7 +158,7 @@ struct GraphBuilder {
         n.C = src.C;
         n.H = (src.H + 2 * pad - k) / stride + 1;
         n.W = (src.W + 2 * pad - k) / stride + 1;
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActNHWC);
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
         m.nodes.push_back(n);
         return (int)m.nodes.size() - 1;
     }
@@ -189,7 +185,7 @@ static void build_resnet(gpx_model &m, int batch, const int layers[4]) {
         planes *= 2;
     }
     x = g.pool("avgpool", x, Op::AvgPool, 7, 1, 0);
-    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "fc");
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "fc", true);
     m.head_node = x;
 }
 
@@ -207,7 +203,7 @@ static void build_vgg(gpx_model &m, int batch, const int *cfg, int ncfg) {
     }
     x = g.dense("classifier.0", x, 4096, true);
     x = g.dense("classifier.3", x, 4096, true);
-    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "classifier.6");
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "classifier.6", true);
     m.head_node = x;
 }
 
@@ -246,35 +242,219 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
 
 // ---- storages and kernel list ---------------------------------------------------------------
 
+static inline bf16_bits host_f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (bf16_bits)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (bf16_bits)(u >> 16);
+}
+static inline float host_bf16_to_f32(bf16_bits v) {
+    uint32_t u = (uint32_t)v << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+// Shape test for the tensor-core convolution: 64-channel granularity on both sides and one of
+// the four geometries it implements as row-shifted GEMMs.
+static bool tensor_core_shape(const Node &n, const Node &src) {
+    if (n.op != Op::Conv) return false;
+    if (src.C % 64 != 0 || n.C % 64 != 0) return false;
+    if (n.k == 1 && n.pad == 0 && n.stride == 1) return true;
+    if (n.k == 1 && n.pad == 0 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
+    if (n.k == 3 && n.pad == 1 && n.stride == 1) return true;
+    if (n.k == 3 && n.pad == 1 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
+    return false;
+}
+
+static int wanted_order(const Node &n) {
+    if (n.k == 3 && n.stride == 1) return ACT_PADDED;
+    if (n.k == 3 && n.stride == 2) return ACT_PHASED;
+    return ACT_PLAIN;
+}
+
+static ActView view_of(const gpx_model &m, const Node &node) {
+    const Storage &s = m.storages[node.storage];
+    ActView v{};
+    if (s.kind == Storage::InputF32) {
+        v.f32 = s.dptr;
+        v.l = make_layout(node.N, node.H, node.W, node.C, ACT_PLAIN);
+    } else {
+        v.hi = s.hi;
+        v.lo = s.lo;
+        v.l = s.layout;
+    }
+    return v;
+}
+
 int finalize_model(gpx_model &m) {
     const DeviceInfo &d = device_info();
     GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
     m.device = d.device;
     m.sm_count = d.sm_count;
-    // One device buffer per storage, zero-filled, no sharing (src/model.cpp:101-113).
-    for (auto &s : m.storages) {
-        GPX_CUDA(cudaMalloc((void **)&s.dptr, s.bytes));
-        GPX_CUDA(cudaMemset(s.dptr, 0, s.bytes));
+    const char *force = getenv("GPX_CONV");
+    const bool allow_tc = !(force && std::string(force) == "simt");
+
+    // 1. which convolutions can run on the tensor cores, judged by shape alone
+    for (auto &n : m.nodes) {
+        if (n.op != Op::Conv) continue;
+        const Node &src = m.nodes[n.inputs[0]];
+        const Storage &out = m.storages[n.storage];
+        const Storage &in = m.storages[src.storage];
+        n.tensor_core = allow_tc && tensor_core_shape(n, src) && in.kind == Storage::ActSplit &&
+                        out.kind == Storage::ActSplit;
+        // The graph head: a dense layer with any number of outputs written as fp32.
+        if (allow_tc && out.kind == Storage::OutputF32 && in.kind == Storage::ActSplit && n.k == 1 &&
+            n.stride == 1 && n.pad == 0 && src.H == 1 && src.W == 1 && src.C % 64 == 0)
+            n.tensor_core = true;
+        // Few input channels (the stem): build the patch matrix, then a 1x1 tensor-core GEMM.
+        if (allow_tc && !n.tensor_core && out.kind == Storage::ActSplit && n.C % 64 == 0 &&
+            src.C % 64 != 0 && n.k * n.k * src.C <= 1024) {
+            n.tensor_core = true;
+            n.via_im2col = true;
+        }
     }
+    // 2. row order of every activation: what its 3x3 tensor-core consumers need, if they agree
+    std::vector<int> order(m.storages.size(), ACT_PLAIN);
+    std::vector<int> votes(m.storages.size(), -1);
+    std::vector<bool> conflict(m.storages.size(), false);
+    for (auto &n : m.nodes) {
+        if (n.op != Op::Conv || !n.tensor_core || n.k != 3 || n.via_im2col) continue;
+        int st = m.nodes[n.inputs[0]].storage;
+        int want = wanted_order(n);
+        if (votes[st] >= 0 && votes[st] != want) conflict[st] = true;
+        votes[st] = want;
+    }
+    for (size_t i = 0; i < m.storages.size(); ++i)
+        if (votes[i] >= 0 && !conflict[i]) order[i] = votes[i];
+    // 3. final decision given the layouts
+    for (auto &n : m.nodes) {
+        if (n.op != Op::Conv || !n.tensor_core || n.via_im2col) continue;
+        int st = m.nodes[n.inputs[0]].storage;
+        if (n.k == 3 && order[st] != wanted_order(n)) n.tensor_core = false;
+        if (n.k == 1 && order[st] == ACT_PHASED) n.tensor_core = false;
+        if (n.k == 1 && n.stride == 2 && order[st] != ACT_PLAIN) n.tensor_core = false;
+        if (n.residual >= 0 && m.storages[m.nodes[n.residual].storage].kind != Storage::ActSplit)
+            n.tensor_core = false;
+    }
+    // 4. compact copies for stride-2 1x1 convolutions (hidden storages)
+    for (size_t ni = 0; ni < m.nodes.size(); ++ni) {
+        Node &n = m.nodes[ni];
+        if (n.op != Op::Conv || !n.tensor_core) continue;
+        const bool sub2 = n.k == 1 && n.stride == 2 && !n.via_im2col;
+        if (!sub2 && !n.via_im2col) continue;
+        const Node &src = m.nodes[n.inputs[0]];
+        Storage s;
+        s.name = n.name + (n.via_im2col ? ".patches" : ".subsampled");
+        s.kind = Storage::ActSplit;
+        s.hidden = true;
+        s.rank = 4;
+        s.dims[0] = n.N;
+        s.dims[1] = n.via_im2col ? (n.k * n.k * src.C + 63) / 64 * 64 : src.C;
+        s.dims[2] = n.H;
+        s.dims[3] = n.W;
+        s.bytes = (size_t)n.N * s.dims[1] * n.H * n.W * sizeof(float);
+        n.sub_storage = m.add_storage(s);
+        order.push_back(ACT_PLAIN);
+    }
+    for (auto &n : m.nodes)
+        if (n.op == Op::Conv && n.tensor_core) {
+            Storage &w = m.storages[n.weight];
+            w.wants_split = true;
+            w.split_k = (int)((w.dims[1] * w.dims[2] * w.dims[3] + 63) / 64 * 64);
+        }
+
+    // 5. allocation: one buffer per storage, zero-filled, no sharing (src/model.cpp:101-113)
+    for (size_t i = 0; i < m.storages.size(); ++i) {
+        Storage &s = m.storages[i];
+        if (s.kind == Storage::ActSplit) {
+            int N = (int)s.dims[0], C = (int)s.dims[1];
+            int H = s.rank == 4 ? (int)s.dims[2] : 1, W = s.rank == 4 ? (int)s.dims[3] : 1;
+            GPX_REQUIRE(C % 8 == 0, GPX_FAIL, "%s: %d channels, need a multiple of 8", s.name.c_str(), C);
+            s.layout = make_layout(N, H, W, C, order[i]);
+            s.plane_elems = (size_t)s.layout.rows * C;
+            GPX_CUDA(cudaMalloc((void **)&s.hi, 2 * s.plane_elems * sizeof(bf16_bits)));
+            GPX_CUDA(cudaMemset(s.hi, 0, 2 * s.plane_elems * sizeof(bf16_bits)));
+            s.lo = s.hi + s.plane_elems;
+        } else {
+            // Rounded up to 512 bytes so a kernel may read a bias in whole 128-channel tiles.
+            size_t alloc = (s.bytes + 511) / 512 * 512;
+            GPX_CUDA(cudaMalloc((void **)&s.dptr, alloc));
+            GPX_CUDA(cudaMemset(s.dptr, 0, alloc));
+            if (s.kind == Storage::Weight && s.wants_split) {
+                s.plane_elems = (size_t)s.dims[0] * s.split_k;
+                GPX_CUDA(cudaMalloc((void **)&s.hi, 2 * s.plane_elems * sizeof(bf16_bits)));
+                GPX_CUDA(cudaMemset(s.hi, 0, 2 * s.plane_elems * sizeof(bf16_bits)));
+                s.lo = s.hi + s.plane_elems;
+            }
+        }
+    }
+    GPX_CUDA(cgemm_prepare(d.device));
+
+    // 6. kernel list
     for (size_t ni = 0; ni < m.nodes.size(); ++ni) {
         const Node &n = m.nodes[ni];
         if (n.op == Op::Input) continue;
         const Node &src = m.nodes[n.inputs[0]];
-        Kernel k;
-        k.name = n.name;
-        k.node = (int)ni;
-        if (n.op == Op::Conv) {
-            GPX_REQUIRE(n.C % 4 == 0, GPX_FAIL, "%s: Cout %d not a multiple of 4", n.name.c_str(),
-                        n.C);
-            ConvParams &p = k.conv;
-            p.in = m.storages[src.storage].dptr;
-            p.w = m.storages[n.weight].dptr;
+        const Storage &out = m.storages[n.storage];
+        auto add_pool = [&](const std::string &name, const ActView &in, const Storage &dst, int k,
+                            int stride, int pad, int mode) {
+            Kernel kn;
+            kn.name = name;
+            kn.node = (int)ni;
+            kn.type = KernelType::Pool;
+            PoolParams &p = kn.pool;
+            p.in = in;
+            p.out_hi = dst.hi;
+            p.out_lo = dst.lo;
+            p.out = dst.layout;
+            p.k = k;
+            p.stride = stride;
+            p.pad = pad;
+            p.mode = mode;
+            long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (dst.layout.C / 8);
+            // Enough tiles to fill the GPU even when the tensor is small (global average pool).
+            long long want_tiles = 4LL * m.sm_count;
+            p.tile_elems = (int)std::max<long long>(64, std::min<long long>(2048, total / want_tiles / 32 * 32));
+            p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
+            kn.total_tiles = p.total_tiles;
+            kn.grid = pool_grid(p, m.sm_count);
+            int taps = mode == 2 ? 1 : k * k;
+            kn.flops = (double)total * 8 * taps;
+            kn.bytes = 4.0 * ((double)total * 8 * (mode == 2 ? 1 : stride * stride) + (double)total * 8);
+            m.kernels.push_back(kn);
+        };
+        if (n.op != Op::Conv) {
+            GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit, GPX_FAIL,
+                        "%s: pooling the graph input is not supported", n.name.c_str());
+            add_pool(n.name, view_of(m, src), out, n.k, n.stride, n.pad, n.op == Op::MaxPool ? 0 : 1);
+            continue;
+        }
+        const Storage &w = m.storages[n.weight];
+        const double flops = 2.0 * n.N * n.H * n.W * (double)n.k * n.k * src.C * n.C;
+        const double bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)n.k * n.k * src.C * n.C +
+                                    (double)n.N * n.H * n.W * n.C * (n.residual >= 0 ? 2 : 1));
+        if (!n.tensor_core) {
+            Kernel kn;
+            kn.name = n.name;
+            kn.node = (int)ni;
+            kn.type = KernelType::ConvSimt;
+            GPX_REQUIRE(n.C % 4 == 0, GPX_FAIL, "%s: Cout %d not a multiple of 4", n.name.c_str(), n.C);
+            ConvParams &p = kn.conv;
+            p.in = view_of(m, src);
+            p.w = w.dptr;
             p.bias = m.storages[n.bias].dptr;
-            p.res = n.residual >= 0 ? m.storages[m.nodes[n.residual].storage].dptr : nullptr;
-            p.out = m.storages[n.storage].dptr;
-            p.N = src.N;
-            p.H = src.H;
-            p.W = src.W;
+            if (n.residual >= 0) p.res = view_of(m, m.nodes[n.residual]);
+            if (out.kind == Storage::OutputF32) {
+                GPX_REQUIRE(n.H == 1 && n.W == 1, GPX_FAIL, "%s: fp32 outputs must be [N][C]", n.name.c_str());
+                p.out_f32 = out.dptr;
+                p.out = make_layout(n.N, 1, 1, n.C, ACT_PLAIN);
+            } else {
+                p.out_hi = out.hi;
+                p.out_lo = out.lo;
+                p.out = out.layout;
+            }
             p.Cin = src.C;
             p.Ho = n.H;
             p.Wo = n.W;
@@ -285,62 +465,116 @@ int finalize_model(gpx_model &m) {
             p.M = n.N * n.H * n.W;
             p.K = n.k * n.k * src.C;
             p.relu = n.relu ? 1 : 0;
-            p.in_nchw = (src.op == Op::Input && (src.H > 1 || src.W > 1)) ? 1 : 0;
-            k.is_conv = true;
-            k.tile = conv_pick_tile(p, m.sm_count);
-            conv_set_tiles(p, k.tile);
-            k.total_tiles = p.tiles_m * p.tiles_n;
-            k.grid = conv_grid(p, k.tile, m.sm_count, true);
-            k.flops = 2.0 * p.M * (double)p.K * p.Cout;
-            k.bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)p.K * p.Cout +
-                             (double)p.M * p.Cout * (p.res ? 2 : 1));
-        } else {
-            GPX_REQUIRE(n.C % 4 == 0, GPX_FAIL, "%s: C %d not a multiple of 4", n.name.c_str(), n.C);
-            PoolParams &p = k.pool;
-            p.in = m.storages[src.storage].dptr;
-            p.out = m.storages[n.storage].dptr;
-            p.N = src.N;
-            p.H = src.H;
-            p.W = src.W;
-            p.C = src.C;
-            p.Ho = n.H;
-            p.Wo = n.W;
-            p.k = n.k;
-            p.stride = n.stride;
-            p.pad = n.pad;
-            p.mode = n.op == Op::MaxPool ? 0 : 1;
-            p.tile_elems = 2048;
-            long long total = (long long)n.N * n.H * n.W * (n.C / 4);
-            p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
-            k.is_conv = false;
-            k.total_tiles = p.total_tiles;
-            k.grid = pool_grid(p, m.sm_count);
-            k.flops = (double)total * 4 * n.k * n.k;
-            k.bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)total * 4);
+            kn.tile = conv_pick_tile(p, m.sm_count);
+            conv_set_tiles(p, kn.tile);
+            kn.total_tiles = p.tiles_m * p.tiles_n;
+            kn.grid = conv_grid(p, kn.tile, m.sm_count);
+            kn.flops = flops;
+            kn.bytes = bytes;
+            m.kernels.push_back(kn);
+            continue;
         }
-        m.kernels.push_back(k);
+        // tensor-core convolution
+        const Storage *in = &m.storages[src.storage];
+        int eff_k = n.k, eff_cin = src.C;
+        if (n.via_im2col) {
+            const Storage &pm = m.storages[n.sub_storage];
+            Kernel ki;
+            ki.name = n.name + ".im2col";
+            ki.node = (int)ni;
+            ki.type = KernelType::Im2col;
+            Im2colParams &q = ki.im2col;
+            q.in = view_of(m, src);
+            q.out_hi = pm.hi;
+            q.out_lo = pm.lo;
+            q.Cin = src.C;
+            q.Ho = n.H;
+            q.Wo = n.W;
+            q.kh = q.kw = n.k;
+            q.stride = n.stride;
+            q.pad = n.pad;
+            q.K = n.k * n.k * src.C;
+            q.Kp = (int)pm.dims[1];
+            q.M = n.N * n.H * n.W;
+            q.tile_elems = 2048;
+            long long total = (long long)q.M * (q.Kp / 8);
+            q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
+            ki.total_tiles = q.total_tiles;
+            ki.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
+            ki.flops = 0;
+            ki.bytes = 4.0 * (double)src.N * src.H * src.W * src.C + 4.0 * (double)q.M * q.Kp;
+            m.kernels.push_back(ki);
+            in = &pm;
+            eff_k = 1;
+            eff_cin = q.Kp;
+        } else if (n.k == 1 && n.stride == 2) {
+            const Storage &sub = m.storages[n.sub_storage];
+            add_pool(n.name + ".subsample", view_of(m, src), sub, 1, 2, 0, 2);
+            in = &sub;
+        }
+        Kernel kn;
+        kn.name = n.name;
+        kn.node = (int)ni;
+        kn.type = KernelType::Cgemm;
+        kn.threads = 192;
+        CgemmParams &p = kn.cgemm;
+        const ActLayout &il = in->layout;
+        const bool head = out.kind == Storage::OutputF32;
+        const int bn = (n.C % 128 == 0 || head) ? 128 : 64;
+        kn.tile = bn;
+        p.taps = eff_k * eff_k;
+        p.cin = eff_cin;
+        p.cin_blocks = eff_cin / 64;
+        for (int t = 0; t < 9; ++t) p.tap_shift[t] = 0;
+        if (eff_k == 3) {
+            for (int fh = 0; fh < 3; ++fh)
+                for (int fw = 0; fw < 3; ++fw) {
+                    int t = fh * 3 + fw;
+                    if (n.stride == 1)
+                        p.tap_shift[t] = (fh - 1) * il.Ws + (fw - 1);
+                    else
+                        p.tap_shift[t] = (((fh & 1) << 1) | (fw & 1)) * il.plane + (fh >> 1) * il.Ws + (fw >> 1);
+                }
+        }
+        p.m_rows = il.plane;
+        p.in_hs = il.Hs;
+        p.in_ws = il.Ws;
+        p.in_off = il.order == ACT_PADDED ? 1 : 0;
+        p.tiles_m = (p.m_rows + 127) / 128;
+        p.tiles_n = (n.C + bn - 1) / bn;
+        p.cout_valid = n.C;
+        p.relu = n.relu ? 1 : 0;
+        p.bias = m.storages[n.bias].dptr;
+        if (n.residual >= 0) {
+            const Storage &r = m.storages[m.nodes[n.residual].storage];
+            p.res_hi = r.hi;
+            p.res_lo = r.lo;
+            p.res = r.layout;
+        }
+        if (head) {
+            p.out_f32 = out.dptr;
+            p.out = make_layout(n.N, n.H, n.W, n.C, ACT_PLAIN);
+        } else {
+            p.out_hi = out.hi;
+            p.out_lo = out.lo;
+            p.out = out.layout;
+        }
+        GPX_TRY(make_tmap_2d_bf16(&p.a_hi, in->hi, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
+        GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
+        GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
+        GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
+        kn.total_tiles = p.tiles_m * p.tiles_n;
+        kn.grid = std::min(kn.total_tiles, m.sm_count);
+        m.max_cgemm_grid = std::max(m.max_cgemm_grid, kn.grid);
+        kn.flops = flops;
+        kn.bytes = bytes;
+        m.kernels.push_back(kn);
     }
     return GPX_SUCC;
 }
 
-// ---- layout transforms between canonical (NCHW / OIHW) and device layouts -------------------
+// ---- conversions between canonical tensors (NCHW / OIHW fp32) and device layouts -------------
 
-static void nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W) {
-    for (int n = 0; n < N; ++n)
-        for (int c = 0; c < C; ++c)
-            for (int h = 0; h < H; ++h)
-                for (int w = 0; w < W; ++w)
-                    dst[(((size_t)n * H + h) * W + w) * C + c] =
-                        src[(((size_t)n * C + c) * H + h) * W + w];
-}
-static void nhwc_to_nchw(const float *src, float *dst, int N, int C, int H, int W) {
-    for (int n = 0; n < N; ++n)
-        for (int h = 0; h < H; ++h)
-            for (int w = 0; w < W; ++w)
-                for (int c = 0; c < C; ++c)
-                    dst[(((size_t)n * C + c) * H + h) * W + w] =
-                        src[(((size_t)n * H + h) * W + w) * C + c];
-}
 static void oihw_to_khwc_o(const float *src, float *dst, int O, int I, int KH, int KW) {
     for (int o = 0; o < O; ++o)
         for (int i = 0; i < I; ++i)
@@ -363,19 +597,52 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
     GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "set %s: %zu bytes given, %zu needed",
                 s.name.c_str(), len, s.bytes);
     (void)m;
-    if (s.kind == Storage::ActCanonical || s.kind == Storage::Vec) {
+    const float *src = (const float *)host;
+    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec) {
         GPX_CUDA(cudaMemcpyAsync(s.dptr, host, s.bytes, cudaMemcpyHostToDevice, st));
         return GPX_SUCC;
     }
-    std::vector<float> tmp(s.bytes / sizeof(float));
-    if (s.kind == Storage::ActNHWC)
-        nchw_to_nhwc((const float *)host, tmp.data(), (int)s.dims[0], (int)s.dims[1],
-                     (int)s.dims[2], (int)s.dims[3]);
-    else
-        oihw_to_khwc_o((const float *)host, tmp.data(), (int)s.dims[0], (int)s.dims[1],
-                       (int)s.dims[2], (int)s.dims[3]);
-    // The staging vector dies at return, so this copy completes before returning.
-    GPX_CUDA(cudaMemcpyAsync(s.dptr, tmp.data(), s.bytes, cudaMemcpyHostToDevice, st));
+    if (s.kind == Storage::Weight) {
+        const int O = (int)s.dims[0], I = (int)s.dims[1], KH = (int)s.dims[2], KW = (int)s.dims[3];
+        std::vector<float> tmp(s.bytes / sizeof(float));
+        oihw_to_khwc_o(src, tmp.data(), O, I, KH, KW);
+        GPX_CUDA(cudaMemcpyAsync(s.dptr, tmp.data(), s.bytes, cudaMemcpyHostToDevice, st));
+        GPX_CUDA(cudaStreamSynchronize(st));
+        if (s.wants_split) {
+            // [Cout][tap][Cin] hi/lo planes for the tensor-core kernel
+            std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
+            const size_t K = (size_t)s.split_k;  // rows are zero-padded to a multiple of 64
+            for (int o = 0; o < O; ++o)
+                for (int h = 0; h < KH; ++h)
+                    for (int w = 0; w < KW; ++w)
+                        for (int i = 0; i < I; ++i) {
+                            float v = src[(((size_t)o * I + i) * KH + h) * KW + w];
+                            bf16_bits hi = host_f32_to_bf16(v);
+                            size_t off = (size_t)o * K + ((size_t)h * KW + w) * I + i;
+                            planes[off] = hi;
+                            planes[s.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                        }
+            GPX_CUDA(cudaMemcpyAsync(s.hi, planes.data(), planes.size() * sizeof(bf16_bits),
+                                     cudaMemcpyHostToDevice, st));
+            GPX_CUDA(cudaStreamSynchronize(st));
+        }
+        return GPX_SUCC;
+    }
+    // ActSplit: NCHW fp32 -> hi/lo planes in the storage's row order (borders stay zero)
+    const ActLayout &l = s.layout;
+    std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
+    for (int n = 0; n < l.N; ++n)
+        for (int c = 0; c < l.C; ++c)
+            for (int h = 0; h < l.H; ++h)
+                for (int w = 0; w < l.W; ++w) {
+                    float v = src[(((size_t)n * l.C + c) * l.H + h) * l.W + w];
+                    bf16_bits hi = host_f32_to_bf16(v);
+                    size_t off = (size_t)layout_row(l, n, h, w) * l.C + c;
+                    planes[off] = hi;
+                    planes[s.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                }
+    GPX_CUDA(cudaMemcpyAsync(s.hi, planes.data(), planes.size() * sizeof(bf16_bits),
+                             cudaMemcpyHostToDevice, st));
     GPX_CUDA(cudaStreamSynchronize(st));
     return GPX_SUCC;
 }
@@ -385,19 +652,31 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
     GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "get %s: %zu bytes given, %zu needed",
                 s.name.c_str(), len, s.bytes);
     (void)m;
-    if (s.kind == Storage::ActCanonical || s.kind == Storage::Vec) {
+    float *dst = (float *)host;
+    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec) {
         GPX_CUDA(cudaMemcpyAsync(host, s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
         return GPX_SUCC;
     }
-    std::vector<float> tmp(s.bytes / sizeof(float));
-    GPX_CUDA(cudaMemcpyAsync(tmp.data(), s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
+    if (s.kind == Storage::Weight) {
+        std::vector<float> tmp(s.bytes / sizeof(float));
+        GPX_CUDA(cudaMemcpyAsync(tmp.data(), s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
+        GPX_CUDA(cudaStreamSynchronize(st));
+        khwc_o_to_oihw(tmp.data(), dst, (int)s.dims[0], (int)s.dims[1], (int)s.dims[2], (int)s.dims[3]);
+        return GPX_SUCC;
+    }
+    const ActLayout &l = s.layout;
+    std::vector<bf16_bits> planes(2 * s.plane_elems);
+    GPX_CUDA(cudaMemcpyAsync(planes.data(), s.hi, planes.size() * sizeof(bf16_bits),
+                             cudaMemcpyDeviceToHost, st));
     GPX_CUDA(cudaStreamSynchronize(st));
-    if (s.kind == Storage::ActNHWC)
-        nhwc_to_nchw(tmp.data(), (float *)host, (int)s.dims[0], (int)s.dims[1], (int)s.dims[2],
-                     (int)s.dims[3]);
-    else
-        khwc_o_to_oihw(tmp.data(), (float *)host, (int)s.dims[0], (int)s.dims[1], (int)s.dims[2],
-                       (int)s.dims[3]);
+    for (int n = 0; n < l.N; ++n)
+        for (int h = 0; h < l.H; ++h)
+            for (int w = 0; w < l.W; ++w) {
+                size_t row = (size_t)layout_row(l, n, h, w) * l.C;
+                for (int c = 0; c < l.C; ++c)
+                    dst[(((size_t)n * l.C + c) * l.H + h) * l.W + w] =
+                        host_bf16_to_f32(planes[row + c]) + host_bf16_to_f32(planes[s.plane_elems + row + c]);
+            }
     return GPX_SUCC;
 }
 
@@ -440,8 +719,10 @@ int gpx_model_open(const char *name, const gpx_model_opts *opts, gpx_model **out
 
 int gpx_model_close(gpx_model *m) {
     if (!m) return GPX_SUCC;
-    for (auto &s : m->storages)
+    for (auto &s : m->storages) {
         if (s.dptr) cudaFree(s.dptr);
+        if (s.hi) cudaFree(s.hi);  // lo lives in the same allocation
+    }
     delete m;
     return GPX_SUCC;
 }
@@ -618,7 +899,7 @@ int gpx_model_kernel_info(gpx_model *m, size_t idx, char *name, size_t name_cap,
     if (launch_params) {
         launch_params[0] = (uint32_t)k.grid;
         launch_params[1] = launch_params[2] = 1;
-        launch_params[3] = 256;
+        launch_params[3] = (uint32_t)k.threads;
         launch_params[4] = launch_params[5] = 1;
     }
     if (total_tiles) *total_tiles = k.total_tiles;

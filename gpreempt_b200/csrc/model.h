@@ -1,8 +1,7 @@
 // Graph, storages and kernel list of one model instance: the native counterpart of
 // foo::Model (include/model.h:32-93, src/model.cpp) in the reference.  The reference parses a
-// TVM graph JSON and binds generated kernels from a cubin; here the graph is built in (or read
-// from a graph JSON written by gpx_model_export_json) and every node maps to a hand-written
-// kernel linked into the library.
+// TVM graph JSON and binds generated kernels from a cubin; here the graph is built in and every
+// node maps to hand-written kernels linked into the library.
 #pragma once
 
 #include "common.h"
@@ -17,20 +16,29 @@ namespace gpx {
 // StorageInfo of the reference (include/model.h:13-18) plus layout knowledge.
 struct Storage {
     enum Kind {
-        ActCanonical,  // device layout == canonical layout (graph input NCHW, 2-D outputs)
-        ActNHWC,       // device NHWC, canonical NCHW
-        Weight,        // device [kh][kw][Cin][Cout], canonical OIHW
-        Vec            // bias and other 1-D parameters
+        InputF32,  // graph input, fp32 NCHW on the device as given by the client
+        OutputF32, // graph output, fp32 [N][C]
+        ActSplit,  // intermediate activation: hi/lo bf16 planes in the row order of `layout`
+        Weight,    // canonical OIHW fp32; device copies: fp32 [kh][kw][Cin][Cout] and, for the
+                   // tensor-core kernel, hi/lo bf16 planes [Cout][kh*kw*Cin]
+        Vec        // bias
     };
     std::string name;
     std::string stype = "float32";
-    Kind kind = ActCanonical;
+    Kind kind = InputF32;
     int rank = 0;
-    int64_t dims[4] = {0, 0, 0, 0};  // canonical dims
-    size_t bytes = 0;
-    float *dptr = nullptr;
+    int64_t dims[4] = {0, 0, 0, 0};  // canonical dims (NCHW / OIHW / [N][C] / [C])
+    size_t bytes = 0;                // canonical size in bytes (what get/set move)
+    float *dptr = nullptr;           // fp32 device buffer (InputF32, OutputF32, Weight, Vec)
+    bf16_bits *hi = nullptr;         // split planes (ActSplit: activation; Weight: tensor-core copy)
+    bf16_bits *lo = nullptr;
+    size_t plane_elems = 0;
+    ActLayout layout{};              // ActSplit only
     bool is_param = false;
-    int fan_in = 0;  // for the seeded initialiser
+    bool hidden = false;             // internal scratch tensor, not listed
+    bool wants_split = false;        // Weight: a tensor-core kernel consumes it
+    int split_k = 0;                 // Weight: row length of the split planes (K padded to 64)
+    int fan_in = 0;
 };
 
 enum class Op { Input, Conv, MaxPool, AvgPool };
@@ -38,26 +46,38 @@ enum class Op { Input, Conv, MaxPool, AvgPool };
 struct Node {
     std::string name;
     Op op = Op::Input;
-    std::vector<int> inputs;  // node ids: data input, then residual if any
-    int storage = -1;         // output storage index
+    std::vector<int> inputs;
+    int storage = -1;
     int weight = -1, bias = -1;
-    int N = 0, H = 0, W = 0, C = 0;  // output shape (logical NHWC)
+    int N = 0, H = 0, W = 0, C = 0;  // output shape
     int k = 0, stride = 1, pad = 0;
     bool relu = false;
-    int residual = -1;  // node id
+    int residual = -1;
+    bool tensor_core = false;  // decided by finalize_model
+    int sub_storage = -1;      // stride-2 1x1: compact copy of the sub-sampled input;
+                               // few-channel input: patch matrix
+    bool via_im2col = false;
 };
+
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col };
 
 struct Kernel {
     std::string name;
     int node = -1;
-    bool is_conv = true;
+    KernelType type = KernelType::ConvSimt;
     ConvParams conv{};
     PoolParams pool{};
-    int tile = 0;
+    CgemmParams cgemm{};
+    Im2colParams im2col{};
+    int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     int grid = 1;
+    int threads = 256;
     int total_tiles = 0;
-    double flops = 0, bytes = 0;  // algorithmic work of the layer
+    double flops = 0, bytes = 0;
 };
+
+int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows, uint32_t box_cols);
 
 }  // namespace gpx
 
@@ -71,6 +91,7 @@ struct gpx_model {
     std::vector<gpx::Node> nodes;
     std::vector<gpx::Kernel> kernels;
     int head_node = -1;
+    int max_cgemm_grid = 0;
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;
@@ -79,7 +100,7 @@ struct gpx_model {
 namespace gpx {
 
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts);
-int finalize_model(gpx_model &m);  // allocate storages, derive the kernel list
+int finalize_model(gpx_model &m);
 void normal_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std);
 void uniform_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float lo, float hi);
 

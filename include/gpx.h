@@ -286,6 +286,12 @@ int gpx_exec_resume(gpx_exec *e, gpx_stream s, int *resumed_from);
 /* Device %globaltimer trace of the last run: per kernel 4 uint64 (see gpx_blp.trace). */
 int gpx_exec_enable_trace(gpx_exec *e, int on);
 int gpx_exec_read_trace(gpx_exec *e, uint64_t *out, size_t cap_u64, size_t *n_u64);
+/* Error word of the executor's tensor-core kernels (blocking read): *code is 0, or the code of
+ * the bounded device wait that gave up; *where is kernel index * 1000 + CTA. */
+int gpx_exec_error(gpx_exec *e, int *code, int *where);
+/* Zeroes every kernel's tile cursor and progress slot on `s`, as BLPExecutor::execute does
+ * before launching (src/executor.cpp:212-214); lets kernels be relaunched one by one. */
+int gpx_exec_reset_cursors(gpx_exec *e, gpx_stream s);
 /* Device address of the executed[] cursor array (one int per kernel); zeroing it re-arms every
  * kernel for a full run, as BLPExecutor::execute does (src/executor.cpp:212-214). */
 int gpx_exec_cursor_dptr(gpx_exec *e, void **dptr);
