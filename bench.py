@@ -297,6 +297,13 @@ def main() -> None:
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         roof = conv_roofline(api, device)
+        # flag-to-drain latency and bit-exact resume of the stand-alone best-effort kernels
+        microbench = {}
+        for kind, size in (("gemm", 8192), ("axpy", 1 << 28)):
+            r = api.preempt_microbench(kind, size, 200, seed=5)
+            microbench[kind] = {k: r[k] for k in ("triggers", "preempted", "mismatches", "kernel_ms",
+                                                  "drain_us_p50", "drain_us_p99", "drain_us_max",
+                                                  "seen_us_p50")}
         tflops = roof["conv_flops_per_step"] / (roof["conv_ms_per_step"] * 1e-3) / 1e12
         peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         line = {
@@ -332,6 +339,8 @@ def main() -> None:
             },
             "be_solo_inf_s": task(be_solo, "resnet50_be")["throughput(inf/s)"],
             "preempt_us": e2e["gpus"][0]["preemptLatency(us)"],
+            "kernel_drain_us": e2e["gpus"][0]["kernelDrain(us)"],
+            "preempt_flag_to_drain_us": microbench,
             "be_resumes": e2e["gpus"][0]["beResumes"],
             "gpu_launches": l1 - l0,
             "wall_s_resident_run": t1 - t0,

@@ -83,8 +83,15 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_tiles = p.tiles_m * p.tiles_n;
-    const int num_kb = p.taps * p.cin_blocks;
+    // A tile is (row block, column block, K split); splits of one output block are adjacent so
+    // they run at the same time.  With k_splits == 1 a tile covers the whole K range.
+    const int total_tiles = p.tiles_m * p.tiles_n * p.k_splits;
+    const int all_kb = p.taps * p.cin_blocks;
+    auto tile_kb_begin = [&](int tile) { return (tile % p.k_splits) * p.kb_per_split; };
+    auto tile_kb_count = [&](int tile) {
+        int left = all_kb - (tile % p.k_splits) * p.kb_per_split;
+        return left < p.kb_per_split ? left : p.kb_per_split;
+    };
     const bool resumable = blp.preempted != nullptr;
 
     CgemmSlot *slot = p.slots + blockIdx.x;
@@ -93,6 +100,28 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     const int first_iter = resumable ? slot->next_iter : 0;
     const int first_k = resumable ? slot->k_done : 0;
     const int slot_grid = resumable ? slot->grid : 0;
+
+    // A kernel that starts while the word is raised (it was queued behind the stop point) leaves
+    // at once, before it allocates tensor memory or touches a barrier: the cursor is unchanged,
+    // the stop point is recorded if this CTA still has work (kernel_transform_be.py:10-12).
+    if (resumable) {
+        __shared__ int s_raised;
+        if (threadIdx.x == 0) {
+            s_raised = load_word(blp.preempted);
+            if (s_raised) {
+                if ((int)blockIdx.x + first_iter * (int)gridDim.x < total_tiles && blp.stop_index)
+                    atomicCAS(blp.stop_index, -1, blp.kernel_id);
+                if (blp.trace) {
+                    unsigned long long t = globaltimer_ns();
+                    atomicMin(blp.trace + 0, t);
+                    atomicMin(blp.trace + 2, t);
+                    atomicMax(blp.trace + 1, t);
+                }
+            }
+        }
+        __syncthreads();
+        if (s_raised) return;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -135,9 +164,11 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 int tile = blockIdx.x + it * gridDim.x;
                 if (tile >= total_tiles) break;
                 // Column tiles vary fastest: CTAs that run together share the same A rows.
-                const int n_blk = tile % p.tiles_n;
-                const int m_blk = tile / p.tiles_n;
+                const int n_blk = (tile / p.k_splits) % p.tiles_n;
+                const int m_blk = (tile / p.k_splits) / p.tiles_n;
                 const int kb0 = it == first_iter ? first_k : 0;
+                const int num_kb = tile_kb_count(tile);
+                const int kb_base = tile_kb_begin(tile);
                 for (int kb = kb0; kb < num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs)) {
                         fail(101);
@@ -152,8 +183,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                         flag = load_word(blp.preempted);
                     }
-                    const int tap = kb / p.cin_blocks;
-                    const int cb = kb - tap * p.cin_blocks;
+                    const int tap = (kb_base + kb) / p.cin_blocks;
+                    const int cb = (kb_base + kb) - tap * p.cin_blocks;
                     ctl->stage_msg[stage] = CMSG_DATA;
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
                     mbar_arrive_expect_tx(bar, Cfg::kStageBytes);
@@ -191,6 +222,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             uint32_t phase = 0;
             uint32_t seg = 0;
             int kb = first_k;
+            int it = first_iter;
+            int num_kb = tile_kb_count(blockIdx.x + it * gridDim.x);
             bool seg_open = false;
             for (;;) {
                 if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, kCWaitLimitNs)) {
@@ -245,6 +278,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     mma_commit(smem_u32(&ctl->tmem_full));
                     mbar_arrive(smem_u32(&ctl->tmem_full));
                     ++seg;
+                    ++it;
+                    num_kb = tile_kb_count(blockIdx.x + it * gridDim.x);
                     kb = 0;
                     seg_open = false;
                 }
@@ -301,8 +336,9 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
             if (kind == CEPI_COMPLETE) {
                 const int tile = blockIdx.x + it * gridDim.x;
-                const int n_blk = tile % p.tiles_n;
-                const int m_blk = tile / p.tiles_n;
+                const int n_blk = (tile / p.k_splits) % p.tiles_n;
+                const int m_blk = (tile / p.k_splits) / p.tiles_n;
+                const int split = tile % p.k_splits;
                 // Which output pixel, if any, does this GEMM row stand for?
                 const int vrow = m_blk * kCBM + row;
                 bool valid = vrow < p.m_rows;
@@ -340,6 +376,18 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] += g[j] + __uint_as_float(v[j]);
+                    if (p.partial) {
+                        // Split K: the raw fp32 sum of this K range goes to the workspace; the
+                        // finishing kernel adds the ranges in split order and applies the rest.
+                        if (vrow < p.m_rows) {
+                            float4 *dst = reinterpret_cast<float4 *>(
+                                p.partial + ((size_t)split * p.partial_rows + vrow) * p.partial_ld + n_blk * BN + c);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                dst[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                        }
+                        continue;
+                    }
                     if (!valid) continue;
                     if (p.bias) {
                         const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + n_blk * BN + c);

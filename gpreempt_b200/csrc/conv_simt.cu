@@ -287,6 +287,64 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
         if (tile < 0) break;
         long long begin = (long long)tile * p.tile_elems;
         long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        if (p.mode == 1 && p.k * p.k >= 16) {
+            // Large averaging window (global average pool): one warp per output vector, lanes
+            // take taps lane, lane+32, ...; a fixed shuffle tree adds the lane sums, so the
+            // result is the same on every run.
+            const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+            for (long long e = begin + wid; e < end; e += kPoolThreads / 32) {
+                int c8 = (int)(e % C8);
+                long long t = e / C8;
+                int wo = (int)(t % Wo);
+                t /= Wo;
+                int ho = (int)(t % Ho);
+                int n = (int)(t / Ho);
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                int cnt = 0;
+                for (int tap = lane; tap < p.k * p.k; tap += 32) {
+                    int fh = tap / p.k, fw = tap - fh * p.k;
+                    int hi = ho * p.stride - p.pad + fh, wi = wo * p.stride - p.pad + fw;
+                    if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
+                    size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * C + c8 * 8;
+                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
+                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
+                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        acc[2 * q] += __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
+                        acc[2 * q + 1] += __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+                    }
+                    ++cnt;
+                }
+#pragma unroll
+                for (int sh = 16; sh >= 1; sh >>= 1) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], sh);
+                    cnt += __shfl_xor_sync(0xffffffffu, cnt, sh);
+                }
+                if (lane == 0) {
+                    float inv = 1.0f / (float)cnt;
+                    unsigned hi4[4], lo4[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float x0 = acc[2 * q] * inv, x1 = acc[2 * q + 1] * inv;
+                        bf16_bits h0 = f32_to_bf16_bits(x0), h1 = f32_to_bf16_bits(x1);
+                        bf16_bits l0 = f32_to_bf16_bits(x0 - bf16_bits_to_f32(h0));
+                        bf16_bits l1 = f32_to_bf16_bits(x1 - bf16_bits_to_f32(h1));
+                        hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+                        lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+                    }
+                    size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
+                    *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                    *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                }
+            }
+            ++iter;
+            if (dynamic) __syncthreads();
+            continue;
+        }
         for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
             int c8 = (int)(e % C8);
             long long t = e / C8;
@@ -358,6 +416,22 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
     const int K8 = p.Kp / 8;
     const long long total = (long long)p.M * K8;
     const int H = p.in.l.H, W = p.in.l.W;
+    // Column k of the patch matrix is filter tap (fh, fw) of channel ci; the decomposition and,
+    // for an fp32 NCHW input, the element offset relative to the window origin are tabulated
+    // once per CTA (K <= 1024).
+    __shared__ int s_off[1024];
+    __shared__ unsigned char s_fh[1024], s_fw[1024], s_ci[1024];
+    for (int k = threadIdx.x; k < p.Kp; k += kPoolThreads) {
+        int tap = k / p.Cin;
+        int ci = k - tap * p.Cin;
+        int fh = tap / p.kw;
+        int fw = tap - fh * p.kw;
+        s_fh[k] = k < p.K ? (unsigned char)fh : 255;
+        s_fw[k] = (unsigned char)fw;
+        s_ci[k] = (unsigned char)ci;
+        s_off[k] = (ci * H + fh) * W + fw;
+    }
+    __syncthreads();
     int iter = 0;
     for (;;) {
         int tile;
@@ -378,6 +452,8 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
             int t = m / p.Wo;
             int ho = t % p.Ho;
             int n = t / p.Ho;
+            const int h0 = ho * p.stride - p.pad, w0 = wo * p.stride - p.pad;
+            const long long origin = ((long long)n * p.Cin * H + h0) * W + w0;
             unsigned hi4[4], lo4[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -386,14 +462,10 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
                 for (int u = 0; u < 2; ++u) {
                     int k = k8 * 8 + q * 2 + u;
                     float v = 0.f;
-                    if (k < p.K) {
-                        int tap = k / p.Cin;
-                        int ci = k - tap * p.Cin;
-                        int fh = tap / p.kw;
-                        int fw = tap - fh * p.kw;
-                        int hi = ho * p.stride - p.pad + fh, wi = wo * p.stride - p.pad + fw;
-                        if (hi >= 0 && hi < H && wi >= 0 && wi < W) v = view_load(p.in, n, hi, wi, ci);
-                    }
+                    int fh = s_fh[k];
+                    int hi = h0 + fh, wi = w0 + s_fw[k];
+                    if (fh != 255 && hi >= 0 && hi < H && wi >= 0 && wi < W)
+                        v = p.in.f32 ? p.in.f32[origin + s_off[k]] : view_load(p.in, n, hi, wi, s_ci[k]);
                     x[u] = v;
                 }
                 bf16_bits h0 = f32_to_bf16_bits(x[0]), h1 = f32_to_bf16_bits(x[1]);
@@ -414,6 +486,100 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
 
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
     im2col_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    return cudaGetLastError();
+}
+
+// Finishing pass of a split-K tensor-core convolution: one thread-iteration handles eight
+// channels of one GEMM row.  The per-split sums are added in split order, so the result does
+// not depend on which CTA produced which split or in which order they finished.
+__global__ void __launch_bounds__(kPoolThreads)
+splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
+    __shared__ int s_tile;
+    const bool dynamic = blp.preempted != nullptr;
+    if (threadIdx.x == 0) trace_begin(blp);
+    const int C8 = p.cout_padded / 8;
+    const long long total = (long long)p.m_rows * C8;
+    const int img = p.in_hs * p.in_ws;
+    int iter = 0;
+    for (;;) {
+        int tile;
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = blp_claim(blp, iter);
+        }
+        if (tile < 0) break;
+        long long begin = (long long)tile * p.tile_elems;
+        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+            const int c8 = (int)(e % C8);
+            const int vrow = (int)(e / C8);
+            const int n_img = vrow / img;
+            const int r = vrow - n_img * img;
+            const int hs = r / p.in_ws;
+            const int h = hs - p.in_off;
+            const int w = r - hs * p.in_ws - p.in_off;
+            if (h < 0 || h >= p.out.H || w < 0 || w >= p.out.W) continue;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+            for (int s = 0; s < p.k_splits; ++s) {
+                const float4 *src = reinterpret_cast<const float4 *>(
+                    p.partial + ((size_t)s * p.partial_rows + vrow) * p.partial_ld + c8 * 8);
+                float4 a = src[0], b = src[1];
+                f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+                f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+            }
+            const int col0 = c8 * 8;
+            if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += p.bias[col0 + j];  // bias buffers are padded
+            }
+            if (p.res_hi) {
+                size_t off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + col0;
+                uint4 a = *reinterpret_cast<const uint4 *>(p.res_hi + off);
+                uint4 b = *reinterpret_cast<const uint4 *>(p.res_lo + off);
+                const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    f[2 * q] += __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
+                    f[2 * q + 1] += __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+                }
+            }
+            if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+            }
+            if (p.out_f32) {
+                size_t off = ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (col0 + j < p.cout_valid) p.out_f32[off + col0 + j] = f[j];
+                continue;
+            }
+            unsigned hi4[4], lo4[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                bf16_bits h0 = f32_to_bf16_bits(f[2 * q]), h1 = f32_to_bf16_bits(f[2 * q + 1]);
+                bf16_bits l0 = f32_to_bf16_bits(f[2 * q] - bf16_bits_to_f32(h0));
+                bf16_bits l1 = f32_to_bf16_bits(f[2 * q + 1] - bf16_bits_to_f32(h1));
+                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+            }
+            size_t out_off = (size_t)layout_row(p.out, n_img, h, w) * p.out.C + col0;
+            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+        }
+        ++iter;
+        if (dynamic) __syncthreads();
+    }
+    if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    splitk_finish_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
     return cudaGetLastError();
 }
 

@@ -38,7 +38,12 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         p.slots = e->d_slots + idx * kSlotsPerKernel;
         p.spill = e->d_spill;
         p.error = e->d_error;
+        if (p.k_splits > 1) p.partial = e->d_partial;
         err = cgemm_launch(p, k.tile, k.grid, b, s);
+    } else if (k.type == KernelType::SplitK) {
+        SplitKParams p = k.splitk;
+        p.partial = e->d_partial;
+        err = splitk_launch(p, k.grid, b, s);
     } else if (k.type == KernelType::Im2col) {
         err = im2col_launch(k.im2col, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {
@@ -77,12 +82,15 @@ int gpx_exec_create(gpx_model *m, int kind, gpx_exec **out) {
     GPX_CUDA(cudaMemset(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * (nk + 1)));
     size_t spill_bytes = sizeof(float) * cgemm_spill_floats_per_cta() * (size_t)(m->max_cgemm_grid + 1);
     GPX_CUDA(cudaMalloc((void **)&e->d_spill, spill_bytes));
+    GPX_CUDA(cudaMalloc((void **)&e->d_partial, sizeof(float) * (m->max_partial_floats + 64)));
     GPX_CUDA(cudaMalloc((void **)&e->d_error, 64));
     GPX_CUDA(cudaMemset(e->d_error, 0, 64));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_stop_index, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_minus_one, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_trace_init, sizeof(uint64_t) * 4 * (nk + 1),
                            cudaHostAllocPortable));
+    GPX_CUDA(cudaHostAlloc((void **)&e->h_trace, sizeof(uint64_t) * 4 * (nk + 1), cudaHostAllocPortable));
+    memset(e->h_trace, 0, sizeof(uint64_t) * 4 * (nk + 1));
     *e->h_stop_index = -1;
     *e->h_minus_one = -1;
     for (size_t i = 0; i < nk + 1; ++i) {
@@ -108,10 +116,12 @@ int gpx_exec_destroy(gpx_exec *e) {
     cudaFree(e->d_trace);
     cudaFree(e->d_slots);
     cudaFree(e->d_spill);
+    cudaFree(e->d_partial);
     cudaFree(e->d_error);
     cudaFreeHost(e->h_stop_index);
     cudaFreeHost(e->h_minus_one);
     cudaFreeHost(e->h_trace_init);
+    cudaFreeHost(e->h_trace);
     delete e;
     return GPX_SUCC;
 }

@@ -12,11 +12,13 @@ struct gpx_exec {
     int *d_executed = nullptr;        // BLPExecutor::executed, one cursor per kernel
     unsigned long long *d_trace = nullptr;
     gpx::CgemmSlot *d_slots = nullptr;  // [kernel][kSlotsPerKernel] progress of tensor-core kernels
+    float *d_partial = nullptr;         // split-K partial sums of the tensor-core kernels
     float *d_spill = nullptr;           // accumulator spill area shared by this executor's kernels
     int *d_error = nullptr;             // {code, where} written by a kernel whose bounded wait gave up
     int *h_stop_index = nullptr;      // pinned landing slot of the stop index
     int *h_minus_one = nullptr;       // pinned -1 used to re-arm the stop index
     unsigned long long *h_trace_init = nullptr;
+    unsigned long long *h_trace = nullptr;  // pinned landing area for asynchronous trace read-back
     int stop_index = -1;
     bool trace_on = false;
     cudaGraph_t graph = nullptr;

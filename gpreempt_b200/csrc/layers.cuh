@@ -49,6 +49,10 @@ struct CgemmParams {
     ActLayout out;
     float *out_f32;          // non-null: fp32 [pixel][cout_valid] output (graph heads) instead of planes
     int cout_valid;          // real output channels (the last column tile may be partly padding)
+    int k_splits;            // >= 1: the K range is cut into this many tiles per output block
+    int kb_per_split;        // K blocks per split (the last split may be shorter)
+    float *partial;          // k_splits > 1: fp32 workspace [split][partial_rows][partial_ld]
+    int partial_rows, partial_ld;
     CgemmSlot *slots;        // one per CTA of this kernel
     float *spill;            // [grid][128*BN] fp32, shared by the kernels of one executor
     int *error;              // {code, kernel*1000+cta}
@@ -87,6 +91,26 @@ struct PoolParams {
     int total_tiles;
     int tile_elems;   // output 8-channel vectors per tile
 };
+
+// Second half of a split-K tensor-core convolution: adds the per-split fp32 partial sums in
+// split order, then bias, residual and ReLU, and stores the result like the one-pass epilogue.
+struct SplitKParams {
+    const float *partial;
+    int k_splits, partial_rows, partial_ld;
+    int m_rows, in_hs, in_ws, in_off;  // decode of a GEMM row, as in CgemmParams
+    int relu;
+    const float *bias;
+    const bf16_bits *res_hi, *res_lo;
+    ActLayout res;
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
+    float *out_f32;
+    int cout_valid;
+    int cout_padded;       // multiple of 8 covered by the partial sums
+    int total_tiles;
+    int tile_elems;        // (row, 8-channel group) pairs per tile
+};
+cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
 // Patch matrix of a convolution whose input has too few channels for the tensor-core kernel
 // (the stem): row m = output pixel, column k = (fh, fw, ci), zero-padded to a multiple of 64

@@ -416,7 +416,8 @@ int finalize_model(gpx_model &m) {
             long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (dst.layout.C / 8);
             // Enough tiles to fill the GPU even when the tensor is small (global average pool).
             long long want_tiles = 4LL * m.sm_count;
-            p.tile_elems = (int)std::max<long long>(64, std::min<long long>(2048, total / want_tiles / 32 * 32));
+            p.tile_elems = (int)std::max<long long>(mode == 1 && k * k >= 16 ? 8 : 64,
+                                                    std::min<long long>(2048, total / want_tiles / 8 * 8));
             p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
             kn.total_tiles = p.total_tiles;
             kn.grid = pool_grid(p, m.sm_count);
@@ -496,8 +497,8 @@ int finalize_model(gpx_model &m) {
             q.K = n.k * n.k * src.C;
             q.Kp = (int)pm.dims[1];
             q.M = n.N * n.H * n.W;
-            q.tile_elems = 2048;
             long long total = (long long)q.M * (q.Kp / 8);
+            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2048, total / (8LL * m.sm_count) / 32 * 32));
             q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
             ki.total_tiles = q.total_tiles;
             ki.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
@@ -520,7 +521,12 @@ int finalize_model(gpx_model &m) {
         CgemmParams &p = kn.cgemm;
         const ActLayout &il = in->layout;
         const bool head = out.kind == Storage::OutputF32;
-        const int bn = (n.C % 128 == 0 || head) ? 128 : 64;
+        int bn = (n.C % 128 == 0 || head) ? 128 : 64;
+        {
+            // Few output tiles (batch 1, late stages): narrower column tiles expose more CTAs.
+            long long tiles128 = (long long)((in->layout.plane + 127) / 128) * ((n.C + 127) / 128);
+            if (tiles128 * 2 <= m.sm_count) bn = 64;
+        }
         kn.tile = bn;
         p.taps = eff_k * eff_k;
         p.cin = eff_cin;
@@ -563,12 +569,68 @@ int finalize_model(gpx_model &m) {
         GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
         GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
         GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
-        kn.total_tiles = p.tiles_m * p.tiles_n;
+        // Split K when the output alone cannot fill the GPU: each split gets at least four K
+        // blocks, the finishing kernel adds the splits in order.
+        const int all_kb = p.taps * p.cin_blocks;
+        const int out_tiles = p.tiles_m * p.tiles_n;
+        p.k_splits = 1;
+        p.kb_per_split = all_kb;
+        if (out_tiles * 2 <= m.sm_count && all_kb >= 8) {
+            int s_want = std::min(all_kb / 4, m.sm_count / out_tiles);
+            if (s_want >= 2) {
+                p.kb_per_split = (all_kb + s_want - 1) / s_want;
+                p.k_splits = (all_kb + p.kb_per_split - 1) / p.kb_per_split;
+            }
+        }
+        kn.total_tiles = out_tiles * p.k_splits;
         kn.grid = std::min(kn.total_tiles, m.sm_count);
         m.max_cgemm_grid = std::max(m.max_cgemm_grid, kn.grid);
         kn.flops = flops;
         kn.bytes = bytes;
+        if (p.k_splits == 1) {
+            m.kernels.push_back(kn);
+            continue;
+        }
+        p.partial_rows = p.tiles_m * 128;
+        p.partial_ld = p.tiles_n * bn;
+        m.max_partial_floats = std::max(m.max_partial_floats,
+                                        (size_t)p.k_splits * p.partial_rows * p.partial_ld);
+        Kernel kf;
+        kf.name = n.name + ".finish";
+        kf.node = (int)ni;
+        kf.type = KernelType::SplitK;
+        SplitKParams &q = kf.splitk;
+        q.k_splits = p.k_splits;
+        q.partial_rows = p.partial_rows;
+        q.partial_ld = p.partial_ld;
+        q.m_rows = p.m_rows;
+        q.in_hs = p.in_hs;
+        q.in_ws = p.in_ws;
+        q.in_off = p.in_off;
+        q.relu = p.relu;
+        q.bias = p.bias;
+        q.res_hi = p.res_hi;
+        q.res_lo = p.res_lo;
+        q.res = p.res;
+        q.out_hi = p.out_hi;
+        q.out_lo = p.out_lo;
+        q.out = p.out;
+        q.out_f32 = p.out_f32;
+        q.cout_valid = p.cout_valid;
+        q.cout_padded = (n.C + 7) / 8 * 8;
+        q.tile_elems = 256;
+        long long total = (long long)q.m_rows * (q.cout_padded / 8);
+        q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
+        kf.total_tiles = q.total_tiles;
+        kf.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
+        kf.flops = 0;
+        kf.bytes = 4.0 * p.k_splits * (double)q.m_rows * q.cout_padded;
+        // In the GEMM kernel itself the epilogue only writes partial sums.
+        p.bias = nullptr;
+        p.res_hi = p.res_lo = nullptr;
+        p.relu = 0;
         m.kernels.push_back(kn);
+        m.kernels.push_back(kf);
     }
     return GPX_SUCC;
 }

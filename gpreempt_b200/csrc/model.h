@@ -59,7 +59,7 @@ struct Node {
     bool via_im2col = false;
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK };
 
 struct Kernel {
     std::string name;
@@ -69,6 +69,7 @@ struct Kernel {
     PoolParams pool{};
     CgemmParams cgemm{};
     Im2colParams im2col{};
+    SplitKParams splitk{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     int grid = 1;
     int threads = 256;
@@ -92,6 +93,7 @@ struct gpx_model {
     std::vector<gpx::Kernel> kernels;
     int head_node = -1;
     int max_cgemm_grid = 0;
+    size_t max_partial_floats = 0;  // split-K workspace an executor must provide
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;

@@ -150,7 +150,7 @@ struct Load {
 
 // ---- tenants ----------------------------------------------------------------------------------
 
-enum ReqState : int { ST_IDLE = 0, ST_HINTED, ST_SUBMITTED, ST_RUNNING, ST_SUSPENDED, ST_DONE };
+enum ReqState : int { ST_IDLE = 0, ST_HINTED, ST_SUBMITTED, ST_RUNNING, ST_SUSPENDED, ST_RESUMING, ST_DONE };
 
 struct Record {
     uint64_t arrive, prepare, preprocess, copy_in, infer, copy_out, postprocess;  // ns
@@ -176,6 +176,8 @@ struct Tenant {
     std::atomic<uint64_t> ticket{0};
     uint64_t submit_ns = 0;
     int stop_index = -1;
+    size_t resume_next = 0;   // next kernel a resume in progress has to launch
+    int unlaunched_from = -1; // first kernel a cut-short resume never launched (-1: none)
     int resumes = 0;
     std::vector<Record> records;
     Record standalone{};
@@ -186,6 +188,7 @@ struct Tenant {
 
 struct Stats {
     std::vector<double> drain_us;      // word raised -> every best-effort stream idle (host-observed)
+    std::vector<double> kernel_drain_us;  // preempted kernel: word first seen -> last CTA gone (device clock)
     std::vector<double> hp_queue_us;   // request seen by the dispatcher -> launched
     long long raises = 0;
     long long be_resumes = 0;
@@ -222,26 +225,65 @@ struct Dispatcher {
         if (e->kind == GPX_EXEC_BLP && word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
         GPX_TRY(gpx_exec_execute(e, t->stream));
-        if (e->kind == GPX_EXEC_BLP)
+        if (e->kind == GPX_EXEC_BLP) {
             GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
                                      cudaMemcpyDeviceToHost, t->stream));
+            GPX_TRY(read_trace_async(t));
+        }
         GPX_CUDA(cudaEventRecord(t->done, t->stream));
         return GPX_SUCC;
     }
 
-    int launch_resume(Tenant *t) {
+    int read_trace_async(Tenant *t) {
+        gpx_exec *e = t->exec;
+        if (!e->trace_on) return GPX_SUCC;
+        GPX_CUDA(cudaMemcpyAsync(e->h_trace, e->d_trace, sizeof(uint64_t) * 4 * e->model->kernels.size(),
+                                 cudaMemcpyDeviceToHost, t->stream));
+        return GPX_SUCC;
+    }
+
+    // Resume = re-arm the stop index and replay kernels stop..N-1 with the saved cursors
+    // (BLPExecutor::resume, src/executor.cpp:280-298).  The replay is issued a few launches per
+    // dispatcher pass, so a latency-critical request that arrives meanwhile is seen between
+    // launches (the REEF scheduler checks its real-time queue the same way,
+    // src/reef-client/reef_scheduler.cpp:498-504).
+    static constexpr size_t kResumeBurst = 4;
+
+    int resume_begin(Tenant *t) {
         gpx_exec *e = t->exec;
         if (word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
-        // Re-arm the stop index, then replay kernels stop..N-1 with the saved cursors
-        // (BLPExecutor::resume, src/executor.cpp:280-298).
         GPX_CUDA(cudaMemcpyAsync(e->d_stop_index, e->h_minus_one, sizeof(int),
                                  cudaMemcpyHostToDevice, t->stream));
-        size_t nk = e->model->kernels.size();
-        for (size_t i = (size_t)t->stop_index; i < nk; ++i) GPX_TRY(exec_launch(e, i, t->stream));
+        t->resume_next = (size_t)t->stop_index;
+        t->unlaunched_from = -1;
+        return GPX_SUCC;
+    }
+
+    int resume_finish(Tenant *t) {
+        gpx_exec *e = t->exec;
         GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
                                  cudaMemcpyDeviceToHost, t->stream));
+        GPX_TRY(read_trace_async(t));
         GPX_CUDA(cudaEventRecord(t->done, t->stream));
+        return GPX_SUCC;
+    }
+
+    // Returns with the tenant RUNNING once everything is enqueued, or still RESUMING.
+    int resume_continue(Tenant *t, bool cut_short) {
+        gpx_exec *e = t->exec;
+        const size_t nk = e->model->kernels.size();
+        if (cut_short) {
+            // The word went up again: kernels not launched yet stay unlaunched and become the
+            // stop point unless an earlier kernel reports one.
+            if (t->resume_next < nk) t->unlaunched_from = (int)t->resume_next;
+        } else {
+            size_t end = std::min(nk, t->resume_next + kResumeBurst);
+            for (; t->resume_next < end; ++t->resume_next) GPX_TRY(exec_launch(e, t->resume_next, t->stream));
+            if (t->resume_next < nk) return GPX_SUCC;
+        }
+        GPX_TRY(resume_finish(t));
+        t->state.store(ST_RUNNING, std::memory_order_release);
         return GPX_SUCC;
     }
 
@@ -253,7 +295,9 @@ struct Dispatcher {
         ++stats.raises;
         drain_pending = false;
         for (Tenant *t : be)
-            if (t->state.load(std::memory_order_relaxed) == ST_RUNNING) drain_pending = true;
+            if (t->state.load(std::memory_order_relaxed) == ST_RUNNING ||
+                t->state.load(std::memory_order_relaxed) == ST_RESUMING)
+                drain_pending = true;
         return GPX_SUCC;
     }
 
@@ -282,7 +326,9 @@ struct Dispatcher {
                     // Wait-based: the latency-critical kernels are only launched once every
                     // best-effort executor has drained (blpclient.cpp:185-191).
                     for (Tenant *b : be)
-                        if (b->state.load(std::memory_order_relaxed) == ST_RUNNING) may_launch = false;
+                        if (b->state.load(std::memory_order_relaxed) == ST_RUNNING ||
+                            b->state.load(std::memory_order_relaxed) == ST_RESUMING)
+                            may_launch = false;
                 } else if (policy == POLICY_SEQ) {
                     may_launch = seq_turn(t);
                 }
@@ -314,11 +360,18 @@ struct Dispatcher {
                 cudaError_t q = cudaEventQuery(t->done);
                 if (q == cudaSuccess) {
                     int stop = t->exec->kind == GPX_EXEC_BLP ? *t->exec->h_stop_index : -1;
+                    if (stop == -1 && t->unlaunched_from >= 0) stop = t->unlaunched_from;
+                    t->unlaunched_from = -1;
                     if (stop == -1) {
                         t->state.store(ST_DONE, std::memory_order_release);
                         seq_release(t);
                     } else {
                         t->stop_index = stop;
+                        if (t->exec->trace_on && (size_t)stop < t->exec->model->kernels.size()) {
+                            const unsigned long long *tr = t->exec->h_trace + 4 * (size_t)stop;
+                            if (tr[2] != ~0ull && tr[1] >= tr[2])
+                                stats.kernel_drain_us.push_back((double)(tr[1] - tr[2]) / 1e3);
+                        }
                         t->state.store(ST_SUSPENDED, std::memory_order_release);
                     }
                 } else if (q != cudaErrorNotReady) {
@@ -327,6 +380,9 @@ struct Dispatcher {
                 } else {
                     ++be_running;
                 }
+            } else if (st == ST_RESUMING) {
+                ++be_running;
+                if (word_raised) GPX_TRY(resume_continue(t, true));
             }
         }
         if (word_raised && drain_pending && be_running == 0) {
@@ -347,10 +403,13 @@ struct Dispatcher {
                     ++stats.be_launches;
                     t->state.store(ST_RUNNING, std::memory_order_release);
                 } else if (st == ST_SUSPENDED) {
-                    GPX_TRY(launch_resume(t));
+                    GPX_TRY(resume_begin(t));
                     ++stats.be_resumes;
                     ++t->resumes;
-                    t->state.store(ST_RUNNING, std::memory_order_release);
+                    t->state.store(ST_RESUMING, std::memory_order_release);
+                    GPX_TRY(resume_continue(t, false));
+                } else if (st == ST_RESUMING) {
+                    GPX_TRY(resume_continue(t, false));
                 }
             }
         }
@@ -407,6 +466,7 @@ struct Suite {
     uint64_t seed = 0;
     bool hint = true;
     int word_transport = GPX_WORD_DEVICE;
+    size_t copy_chunk = 2u << 20;  // best-effort input copies are issued in pieces of this size
     bool resident = false;  // inputs stay in HBM: no per-request host<->device copies
     std::string end_when;  // "" = time; otherwise run ends when this task hits max_requests
     std::atomic<bool> stop{false};
@@ -433,9 +493,15 @@ struct Suite {
         uint64_t t2 = now_ns();
         if (hinting) t->state.store(ST_HINTED, std::memory_order_release);
         if (!resident) {
-            GPX_CUDA(cudaMemcpyAsync(t->model->storages[0].dptr, t->h_in, t->in_bytes,
-                                     cudaMemcpyHostToDevice, t->stream));
-            GPX_CUDA(cudaStreamSynchronize(t->stream));
+            // Best-effort inputs are copied in pieces with a synchronisation after each, so a
+            // latency-critical input copy never queues behind a whole best-effort batch.
+            const size_t chunk = (t->priority != 0 && copy_chunk) ? copy_chunk : t->in_bytes;
+            for (size_t off = 0; off < t->in_bytes; off += chunk) {
+                size_t nb = std::min(chunk, t->in_bytes - off);
+                GPX_CUDA(cudaMemcpyAsync((char *)t->model->storages[0].dptr + off, (char *)t->h_in + off, nb,
+                                         cudaMemcpyHostToDevice, t->stream));
+                GPX_CUDA(cudaStreamSynchronize(t->stream));
+            }
         }
         uint64_t t3 = now_ns();
         t->submit_ns = t3;
@@ -523,6 +589,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         s.word_transport = cfg["word_transport"].as_string() == "mapped" ? GPX_WORD_MAPPED : GPX_WORD_DEVICE;
     s.end_when = cfg["end_when"].as_string();
     s.resident = cfg["resident_inputs"].as_bool(false);
+    if (cfg.has("copy_chunk_bytes")) s.copy_chunk = (size_t)cfg["copy_chunk_bytes"].as_int(0);
     int default_gpu = (int)cfg["device"].as_int(0);
     const Json &tasks = cfg["tasks"];
     GPX_REQUIRE(tasks.is_array() && tasks.size() > 0, GPX_FAIL, "config has no tasks");
@@ -572,6 +639,7 @@ static int init_tenant(Suite &s, Tenant *t) {
     GPX_TRY(gpx_model_init_random(t->model, 1));
     bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);
     GPX_TRY(gpx_exec_create(t->model, blp ? GPX_EXEC_BLP : GPX_EXEC_BASE, &t->exec));
+    if (blp) GPX_TRY(gpx_exec_enable_trace(t->exec, 1));
     Dispatcher *d = s.dispatcher_for(t->gpu);
     if (blp) GPX_TRY(gpx_exec_set_word(t->exec, d->word));
     gpx_stream st;
@@ -794,6 +862,7 @@ static int run_suite(Suite &s, Json *report) {
         j.set("beLaunches", Json(d->stats.be_launches));
         j.set("beResumes", Json(d->stats.be_resumes));
         j.set("preemptLatency(us)", summarize(d->stats.drain_us));
+        j.set("kernelDrain(us)", summarize(d->stats.kernel_drain_us));
         j.set("hpDispatchDelay(us)", summarize(d->stats.hp_queue_us));
         jd.push(j);
     }
