@@ -26,7 +26,14 @@ namespace gpx {
 using namespace sm100;
 
 constexpr int kCBM = 128, kCBK = 64, kCUmmaK = 16;
-constexpr int kCgemmThreads = 192;
+// Warp 0 feeds TMA, warp 1 issues MMAs, warps 2-9 are the epilogue: two warps per TMEM lane
+// quarter, each taking half of the columns, so twice as many loads and stores are in flight
+// while a tile is drained (the epilogue, not the tensor pipe, bounds the small-K layers).
+constexpr int kCgemmThreads = 320;
+constexpr int kCEpiThreads = 256;
+// Epilogue staging: 32 rows of 64 data bytes per warp, padded to 80 bytes so that the row-wise
+// and the four-lanes-per-row access patterns both spread over the shared-memory banks.
+constexpr int kCStageRowBytes = 80;
 constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
 constexpr int kCPollEvery = 2;
 
@@ -36,7 +43,8 @@ struct CgemmCfg {
     static constexpr uint32_t kWBytes = BN * kCBK * 2;          // one plane of W
     static constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kWBytes;
     static constexpr int kStages = BN == 128 ? 3 : 4;
-    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + 256;
+    // ring + alignment slack + control block + one staging buffer per epilogue warp
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + 256 + 8 * 32 * kCStageRowBytes;
     // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
     // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
     static constexpr int kAccs = 4;
@@ -79,6 +87,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     unsigned char *smem = smem_raw + pad;
     CgemmControl *ctl = reinterpret_cast<CgemmControl *>(smem + (size_t)kStages * Cfg::kStageBytes);
     const uint32_t smem_base = smem_u32(smem);
+    unsigned char *epi_stage = smem + (size_t)kStages * Cfg::kStageBytes + 256;
     volatile int *abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -286,14 +295,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps)
+        // ------------------------------------------------------------------ epilogue (8 warps)
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                 // which half of the columns
+        const int c_lo = half * (BN / 2), c_hi = c_lo + BN / 2;
+        const int s_lo = half * (Cfg::kTmemCols / 2), s_hi = s_lo + Cfg::kTmemCols / 2;
         const int row = quarter * 32 + lane;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const bool leader = threadIdx.x == 64;
         uint32_t v[32];
         if (first_k > 0) {
-            for (int c = 0; c < Cfg::kTmemCols; c += 32) {
+            for (int c = s_lo; c < s_hi; c += 32) {
                 const uint4 *src = reinterpret_cast<const uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -308,7 +320,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             tmem_st_wait();
         }
         tc_fence_before_sync();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (leader) mbar_arrive(smem_u32(&ctl->tmem_empty));
 
         int it = first_iter;
@@ -321,7 +333,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 if (!ok) fail(301);
                 ctl->epi_go = ok ? 1 : 0;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (!ctl->epi_go) break;
             tc_fence_after_sync();
             const int kind = ctl->epi_kind;
@@ -358,8 +370,60 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                                         : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
                     if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
                 }
-                for (int c = 0; c < BN; c += 32) {
+                // Rows whose planes this lane moves in the coalesced phases: row (lane/4 + 8i) of the
+                // warp's 32, 16 bytes at column group (lane%4).  ~0 marks a row that is not an
+                // output pixel.
+                const bool staged = !p.partial && !p.out_f32;
+                unsigned long long my_out = valid ? (unsigned long long)out_off : ~0ull;
+                unsigned long long my_res = (valid && p.res_hi) ? (unsigned long long)res_off : ~0ull;
+                unsigned long long row_out[4], row_res[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    row_out[i] = __shfl_sync(0xffffffffu, my_out, (lane >> 2) + 8 * i);
+                    row_res[i] = __shfl_sync(0xffffffffu, my_res, (lane >> 2) + 8 * i);
+                }
+                unsigned char *stg = epi_stage + (size_t)(warp - 2) * kCStageRowBytes * 32;
+                const int seg = lane & 3;
+                // One plane of a 32-row x 32-column piece: global -> shared with full 64-byte row
+                // pieces per four lanes, then every lane picks up its own row.
+                auto fetch_plane = [&](const bf16_bits *base, int c, uint4 (&dst)[4]) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = (lane >> 2) + 8 * i;
+                        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                        if (row_res[i] != ~0ull)
+                            q = *reinterpret_cast<const uint4 *>(base + row_res[i] + c + seg * 8);
+                        *reinterpret_cast<uint4 *>(stg + r * kCStageRowBytes + seg * 16) = q;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        dst[j] = *reinterpret_cast<const uint4 *>(stg + lane * kCStageRowBytes + j * 16);
+                    __syncwarp();
+                };
+                auto flush_plane = [&](bf16_bits *base, int c, const uint4 (&src)[4]) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4 *>(stg + lane * kCStageRowBytes + j * 16) = src[j];
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = (lane >> 2) + 8 * i;
+                        uint4 q = *reinterpret_cast<const uint4 *>(stg + r * kCStageRowBytes + seg * 16);
+                        if (row_out[i] != ~0ull)
+                            *reinterpret_cast<uint4 *>(base + row_out[i] + c + seg * 8) = q;
+                    }
+                    __syncwarp();
+                };
+                for (int c = c_lo; c < c_hi; c += 32) {
                     float f[32], g[32];
+                    // The residual is requested first so its latency overlaps the TMEM reads.
+                    uint4 rh4[4], rl4[4];
+                    const bool use_res = staged && p.res_hi;
+                    if (use_res) {
+                        fetch_plane(p.res_hi, c, rh4);
+                        fetch_plane(p.res_lo, c, rl4);
+                    }
                     tmem_ld_32x32(t_lane + c, v);
                     tmem_ld_wait();
 #pragma unroll
@@ -388,7 +452,6 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                         continue;
                     }
-                    if (!valid) continue;
                     if (p.bias) {
                         const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + n_blk * BN + c);
 #pragma unroll
@@ -400,12 +463,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                             f[4 * j + 3] += b.w;
                         }
                     }
-                    if (p.res_hi) {
-                        const uint4 *rh = reinterpret_cast<const uint4 *>(p.res_hi + res_off + c);
-                        const uint4 *rl = reinterpret_cast<const uint4 *>(p.res_lo + res_off + c);
+                    if (use_res) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            uint4 a = rh[j], b = rl[j];
+                            uint4 a = rh4[j], b = rl4[j];
                             const uint32_t ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
@@ -420,13 +481,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                     if (p.out_f32) {
                         const int col0 = n_blk * BN + c;
+                        if (valid) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.cout_valid) p.out_f32[out_off + col0 + j] = f[j];
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.cout_valid) p.out_f32[out_off + col0 + j] = f[j];
+                        }
                         continue;
                     }
-                    uint4 *oh = reinterpret_cast<uint4 *>(p.out_hi + out_off + c);
-                    uint4 *ol = reinterpret_cast<uint4 *>(p.out_lo + out_off + c);
+                    uint4 hi4[4], lo4[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t hi[4], lo[4];
@@ -437,15 +499,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                             hi[q] = ph;
                             lo[q] = pack_bf16(x0 - bf16_lo_to_f32(ph), x1 - bf16_hi_to_f32(ph));
                         }
-                        oh[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        ol[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        lo4[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     }
+                    flush_plane(p.out_hi, c, hi4);
+                    flush_plane(p.out_lo, c, lo4);
                 }
                 ++it;
                 ++tiles_done;
                 seg_k0 = 0;
                 tc_fence_before_sync();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (leader) {
                     mbar_arrive(smem_u32(&ctl->tmem_empty));
                     if (blp.executed) atomicAdd(blp.executed, 1);
@@ -454,7 +518,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
             // CEPI_PARTIAL
             if (k_done > seg_k0) {
-                for (int c = 0; c < Cfg::kTmemCols; c += 32) {
+                for (int c = s_lo; c < s_hi; c += 32) {
                     tmem_ld_32x32(t_lane + c, v);
                     tmem_ld_wait();
                     uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);

@@ -517,7 +517,7 @@ int finalize_model(gpx_model &m) {
         kn.name = n.name;
         kn.node = (int)ni;
         kn.type = KernelType::Cgemm;
-        kn.threads = 192;
+        kn.threads = 320;
         CgemmParams &p = kn.cgemm;
         const ActLayout &il = in->layout;
         const bool head = out.kind == Storage::OutputF32;

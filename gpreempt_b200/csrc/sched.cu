@@ -255,6 +255,13 @@ struct Dispatcher {
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
         GPX_CUDA(cudaMemcpyAsync(e->d_stop_index, e->h_minus_one, sizeof(int),
                                  cudaMemcpyHostToDevice, t->stream));
+        if (e->trace_on) {
+            // Fresh time stamps for the kernels that are about to be replayed, so a second
+            // preemption of the same kernel is measured from its own observation of the word.
+            size_t nk = e->model->kernels.size(), from = (size_t)t->stop_index;
+            GPX_CUDA(cudaMemcpyAsync(e->d_trace + 4 * from, e->h_trace_init + 4 * from,
+                                     sizeof(uint64_t) * 4 * (nk - from), cudaMemcpyHostToDevice, t->stream));
+        }
         t->resume_next = (size_t)t->stop_index;
         t->unlaunched_from = -1;
         return GPX_SUCC;

@@ -257,3 +257,45 @@ def test_export_json_has_the_tvm_graph_skeleton(gpx):
     assert g["attrs"]["dltype"][0] == "list_str" and len(g["attrs"]["dltype"][1]) == len(names)
     assert g["attrs"]["shape"][1][0] == [1, 3, 224, 224]
     m.clear()
+
+
+def test_cuda_core_convolution_path_matches_oracle(gpx, oracle, monkeypatch):
+    """GPX_CONV=simt keeps every convolution on the FFMA kernel (same split-plane storage); it
+    must meet the same bound, which also pins the tensor-core path against a second GPU path."""
+    monkeypatch.setenv("GPX_CONV", "simt")
+    ex = gpx.BaseExecutor()
+    ex.init("resnet_tiny", batch=2, seed=1)
+    monkeypatch.delenv("GPX_CONV")
+    threads = {ex.model.get_kernel_info(i)["launch_params"][3] for i in range(ex.get_kernel_num())}
+    assert threads == {256}, "a tensor-core kernel was selected despite GPX_CONV=simt"
+    data = _data(gpx, 2)
+    ex.set_input("data", data)
+    ex.execute()
+    simt = ex.get_output("heads")
+    want = oracle.forward("resnet_tiny", ex.model.params(), data)
+    assert _rel(simt, want) <= RTOL_FP32
+    tc = gpx.BaseExecutor()
+    tc.init("resnet_tiny", batch=2, seed=1)
+    assert 320 in {tc.model.get_kernel_info(i)["launch_params"][3] for i in range(tc.get_kernel_num())}
+    tc.set_input("data", data)
+    tc.execute()
+    assert tc.error() == (0, 0)
+    assert _rel(tc.get_output("heads"), simt) <= RTOL_FP32
+    ex.clear(), tc.clear()
+
+
+def test_batch_one_uses_split_k_and_matches_oracle(gpx, oracle):
+    """Batch 1 (the latency-critical shape) cuts K over several CTAs; partial sums are added in
+    split order by the finishing kernel."""
+    ex = gpx.BaseExecutor()
+    ex.init("resnet50", batch=1, seed=3)
+    names = [ex.model.get_kernel_info(i)["name"] for i in range(ex.get_kernel_num())]
+    assert any(n.endswith(".finish") for n in names)
+    data = _data(gpx, 1, seed=9)
+    ex.set_input("data", data)
+    ex.execute()
+    a = ex.get_output("heads")
+    ex.execute()
+    assert np.array_equal(a, ex.get_output("heads")), "split-K result changed between runs"
+    assert _rel(a, oracle.forward("resnet50", ex.model.params(), data)) <= RTOL_FP32
+    ex.clear()
