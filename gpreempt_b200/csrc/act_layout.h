@@ -66,4 +66,16 @@ GPX_HD int layout_row(const ActLayout &l, int n, int h, int w) {
     return ph * l.plane + (n * l.Hs + (hp >> 1)) * l.Ws + (wp >> 1);
 }
 
+// Activation fused into a layer's epilogue.
+enum ActKind : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_RELU6 = 3 };
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == ACT_RELU) return fmaxf(v, 0.f);
+    if (act == ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));  // exact GELU
+    if (act == ACT_RELU6) return fminf(fmaxf(v, 0.f), 6.f);
+    return v;
+}
+#endif
+
 }  // namespace gpx

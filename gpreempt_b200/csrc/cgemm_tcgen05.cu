@@ -386,14 +386,19 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 const int seg = lane & 3;
                 // One plane of a 32-row x 32-column piece: global -> shared with full 64-byte row
                 // pieces per four lanes, then every lane picks up its own row.
-                auto fetch_plane = [&](const bf16_bits *base, int c, uint4 (&dst)[4]) {
+                auto load_plane = [&](const bf16_bits *base, int c, uint4 (&q)[4]) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        q[i] = make_uint4(0u, 0u, 0u, 0u);
+                        if (row_res[i] != ~0ull)
+                            q[i] = *reinterpret_cast<const uint4 *>(base + row_res[i] + c + seg * 8);
+                    }
+                };
+                auto transpose_plane = [&](const uint4 (&q)[4], uint4 (&dst)[4]) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int r = (lane >> 2) + 8 * i;
-                        uint4 q = make_uint4(0u, 0u, 0u, 0u);
-                        if (row_res[i] != ~0ull)
-                            q = *reinterpret_cast<const uint4 *>(base + row_res[i] + c + seg * 8);
-                        *reinterpret_cast<uint4 *>(stg + r * kCStageRowBytes + seg * 16) = q;
+                        *reinterpret_cast<uint4 *>(stg + r * kCStageRowBytes + seg * 16) = q[i];
                     }
                     __syncwarp();
 #pragma unroll
@@ -420,9 +425,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     // The residual is requested first so its latency overlaps the TMEM reads.
                     uint4 rh4[4], rl4[4];
                     const bool use_res = staged && p.res_hi;
+                    uint4 gh[4], gl[4];
                     if (use_res) {
-                        fetch_plane(p.res_hi, c, rh4);
-                        fetch_plane(p.res_lo, c, rl4);
+                        load_plane(p.res_hi, c, gh);  // both planes are in flight together
+                        load_plane(p.res_lo, c, gl);
                     }
                     tmem_ld_32x32(t_lane + c, v);
                     tmem_ld_wait();
@@ -464,6 +470,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                     }
                     if (use_res) {
+                        transpose_plane(gh, rh4);
+                        transpose_plane(gl, rl4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint4 a = rh4[j], b = rl4[j];
@@ -477,7 +485,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                     if (p.relu) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+                        for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.relu);
                     }
                     if (p.out_f32) {
                         const int col0 = n_blk * BN + c;

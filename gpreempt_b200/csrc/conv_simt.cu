@@ -174,7 +174,7 @@ conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
                 float v = acc[i][j];
                 if (p.bias) v += p.bias[n];
                 if (p.res.hi || p.res.f32) v += view_load(p.res, n_img, ho, wo, n);
-                if (p.relu) v = fmaxf(v, 0.f);
+                v = apply_act(v, p.relu);
                 if (p.out_f32) {
                     p.out_f32[out_row * p.Cout + n] = v;
                 } else {
@@ -550,7 +550,7 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
             }
             if (p.relu) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+                for (int j = 0; j < 8; ++j) f[j] = apply_act(f[j], p.relu);
             }
             if (p.out_f32) {
                 size_t off = ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid;

@@ -83,8 +83,8 @@ int gpx_exec_create(gpx_model *m, int kind, gpx_exec **out) {
     size_t spill_bytes = sizeof(float) * cgemm_spill_floats_per_cta() * (size_t)(m->max_cgemm_grid + 1);
     GPX_CUDA(cudaMalloc((void **)&e->d_spill, spill_bytes));
     GPX_CUDA(cudaMalloc((void **)&e->d_partial, sizeof(float) * (m->max_partial_floats + 64)));
-    GPX_CUDA(cudaMalloc((void **)&e->d_error, 64));
-    GPX_CUDA(cudaMemset(e->d_error, 0, 64));
+    GPX_CUDA(cudaMalloc((void **)&e->d_error, 1024));
+    GPX_CUDA(cudaMemset(e->d_error, 0, 1024));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_stop_index, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_minus_one, 64, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc((void **)&e->h_trace_init, sizeof(uint64_t) * 4 * (nk + 1),

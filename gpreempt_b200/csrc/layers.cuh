@@ -127,6 +127,32 @@ struct Im2colParams {
 };
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
+// LayerNorm over the channels of a [rows][H] matrix (H <= 1024, multiple of 8).  With `ids` set
+// the input row is the sum of the word, position and token-type embeddings instead of planes.
+struct LayerNormParams {
+    const bf16_bits *in_hi, *in_lo;
+    const long long *ids;                   // [rows] token ids or null
+    const float *word, *pos, *type;         // embedding tables (ids != null)
+    const float *gamma, *beta;
+    bf16_bits *out_hi, *out_lo;
+    float *out_f32;                         // non-null: fp32 output (graph heads)
+    int rows, H, S;
+    float eps;
+    int total_tiles;
+};
+cudaError_t layernorm_launch(const LayerNormParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+
+// Multi-head self-attention over [B*S][ld] matrices of queries, keys and values (head h owns
+// columns h*64 .. h*64+63); no mask.
+struct AttnParams {
+    const bf16_bits *q_hi, *q_lo, *k_hi, *k_lo, *v_hi, *v_lo;
+    bf16_bits *out_hi, *out_lo;
+    int B, S, heads, ld;
+    float scale;
+    int total_tiles;
+};
+cudaError_t attention_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+
 enum ConvTile { CONV_TILE_128 = 0, CONV_TILE_64 = 1, CONV_TILE_32 = 2 };
 
 int conv_pick_tile(const ConvParams &p, int sm_count);

@@ -107,7 +107,7 @@ struct GraphBuilder {
         n.k = k;
         n.stride = stride;
         n.pad = pad;
-        n.relu = relu;
+        n.act = relu ? ACT_RELU : ACT_NONE;
         n.N = src.N;
         n.H = (src.H + 2 * pad - k) / stride + 1;
         n.W = (src.W + 2 * pad - k) / stride + 1;
@@ -465,7 +465,7 @@ int finalize_model(gpx_model &m) {
             p.pad = n.pad;
             p.M = n.N * n.H * n.W;
             p.K = n.k * n.k * src.C;
-            p.relu = n.relu ? 1 : 0;
+            p.relu = n.act;
             kn.tile = conv_pick_tile(p, m.sm_count);
             conv_set_tiles(p, kn.tile);
             kn.total_tiles = p.tiles_m * p.tiles_n;
@@ -549,7 +549,7 @@ int finalize_model(gpx_model &m) {
         p.tiles_m = (p.m_rows + 127) / 128;
         p.tiles_n = (n.C + bn - 1) / bn;
         p.cout_valid = n.C;
-        p.relu = n.relu ? 1 : 0;
+        p.relu = n.act;
         p.bias = m.storages[n.bias].dptr;
         if (n.residual >= 0) {
             const Storage &r = m.storages[m.nodes[n.residual].storage];
@@ -1020,7 +1020,8 @@ int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
         attrs.set("kernel", Json(n.k));
         attrs.set("stride", Json(n.stride));
         attrs.set("padding", Json(n.pad));
-        attrs.set("relu", Json(n.relu));
+        attrs.set("relu", Json(n.act == ACT_RELU));
+        attrs.set("activation", Json(n.act));
         attrs.set("channels", Json(n.C));
         Json inputs = Json::array();
         auto ref = [&](int storage) {

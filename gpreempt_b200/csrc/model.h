@@ -51,7 +51,7 @@ struct Node {
     int weight = -1, bias = -1;
     int N = 0, H = 0, W = 0, C = 0;  // output shape
     int k = 0, stride = 1, pad = 0;
-    bool relu = false;
+    int act = 0;  // ActKind applied after bias and residual
     int residual = -1;
     bool tensor_core = false;  // decided by finalize_model
     int sub_storage = -1;      // stride-2 1x1: compact copy of the sub-sampled input;

@@ -277,3 +277,91 @@ def blp_simulate(total_tiles, n_ctas, tile_cost, raise_at, cursor=0, stop_index=
         done.append(idx)
         heapq.heappush(ready, (t_end, c))
     return done, cursor, stop_index, last_exit
+
+
+# ---- BERT encoder (post-LayerNorm transformer, Devlin et al. 2018) ------------------------------
+# Parameter names follow the Hugging Face BertModel state dict, which is what the reference's
+# compile script traces (scripts/compile/compile-bert.py:33-52 uses a DistilBERT checkpoint; the
+# baseline configuration asks for BERT-base).  All arithmetic is numpy float64.
+
+def bert_param_shapes(layers=12, hidden=768, heads=12, ffn=3072, vocab=30522, max_pos=512):
+    s = {
+        "embeddings.word_embeddings.weight": (vocab, hidden),
+        "embeddings.position_embeddings.weight": (max_pos, hidden),
+        "embeddings.token_type_embeddings.weight": (2, hidden),
+        "embeddings.LayerNorm.weight": (hidden,),
+        "embeddings.LayerNorm.bias": (hidden,),
+    }
+    for i in range(layers):
+        p = f"encoder.layer.{i}"
+        for nm in ("query", "key", "value"):
+            s[f"{p}.attention.self.{nm}.weight"] = (hidden, hidden)
+            s[f"{p}.attention.self.{nm}.bias"] = (hidden,)
+        s[f"{p}.attention.output.dense.weight"] = (hidden, hidden)
+        s[f"{p}.attention.output.dense.bias"] = (hidden,)
+        s[f"{p}.attention.output.LayerNorm.weight"] = (hidden,)
+        s[f"{p}.attention.output.LayerNorm.bias"] = (hidden,)
+        s[f"{p}.intermediate.dense.weight"] = (ffn, hidden)
+        s[f"{p}.intermediate.dense.bias"] = (ffn,)
+        s[f"{p}.output.dense.weight"] = (hidden, ffn)
+        s[f"{p}.output.dense.bias"] = (hidden,)
+        s[f"{p}.output.LayerNorm.weight"] = (hidden,)
+        s[f"{p}.output.LayerNorm.bias"] = (hidden,)
+    return s
+
+
+def _layer_norm(x, g, b, eps=1e-12):
+    mu = x.mean(-1, keepdims=True)
+    var = ((x - mu) ** 2).mean(-1, keepdims=True)
+    return (x - mu) / np.sqrt(var + eps) * g + b
+
+
+def _gelu(x):
+    from math import sqrt
+
+    import scipy.special as sp
+
+    return 0.5 * x * (1.0 + sp.erf(x / sqrt(2.0)))
+
+
+def bert_forward(params, ids, layers=12, heads=12, taps=None):
+    """ids: int64 [B][S]; returns the last hidden state [B][S][H] as float32."""
+    P = {k: np.asarray(v, np.float64).reshape(v.shape[0], -1) if np.ndim(v) > 1 else np.asarray(v, np.float64)
+         for k, v in params.items()}
+    ids = np.asarray(ids, np.int64)
+    B, S = ids.shape
+    x = (P["embeddings.word_embeddings.weight"][ids] +
+         P["embeddings.position_embeddings.weight"][np.arange(S)][None, :, :] +
+         P["embeddings.token_type_embeddings.weight"][0][None, None, :])
+    x = _layer_norm(x, P["embeddings.LayerNorm.weight"], P["embeddings.LayerNorm.bias"])
+    if taps is not None:
+        taps["embeddings"] = x.astype(np.float32)
+    H = x.shape[-1]
+    dh = H // heads
+    for i in range(layers):
+        p = f"encoder.layer.{i}"
+        q = x @ P[f"{p}.attention.self.query.weight"].T + P[f"{p}.attention.self.query.bias"]
+        k = x @ P[f"{p}.attention.self.key.weight"].T + P[f"{p}.attention.self.key.bias"]
+        v = x @ P[f"{p}.attention.self.value.weight"].T + P[f"{p}.attention.self.value.bias"]
+        qh = q.reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        kh = k.reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        vh = v.reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        sc = qh @ kh.transpose(0, 1, 3, 2) / np.sqrt(dh)
+        sc = sc - sc.max(-1, keepdims=True)
+        pr = np.exp(sc)
+        pr = pr / pr.sum(-1, keepdims=True)
+        ctx = (pr @ vh).transpose(0, 2, 1, 3).reshape(B, S, H)
+        if taps is not None:
+            taps[f"{p}.attention.context"] = ctx.astype(np.float32)
+        a = ctx @ P[f"{p}.attention.output.dense.weight"].T + P[f"{p}.attention.output.dense.bias"]
+        x = _layer_norm(a + x, P[f"{p}.attention.output.LayerNorm.weight"],
+                        P[f"{p}.attention.output.LayerNorm.bias"])
+        h = _gelu(x @ P[f"{p}.intermediate.dense.weight"].T + P[f"{p}.intermediate.dense.bias"])
+        o = h @ P[f"{p}.output.dense.weight"].T + P[f"{p}.output.dense.bias"]
+        x = _layer_norm(o + x, P[f"{p}.output.LayerNorm.weight"], P[f"{p}.output.LayerNorm.bias"])
+        if taps is not None:
+            taps[f"{p}.output"] = x.astype(np.float32)
+    out = x.astype(np.float32)
+    if taps is not None:
+        taps["heads"] = out
+    return out

@@ -183,3 +183,20 @@ def test_blp_protocol_runs_every_tile_exactly_once_across_resumes(oracle):
         # a claimed tile always completes, so the drain never exceeds the longest tile
         d, c2, s2, t_exit = oracle.blp_simulate(total, ctas, cost, 3.0)
         assert t_exit <= 3.0 + 2.5 + 1e-9 or s2 == -1
+
+
+def test_bert_restatement_matches_huggingface_bert(oracle):
+    """The oracle's BERT encoder against transformers.BertModel (random weights, float64)."""
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.BertConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                  intermediate_size=256, vocab_size=1000, max_position_embeddings=64,
+                                  hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    torch.manual_seed(0)
+    net = transformers.BertModel(cfg, add_pooling_layer=False).double().eval()
+    params = {k: v.detach().numpy() for k, v in net.state_dict().items() if "position_ids" not in k}
+    ids = np.random.default_rng(6).integers(0, 1000, (2, 16))
+    with torch.no_grad():
+        ref = net(input_ids=torch.from_numpy(ids)).last_hidden_state.numpy()
+    got = oracle.bert_forward(params, ids, layers=2, heads=4)
+    assert got.shape == ref.shape
+    assert _rel(got, ref) < 2e-6
