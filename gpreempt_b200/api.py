@@ -277,9 +277,9 @@ def synth_uniform(n: int, seed: int, stream: int = 0, lo: float = -1.0, hi: floa
 class Model:
     """foo::Model (include/model.h:32-93)."""
 
-    def __init__(self, name: str, batch: int = 1, dtype: str = "float32"):
+    def __init__(self, name: str, batch: int = 1, dtype: str = "float32", seq_len: int = 0):
         self.handle = ctypes.c_void_p()
-        opts = B.ModelOpts(batch, dtype.encode(), 0)
+        opts = B.ModelOpts(batch, dtype.encode(), seq_len)
         check(B.load().gpx_model_open(name.encode(), ctypes.byref(opts), ctypes.byref(self.handle)))
         self.name = name
 
@@ -377,8 +377,8 @@ class Executor:
         self.batch = 1
         self.dtype = "float32"
 
-    def init(self, workload: str, batch: int = 1, seed: int | None = None) -> None:
-        self.model = Model(workload, batch=batch, dtype=self.dtype)
+    def init(self, workload: str, batch: int = 1, seed: int | None = None, seq_len: int = 0) -> None:
+        self.model = Model(workload, batch=batch, dtype=self.dtype, seq_len=seq_len)
         self.batch = batch
         if seed is not None:
             self.model.init_random(seed)

@@ -179,8 +179,9 @@ conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
                     p.out_f32[out_row * p.Cout + n] = v;
                 } else {
                     bf16_bits h = f32_to_bf16_bits(v);
-                    p.out_hi[out_row * p.Cout + n] = h;
-                    p.out_lo[out_row * p.Cout + n] = f32_to_bf16_bits(v - bf16_bits_to_f32(h));
+                    // the row stride is the stored channel count, which may exceed Cout
+                    p.out_hi[out_row * p.out.C + n] = h;
+                    p.out_lo[out_row * p.out.C + n] = f32_to_bf16_bits(v - bf16_bits_to_f32(h));
                 }
             }
         }
@@ -261,6 +262,42 @@ cudaError_t conv_launch(const ConvParams &p, int tile, int grid, const BlpArgs &
 
 constexpr int kPoolThreads = 256;
 
+// Eight channels of one input pixel as fp32: the sum of the planes, then the optional
+// per-channel affine + activation of PoolParams.
+__device__ __forceinline__ void pool_load8(const PoolParams &p, size_t off, int c0, float (&x)[8]) {
+    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
+    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
+    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        x[2 * q] = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
+        x[2 * q + 1] = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+    }
+    if (p.scale) {
+        const float4 *sc = reinterpret_cast<const float4 *>(p.scale + c0);
+        const float4 *sh = reinterpret_cast<const float4 *>(p.shift + c0);
+        float4 s0 = __ldg(sc), s1 = __ldg(sc + 1), h0 = __ldg(sh), h1 = __ldg(sh + 1);
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = apply_act(fmaf(x[j], sv[j], hv[j]), p.act);
+    }
+}
+
+__device__ __forceinline__ void pool_store8(const PoolParams &p, size_t off, const float (&x)[8]) {
+    unsigned hi4[4], lo4[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        bf16_bits h0 = f32_to_bf16_bits(x[2 * q]), h1 = f32_to_bf16_bits(x[2 * q + 1]);
+        bf16_bits l0 = f32_to_bf16_bits(x[2 * q] - bf16_bits_to_f32(h0));
+        bf16_bits l1 = f32_to_bf16_bits(x[2 * q + 1] - bf16_bits_to_f32(h1));
+        hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+        lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+    }
+    *reinterpret_cast<uint4 *>(p.out_hi + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+    *reinterpret_cast<uint4 *>(p.out_lo + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+}
+
 // Max / average pooling, or a strided copy, over split-plane activations; eight channels (one
 // 16-byte vector per plane) per thread-iteration.  A tile is tile_elems consecutive output
 // vectors in (n, ho, wo, c/8) order.
@@ -269,8 +306,8 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
-    const int C = p.out.C;
-    const int C8 = C / 8;
+    const int Cin = p.in.l.C, Cout = p.out.C;  // row strides
+    const int C8 = p.channels / 8;
     const int Ho = p.out.H, Wo = p.out.W;
     const int H = p.in.l.H, W = p.in.l.W;
     const long long total = (long long)p.out.N * Ho * Wo * C8;
@@ -303,18 +340,16 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
                 int cnt = 0;
+                const bool readable = c8 * 8 < p.in_valid;
                 for (int tap = lane; tap < p.k * p.k; tap += 32) {
                     int fh = tap / p.k, fw = tap - fh * p.k;
                     int hi = ho * p.stride - p.pad + fh, wi = wo * p.stride - p.pad + fw;
                     if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
-                    size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * C + c8 * 8;
-                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
-                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
-                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+                    if (readable) {
+                        float x[8];
+                        pool_load8(p, (size_t)layout_row(p.in.l, n, hi, wi) * Cin + c8 * 8, c8 * 8, x);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        acc[2 * q] += __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
-                        acc[2 * q + 1] += __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+                        for (int j = 0; j < 8; ++j) acc[j] += x[j];
                     }
                     ++cnt;
                 }
@@ -326,19 +361,9 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
                 }
                 if (lane == 0) {
                     float inv = 1.0f / (float)cnt;
-                    unsigned hi4[4], lo4[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float x0 = acc[2 * q] * inv, x1 = acc[2 * q + 1] * inv;
-                        bf16_bits h0 = f32_to_bf16_bits(x0), h1 = f32_to_bf16_bits(x1);
-                        bf16_bits l0 = f32_to_bf16_bits(x0 - bf16_bits_to_f32(h0));
-                        bf16_bits l1 = f32_to_bf16_bits(x1 - bf16_bits_to_f32(h1));
-                        hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-                        lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
-                    }
-                    size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
-                    *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                    *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+                    pool_store8(p, (size_t)layout_row(p.out, n, ho, wo) * Cout + c8 * 8, acc);
                 }
             }
             ++iter;
@@ -353,8 +378,9 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
             int ho = (int)(t % Ho);
             int n = (int)(t / Ho);
             float acc[8];
+            const bool readable = c8 * 8 < p.in_valid;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = p.mode == 0 ? -INFINITY : 0.f;
+            for (int j = 0; j < 8; ++j) acc[j] = (p.mode == 0 && readable) ? -INFINITY : 0.f;
             int cnt = 0;
             const int kk = p.mode == 2 ? 1 : p.k;
             for (int fh = 0; fh < kk; ++fh) {
@@ -363,23 +389,17 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
                 for (int fw = 0; fw < kk; ++fw) {
                     int wi = wo * p.stride - p.pad + fw;
                     if (wi < 0 || wi >= W) continue;
-                    size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * C + c8 * 8;
-                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
-                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
-                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float x0 = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
-                        float x1 = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
-                        if (p.mode == 0) {
-                            acc[2 * q] = fmaxf(acc[2 * q], x0);
-                            acc[2 * q + 1] = fmaxf(acc[2 * q + 1], x1);
-                        } else {
-                            acc[2 * q] += x0;
-                            acc[2 * q + 1] += x1;
-                        }
-                    }
                     ++cnt;
+                    if (!readable) continue;
+                    float x[8];
+                    pool_load8(p, (size_t)layout_row(p.in.l, n, hi, wi) * Cin + c8 * 8, c8 * 8, x);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (p.mode == 0)
+                            acc[j] = fmaxf(acc[j], x[j]);
+                        else
+                            acc[j] += x[j];
+                    }
                 }
             }
             if (p.mode == 1) {
@@ -387,18 +407,7 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] *= inv;
             }
-            unsigned hi4[4], lo4[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                bf16_bits h0 = f32_to_bf16_bits(acc[2 * q]), h1 = f32_to_bf16_bits(acc[2 * q + 1]);
-                bf16_bits l0 = f32_to_bf16_bits(acc[2 * q] - bf16_bits_to_f32(h0));
-                bf16_bits l1 = f32_to_bf16_bits(acc[2 * q + 1] - bf16_bits_to_f32(h1));
-                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
-            }
-            size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
-            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+            pool_store8(p, (size_t)layout_row(p.out, n, ho, wo) * Cout + c8 * 8, acc);
         }
         ++iter;
         if (dynamic) __syncthreads();
@@ -580,6 +589,94 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
 
 cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
     splitk_finish_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    return cudaGetLastError();
+}
+
+// Depthwise convolution: one thread-iteration produces eight channels of one output pixel,
+// taps walked in (fh, fw) order with one FFMA each, so the result is independent of the tiling.
+__global__ void __launch_bounds__(kPoolThreads)
+dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
+    __shared__ int s_tile;
+    const bool dynamic = blp.preempted != nullptr;
+    if (threadIdx.x == 0) trace_begin(blp);
+    const int C = p.out.C;
+    const int C8 = C / 8;
+    const int Ho = p.out.H, Wo = p.out.W;
+    const int H = p.in.l.H, W = p.in.l.W;
+    const long long total = (long long)p.out.N * Ho * Wo * C8;
+    int iter = 0;
+    for (;;) {
+        int tile;
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = blp_claim(blp, iter);
+        }
+        if (tile < 0) break;
+        long long begin = (long long)tile * p.tile_elems;
+        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+            int c8 = (int)(e % C8);
+            long long t = e / C8;
+            int wo = (int)(t % Wo);
+            t /= Wo;
+            int ho = (int)(t % Ho);
+            int n = (int)(t / Ho);
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int fh = 0; fh < p.k; ++fh) {
+                int hi = ho * p.stride - p.pad + fh;
+                if (hi < 0 || hi >= H) continue;
+                for (int fw = 0; fw < p.k; ++fw) {
+                    int wi = wo * p.stride - p.pad + fw;
+                    if (wi < 0 || wi >= W) continue;
+                    size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * p.in.l.C + c8 * 8;
+                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
+                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
+                    const float4 *wv = reinterpret_cast<const float4 *>(p.w + (size_t)(fh * p.k + fw) * C + c8 * 8);
+                    float4 w0 = wv[0], w1 = wv[1];
+                    const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float x0 = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
+                        float x1 = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
+                        acc[2 * q] = fmaf(x0, wf[2 * q], acc[2 * q]);
+                        acc[2 * q + 1] = fmaf(x1, wf[2 * q + 1], acc[2 * q + 1]);
+                    }
+                }
+            }
+            unsigned hi4[4], lo4[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float x0 = acc[2 * q], x1 = acc[2 * q + 1];
+                if (p.bias) {
+                    x0 += p.bias[c8 * 8 + 2 * q];
+                    x1 += p.bias[c8 * 8 + 2 * q + 1];
+                }
+                x0 = apply_act(x0, p.act);
+                x1 = apply_act(x1, p.act);
+                bf16_bits h0 = f32_to_bf16_bits(x0), h1 = f32_to_bf16_bits(x1);
+                bf16_bits l0 = f32_to_bf16_bits(x0 - bf16_bits_to_f32(h0));
+                bf16_bits l1 = f32_to_bf16_bits(x1 - bf16_bits_to_f32(h1));
+                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
+                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+            }
+            size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
+            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+        }
+        ++iter;
+        if (dynamic) __syncthreads();
+    }
+    if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+cudaError_t dwconv_launch(const DwConvParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    dwconv_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
     return cudaGetLastError();
 }
 

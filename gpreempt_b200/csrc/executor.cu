@@ -44,6 +44,12 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         SplitKParams p = k.splitk;
         p.partial = e->d_partial;
         err = splitk_launch(p, k.grid, b, s);
+    } else if (k.type == KernelType::DwConv) {
+        err = dwconv_launch(k.dw, k.grid, b, s);
+    } else if (k.type == KernelType::LayerNorm) {
+        err = layernorm_launch(k.ln, k.grid, b, s);
+    } else if (k.type == KernelType::Attention) {
+        err = attention_launch(k.attn, k.grid, b, s);
     } else if (k.type == KernelType::Im2col) {
         err = im2col_launch(k.im2col, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {

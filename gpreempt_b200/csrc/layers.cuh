@@ -90,6 +90,15 @@ struct PoolParams {
     int mode;         // 0 = max, 1 = average over valid taps, 2 = copy of the tap (0,0) (subsample)
     int total_tiles;
     int tile_elems;   // output 8-channel vectors per tile
+    // The output may be a channel slice of a wider tensor and the input a channel prefix of one:
+    // `channels` are produced (out.C and in.l.C are only the row strides); of those the first
+    // `in_valid` are read from the input, the rest are written as zeros.
+    int channels;
+    int in_valid;
+    // Optional per-channel affine + activation applied to every input value as it is loaded
+    // (a batch norm that precedes its consumer, as in DenseNet): x -> act(x * scale + shift).
+    const float *scale, *shift;
+    int act;
 };
 
 // Second half of a split-K tensor-core convolution: adds the per-split fp32 partial sums in
@@ -152,6 +161,20 @@ struct AttnParams {
     int total_tiles;
 };
 cudaError_t attention_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+
+// Depthwise k x k convolution + bias + activation over split-plane activations; the filter is
+// stored [kh*kw][C] so that eight channels of one tap are one 32-byte load.
+struct DwConvParams {
+    ActView in;
+    const float *w;      // [k*k][C stored]
+    const float *bias;   // [C] (zero-padded to the stored channel count)
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
+    int k, stride, pad, act;
+    int total_tiles;
+    int tile_elems;      // output 8-channel vectors per tile
+};
+cudaError_t dwconv_launch(const DwConvParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
 enum ConvTile { CONV_TILE_128 = 0, CONV_TILE_64 = 1, CONV_TILE_32 = 2 };
 

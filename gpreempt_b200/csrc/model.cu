@@ -79,7 +79,44 @@ struct GraphBuilder {
             s.dims[3] = W;
         }
         s.bytes = (size_t)N * C * H * W * sizeof(float);
+        // Models with channel counts that are not multiples of 64 keep their activations padded
+        // with zero channels, so every convolution still fits the tensor-core tile shapes.
+        if (kind == Storage::ActSplit && m.pad_channels) s.cs = (C + 63) / 64 * 64;
         return m.add_storage(s);
+    }
+
+    // Depthwise k x k convolution + bias + activation (MobileNet's spatial filter).
+    int dwconv(const std::string &name, int in, int k, int stride, int pad, int act) {
+        const Node &src = m.nodes[in];
+        Node n;
+        n.name = name;
+        n.op = Op::DwConv;
+        n.inputs.push_back(in);
+        n.k = k;
+        n.stride = stride;
+        n.pad = pad;
+        n.act = act;
+        n.N = src.N;
+        n.C = src.C;
+        n.H = (src.H + 2 * pad - k) / stride + 1;
+        n.W = (src.W + 2 * pad - k) / stride + 1;
+        Storage w;
+        w.name = name + ".weight";
+        w.kind = Storage::Weight;
+        w.is_param = true;
+        w.depthwise = true;
+        w.rank = 4;
+        w.dims[0] = src.C;
+        w.dims[1] = 1;
+        w.dims[2] = k;
+        w.dims[3] = k;
+        w.bytes = (size_t)src.C * k * k * sizeof(float);
+        w.fan_in = k * k;
+        n.weight = m.add_storage(w);
+        n.bias = add_vec(name + ".bias", src.C, 0.f, 0.f);
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
     }
 
     int input(const std::string &name, int N, int C, int H, int W) {
@@ -145,6 +182,104 @@ struct GraphBuilder {
         return conv(name, in, cout, src.H, 1, 0, relu);
     }
 
+    // Token ids [N][S] (int64), the "data" input of sequence models.
+    int input_ids(const std::string &name, int N, int S) {
+        Node n;
+        n.name = name;
+        n.op = Op::Input;
+        n.N = N;
+        n.H = 1;
+        n.W = S;
+        n.C = 1;
+        Storage s;
+        s.name = name;
+        s.kind = Storage::InputI64;
+        s.stype = "int64";
+        s.rank = 2;
+        s.dims[0] = N;
+        s.dims[1] = S;
+        s.bytes = (size_t)N * S * sizeof(long long);
+        n.storage = m.add_storage(s);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    int add_vec(const std::string &name, int n, float mean, float std) {
+        Storage s;
+        s.name = name;
+        s.kind = Storage::Vec;
+        s.is_param = true;
+        s.rank = 1;
+        s.dims[0] = n;
+        s.bytes = (size_t)n * sizeof(float);
+        s.init_mean = mean;
+        s.init_std = std;
+        return m.add_storage(s);
+    }
+
+    int add_table(const std::string &name, int rows, int cols, float std) {
+        Storage s;
+        s.name = name;
+        s.kind = Storage::Table;
+        s.is_param = true;
+        s.rank = 2;
+        s.dims[0] = rows;
+        s.dims[1] = cols;
+        s.bytes = (size_t)rows * cols * sizeof(float);
+        s.init_std = std;
+        return m.add_storage(s);
+    }
+
+    // LayerNorm over channels.  `in` is an activation, or the token-id input when `tables` names
+    // the word / position / token-type embedding tables (the sum is formed on the fly).
+    int layer_norm(const std::string &name, int in, int C, const std::string &param_prefix,
+                   const int *tables = nullptr, bool is_head = false) {
+        const Node &src = m.nodes[in];
+        Node n;
+        n.name = name;
+        n.op = Op::LayerNorm;
+        n.inputs.push_back(in);
+        n.N = src.N;
+        n.H = src.H;
+        n.W = src.W;
+        n.C = C;
+        n.weight = add_vec(param_prefix + ".weight", C, 1.0f, 0.02f);
+        n.bias = add_vec(param_prefix + ".bias", C, 0.0f, 0.02f);
+        if (tables)
+            for (int i = 0; i < 3; ++i) n.tables[i] = tables[i];
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, is_head ? Storage::OutputF32 : Storage::ActSplit);
+        m.storages[n.storage].token_major = true;
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    int attention(const std::string &name, int q, int k, int v, int heads) {
+        const Node &src = m.nodes[q];
+        Node n;
+        n.name = name;
+        n.op = Op::Attention;
+        n.inputs = {q, k, v};
+        n.N = src.N;
+        n.H = src.H;
+        n.W = src.W;
+        n.C = src.C;
+        n.heads = heads;
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
+        m.storages[n.storage].token_major = true;
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    // Dense layer of a sequence model: a 1x1 convolution over [N][1][S][C] with N(0, 0.02) weights.
+    int linear(const std::string &name, int in, int cout, int act, int residual = -1) {
+        int id = conv(name + ".out", in, cout, 1, 1, 0, false, residual, name);
+        m.nodes[id].act = act;
+        m.storages[m.nodes[id].storage].token_major = true;
+        m.storages[m.nodes[id].weight].init_std = 0.02f;
+        m.storages[m.nodes[id].bias].init_std = 0.02f;
+        return id;
+    }
+
     int pool(const std::string &name, int in, Op op, int k, int stride, int pad) {
         const Node &src = m.nodes[in];
         Node n;
@@ -207,6 +342,74 @@ static void build_vgg(gpx_model &m, int batch, const int *cfg, int ncfg) {
     m.head_node = x;
 }
 
+// MobileNetV2 (Sandler et al. 2018, the torchvision layer schedule): 3x3 stride-2 stem, 17
+// inverted-residual blocks (1x1 expand + ReLU6, 3x3 depthwise + ReLU6, 1x1 linear projection,
+// identity shortcut when the shape is kept), 1x1 to 1280 channels, global average pool, dense.
+// Batch norm is folded into each convolution's bias.
+static void build_mobilenet_v2(gpx_model &m, int batch) {
+    m.pad_channels = true;
+    GraphBuilder g(m);
+    int x = g.input("data", batch, 3, 224, 224);
+    x = g.conv("features.0", x, 32, 3, 2, 1, false);
+    m.nodes[x].act = ACT_RELU6;
+    static const int cfg[7][4] = {{1, 16, 1, 1}, {6, 24, 2, 2}, {6, 32, 3, 2}, {6, 64, 4, 2},
+                                  {6, 96, 3, 1}, {6, 160, 3, 2}, {6, 320, 1, 1}};
+    int cin = 32, idx = 1;
+    for (int s = 0; s < 7; ++s) {
+        for (int r = 0; r < cfg[s][2]; ++r, ++idx) {
+            const std::string p = "features." + std::to_string(idx);
+            const int t = cfg[s][0], cout = cfg[s][1], stride = r == 0 ? cfg[s][3] : 1;
+            int y = x;
+            if (t != 1) {
+                y = g.conv(p + ".expand", y, cin * t, 1, 1, 0, false);
+                m.nodes[y].act = ACT_RELU6;
+            }
+            y = g.dwconv(p + ".dw", y, 3, stride, 1, ACT_RELU6);
+            const bool shortcut = stride == 1 && cin == cout;
+            x = g.conv(p + ".project", y, cout, 1, 1, 0, false, shortcut ? x : -1);
+            cin = cout;
+        }
+    }
+    x = g.conv("features.18", x, 1280, 1, 1, 0, false);
+    m.nodes[x].act = ACT_RELU6;
+    x = g.pool("avgpool", x, Op::AvgPool, 7, 1, 0);
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "classifier", true);
+    m.head_node = x;
+    // Without batch norm a He-normal draw drives the ReLU6 units into saturation through the
+    // linear bottlenecks; N(0, 1/fan_in) keeps the seeded activations in the unclamped range.
+    for (auto &s : m.storages)
+        if (s.kind == Storage::Weight && s.fan_in > 0) s.init_std = sqrtf(1.0f / (float)s.fan_in);
+}
+
+// BERT encoder (post-LayerNorm): embeddings + LayerNorm, then per layer Q/K/V projections,
+// multi-head attention, output projection + residual + LayerNorm, GELU feed-forward + residual +
+// LayerNorm.  "heads" is the last hidden state [N][S][hidden] in fp32.  Parameter names follow
+// the Hugging Face BertModel state dict.
+static void build_bert(gpx_model &m, int batch, int seq, int layers, int hidden, int heads, int ffn,
+                       int vocab, int max_pos) {
+    GraphBuilder g(m);
+    int ids = g.input_ids("data", batch, seq);
+    int tables[3];
+    tables[0] = g.add_table("embeddings.word_embeddings.weight", vocab, hidden, 0.02f);
+    tables[1] = g.add_table("embeddings.position_embeddings.weight", max_pos, hidden, 0.02f);
+    tables[2] = g.add_table("embeddings.token_type_embeddings.weight", 2, hidden, 0.02f);
+    int x = g.layer_norm("embeddings", ids, hidden, "embeddings.LayerNorm", tables);
+    for (int l = 0; l < layers; ++l) {
+        const std::string p = "encoder.layer." + std::to_string(l);
+        int q = g.linear(p + ".attention.self.query", x, hidden, ACT_NONE);
+        int k = g.linear(p + ".attention.self.key", x, hidden, ACT_NONE);
+        int v = g.linear(p + ".attention.self.value", x, hidden, ACT_NONE);
+        int ctx = g.attention(p + ".attention.context", q, k, v, heads);
+        int a = g.linear(p + ".attention.output.dense", ctx, hidden, ACT_NONE, x);
+        x = g.layer_norm(p + ".attention.output", a, hidden, p + ".attention.output.LayerNorm");
+        int h = g.linear(p + ".intermediate.dense", x, ffn, ACT_GELU);
+        int o = g.linear(p + ".output.dense", h, hidden, ACT_NONE, x);
+        bool last = l == layers - 1;
+        x = g.layer_norm(last ? "heads" : p + ".output", o, hidden, p + ".output.LayerNorm", nullptr, last);
+    }
+    m.head_node = x;
+}
+
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts) {
     int batch = opts.batch > 0 ? opts.batch : 1;
     m.batch = batch;
@@ -232,6 +435,19 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         const int cfg[] = {64, 64, 0, 128, 128, 0, 256, 256, 256, 256, 0, 512, 512, 512, 512, 0,
                            512, 512, 512, 512, 0};
         build_vgg(m, batch, cfg, (int)(sizeof(cfg) / sizeof(int)));
+    } else if (name == "mobilenet_v2") {
+        build_mobilenet_v2(m, batch);
+    } else if (name == "bert_base" || name == "bert") {
+        int seq = opts.seq_len > 0 ? opts.seq_len : 128;
+        if (seq > 512 || seq % 8 != 0) {
+            set_error("bert_base: seq_len %d must be a multiple of 8 and at most 512", seq);
+            return GPX_OUT_OF_RANGE;
+        }
+        build_bert(m, batch, seq, 12, 768, 12, 3072, 30522, 512);
+    } else if (name == "bert_tiny") {
+        // Two-layer miniature with the same structure, for fast tests.
+        int seq = opts.seq_len > 0 ? opts.seq_len : 64;
+        build_bert(m, batch, seq, 2, 128, 2, 256, 1000, 512);
     } else {
         set_error("unknown model '%s'", name.c_str());
         return GPX_NOT_FOUND;
@@ -258,9 +474,15 @@ static inline float host_bf16_to_f32(bf16_bits v) {
 
 // Shape test for the tensor-core convolution: 64-channel granularity on both sides and one of
 // the four geometries it implements as row-shifted GEMMs.
-static bool tensor_core_shape(const Node &n, const Node &src) {
+// Channels as stored: the logical count, or its padding to 64 in models that pad.
+static int stored_c(const gpx_model &m, const Node &n) {
+    const Storage &s = m.storages[n.storage];
+    return s.cs ? s.cs : n.C;
+}
+
+static bool tensor_core_shape(const gpx_model &m, const Node &n, const Node &src) {
     if (n.op != Op::Conv) return false;
-    if (src.C % 64 != 0 || n.C % 64 != 0) return false;
+    if (stored_c(m, src) % 64 != 0 || stored_c(m, n) % 64 != 0) return false;
     if (n.k == 1 && n.pad == 0 && n.stride == 1) return true;
     if (n.k == 1 && n.pad == 0 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
     if (n.k == 3 && n.pad == 1 && n.stride == 1) return true;
@@ -302,15 +524,15 @@ int finalize_model(gpx_model &m) {
         const Node &src = m.nodes[n.inputs[0]];
         const Storage &out = m.storages[n.storage];
         const Storage &in = m.storages[src.storage];
-        n.tensor_core = allow_tc && tensor_core_shape(n, src) && in.kind == Storage::ActSplit &&
+        n.tensor_core = allow_tc && tensor_core_shape(m, n, src) && in.kind == Storage::ActSplit &&
                         out.kind == Storage::ActSplit;
         // The graph head: a dense layer with any number of outputs written as fp32.
         if (allow_tc && out.kind == Storage::OutputF32 && in.kind == Storage::ActSplit && n.k == 1 &&
-            n.stride == 1 && n.pad == 0 && src.H == 1 && src.W == 1 && src.C % 64 == 0)
+            n.stride == 1 && n.pad == 0 && src.H == 1 && src.W == 1 && stored_c(m, src) % 64 == 0)
             n.tensor_core = true;
         // Few input channels (the stem): build the patch matrix, then a 1x1 tensor-core GEMM.
-        if (allow_tc && !n.tensor_core && out.kind == Storage::ActSplit && n.C % 64 == 0 &&
-            src.C % 64 != 0 && n.k * n.k * src.C <= 1024) {
+        if (allow_tc && !n.tensor_core && out.kind == Storage::ActSplit && stored_c(m, n) % 64 == 0 &&
+            in.kind == Storage::InputF32 && n.k * n.k * src.C <= 1024) {
             n.tensor_core = true;
             n.via_im2col = true;
         }
@@ -355,21 +577,28 @@ int finalize_model(gpx_model &m) {
         s.dims[2] = n.H;
         s.dims[3] = n.W;
         s.bytes = (size_t)n.N * s.dims[1] * n.H * n.W * sizeof(float);
+        if (!n.via_im2col && stored_c(m, src) != src.C) s.cs = stored_c(m, src);
         n.sub_storage = m.add_storage(s);
         order.push_back(ACT_PLAIN);
     }
     for (auto &n : m.nodes)
+        if (n.op == Op::DwConv) m.storages[n.weight].cin_pad = stored_c(m, n);
+    for (auto &n : m.nodes)
         if (n.op == Op::Conv && n.tensor_core) {
+            const Node &src = m.nodes[n.inputs[0]];
             Storage &w = m.storages[n.weight];
             w.wants_split = true;
-            w.split_k = (int)((w.dims[1] * w.dims[2] * w.dims[3] + 63) / 64 * 64);
+            // rows of the planes: [tap][stored input channel], zero where the channel is padding
+            w.cin_pad = n.via_im2col ? src.C : stored_c(m, src);
+            w.cout_pad = m.storages[n.storage].kind == Storage::OutputF32 ? n.C : stored_c(m, n);
+            w.split_k = (int)((w.dims[2] * w.dims[3] * w.cin_pad + 63) / 64 * 64);
         }
 
     // 5. allocation: one buffer per storage, zero-filled, no sharing (src/model.cpp:101-113)
     for (size_t i = 0; i < m.storages.size(); ++i) {
         Storage &s = m.storages[i];
         if (s.kind == Storage::ActSplit) {
-            int N = (int)s.dims[0], C = (int)s.dims[1];
+            int N = (int)s.dims[0], C = s.cs ? s.cs : (int)s.dims[1];
             int H = s.rank == 4 ? (int)s.dims[2] : 1, W = s.rank == 4 ? (int)s.dims[3] : 1;
             GPX_REQUIRE(C % 8 == 0, GPX_FAIL, "%s: %d channels, need a multiple of 8", s.name.c_str(), C);
             s.layout = make_layout(N, H, W, C, order[i]);
@@ -380,10 +609,13 @@ int finalize_model(gpx_model &m) {
         } else {
             // Rounded up to 512 bytes so a kernel may read a bias in whole 128-channel tiles.
             size_t alloc = (s.bytes + 511) / 512 * 512;
+            // A depthwise filter is stored [kh*kw][stored channels].
+            if (s.kind == Storage::Weight && s.depthwise)
+                alloc = (size_t)s.dims[2] * s.dims[3] * s.cin_pad * sizeof(float);
             GPX_CUDA(cudaMalloc((void **)&s.dptr, alloc));
             GPX_CUDA(cudaMemset(s.dptr, 0, alloc));
             if (s.kind == Storage::Weight && s.wants_split) {
-                s.plane_elems = (size_t)s.dims[0] * s.split_k;
+                s.plane_elems = (size_t)s.cout_pad * s.split_k;
                 GPX_CUDA(cudaMalloc((void **)&s.hi, 2 * s.plane_elems * sizeof(bf16_bits)));
                 GPX_CUDA(cudaMemset(s.hi, 0, 2 * s.plane_elems * sizeof(bf16_bits)));
                 s.lo = s.hi + s.plane_elems;
@@ -413,6 +645,8 @@ int finalize_model(gpx_model &m) {
             p.stride = stride;
             p.pad = pad;
             p.mode = mode;
+            p.channels = dst.layout.C;
+            p.in_valid = dst.layout.C;
             long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (dst.layout.C / 8);
             // Enough tiles to fill the GPU even when the tensor is small (global average pool).
             long long want_tiles = 4LL * m.sm_count;
@@ -426,6 +660,108 @@ int finalize_model(gpx_model &m) {
             kn.bytes = 4.0 * ((double)total * 8 * (mode == 2 ? 1 : stride * stride) + (double)total * 8);
             m.kernels.push_back(kn);
         };
+        if (n.op == Op::LayerNorm) {
+            Kernel kn;
+            kn.name = n.name;
+            kn.node = (int)ni;
+            kn.type = KernelType::LayerNorm;
+            LayerNormParams &q = kn.ln;
+            const Storage &in = m.storages[src.storage];
+            GPX_REQUIRE(n.C % 8 == 0 && n.C <= 1024, GPX_FAIL, "%s: LayerNorm width %d unsupported",
+                        n.name.c_str(), n.C);
+            if (in.kind == Storage::InputI64) {
+                GPX_REQUIRE(n.tables[0] >= 0, GPX_FAIL, "%s: token input without embedding tables", n.name.c_str());
+                q.ids = reinterpret_cast<const long long *>(in.dptr);
+                q.word = m.storages[n.tables[0]].dptr;
+                q.pos = m.storages[n.tables[1]].dptr;
+                q.type = m.storages[n.tables[2]].dptr;
+            } else {
+                GPX_REQUIRE(in.kind == Storage::ActSplit && in.layout.order == ACT_PLAIN, GPX_FAIL,
+                            "%s: LayerNorm needs a plain activation", n.name.c_str());
+                q.in_hi = in.hi;
+                q.in_lo = in.lo;
+            }
+            q.gamma = m.storages[n.weight].dptr;
+            q.beta = m.storages[n.bias].dptr;
+            if (out.kind == Storage::OutputF32) {
+                q.out_f32 = out.dptr;
+            } else {
+                q.out_hi = out.hi;
+                q.out_lo = out.lo;
+            }
+            q.rows = n.N * n.H * n.W;
+            q.H = n.C;
+            q.S = n.W;
+            q.eps = 1e-12f;
+            q.total_tiles = (q.rows + 7) / 8;
+            kn.total_tiles = q.total_tiles;
+            kn.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
+            kn.flops = 8.0 * q.rows * q.H;
+            kn.bytes = 8.0 * q.rows * q.H;
+            m.kernels.push_back(kn);
+            continue;
+        }
+        if (n.op == Op::Attention) {
+            Kernel kn;
+            kn.name = n.name;
+            kn.node = (int)ni;
+            kn.type = KernelType::Attention;
+            kn.threads = 128;
+            AttnParams &q = kn.attn;
+            const Storage &sq = m.storages[m.nodes[n.inputs[0]].storage];
+            const Storage &sk = m.storages[m.nodes[n.inputs[1]].storage];
+            const Storage &sv = m.storages[m.nodes[n.inputs[2]].storage];
+            GPX_REQUIRE(n.heads > 0 && n.C == n.heads * 64, GPX_FAIL, "%s: head dimension must be 64", n.name.c_str());
+            q.q_hi = sq.hi;
+            q.q_lo = sq.lo;
+            q.k_hi = sk.hi;
+            q.k_lo = sk.lo;
+            q.v_hi = sv.hi;
+            q.v_lo = sv.lo;
+            q.out_hi = out.hi;
+            q.out_lo = out.lo;
+            q.B = n.N;
+            q.S = n.W;
+            q.heads = n.heads;
+            q.ld = n.C;
+            q.scale = 0.125f;  // 1 / sqrt(64)
+            q.total_tiles = n.N * n.heads * ((n.W + 31) / 32);
+            kn.total_tiles = q.total_tiles;
+            kn.grid = (int)std::min<long long>((long long)m.sm_count * 4, q.total_tiles);
+            kn.flops = 4.0 * n.N * n.heads * (double)n.W * n.W * 64;
+            kn.bytes = 4.0 * 4 * (double)n.N * n.W * n.C;
+            m.kernels.push_back(kn);
+            continue;
+        }
+        if (n.op == Op::DwConv) {
+            GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit && out.kind == Storage::ActSplit,
+                        GPX_FAIL, "%s: depthwise convolution needs plane activations", n.name.c_str());
+            Kernel kn;
+            kn.name = n.name;
+            kn.node = (int)ni;
+            kn.type = KernelType::DwConv;
+            DwConvParams &q = kn.dw;
+            q.in = view_of(m, src);
+            q.w = m.storages[n.weight].dptr;
+            q.bias = m.storages[n.bias].dptr;
+            q.out_hi = out.hi;
+            q.out_lo = out.lo;
+            q.out = out.layout;
+            GPX_REQUIRE(q.in.l.C == q.out.C, GPX_FAIL, "%s: channel counts differ", n.name.c_str());
+            q.k = n.k;
+            q.stride = n.stride;
+            q.pad = n.pad;
+            q.act = n.act;
+            long long total = (long long)n.N * n.H * n.W * (q.out.C / 8);
+            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2048, total / (8LL * m.sm_count) / 32 * 32));
+            q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
+            kn.total_tiles = q.total_tiles;
+            kn.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
+            kn.flops = 2.0 * n.N * n.H * n.W * (double)n.k * n.k * n.C;
+            kn.bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)n.N * n.H * n.W * n.C);
+            m.kernels.push_back(kn);
+            continue;
+        }
         if (n.op != Op::Conv) {
             GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit, GPX_FAIL,
                         "%s: pooling the graph input is not supported", n.name.c_str());
@@ -477,7 +813,7 @@ int finalize_model(gpx_model &m) {
         }
         // tensor-core convolution
         const Storage *in = &m.storages[src.storage];
-        int eff_k = n.k, eff_cin = src.C;
+        int eff_k = n.k, eff_cin = stored_c(m, src);
         if (n.via_im2col) {
             const Storage &pm = m.storages[n.sub_storage];
             Kernel ki;
@@ -521,10 +857,11 @@ int finalize_model(gpx_model &m) {
         CgemmParams &p = kn.cgemm;
         const ActLayout &il = in->layout;
         const bool head = out.kind == Storage::OutputF32;
-        int bn = (n.C % 128 == 0 || head) ? 128 : 64;
+        const int cout_st = head ? n.C : stored_c(m, n);  // output channels as stored
+        int bn = (cout_st % 128 == 0 || head) ? 128 : 64;
         {
             // Few output tiles (batch 1, late stages): narrower column tiles expose more CTAs.
-            long long tiles128 = (long long)((in->layout.plane + 127) / 128) * ((n.C + 127) / 128);
+            long long tiles128 = (long long)((in->layout.plane + 127) / 128) * ((cout_st + 127) / 128);
             if (tiles128 * 2 <= m.sm_count) bn = 64;
         }
         kn.tile = bn;
@@ -547,8 +884,8 @@ int finalize_model(gpx_model &m) {
         p.in_ws = il.Ws;
         p.in_off = il.order == ACT_PADDED ? 1 : 0;
         p.tiles_m = (p.m_rows + 127) / 128;
-        p.tiles_n = (n.C + bn - 1) / bn;
-        p.cout_valid = n.C;
+        p.tiles_n = (cout_st + bn - 1) / bn;
+        p.cout_valid = cout_st;
         p.relu = n.act;
         p.bias = m.storages[n.bias].dptr;
         if (n.residual >= 0) {
@@ -567,8 +904,8 @@ int finalize_model(gpx_model &m) {
         }
         GPX_TRY(make_tmap_2d_bf16(&p.a_hi, in->hi, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
         GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
-        GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
-        GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)n.C, (uint64_t)w.split_k, bn, 64));
+        GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));
+        GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));
         // Split K when the output alone cannot fill the GPU: each split gets at least four K
         // blocks, the finishing kernel adds the splits in order.
         const int all_kb = p.taps * p.cin_blocks;
@@ -617,7 +954,7 @@ int finalize_model(gpx_model &m) {
         q.out = p.out;
         q.out_f32 = p.out_f32;
         q.cout_valid = p.cout_valid;
-        q.cout_padded = (n.C + 7) / 8 * 8;
+        q.cout_padded = (p.cout_valid + 7) / 8 * 8;
         q.tile_elems = 256;
         long long total = (long long)q.m_rows * (q.cout_padded / 8);
         q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
@@ -660,12 +997,22 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
                 s.name.c_str(), len, s.bytes);
     (void)m;
     const float *src = (const float *)host;
-    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec) {
+    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec ||
+        s.kind == Storage::InputI64 || s.kind == Storage::Table) {
         GPX_CUDA(cudaMemcpyAsync(s.dptr, host, s.bytes, cudaMemcpyHostToDevice, st));
         return GPX_SUCC;
     }
     if (s.kind == Storage::Weight) {
         const int O = (int)s.dims[0], I = (int)s.dims[1], KH = (int)s.dims[2], KW = (int)s.dims[3];
+        if (s.depthwise) {
+            // [C][1][kh][kw] -> [tap][stored channels], zero where the channel is padding
+            std::vector<float> dw((size_t)KH * KW * s.cin_pad, 0.f);
+            for (int c = 0; c < O; ++c)
+                for (int t = 0; t < KH * KW; ++t) dw[(size_t)t * s.cin_pad + c] = src[(size_t)c * KH * KW + t];
+            GPX_CUDA(cudaMemcpyAsync(s.dptr, dw.data(), dw.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+            GPX_CUDA(cudaStreamSynchronize(st));
+            return GPX_SUCC;
+        }
         std::vector<float> tmp(s.bytes / sizeof(float));
         oihw_to_khwc_o(src, tmp.data(), O, I, KH, KW);
         GPX_CUDA(cudaMemcpyAsync(s.dptr, tmp.data(), s.bytes, cudaMemcpyHostToDevice, st));
@@ -680,7 +1027,7 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
                         for (int i = 0; i < I; ++i) {
                             float v = src[(((size_t)o * I + i) * KH + h) * KW + w];
                             bf16_bits hi = host_f32_to_bf16(v);
-                            size_t off = (size_t)o * K + ((size_t)h * KW + w) * I + i;
+                            size_t off = (size_t)o * K + ((size_t)h * KW + w) * s.cin_pad + i;
                             planes[off] = hi;
                             planes[s.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
                         }
@@ -693,11 +1040,19 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
     // ActSplit: NCHW fp32 -> hi/lo planes in the storage's row order (borders stay zero)
     const ActLayout &l = s.layout;
     std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
+    if (s.token_major) {
+        const size_t total = (size_t)l.N * l.W * l.C;
+        for (size_t i = 0; i < total; ++i) {
+            bf16_bits hi = host_f32_to_bf16(src[i]);
+            planes[i] = hi;
+            planes[s.plane_elems + i] = host_f32_to_bf16(src[i] - host_bf16_to_f32(hi));
+        }
+    } else
     for (int n = 0; n < l.N; ++n)
-        for (int c = 0; c < l.C; ++c)
+        for (int c = 0; c < (int)s.dims[1]; ++c)  // logical channels; stored padding stays zero
             for (int h = 0; h < l.H; ++h)
                 for (int w = 0; w < l.W; ++w) {
-                    float v = src[(((size_t)n * l.C + c) * l.H + h) * l.W + w];
+                    float v = src[(((size_t)n * s.dims[1] + c) * l.H + h) * l.W + w];
                     bf16_bits hi = host_f32_to_bf16(v);
                     size_t off = (size_t)layout_row(l, n, h, w) * l.C + c;
                     planes[off] = hi;
@@ -715,11 +1070,21 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
                 s.name.c_str(), len, s.bytes);
     (void)m;
     float *dst = (float *)host;
-    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec) {
+    if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec ||
+        s.kind == Storage::InputI64 || s.kind == Storage::Table) {
         GPX_CUDA(cudaMemcpyAsync(host, s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
         return GPX_SUCC;
     }
     if (s.kind == Storage::Weight) {
+        if (s.depthwise) {
+            const int C = (int)s.dims[0], T = (int)(s.dims[2] * s.dims[3]);
+            std::vector<float> dw((size_t)T * s.cin_pad);
+            GPX_CUDA(cudaMemcpyAsync(dw.data(), s.dptr, dw.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
+            GPX_CUDA(cudaStreamSynchronize(st));
+            for (int c = 0; c < C; ++c)
+                for (int t = 0; t < T; ++t) dst[(size_t)c * T + t] = dw[(size_t)t * s.cin_pad + c];
+            return GPX_SUCC;
+        }
         std::vector<float> tmp(s.bytes / sizeof(float));
         GPX_CUDA(cudaMemcpyAsync(tmp.data(), s.dptr, s.bytes, cudaMemcpyDeviceToHost, st));
         GPX_CUDA(cudaStreamSynchronize(st));
@@ -731,12 +1096,19 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
     GPX_CUDA(cudaMemcpyAsync(planes.data(), s.hi, planes.size() * sizeof(bf16_bits),
                              cudaMemcpyDeviceToHost, st));
     GPX_CUDA(cudaStreamSynchronize(st));
+    if (s.token_major) {
+        // [N][S][C]: the stored rows in order
+        const size_t total = (size_t)l.N * l.W * l.C;
+        for (size_t i = 0; i < total; ++i)
+            dst[i] = host_bf16_to_f32(planes[i]) + host_bf16_to_f32(planes[s.plane_elems + i]);
+        return GPX_SUCC;
+    }
     for (int n = 0; n < l.N; ++n)
         for (int h = 0; h < l.H; ++h)
             for (int w = 0; w < l.W; ++w) {
                 size_t row = (size_t)layout_row(l, n, h, w) * l.C;
-                for (int c = 0; c < l.C; ++c)
-                    dst[(((size_t)n * l.C + c) * l.H + h) * l.W + w] =
+                for (int c = 0; c < (int)s.dims[1]; ++c)
+                    dst[(((size_t)n * s.dims[1] + c) * l.H + h) * l.W + w] =
                         host_bf16_to_f32(planes[row + c]) + host_bf16_to_f32(planes[s.plane_elems + row + c]);
             }
     return GPX_SUCC;
@@ -846,6 +1218,15 @@ int gpx_model_shape(gpx_model *m, const char *name, int64_t dims[4], int *rank) 
         return GPX_NOT_FOUND;
     }
     const Storage &s = m->storages[i];
+    if (s.token_major) {
+        // sequence activations are reported as [N][S][C]
+        *rank = 3;
+        dims[0] = s.dims[0];
+        dims[1] = s.dims[3];
+        dims[2] = s.dims[1];
+        dims[3] = 1;
+        return GPX_SUCC;
+    }
     *rank = s.rank;
     for (int d = 0; d < 4; ++d) dims[d] = d < s.rank ? s.dims[d] : 1;
     return GPX_SUCC;
@@ -859,7 +1240,9 @@ int gpx_model_init_random(gpx_model *m, uint64_t seed) {
         if (!s.is_param) continue;
         size_t n = s.bytes / sizeof(float);
         tmp.resize(n);
-        if (s.kind == Storage::Weight)
+        if (s.init_std > 0.f)
+            normal_fill(tmp.data(), n, seed, stream, s.init_mean, s.init_std);
+        else if (s.kind == Storage::Weight)
             normal_fill(tmp.data(), n, seed, stream, 0.f, std::sqrt(2.0f / (float)s.fan_in));
         else
             normal_fill(tmp.data(), n, seed, stream, 0.f, 0.01f);
@@ -1011,9 +1394,11 @@ int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
         jn.set("op", "tvm_op");
         jn.set("name", n.name);
         Json attrs = Json::object();
-        const char *fn = n.op == Op::Conv      ? "gpx_conv2d"
-                         : n.op == Op::MaxPool ? "gpx_max_pool2d"
-                                               : "gpx_avg_pool2d";
+        const char *fn = n.op == Op::Conv        ? "gpx_conv2d"
+                         : n.op == Op::MaxPool   ? "gpx_max_pool2d"
+                         : n.op == Op::AvgPool   ? "gpx_avg_pool2d"
+                         : n.op == Op::LayerNorm ? "gpx_layer_norm"
+                                                 : "gpx_attention";
         attrs.set("func_name", fn);
         attrs.set("flatten_data", "0");
         attrs.set("num_outputs", "1");

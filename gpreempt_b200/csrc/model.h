@@ -19,6 +19,8 @@ struct Storage {
         InputF32,  // graph input, fp32 NCHW on the device as given by the client
         OutputF32, // graph output, fp32 [N][C]
         ActSplit,  // intermediate activation: hi/lo bf16 planes in the row order of `layout`
+        InputI64,  // graph input of token ids, int64 [N][S]
+        Table,     // fp32 parameter matrix used as is (embedding tables)
         Weight,    // canonical OIHW fp32; device copies: fp32 [kh][kw][Cin][Cout] and, for the
                    // tensor-core kernel, hi/lo bf16 planes [Cout][kh*kw*Cin]
         Vec        // bias
@@ -39,9 +41,14 @@ struct Storage {
     bool wants_split = false;        // Weight: a tensor-core kernel consumes it
     int split_k = 0;                 // Weight: row length of the split planes (K padded to 64)
     int fan_in = 0;
+    int cs = 0;                      // ActSplit: stored channels (logical channels padded to 64), 0 = dims[1]
+    int cin_pad = 0, cout_pad = 0;   // Weight: padded channel counts of the tensor-core planes
+    bool depthwise = false;          // Weight: [C][1][kh][kw] filter of a depthwise convolution
+    float init_mean = 0.f, init_std = 0.f;  // seeded initialiser; std 0 = He-normal / 0.01 default
+    bool token_major = false;        // activations of sequence models: canonical [N][S][C]
 };
 
-enum class Op { Input, Conv, MaxPool, AvgPool };
+enum class Op { Input, Conv, MaxPool, AvgPool, LayerNorm, Attention, DwConv };
 
 struct Node {
     std::string name;
@@ -57,9 +64,12 @@ struct Node {
     int sub_storage = -1;      // stride-2 1x1: compact copy of the sub-sampled input;
                                // few-channel input: patch matrix
     bool via_im2col = false;
+    int tables[3] = {-1, -1, -1};  // LayerNorm fed by embeddings: word, position, token-type tables
+    int heads = 0;                 // Attention
+    int Cs = 0;                    // stored output channels (C padded to 64 when the model pads)
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv };
 
 struct Kernel {
     std::string name;
@@ -70,6 +80,9 @@ struct Kernel {
     CgemmParams cgemm{};
     Im2colParams im2col{};
     SplitKParams splitk{};
+    LayerNormParams ln{};
+    AttnParams attn{};
+    DwConvParams dw{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     int grid = 1;
     int threads = 256;
@@ -94,6 +107,7 @@ struct gpx_model {
     int head_node = -1;
     int max_cgemm_grid = 0;
     size_t max_partial_floats = 0;  // split-K workspace an executor must provide
+    bool pad_channels = false;      // store activations with channels padded to a multiple of 64
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;

@@ -161,6 +161,7 @@ struct Tenant {
     std::string id, name, model_name;
     int priority = 1;
     int batch = 1;
+    int seq_len = 0;
     bool use_graph = false;
     uint64_t preprocess_us = 0;
     int gpu = 0;
@@ -612,6 +613,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         t->model_name = jc["model_name"].as_string();
         t->priority = (int)jc["priority"].as_int(1);
         t->batch = (int)jc["batch_size"].as_int(1);
+        t->seq_len = (int)jc["seq_len"].as_int(0);
         t->use_graph = jc["use_cuda_graph"].as_bool(false);
         t->preprocess_us = (uint64_t)jc["preprocess_time"].as_int(0);
         t->gpu = jc.has("gpu") ? (int)jc["gpu"].as_int() : default_gpu;
@@ -642,6 +644,7 @@ static int init_tenant(Suite &s, Tenant *t) {
     GPX_TRY(gpx_init(t->gpu));
     gpx_model_opts o{};
     o.batch = t->batch;
+    o.seq_len = t->seq_len;
     GPX_TRY(gpx_model_open(t->model_name.c_str(), &o, &t->model));
     GPX_TRY(gpx_model_init_random(t->model, 1));
     bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);
@@ -661,7 +664,17 @@ static int init_tenant(Suite &s, Tenant *t) {
     t->out_bytes = out.bytes;
     GPX_CUDA(cudaHostAlloc(&t->h_in, t->in_bytes, cudaHostAllocPortable));
     GPX_CUDA(cudaHostAlloc(&t->h_out, t->out_bytes, cudaHostAllocPortable));
-    normal_fill((float *)t->h_in, t->in_bytes / sizeof(float), t->seed, 0, 0.f, 1.f);
+    if (in.kind == Storage::InputI64) {
+        // token ids uniform over the vocabulary (rows of the word-embedding table)
+        int wi = t->model->find("embeddings.word_embeddings.weight");
+        double vocab = wi >= 0 ? (double)t->model->storages[wi].dims[0] : 1000.0;
+        size_t n = t->in_bytes / sizeof(long long);
+        std::vector<float> u(n);
+        uniform_fill(u.data(), n, t->seed, 0, 0.f, 1.f);
+        for (size_t i = 0; i < n; ++i) ((long long *)t->h_in)[i] = (long long)(u[i] * vocab);
+    } else {
+        normal_fill((float *)t->h_in, t->in_bytes / sizeof(float), t->seed, 0, 0.f, 1.f);
+    }
     GPX_CUDA(cudaMemcpy(in.dptr, t->h_in, t->in_bytes, cudaMemcpyHostToDevice));
     if (t->use_graph) GPX_TRY(gpx_exec_capture_graph(t->exec, t->stream));
     return GPX_SUCC;

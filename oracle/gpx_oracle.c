@@ -75,6 +75,7 @@ void orc_conv2d_nchw(const float *in, const float *w, const float *bias, const f
                     double v = acc[i] + b;
                     if (r) v += (double)r[i];
                     if (relu && v < 0.0) v = 0.0;
+                    if (relu == 3 && v > 6.0) v = 6.0; /* ReLU6 */
                     o[i] = (float)v;
                 }
             }
@@ -128,11 +129,46 @@ void orc_conv2d_nchw_fast(const float *in, const float *w, const float *bias, co
                     float v = acc[i];
                     if (r) v += r[i];
                     if (relu && v < 0.0f) v = 0.0f;
+                    if (relu == 3 && v > 6.0f) v = 6.0f;
                     o[i] = v;
                 }
             }
         }
         free(acc);
+    }
+}
+
+/* Depthwise convolution (groups == channels) + bias + activation (0 none, 1 ReLU, 3 ReLU6), the
+ * building block of MobileNetV2.  in [N][C][H][W], w [C][1][kh][kw]; fp64 accumulation. */
+void orc_dwconv2d_nchw(const float *in, const float *w, const float *bias, float *out, int N, int C,
+                       int H, int W, int kh, int kw, int stride, int pad, int relu) {
+    const int Ho = (H + 2 * pad - kh) / stride + 1;
+    const int Wo = (W + 2 * pad - kw) / stride + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n) {
+        for (int c = 0; c < C; ++c) {
+            const float *plane = in + ((size_t)n * C + c) * H * W;
+            const float *f = w + (size_t)c * kh * kw;
+            float *o = out + ((size_t)n * C + c) * Ho * Wo;
+            for (int ho = 0; ho < Ho; ++ho) {
+                for (int wo = 0; wo < Wo; ++wo) {
+                    double acc = 0.0;
+                    for (int fh = 0; fh < kh; ++fh) {
+                        int hi = ho * stride - pad + fh;
+                        if (hi < 0 || hi >= H) continue;
+                        for (int fw = 0; fw < kw; ++fw) {
+                            int wi = wo * stride - pad + fw;
+                            if (wi < 0 || wi >= W) continue;
+                            acc += (double)f[fh * kw + fw] * (double)plane[(size_t)hi * W + wi];
+                        }
+                    }
+                    if (bias) acc += (double)bias[c];
+                    if (relu && acc < 0.0) acc = 0.0;
+                    if (relu == 3 && acc > 6.0) acc = 6.0;
+                    o[(size_t)ho * Wo + wo] = (float)acc;
+                }
+            }
+        }
     }
 }
 

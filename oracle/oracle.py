@@ -46,6 +46,7 @@ def lib() -> ctypes.CDLL:
         _lib.orc_conv2d_nchw.argtypes = conv_args
         _lib.orc_conv2d_nchw_fast.argtypes = conv_args
         _lib.orc_pool2d_nchw.argtypes = [_f32p, _f32p] + [ctypes.c_int] * 8
+        _lib.orc_dwconv2d_nchw.argtypes = [_f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 9
         _lib.orc_axpy_f32.argtypes = [ctypes.c_float, _f32p, _f32p, ctypes.c_size_t]
         _lib.orc_f32_to_bf16.argtypes = [_f32p, _u16p, ctypes.c_size_t]
         _lib.orc_bf16_to_f32.argtypes = [_u16p, _f32p, ctypes.c_size_t]
@@ -69,7 +70,8 @@ def _c(a, dtype=np.float32) -> np.ndarray:
 # ---- layer functions ---------------------------------------------------------------------------
 
 def conv2d(x, w, bias=None, stride=1, pad=0, relu=False, residual=None, fast=False):
-    """Fused conv2d + bias + residual + ReLU.  x NCHW, w OIHW."""
+    """Fused conv2d + bias + residual + activation.  x NCHW, w OIHW; `relu` is False/True or
+    the string "relu6"."""
     x, w = _c(x), _c(w)
     n, cin, h, wd = x.shape
     cout, cin2, kh, kw = w.shape
@@ -83,7 +85,22 @@ def conv2d(x, w, bias=None, stride=1, pad=0, relu=False, residual=None, fast=Fal
         assert r.shape == out.shape
     fn = lib().orc_conv2d_nchw_fast if fast else lib().orc_conv2d_nchw
     fn(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(r, _f32p), _p(out, _f32p), n, cin, h, wd,
-       cout, kh, kw, stride, pad, int(relu))
+       cout, kh, kw, stride, pad, 3 if relu == "relu6" else int(bool(relu)))
+    return out
+
+
+def dwconv2d(x, w, bias=None, stride=1, pad=0, relu=False):
+    """Depthwise conv2d + bias + activation.  x NCHW, w [C][1][kh][kw]."""
+    x, w = _c(x), _c(w)
+    n, c, h, wd = x.shape
+    assert w.shape[0] == c and w.shape[1] == 1
+    kh, kw = w.shape[2], w.shape[3]
+    ho = (h + 2 * pad - kh) // stride + 1
+    wo = (wd + 2 * pad - kw) // stride + 1
+    out = np.empty((n, c, ho, wo), np.float32)
+    b = _c(bias) if bias is not None else None
+    lib().orc_dwconv2d_nchw(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(out, _f32p), n, c, h, wd,
+                            kh, kw, stride, pad, 3 if relu == "relu6" else int(bool(relu)))
     return out
 
 
@@ -232,7 +249,69 @@ def vgg_forward(params, data, cfg="vgg16", fast=False, taps=None):
     return out
 
 
+# MobileNetV2 (Sandler et al. 2018): (expansion t, output channels c, repeats n, first stride s).
+MOBILENET_V2_CFG = ((1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1),
+                    (6, 160, 3, 2), (6, 320, 1, 1))
+
+
+def mobilenet_v2_param_shapes(num_classes=1000):
+    s = {"features.0.weight": (32, 3, 3, 3), "features.0.bias": (32,)}
+    cin, idx = 32, 1
+    for t, c, n, _ in MOBILENET_V2_CFG:
+        for _r in range(n):
+            p = f"features.{idx}"
+            hid = cin * t
+            if t != 1:
+                s[f"{p}.expand.weight"] = (hid, cin, 1, 1)
+                s[f"{p}.expand.bias"] = (hid,)
+            s[f"{p}.dw.weight"] = (hid, 1, 3, 3)
+            s[f"{p}.dw.bias"] = (hid,)
+            s[f"{p}.project.weight"] = (c, hid, 1, 1)
+            s[f"{p}.project.bias"] = (c,)
+            cin = c
+            idx += 1
+    s["features.18.weight"] = (1280, cin, 1, 1)
+    s["features.18.bias"] = (1280,)
+    s["classifier.weight"] = (num_classes, 1280, 1, 1)
+    s["classifier.bias"] = (num_classes,)
+    return s
+
+
+def mobilenet_v2_forward(params, data, fast=False, taps=None):
+    """Inverted-residual network with batch norm folded into the biases: 1x1 expand + ReLU6, 3x3
+    depthwise + ReLU6, linear 1x1 projection, identity shortcut when stride 1 keeps the shape."""
+    def keep(name, v):
+        if taps is not None:
+            taps[name] = v
+        return v
+
+    P = params
+    x = keep("features.0", conv2d(data, P["features.0.weight"], P["features.0.bias"], 2, 1, "relu6",
+                                  fast=fast))
+    cin, idx = 32, 1
+    for t, c, n, s0 in MOBILENET_V2_CFG:
+        for r in range(n):
+            p = f"features.{idx}"
+            stride = s0 if r == 0 else 1
+            y = x
+            if t != 1:
+                y = keep(f"{p}.expand", conv2d(y, P[f"{p}.expand.weight"], P[f"{p}.expand.bias"], 1, 0,
+                                               "relu6", fast=fast))
+            y = keep(f"{p}.dw", dwconv2d(y, P[f"{p}.dw.weight"], P[f"{p}.dw.bias"], stride, 1, "relu6"))
+            res = x if (stride == 1 and cin == c) else None
+            x = keep(f"{p}.project", conv2d(y, P[f"{p}.project.weight"], P[f"{p}.project.bias"], 1, 0,
+                                            False, residual=res, fast=fast))
+            cin = c
+            idx += 1
+    x = keep("features.18", conv2d(x, P["features.18.weight"], P["features.18.bias"], 1, 0, "relu6",
+                                   fast=fast))
+    x = keep("avgpool", pool2d(x, x.shape[2], 1, 0, "avg"))
+    x = conv2d(x, P["classifier.weight"], P["classifier.bias"], 1, 0, False, fast=fast)
+    return keep("heads", x.reshape(x.shape[0], -1))
+
+
 MODELS = {
+    "mobilenet_v2": lambda p, d, **kw: mobilenet_v2_forward(p, d, **kw),
     "resnet50": lambda p, d, **kw: resnet_forward(p, d, (3, 4, 6, 3), **kw),
     "resnet152": lambda p, d, **kw: resnet_forward(p, d, (3, 8, 36, 3), **kw),
     "resnet_tiny": lambda p, d, **kw: resnet_forward(p, d, (1, 1, 1, 1), **kw),
@@ -359,7 +438,7 @@ def bert_forward(params, ids, layers=12, heads=12, taps=None):
         h = _gelu(x @ P[f"{p}.intermediate.dense.weight"].T + P[f"{p}.intermediate.dense.bias"])
         o = h @ P[f"{p}.output.dense.weight"].T + P[f"{p}.output.dense.bias"]
         x = _layer_norm(o + x, P[f"{p}.output.LayerNorm.weight"], P[f"{p}.output.LayerNorm.bias"])
-        if taps is not None:
+        if taps is not None and i != layers - 1:
             taps[f"{p}.output"] = x.astype(np.float32)
     out = x.astype(np.float32)
     if taps is not None:

@@ -19,7 +19,7 @@ def _data(gpx, batch, seed=0):
 
 
 @pytest.mark.parametrize("model,batch", [("resnet_tiny", 1), ("resnet_tiny", 3), ("resnet50", 1),
-                                         ("resnet50", 2)])
+                                         ("resnet50", 2), ("mobilenet_v2", 1), ("mobilenet_v2", 3)])
 def test_forward_matches_oracle_layer_by_layer(gpx, oracle, model, batch):
     ex = gpx.BaseExecutor()
     ex.init(model, batch=batch, seed=1)
@@ -135,7 +135,7 @@ def _all_activations(ex):
 
 
 @pytest.mark.parametrize("model,batch,transport", [("resnet_tiny", 8, 0), ("resnet50", 8, 0),
-                                                   ("resnet50", 8, 1)])
+                                                   ("resnet50", 8, 1), ("mobilenet_v2", 8, 0)])
 def test_model_preempt_resume_bit_identical(gpx, model, batch, transport):
     """Asserted form of src/tests/test-dnn-blp.cpp:36-43: execute, raise the word, drain, clear,
     resume; every activation equals the uninterrupted run bit for bit."""
@@ -299,3 +299,84 @@ def test_batch_one_uses_split_k_and_matches_oracle(gpx, oracle):
     assert np.array_equal(a, ex.get_output("heads")), "split-K result changed between runs"
     assert _rel(a, oracle.forward("resnet50", ex.model.params(), data)) <= RTOL_FP32
     ex.clear()
+
+
+def _ids(batch, seq, vocab, seed=6):
+    return np.random.default_rng(seed).integers(0, vocab, (batch, seq)).astype(np.int64)
+
+
+@pytest.mark.parametrize("model,batch,seq,layers,heads,vocab", [("bert_tiny", 2, 64, 2, 2, 1000),
+                                                                ("bert_tiny", 1, 40, 2, 2, 1000),
+                                                                ("bert_base", 1, 128, 12, 12, 30522)])
+def test_bert_matches_oracle(gpx, oracle, model, batch, seq, layers, heads, vocab):
+    """Token ids U[0, vocab), weights N(0, 0.02): last hidden state against the float64 oracle,
+    layer by layer, with the fp32 bound."""
+    ex = gpx.BaseExecutor()
+    ex.init(model, batch=batch, seed=7, seq_len=seq)
+    ids = _ids(batch, seq, vocab)
+    ex.set_input("data", ids)
+    ex.execute()
+    assert ex.error() == (0, 0)
+    heads_out = ex.get_output("heads")
+    assert heads_out.shape == (batch, seq, ex.model.shape("heads")[2])
+    params = {k: v.reshape(v.shape[0], -1) if v.ndim == 4 else v for k, v in ex.model.params().items()}
+    taps = {}
+    want = oracle.bert_forward(params, ids, layers=layers, heads=heads, taps=taps)
+    for name, ref in taps.items():
+        if name == "heads":
+            continue
+        got = ex.model.get(name).reshape(ref.shape)
+        assert _rel(got, ref) <= RTOL_FP32, f"{model} node {name}"
+    assert _rel(heads_out, want) <= RTOL_FP32
+    ex.clear()
+
+
+def test_bert_preempt_resume_bit_identical(gpx):
+    base = gpx.BaseExecutor()
+    base.init("bert_tiny", batch=8, seed=7, seq_len=128)
+    ids = _ids(8, 128, 1000)
+    base.set_input("data", ids)
+    base.execute()
+    want = base.get_output("heads")
+    word = gpx.PreemptWord(1)
+    ex = gpx.BLPExecutor()
+    ex.init("bert_tiny", batch=8, seq_len=128)
+    for k, v in base.model.params().items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.set_input("data", ids)
+    s = gpx.Stream(1)
+    ex.execute(s)
+    assert ex.getStopPoint(s) == -1
+    assert np.array_equal(ex.get_output("heads"), want)
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    rng = np.random.default_rng(3)
+    stops = 0
+    for trial in range(8):
+        word.clear()
+        time.sleep(0.001)
+        ex.execute(s)
+        rounds = 0
+        while True:
+            if rounds < 3:
+                delay = float(rng.uniform(0, run_us / 2))
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < delay:
+                    pass
+                word.raise_()
+            s.sync()
+            word.clear()
+            time.sleep(0.0005)
+            stop = ex.resume(s)
+            rounds += 1
+            if stop == -1:
+                break
+            stops += 1
+            assert rounds < 60
+        s.sync()
+        assert np.array_equal(ex.get_output("heads"), want), f"trial {trial}"
+    assert stops > 0
+    base.clear(), ex.clear(), word.destroy(), s.destroy()

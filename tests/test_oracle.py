@@ -165,6 +165,46 @@ def test_vgg16_restatement_matches_torchvision_topology(oracle):
     assert _rel(got, ref) < 5e-6
 
 
+def test_mobilenet_v2_restatement_matches_torchvision_topology(oracle):
+    import torchvision
+
+    rng = np.random.default_rng(5)
+    params = {}
+    for name, shape in oracle.mobilenet_v2_param_shapes().items():
+        if name.endswith("weight"):
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    net = torchvision.models.mobilenet_v2(weights=None).double().eval()
+
+    def put(seq, conv_idx, prefix):
+        # seq[conv_idx] is the convolution, seq[conv_idx + 1] its batch norm
+        seq[conv_idx].weight.data = torch.from_numpy(params[prefix + ".weight"]).double()
+        seq[conv_idx + 1] = _Bias(torch.from_numpy(params[prefix + ".bias"]).double())
+
+    put(net.features[0], 0, "features.0")
+    for idx in range(1, 18):
+        block = net.features[idx].conv
+        p = f"features.{idx}"
+        if len(block) == 4:
+            put(block[0], 0, p + ".expand")
+            put(block[1], 0, p + ".dw")
+            put(block, 2, p + ".project")
+        else:
+            put(block[0], 0, p + ".dw")
+            put(block, 1, p + ".project")
+    put(net.features[18], 0, "features.18")
+    net.classifier[1].weight.data = torch.from_numpy(params["classifier.weight"].reshape(1000, 1280)).double()
+    net.classifier[1].bias.data = torch.from_numpy(params["classifier.bias"]).double()
+    data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
+    with torch.no_grad():
+        ref = net(torch.from_numpy(data).double()).numpy()
+    got = oracle.forward("mobilenet_v2", params, data)
+    assert got.shape == (1, 1000)
+    assert _rel(got, ref) < 5e-6
+
+
 def test_blp_protocol_runs_every_tile_exactly_once_across_resumes(oracle):
     rng = np.random.default_rng(9)
     for trial in range(50):
