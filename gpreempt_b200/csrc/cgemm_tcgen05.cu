@@ -384,6 +384,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 }
                 unsigned char *stg = epi_stage + (size_t)(warp - 2) * kCStageRowBytes * 32;
                 const int seg = lane & 3;
+                const int col_lim = p.cout_valid - n_blk * BN;
                 // One plane of a 32-row x 32-column piece: global -> shared with full 64-byte row
                 // pieces per four lanes, then every lane picks up its own row.
                 auto load_plane = [&](const bf16_bits *base, int c, uint4 (&q)[4]) {
@@ -415,7 +416,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     for (int i = 0; i < 4; ++i) {
                         const int r = (lane >> 2) + 8 * i;
                         uint4 q = *reinterpret_cast<const uint4 *>(stg + r * kCStageRowBytes + seg * 16);
-                        if (row_out[i] != ~0ull)
+                        // The output may be a channel slice: nothing is stored past cout_valid.
+                        if (row_out[i] != ~0ull && c + seg * 8 < col_lim)
                             *reinterpret_cast<uint4 *>(base + row_out[i] + c + seg * 8) = q;
                     }
                     __syncwarp();

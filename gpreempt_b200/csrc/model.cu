@@ -280,7 +280,10 @@ struct GraphBuilder {
         return id;
     }
 
-    int pool(const std::string &name, int in, Op op, int k, int stride, int pad) {
+    // Pooling; with `norm_prefix` the input first goes through a per-channel affine + ReLU (a
+    // batch norm that sits between the producer and the pooling, as DenseNet's last one does).
+    int pool(const std::string &name, int in, Op op, int k, int stride, int pad,
+             const std::string &norm_prefix = "") {
         const Node &src = m.nodes[in];
         Node n;
         n.name = name;
@@ -293,6 +296,54 @@ struct GraphBuilder {
         n.C = src.C;
         n.H = (src.H + 2 * pad - k) / stride + 1;
         n.W = (src.W + 2 * pad - k) / stride + 1;
+        if (!norm_prefix.empty()) {
+            n.scale = add_vec(norm_prefix + ".weight", src.C, 1.0f, 0.02f);
+            n.shift = add_vec(norm_prefix + ".bias", src.C, 0.0f, 0.02f);
+            n.act = ACT_RELU;
+        }
+        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    // A tensor that other nodes fill slice by slice: concatenation along channels by placement.
+    int buffer(const std::string &name, int N, int C, int H, int W) {
+        Node n;
+        n.name = name;
+        n.op = Op::Buffer;
+        n.N = N;
+        n.C = C;
+        n.H = H;
+        n.W = W;
+        n.storage = add_act(name, N, C, H, W, Storage::ActSplit);
+        m.nodes.push_back(n);
+        return (int)m.nodes.size() - 1;
+    }
+
+    // Makes the output of node `id` the channels [off, off + C) of the buffer node `buf`.
+    void place(int id, int buf, int off) {
+        Storage &s = m.storages[m.nodes[id].storage];
+        s.parent = m.nodes[buf].storage;
+        s.ch_off = off;
+        s.cs = 0;
+    }
+
+    // act(x * scale + shift) over the first `in_c` channels of `in` (a batch norm ahead of its
+    // convolution, folded to an affine map), written as a tensor of its own.
+    int affine(const std::string &name, int in, int in_c, int act) {
+        const Node &src = m.nodes[in];
+        Node n;
+        n.name = name;
+        n.op = Op::Affine;
+        n.inputs.push_back(in);
+        n.in_c = in_c;
+        n.act = act;
+        n.N = src.N;
+        n.C = in_c;
+        n.H = src.H;
+        n.W = src.W;
+        n.scale = add_vec(name + ".weight", in_c, 1.0f, 0.02f);
+        n.shift = add_vec(name + ".bias", in_c, 0.0f, 0.02f);
         n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
         m.nodes.push_back(n);
         return (int)m.nodes.size() - 1;
@@ -381,6 +432,44 @@ static void build_mobilenet_v2(gpx_model &m, int batch) {
         if (s.kind == Storage::Weight && s.fan_in > 0) s.init_std = sqrtf(1.0f / (float)s.fan_in);
 }
 
+// DenseNet (Huang et al. 2017, the torchvision layer schedule and parameter names): 7x7 stem,
+// four dense blocks of {6, 12, 48, 32} layers for DenseNet-201 with growth 32, transitions that
+// halve channels and resolution.  Every dense layer is norm-ReLU-1x1(128)-norm-ReLU-3x3(32); the
+// first norm acts on the running concatenation and stays an affine node of its own, the second
+// is folded into the 1x1 convolution's bias.  A block's concatenation is one buffer that the
+// block's layers write 32-channel slices of.
+static void build_densenet(gpx_model &m, int batch, const int *cfg, int growth, int init_features) {
+    m.pad_channels = true;
+    GraphBuilder g(m);
+    int x = g.input("data", batch, 3, 224, 224);
+    x = g.conv("features.conv0", x, init_features, 7, 2, 3, true);
+    int C = init_features, H = 56;
+    int buf = g.buffer("features.denseblock1", batch, C + growth * cfg[0], H, H);
+    g.place(g.pool("features.pool0", x, Op::MaxPool, 3, 2, 1), buf, 0);
+    for (int b = 0; b < 4; ++b) {
+        for (int l = 0; l < cfg[b]; ++l) {
+            const std::string p = "features.denseblock" + std::to_string(b + 1) + ".denselayer" + std::to_string(l + 1);
+            const int cin = C + growth * l;
+            int a = g.affine(p + ".norm1", buf, cin, ACT_RELU);
+            int y = g.conv(p + ".conv1", a, 4 * growth, 1, 1, 0, true);
+            int z = g.conv(p + ".conv2", y, growth, 3, 1, 1, false);
+            g.place(z, buf, cin);
+        }
+        C += growth * cfg[b];
+        if (b == 3) break;
+        const std::string t = "features.transition" + std::to_string(b + 1);
+        int a = g.affine(t + ".norm", buf, C, ACT_RELU);
+        int y = g.conv(t + ".conv", a, C / 2, 1, 1, 0, false);
+        C /= 2;
+        H /= 2;
+        buf = g.buffer("features.denseblock" + std::to_string(b + 2), batch, C + growth * cfg[b + 1], H, H);
+        g.place(g.pool(t + ".pool", y, Op::AvgPool, 2, 2, 0), buf, 0);
+    }
+    x = g.pool("avgpool", buf, Op::AvgPool, H, 1, 0, "features.norm5");
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "classifier", true);
+    m.head_node = x;
+}
+
 // BERT encoder (post-LayerNorm): embeddings + LayerNorm, then per layer Q/K/V projections,
 // multi-head attention, output projection + residual + LayerNorm, GELU feed-forward + residual +
 // LayerNorm.  "heads" is the last hidden state [N][S][hidden] in fp32.  Parameter names follow
@@ -437,6 +526,13 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         build_vgg(m, batch, cfg, (int)(sizeof(cfg) / sizeof(int)));
     } else if (name == "mobilenet_v2") {
         build_mobilenet_v2(m, batch);
+    } else if (name == "densenet201" || name == "densenet") {
+        const int cfg[4] = {6, 12, 48, 32};
+        build_densenet(m, batch, cfg, 32, 64);
+    } else if (name == "densenet_tiny") {
+        // Same structure with two or three layers per block, for fast tests.
+        const int cfg[4] = {2, 3, 2, 2};
+        build_densenet(m, batch, cfg, 32, 64);
     } else if (name == "bert_base" || name == "bert") {
         int seq = opts.seq_len > 0 ? opts.seq_len : 128;
         if (seq > 512 || seq % 8 != 0) {
@@ -482,7 +578,9 @@ static int stored_c(const gpx_model &m, const Node &n) {
 
 static bool tensor_core_shape(const gpx_model &m, const Node &n, const Node &src) {
     if (n.op != Op::Conv) return false;
-    if (stored_c(m, src) % 64 != 0 || stored_c(m, n) % 64 != 0) return false;
+    // Input channels in whole 64-wide K blocks; output channels in 16-byte vectors (the epilogue
+    // masks the last column tile).
+    if (stored_c(m, src) % 64 != 0 || stored_c(m, n) % 8 != 0) return false;
     if (n.k == 1 && n.pad == 0 && n.stride == 1) return true;
     if (n.k == 1 && n.pad == 0 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
     if (n.k == 3 && n.pad == 1 && n.stride == 1) return true;
@@ -590,13 +688,14 @@ int finalize_model(gpx_model &m) {
             w.wants_split = true;
             // rows of the planes: [tap][stored input channel], zero where the channel is padding
             w.cin_pad = n.via_im2col ? src.C : stored_c(m, src);
-            w.cout_pad = m.storages[n.storage].kind == Storage::OutputF32 ? n.C : stored_c(m, n);
+            w.cout_pad = m.storages[n.storage].kind == Storage::OutputF32 ? n.C : (stored_c(m, n) + 63) / 64 * 64;
             w.split_k = (int)((w.dims[2] * w.dims[3] * w.cin_pad + 63) / 64 * 64);
         }
 
     // 5. allocation: one buffer per storage, zero-filled, no sharing (src/model.cpp:101-113)
     for (size_t i = 0; i < m.storages.size(); ++i) {
         Storage &s = m.storages[i];
+        if (s.kind == Storage::ActSplit && s.parent >= 0) continue;  // a slice: bound below
         if (s.kind == Storage::ActSplit) {
             int N = (int)s.dims[0], C = s.cs ? s.cs : (int)s.dims[1];
             int H = s.rank == 4 ? (int)s.dims[2] : 1, W = s.rank == 4 ? (int)s.dims[3] : 1;
@@ -622,16 +721,28 @@ int finalize_model(gpx_model &m) {
             }
         }
     }
+    for (auto &s : m.storages) {
+        if (s.kind != Storage::ActSplit || s.parent < 0) continue;
+        const Storage &par = m.storages[s.parent];
+        GPX_REQUIRE(par.parent < 0 && par.layout.order == ACT_PLAIN && s.ch_off % 8 == 0 && s.dims[1] % 8 == 0 &&
+                        s.ch_off + s.dims[1] <= par.layout.C,
+                    GPX_FAIL, "%s: bad slice of %s", s.name.c_str(), par.name.c_str());
+        s.layout = par.layout;
+        s.plane_elems = par.plane_elems;
+        s.hi = par.hi + s.ch_off;
+        s.lo = par.lo + s.ch_off;
+    }
     GPX_CUDA(cgemm_prepare(d.device));
 
     // 6. kernel list
     for (size_t ni = 0; ni < m.nodes.size(); ++ni) {
         const Node &n = m.nodes[ni];
-        if (n.op == Op::Input) continue;
+        if (n.op == Op::Input || n.op == Op::Buffer) continue;
         const Node &src = m.nodes[n.inputs[0]];
         const Storage &out = m.storages[n.storage];
         auto add_pool = [&](const std::string &name, const ActView &in, const Storage &dst, int k,
-                            int stride, int pad, int mode) {
+                            int stride, int pad, int mode, int in_valid = -1, int scale = -1,
+                            int shift = -1, int act = 0) {
             Kernel kn;
             kn.name = name;
             kn.node = (int)ni;
@@ -645,9 +756,14 @@ int finalize_model(gpx_model &m) {
             p.stride = stride;
             p.pad = pad;
             p.mode = mode;
-            p.channels = dst.layout.C;
-            p.in_valid = dst.layout.C;
-            long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (dst.layout.C / 8);
+            p.channels = dst.parent >= 0 ? (int)dst.dims[1] : dst.layout.C;
+            p.in_valid = in_valid >= 0 ? in_valid : std::min(p.channels, in.l.C);
+            if (scale >= 0) {
+                p.scale = m.storages[scale].dptr;
+                p.shift = m.storages[shift].dptr;
+                p.act = act;
+            }
+            long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (p.channels / 8);
             // Enough tiles to fill the GPU even when the tensor is small (global average pool).
             long long want_tiles = 4LL * m.sm_count;
             p.tile_elems = (int)std::max<long long>(mode == 1 && k * k >= 16 ? 8 : 64,
@@ -762,10 +878,17 @@ int finalize_model(gpx_model &m) {
             m.kernels.push_back(kn);
             continue;
         }
+        if (n.op == Op::Affine) {
+            GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit && n.in_c % 8 == 0, GPX_FAIL,
+                        "%s: affine needs a plane activation and a channel count in eights", n.name.c_str());
+            add_pool(n.name, view_of(m, src), out, 1, 1, 0, 2, n.in_c, n.scale, n.shift, n.act);
+            continue;
+        }
         if (n.op != Op::Conv) {
             GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit, GPX_FAIL,
                         "%s: pooling the graph input is not supported", n.name.c_str());
-            add_pool(n.name, view_of(m, src), out, n.k, n.stride, n.pad, n.op == Op::MaxPool ? 0 : 1);
+            add_pool(n.name, view_of(m, src), out, n.k, n.stride, n.pad, n.op == Op::MaxPool ? 0 : 1, -1,
+                     n.scale, n.shift, n.act);
             continue;
         }
         const Storage &w = m.storages[n.weight];
@@ -995,7 +1118,6 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
     // Model::set, src/model.cpp:313-321: `len < size` is rejected.
     GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "set %s: %zu bytes given, %zu needed",
                 s.name.c_str(), len, s.bytes);
-    (void)m;
     const float *src = (const float *)host;
     if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec ||
         s.kind == Storage::InputI64 || s.kind == Storage::Table) {
@@ -1039,6 +1161,27 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
     }
     // ActSplit: NCHW fp32 -> hi/lo planes in the storage's row order (borders stay zero)
     const ActLayout &l = s.layout;
+    if (s.parent >= 0) {
+        // A channel slice: patch the owning tensor's planes.
+        Storage &par = m->storages[s.parent];
+        std::vector<bf16_bits> pl(2 * par.plane_elems);
+        GPX_CUDA(cudaMemcpyAsync(pl.data(), par.hi, pl.size() * sizeof(bf16_bits), cudaMemcpyDeviceToHost, st));
+        GPX_CUDA(cudaStreamSynchronize(st));
+        const int C = (int)s.dims[1];
+        for (int n = 0; n < l.N; ++n)
+            for (int c = 0; c < C; ++c)
+                for (int h = 0; h < l.H; ++h)
+                    for (int w = 0; w < l.W; ++w) {
+                        float v = src[(((size_t)n * C + c) * l.H + h) * l.W + w];
+                        bf16_bits hi = host_f32_to_bf16(v);
+                        size_t off = (size_t)layout_row(l, n, h, w) * l.C + s.ch_off + c;
+                        pl[off] = hi;
+                        pl[par.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                    }
+        GPX_CUDA(cudaMemcpyAsync(par.hi, pl.data(), pl.size() * sizeof(bf16_bits), cudaMemcpyHostToDevice, st));
+        GPX_CUDA(cudaStreamSynchronize(st));
+        return GPX_SUCC;
+    }
     std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
     if (s.token_major) {
         const size_t total = (size_t)l.N * l.W * l.C;
@@ -1068,7 +1211,6 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
     // Model::get, src/model.cpp:296-305.
     GPX_REQUIRE(len >= s.bytes, GPX_OUT_OF_RANGE, "get %s: %zu bytes given, %zu needed",
                 s.name.c_str(), len, s.bytes);
-    (void)m;
     float *dst = (float *)host;
     if (s.kind == Storage::InputF32 || s.kind == Storage::OutputF32 || s.kind == Storage::Vec ||
         s.kind == Storage::InputI64 || s.kind == Storage::Table) {
@@ -1092,8 +1234,10 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
         return GPX_SUCC;
     }
     const ActLayout &l = s.layout;
+    const Storage &own = s.parent >= 0 ? m->storages[s.parent] : s;  // who holds the planes
+    const int coff = s.parent >= 0 ? s.ch_off : 0;
     std::vector<bf16_bits> planes(2 * s.plane_elems);
-    GPX_CUDA(cudaMemcpyAsync(planes.data(), s.hi, planes.size() * sizeof(bf16_bits),
+    GPX_CUDA(cudaMemcpyAsync(planes.data(), own.hi, planes.size() * sizeof(bf16_bits),
                              cudaMemcpyDeviceToHost, st));
     GPX_CUDA(cudaStreamSynchronize(st));
     if (s.token_major) {
@@ -1106,7 +1250,7 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
     for (int n = 0; n < l.N; ++n)
         for (int h = 0; h < l.H; ++h)
             for (int w = 0; w < l.W; ++w) {
-                size_t row = (size_t)layout_row(l, n, h, w) * l.C;
+                size_t row = (size_t)layout_row(l, n, h, w) * l.C + coff;
                 for (int c = 0; c < (int)s.dims[1]; ++c)
                     dst[(((size_t)n * s.dims[1] + c) * l.H + h) * l.W + w] =
                         host_bf16_to_f32(planes[row + c]) + host_bf16_to_f32(planes[s.plane_elems + row + c]);
@@ -1155,7 +1299,7 @@ int gpx_model_close(gpx_model *m) {
     if (!m) return GPX_SUCC;
     for (auto &s : m->storages) {
         if (s.dptr) cudaFree(s.dptr);
-        if (s.hi) cudaFree(s.hi);  // lo lives in the same allocation
+        if (s.hi && s.parent < 0) cudaFree(s.hi);  // lo lives in the same allocation; slices own nothing
     }
     delete m;
     return GPX_SUCC;

@@ -46,9 +46,13 @@ struct Storage {
     bool depthwise = false;          // Weight: [C][1][kh][kw] filter of a depthwise convolution
     float init_mean = 0.f, init_std = 0.f;  // seeded initialiser; std 0 = He-normal / 0.01 default
     bool token_major = false;        // activations of sequence models: canonical [N][S][C]
+    int parent = -1;                 // ActSplit: this tensor is a channel slice of that storage
+    int ch_off = 0;                  //   starting at this stored channel (concatenation by placement)
 };
 
-enum class Op { Input, Conv, MaxPool, AvgPool, LayerNorm, Attention, DwConv };
+// Buffer: a tensor other nodes write slices of (the running concatenation of a dense block).
+// Affine: per-channel scale + shift + activation of the first in_c channels of its input.
+enum class Op { Input, Conv, MaxPool, AvgPool, LayerNorm, Attention, DwConv, Buffer, Affine };
 
 struct Node {
     std::string name;
@@ -67,6 +71,8 @@ struct Node {
     int tables[3] = {-1, -1, -1};  // LayerNorm fed by embeddings: word, position, token-type tables
     int heads = 0;                 // Attention
     int Cs = 0;                    // stored output channels (C padded to 64 when the model pads)
+    int in_c = 0;                  // channels of the input that are read (0 = all): a prefix of a Buffer
+    int scale = -1, shift = -1;    // Affine, or a pooling node that normalises its input: Vec storages
 };
 
 enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv };

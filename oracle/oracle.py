@@ -310,7 +310,84 @@ def mobilenet_v2_forward(params, data, fast=False, taps=None):
     return keep("heads", x.reshape(x.shape[0], -1))
 
 
+DENSENET_CFG = {"densenet201": (6, 12, 48, 32), "densenet_tiny": (2, 3, 2, 2)}
+
+
+def densenet_param_shapes(cfg="densenet201", growth=32, init_features=64, num_classes=1000):
+    s = {"features.conv0.weight": (init_features, 3, 7, 7), "features.conv0.bias": (init_features,)}
+    c = init_features
+    blocks = DENSENET_CFG[cfg]
+    for b, nl in enumerate(blocks):
+        for l in range(nl):
+            p = f"features.denseblock{b + 1}.denselayer{l + 1}"
+            cin = c + growth * l
+            s[f"{p}.norm1.weight"] = (cin,)
+            s[f"{p}.norm1.bias"] = (cin,)
+            s[f"{p}.conv1.weight"] = (4 * growth, cin, 1, 1)
+            s[f"{p}.conv1.bias"] = (4 * growth,)
+            s[f"{p}.conv2.weight"] = (growth, 4 * growth, 3, 3)
+            s[f"{p}.conv2.bias"] = (growth,)
+        c += growth * nl
+        if b != len(blocks) - 1:
+            t = f"features.transition{b + 1}"
+            s[f"{t}.norm.weight"] = (c,)
+            s[f"{t}.norm.bias"] = (c,)
+            s[f"{t}.conv.weight"] = (c // 2, c, 1, 1)
+            s[f"{t}.conv.bias"] = (c // 2,)
+            c //= 2
+    s["features.norm5.weight"] = (c,)
+    s["features.norm5.bias"] = (c,)
+    s["classifier.weight"] = (num_classes, c, 1, 1)
+    s["classifier.bias"] = (num_classes,)
+    return s
+
+
+def _affine_relu(x, scale, shift):
+    """relu(x * scale + shift) per channel of an NCHW tensor, in float64, rounded to fp32."""
+    x = np.asarray(x, np.float64)
+    y = x * np.asarray(scale, np.float64)[None, :, None, None] + np.asarray(shift, np.float64)[None, :, None, None]
+    return np.maximum(y, 0.0).astype(np.float32)
+
+
+def densenet_forward(params, data, cfg="densenet201", fast=False, taps=None):
+    """DenseNet-BC forward: stem, dense blocks whose layers see the concatenation of everything
+    before them (norm-ReLU-1x1-norm-ReLU-3x3, the inner norm folded into the 1x1 bias), transitions
+    (norm-ReLU-1x1-avgpool2), final norm-ReLU, global average pool, classifier."""
+    def keep(name, v):
+        if taps is not None:
+            taps[name] = v
+        return v
+
+    P = params
+    x = keep("features.conv0", conv2d(data, P["features.conv0.weight"], P["features.conv0.bias"], 2, 3,
+                                      True, fast=fast))
+    x = keep("features.pool0", pool2d(x, 3, 2, 1, "max"))
+    blocks = DENSENET_CFG[cfg]
+    for b, nl in enumerate(blocks):
+        for l in range(nl):
+            p = f"features.denseblock{b + 1}.denselayer{l + 1}"
+            a = keep(f"{p}.norm1", _affine_relu(x, P[f"{p}.norm1.weight"], P[f"{p}.norm1.bias"]))
+            y = keep(f"{p}.conv1", conv2d(a, P[f"{p}.conv1.weight"], P[f"{p}.conv1.bias"], 1, 0, True,
+                                          fast=fast))
+            z = keep(f"{p}.conv2", conv2d(y, P[f"{p}.conv2.weight"], P[f"{p}.conv2.bias"], 1, 1, False,
+                                          fast=fast))
+            x = np.concatenate([x, z], axis=1)
+        keep(f"features.denseblock{b + 1}", x)
+        if b != len(blocks) - 1:
+            t = f"features.transition{b + 1}"
+            a = keep(f"{t}.norm", _affine_relu(x, P[f"{t}.norm.weight"], P[f"{t}.norm.bias"]))
+            y = keep(f"{t}.conv", conv2d(a, P[f"{t}.conv.weight"], P[f"{t}.conv.bias"], 1, 0, False,
+                                         fast=fast))
+            x = keep(f"{t}.pool", pool2d(y, 2, 2, 0, "avg"))
+    x = _affine_relu(x, P["features.norm5.weight"], P["features.norm5.bias"])
+    x = keep("avgpool", pool2d(x, x.shape[2], 1, 0, "avg"))
+    x = conv2d(x, P["classifier.weight"], P["classifier.bias"], 1, 0, False, fast=fast)
+    return keep("heads", x.reshape(x.shape[0], -1))
+
+
 MODELS = {
+    "densenet201": lambda p, d, **kw: densenet_forward(p, d, "densenet201", **kw),
+    "densenet_tiny": lambda p, d, **kw: densenet_forward(p, d, "densenet_tiny", **kw),
     "mobilenet_v2": lambda p, d, **kw: mobilenet_v2_forward(p, d, **kw),
     "resnet50": lambda p, d, **kw: resnet_forward(p, d, (3, 4, 6, 3), **kw),
     "resnet152": lambda p, d, **kw: resnet_forward(p, d, (3, 8, 36, 3), **kw),

@@ -19,7 +19,8 @@ def _data(gpx, batch, seed=0):
 
 
 @pytest.mark.parametrize("model,batch", [("resnet_tiny", 1), ("resnet_tiny", 3), ("resnet50", 1),
-                                         ("resnet50", 2), ("mobilenet_v2", 1), ("mobilenet_v2", 3)])
+                                         ("resnet50", 2), ("mobilenet_v2", 1), ("mobilenet_v2", 3),
+                                         ("densenet_tiny", 1), ("densenet_tiny", 3), ("densenet201", 1)])
 def test_forward_matches_oracle_layer_by_layer(gpx, oracle, model, batch):
     ex = gpx.BaseExecutor()
     ex.init(model, batch=batch, seed=1)
@@ -135,7 +136,8 @@ def _all_activations(ex):
 
 
 @pytest.mark.parametrize("model,batch,transport", [("resnet_tiny", 8, 0), ("resnet50", 8, 0),
-                                                   ("resnet50", 8, 1), ("mobilenet_v2", 8, 0)])
+                                                   ("resnet50", 8, 1), ("mobilenet_v2", 8, 0),
+                                                   ("densenet_tiny", 8, 0)])
 def test_model_preempt_resume_bit_identical(gpx, model, batch, transport):
     """Asserted form of src/tests/test-dnn-blp.cpp:36-43: execute, raise the word, drain, clear,
     resume; every activation equals the uninterrupted run bit for bit."""

@@ -205,6 +205,66 @@ def test_mobilenet_v2_restatement_matches_torchvision_topology(oracle):
     assert _rel(got, ref) < 5e-6
 
 
+class _Affine(torch.nn.Module):
+    """Stand-in for an inference batch norm: per-channel scale and shift."""
+
+    def __init__(self, scale, shift):
+        super().__init__()
+        self.scale, self.shift = scale, shift
+
+    def forward(self, x):
+        return x * self.scale.view(1, -1, 1, 1) + self.shift.view(1, -1, 1, 1)
+
+
+def test_densenet201_restatement_matches_torchvision_topology(oracle):
+    import torchvision
+
+    rng = np.random.default_rng(6)
+    params = {}
+    for name, shape in oracle.densenet_param_shapes("densenet201").items():
+        if len(shape) == 4:
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        elif ".norm" in name and name.endswith("weight"):
+            params[name] = (1.0 + rng.standard_normal(shape) * 0.02).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    net = torchvision.models.densenet201(weights=None).double().eval()
+    t = lambda k: torch.from_numpy(params[k]).double()
+
+    def conv(mod, prefix, own_bias):
+        mod.weight.data = t(prefix + ".weight")
+        if own_bias:
+            mod.bias = torch.nn.Parameter(t(prefix + ".bias"))
+
+    f = net.features
+    conv(f.conv0, "features.conv0", False)
+    f.norm0 = _Bias(t("features.conv0.bias"))
+    for b, nl in enumerate((6, 12, 48, 32)):
+        block = getattr(f, f"denseblock{b + 1}")
+        for l in range(nl):
+            p = f"features.denseblock{b + 1}.denselayer{l + 1}"
+            layer = getattr(block, f"denselayer{l + 1}")
+            layer.norm1 = _Affine(t(p + ".norm1.weight"), t(p + ".norm1.bias"))
+            conv(layer.conv1, p + ".conv1", False)
+            layer.norm2 = _Bias(t(p + ".conv1.bias"))
+            conv(layer.conv2, p + ".conv2", True)
+        if b < 3:
+            p = f"features.transition{b + 1}"
+            tr = getattr(f, f"transition{b + 1}")
+            tr.norm = _Affine(t(p + ".norm.weight"), t(p + ".norm.bias"))
+            conv(tr.conv, p + ".conv", True)
+    f.norm5 = _Affine(t("features.norm5.weight"), t("features.norm5.bias"))
+    net.classifier.weight.data = t("classifier.weight").reshape(1000, 1920)
+    net.classifier.bias.data = t("classifier.bias")
+    data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
+    with torch.no_grad():
+        ref = net(torch.from_numpy(data).double()).numpy()
+    got = oracle.forward("densenet201", params, data)
+    assert got.shape == (1, 1000)
+    assert _rel(got, ref) < 5e-6
+
+
 def test_blp_protocol_runs_every_tile_exactly_once_across_resumes(oracle):
     rng = np.random.default_rng(9)
     for trial in range(50):
