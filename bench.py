@@ -192,6 +192,8 @@ def run_reference(args, rank: int) -> None:
     absent from its tree), so the CPU port of the same forward is timed, one image per step."""
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; the CPU arm uses every host core.
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
     import numpy as np
     from oracle import oracle as orc
 
@@ -252,6 +254,8 @@ def main() -> None:
 
     group = dist.init(world, rank)
     device = local_rank if world > 1 else 0
+    # each rank's client threads get their own cores
+    os.environ.setdefault("GPX_CORE_BASE", str(4 * local_rank))
     api.init_cuda(device)
 
     def launches() -> int:
@@ -358,7 +362,7 @@ def main() -> None:
             },
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
     dist.finish(group)

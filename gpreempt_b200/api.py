@@ -377,7 +377,10 @@ class Executor:
         self.batch = 1
         self.dtype = "float32"
 
-    def init(self, workload: str, batch: int = 1, seed: int | None = None, seq_len: int = 0) -> None:
+    def init(self, workload: str, batch: int = 1, seed: int | None = None, seq_len: int = 0,
+             dtype: str | None = None) -> None:
+        if dtype is not None:
+            self.dtype = dtype
         self.model = Model(workload, batch=batch, dtype=self.dtype, seq_len=seq_len)
         self.batch = batch
         if seed is not None:

@@ -27,12 +27,17 @@ namespace gpx {
 
 enum ActOrder : int { ACT_PLAIN = 0, ACT_PADDED = 1, ACT_PHASED = 2 };
 
+// Element format of the planes: two bf16 planes hi + lo (float32 models), or one plane of bf16
+// or fp16 (the reduced-precision models).
+enum PlaneFmt : int { PF_SPLIT = 0, PF_BF16 = 1, PF_F16 = 2 };
+
 struct ActLayout {
     int N, H, W, C;  // logical shape
     int order;       // ActOrder
     int Hs, Ws;      // stored rows / columns per image (per phase plane when phased)
     int plane;       // rows of one phase plane (N*Hs*Ws); equals rows when not phased
     int rows;        // stored rows in total
+    int fmt;         // PlaneFmt of the planes that hold the tensor
 };
 
 inline ActLayout make_layout(int N, int H, int W, int C, int order) {
@@ -42,6 +47,7 @@ inline ActLayout make_layout(int N, int H, int W, int C, int order) {
     l.W = W;
     l.C = C;
     l.order = order;
+    l.fmt = PF_SPLIT;
     if (order == ACT_PLAIN) {
         l.Hs = H;
         l.Ws = W;

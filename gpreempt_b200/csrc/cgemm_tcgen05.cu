@@ -102,6 +102,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         return left < p.kb_per_split ? left : p.kb_per_split;
     };
     const bool resumable = blp.preempted != nullptr;
+    // Two-plane operands (float32 models) or one 16-bit plane (reduced-precision models).
+    const bool two_plane = p.fmt == PF_SPLIT;
 
     CgemmSlot *slot = p.slots + blockIdx.x;
     float *spill = p.spill + (size_t)blockIdx.x * (kCBM * Cfg::kTmemCols);
@@ -196,14 +198,16 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     const int cb = (kb_base + kb) - tap * p.cin_blocks;
                     ctl->stage_msg[stage] = CMSG_DATA;
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
-                    mbar_arrive_expect_tx(bar, Cfg::kStageBytes);
+                    mbar_arrive_expect_tx(bar, two_plane ? Cfg::kStageBytes : Cfg::kABytes + Cfg::kWBytes);
                     const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
                     const int a_row = m_blk * kCBM + p.tap_shift[tap];
                     const int w_col = tap * p.cin + cb * kCBK;
                     tma_load_2d(dst, &p.a_hi, bar, cb * kCBK, a_row);
-                    tma_load_2d(dst + Cfg::kABytes, &p.a_lo, bar, cb * kCBK, a_row);
                     tma_load_2d(dst + 2 * Cfg::kABytes, &p.w_hi, bar, w_col, n_blk * BN);
-                    tma_load_2d(dst + 2 * Cfg::kABytes + Cfg::kWBytes, &p.w_lo, bar, w_col, n_blk * BN);
+                    if (two_plane) {
+                        tma_load_2d(dst + Cfg::kABytes, &p.a_lo, bar, cb * kCBK, a_row);
+                        tma_load_2d(dst + 2 * Cfg::kABytes + Cfg::kWBytes, &p.w_lo, bar, w_col, n_blk * BN);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -226,7 +230,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16_f32(kCBM, BN);
+            const uint32_t idesc = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, BN) : make_idesc_bf16_f32(kCBM, BN);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t seg = 0;
@@ -273,8 +277,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     const uint32_t first = kb > 0 ? 1u : 0u;
                     mma_f16_ss(tmem_base + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc,
                                (first || k > 1) ? 1u : 0u);
-                    mma_f16_ss(tmem_base + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
-                    mma_f16_ss(tmem_base + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                    if (two_plane) {
+                        mma_f16_ss(tmem_base + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                        mma_f16_ss(tmem_base + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                    }
                 }
                 mma_commit(smem_u32(&ctl->empty[stage]));
                 if (++stage == kStages) {
@@ -430,7 +436,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     uint4 gh[4], gl[4];
                     if (use_res) {
                         load_plane(p.res_hi, c, gh);  // both planes are in flight together
-                        load_plane(p.res_lo, c, gl);
+                        if (two_plane) load_plane(p.res_lo, c, gl);
                     }
                     tmem_ld_32x32(t_lane + c, v);
                     tmem_ld_wait();
@@ -440,14 +446,16 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
-                    tmem_ld_32x32(t_lane + 2 * BN + c, v);
-                    tmem_ld_wait();
+                    if (two_plane) {
+                        tmem_ld_32x32(t_lane + 2 * BN + c, v);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(v[j]);
-                    tmem_ld_32x32(t_lane + 3 * BN + c, v);
-                    tmem_ld_wait();
+                        for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(v[j]);
+                        tmem_ld_32x32(t_lane + 3 * BN + c, v);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] += g[j] + __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) f[j] += g[j] + __uint_as_float(v[j]);
+                    }
                     if (p.partial) {
                         // Split K: the raw fp32 sum of this K range goes to the workspace; the
                         // finishing kernel adds the ranges in split order and applies the rest.
@@ -473,15 +481,29 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                     if (use_res) {
                         transpose_plane(gh, rh4);
-                        transpose_plane(gl, rl4);
+                        if (two_plane) {
+                            transpose_plane(gl, rl4);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint4 a = rh4[j], b = rl4[j];
-                            const uint32_t ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 a = rh4[j], b = rl4[j];
+                                const uint32_t ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                f[8 * j + 2 * q + 0] += bf16_lo_to_f32(ah[q]) + bf16_lo_to_f32(bl[q]);
-                                f[8 * j + 2 * q + 1] += bf16_hi_to_f32(ah[q]) + bf16_hi_to_f32(bl[q]);
+                                for (int q = 0; q < 4; ++q) {
+                                    f[8 * j + 2 * q + 0] += bf16_lo_to_f32(ah[q]) + bf16_lo_to_f32(bl[q]);
+                                    f[8 * j + 2 * q + 1] += bf16_hi_to_f32(ah[q]) + bf16_hi_to_f32(bl[q]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 a = rh4[j];
+                                const uint32_t ah[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    float2 r = pf_unpack2(ah[q], p.fmt);
+                                    f[8 * j + 2 * q + 0] += r.x;
+                                    f[8 * j + 2 * q + 1] += r.y;
+                                }
                             }
                         }
                     }
@@ -499,21 +521,33 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         continue;
                     }
                     uint4 hi4[4], lo4[4];
+                    if (two_plane) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t hi[4], lo[4];
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t hi[4], lo[4];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            float x0 = f[8 * j + 2 * q], x1 = f[8 * j + 2 * q + 1];
-                            uint32_t ph = pack_bf16(x0, x1);
-                            hi[q] = ph;
-                            lo[q] = pack_bf16(x0 - bf16_lo_to_f32(ph), x1 - bf16_hi_to_f32(ph));
+                            for (int q = 0; q < 4; ++q) {
+                                float x0 = f[8 * j + 2 * q], x1 = f[8 * j + 2 * q + 1];
+                                uint32_t ph = pack_bf16(x0, x1);
+                                hi[q] = ph;
+                                lo[q] = pack_bf16(x0 - bf16_lo_to_f32(ph), x1 - bf16_hi_to_f32(ph));
+                            }
+                            hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                            lo4[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                         }
-                        hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        lo4[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        flush_plane(p.out_hi, c, hi4);
+                        flush_plane(p.out_lo, c, lo4);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t hi[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                hi[q] = pf_pack2(f[8 * j + 2 * q], f[8 * j + 2 * q + 1], p.fmt);
+                            hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        }
+                        flush_plane(p.out_hi, c, hi4);
                     }
-                    flush_plane(p.out_hi, c, hi4);
-                    flush_plane(p.out_lo, c, lo4);
                 }
                 ++it;
                 ++tiles_done;

@@ -27,7 +27,7 @@ __device__ __forceinline__ bf16_bits f32_to_bf16_bits(float f) {
 __device__ __forceinline__ float view_load(const ActView &v, int n, int h, int w, int c) {
     if (v.f32) return v.f32[(((size_t)n * v.l.C + c) * v.l.H + h) * v.l.W + w];
     size_t off = (size_t)layout_row(v.l, n, h, w) * v.l.C + c;
-    return bf16_bits_to_f32(v.hi[off]) + bf16_bits_to_f32(v.lo[off]);
+    return planes_load1(v.hi, v.lo, off, v.l.fmt);
 }
 
 template <int BM, int BN, int TM, int TN>
@@ -178,10 +178,8 @@ conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
                 if (p.out_f32) {
                     p.out_f32[out_row * p.Cout + n] = v;
                 } else {
-                    bf16_bits h = f32_to_bf16_bits(v);
                     // the row stride is the stored channel count, which may exceed Cout
-                    p.out_hi[out_row * p.out.C + n] = h;
-                    p.out_lo[out_row * p.out.C + n] = f32_to_bf16_bits(v - bf16_bits_to_f32(h));
+                    planes_store1(p.out_hi, p.out_lo, out_row * p.out.C + n, p.out.fmt, v);
                 }
             }
         }
@@ -265,14 +263,7 @@ constexpr int kPoolThreads = 256;
 // Eight channels of one input pixel as fp32: the sum of the planes, then the optional
 // per-channel affine + activation of PoolParams.
 __device__ __forceinline__ void pool_load8(const PoolParams &p, size_t off, int c0, float (&x)[8]) {
-    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
-    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
-    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        x[2 * q] = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
-        x[2 * q + 1] = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
-    }
+    planes_load8(p.in.hi, p.in.lo, off, p.in.l.fmt, x);
     if (p.scale) {
         const float4 *sc = reinterpret_cast<const float4 *>(p.scale + c0);
         const float4 *sh = reinterpret_cast<const float4 *>(p.shift + c0);
@@ -285,17 +276,7 @@ __device__ __forceinline__ void pool_load8(const PoolParams &p, size_t off, int 
 }
 
 __device__ __forceinline__ void pool_store8(const PoolParams &p, size_t off, const float (&x)[8]) {
-    unsigned hi4[4], lo4[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        bf16_bits h0 = f32_to_bf16_bits(x[2 * q]), h1 = f32_to_bf16_bits(x[2 * q + 1]);
-        bf16_bits l0 = f32_to_bf16_bits(x[2 * q] - bf16_bits_to_f32(h0));
-        bf16_bits l1 = f32_to_bf16_bits(x[2 * q + 1] - bf16_bits_to_f32(h1));
-        hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-        lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
-    }
-    *reinterpret_cast<uint4 *>(p.out_hi + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-    *reinterpret_cast<uint4 *>(p.out_lo + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+    planes_store8(p.out_hi, p.out_lo, off, p.out.fmt, x);
 }
 
 // Max / average pooling, or a strided copy, over split-plane activations; eight channels (one
@@ -463,29 +444,18 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
             int n = t / p.Ho;
             const int h0 = ho * p.stride - p.pad, w0 = wo * p.stride - p.pad;
             const long long origin = ((long long)n * p.Cin * H + h0) * W + w0;
-            unsigned hi4[4], lo4[4];
+            float x[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float x[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    int k = k8 * 8 + q * 2 + u;
-                    float v = 0.f;
-                    int fh = s_fh[k];
-                    int hi = h0 + fh, wi = w0 + s_fw[k];
-                    if (fh != 255 && hi >= 0 && hi < H && wi >= 0 && wi < W)
-                        v = p.in.f32 ? p.in.f32[origin + s_off[k]] : view_load(p.in, n, hi, wi, s_ci[k]);
-                    x[u] = v;
-                }
-                bf16_bits h0 = f32_to_bf16_bits(x[0]), h1 = f32_to_bf16_bits(x[1]);
-                bf16_bits l0 = f32_to_bf16_bits(x[0] - bf16_bits_to_f32(h0));
-                bf16_bits l1 = f32_to_bf16_bits(x[1] - bf16_bits_to_f32(h1));
-                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+            for (int u = 0; u < 8; ++u) {
+                int k = k8 * 8 + u;
+                float v = 0.f;
+                int fh = s_fh[k];
+                int hi = h0 + fh, wi = w0 + s_fw[k];
+                if (fh != 255 && hi >= 0 && hi < H && wi >= 0 && wi < W)
+                    v = p.in.f32 ? p.in.f32[origin + s_off[k]] : view_load(p.in, n, hi, wi, s_ci[k]);
+                x[u] = v;
             }
-            size_t off = (size_t)m * p.Kp + k8 * 8;
-            *reinterpret_cast<uint4 *>(p.out_hi + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-            *reinterpret_cast<uint4 *>(p.out_lo + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+            planes_store8(p.out_hi, p.out_lo, (size_t)m * p.Kp + k8 * 8, p.fmt, x);
         }
         ++iter;
         if (dynamic) __syncthreads();
@@ -548,14 +518,10 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
             }
             if (p.res_hi) {
                 size_t off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + col0;
-                uint4 a = *reinterpret_cast<const uint4 *>(p.res_hi + off);
-                uint4 b = *reinterpret_cast<const uint4 *>(p.res_lo + off);
-                const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
+                float r[8];
+                planes_load8(p.res_hi, p.res_lo, off, p.res.fmt, r);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    f[2 * q] += __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
-                    f[2 * q + 1] += __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
-                }
+                for (int j = 0; j < 8; ++j) f[j] += r[j];
             }
             if (p.relu) {
 #pragma unroll
@@ -568,18 +534,8 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
                     if (col0 + j < p.cout_valid) p.out_f32[off + col0 + j] = f[j];
                 continue;
             }
-            unsigned hi4[4], lo4[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                bf16_bits h0 = f32_to_bf16_bits(f[2 * q]), h1 = f32_to_bf16_bits(f[2 * q + 1]);
-                bf16_bits l0 = f32_to_bf16_bits(f[2 * q] - bf16_bits_to_f32(h0));
-                bf16_bits l1 = f32_to_bf16_bits(f[2 * q + 1] - bf16_bits_to_f32(h1));
-                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
-            }
-            size_t out_off = (size_t)layout_row(p.out, n_img, h, w) * p.out.C + col0;
-            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+            planes_store8(p.out_hi, p.out_lo, (size_t)layout_row(p.out, n_img, h, w) * p.out.C + col0,
+                          p.out.fmt, f);
         }
         ++iter;
         if (dynamic) __syncthreads();
@@ -634,40 +590,22 @@ dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
                     int wi = wo * p.stride - p.pad + fw;
                     if (wi < 0 || wi >= W) continue;
                     size_t off = (size_t)layout_row(p.in.l, n, hi, wi) * p.in.l.C + c8 * 8;
-                    uint4 a = *reinterpret_cast<const uint4 *>(p.in.hi + off);
-                    uint4 b = *reinterpret_cast<const uint4 *>(p.in.lo + off);
+                    float x[8];
+                    planes_load8(p.in.hi, p.in.lo, off, p.in.l.fmt, x);
                     const float4 *wv = reinterpret_cast<const float4 *>(p.w + (size_t)(fh * p.k + fw) * C + c8 * 8);
                     float4 w0 = wv[0], w1 = wv[1];
                     const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                    const unsigned ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float x0 = __uint_as_float(ah[q] << 16) + __uint_as_float(bl[q] << 16);
-                        float x1 = __uint_as_float(ah[q] & 0xffff0000u) + __uint_as_float(bl[q] & 0xffff0000u);
-                        acc[2 * q] = fmaf(x0, wf[2 * q], acc[2 * q]);
-                        acc[2 * q + 1] = fmaf(x1, wf[2 * q + 1], acc[2 * q + 1]);
-                    }
+                    for (int j = 0; j < 8; ++j) acc[j] = fmaf(x[j], wf[j], acc[j]);
                 }
             }
-            unsigned hi4[4], lo4[4];
+            if (p.bias) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float x0 = acc[2 * q], x1 = acc[2 * q + 1];
-                if (p.bias) {
-                    x0 += p.bias[c8 * 8 + 2 * q];
-                    x1 += p.bias[c8 * 8 + 2 * q + 1];
-                }
-                x0 = apply_act(x0, p.act);
-                x1 = apply_act(x1, p.act);
-                bf16_bits h0 = f32_to_bf16_bits(x0), h1 = f32_to_bf16_bits(x1);
-                bf16_bits l0 = f32_to_bf16_bits(x0 - bf16_bits_to_f32(h0));
-                bf16_bits l1 = f32_to_bf16_bits(x1 - bf16_bits_to_f32(h1));
-                hi4[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-                lo4[q] = (unsigned)l0 | ((unsigned)l1 << 16);
+                for (int j = 0; j < 8; ++j) acc[j] += p.bias[c8 * 8 + j];
             }
-            size_t out_off = (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8;
-            *reinterpret_cast<uint4 *>(p.out_hi + out_off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-            *reinterpret_cast<uint4 *>(p.out_lo + out_off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = apply_act(acc[j], p.act);
+            planes_store8(p.out_hi, p.out_lo, (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8, p.out.fmt, acc);
         }
         ++iter;
         if (dynamic) __syncthreads();

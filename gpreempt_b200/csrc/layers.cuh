@@ -4,6 +4,7 @@
 
 #include "act_layout.h"
 #include "blp.cuh"
+#include "planes.cuh"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -49,6 +50,8 @@ struct CgemmParams {
     ActLayout out;
     float *out_f32;          // non-null: fp32 [pixel][cout_valid] output (graph heads) instead of planes
     int cout_valid;          // real output channels (the last column tile may be partly padding)
+    int fmt;                 // PlaneFmt of operands, residual and output: PF_SPLIT issues three
+                             // products per K step (hi*hi, hi*lo, lo*hi), the others one
     int k_splits;            // >= 1: the K range is cut into this many tiles per output block
     int kb_per_split;        // K blocks per split (the last split may be shorter)
     float *partial;          // k_splits > 1: fp32 workspace [split][partial_rows][partial_ld]
@@ -131,6 +134,7 @@ struct Im2colParams {
     int kh, kw, stride, pad;
     int K, Kp;              // real and padded row length
     int M;
+    int fmt;                // PlaneFmt of the patch matrix
     int total_tiles;
     int tile_elems;         // 8-column vectors per tile
 };
@@ -146,6 +150,7 @@ struct LayerNormParams {
     bf16_bits *out_hi, *out_lo;
     float *out_f32;                         // non-null: fp32 output (graph heads)
     int rows, H, S;
+    int fmt;                                // PlaneFmt of the input and output planes
     float eps;
     int total_tiles;
 };
@@ -157,6 +162,7 @@ struct AttnParams {
     const bf16_bits *q_hi, *q_lo, *k_hi, *k_lo, *v_hi, *v_lo;
     bf16_bits *out_hi, *out_lo;
     int B, S, heads, ld;
+    int fmt;                // PlaneFmt of all four matrices
     float scale;
     int total_tiles;
 };

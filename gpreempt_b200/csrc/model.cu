@@ -502,10 +502,22 @@ static void build_bert(gpx_model &m, int batch, int seq, int layers, int hidden,
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts) {
     int batch = opts.batch > 0 ? opts.batch : 1;
     m.batch = batch;
-    if (opts.dtype && opts.dtype[0] && std::string(opts.dtype) != "float32") {
-        set_error("dtype '%s' is not available for model '%s' (float32 only)", opts.dtype,
-                  name.c_str());
-        return GPX_NOT_FOUND;
+    // Storage and tensor-core operand format between layers; inputs, outputs, parameters and all
+    // arithmetic outside the tensor-core products stay fp32.
+    m.fmt = PF_SPLIT;
+    if (opts.dtype && opts.dtype[0]) {
+        const std::string dt = opts.dtype;
+        if (dt == "float32" || dt == "fp32")
+            m.fmt = PF_SPLIT;
+        else if (dt == "bfloat16" || dt == "bf16")
+            m.fmt = PF_BF16;
+        else if (dt == "float16" || dt == "fp16")
+            m.fmt = PF_F16;
+        else {
+            set_error("dtype '%s' is not available for model '%s' (float32, bfloat16, float16)", opts.dtype,
+                      name.c_str());
+            return GPX_NOT_FOUND;
+        }
     }
     if (name == "resnet50") {
         const int l[4] = {3, 4, 6, 3};
@@ -567,6 +579,30 @@ static inline float host_bf16_to_f32(bf16_bits v) {
     memcpy(&f, &u, 4);
     return f;
 }
+
+// One element into / out of host copies of the planes (`pe` = elements per plane; the second
+// plane exists only in the two-plane format).
+static inline void host_put(std::vector<bf16_bits> &pl, size_t pe, size_t off, float v, int fmt) {
+    if (fmt == PF_F16) {
+        __half h = __float2half_rn(v);
+        memcpy(&pl[off], &h, 2);
+        return;
+    }
+    bf16_bits hi = host_f32_to_bf16(v);
+    pl[off] = hi;
+    if (fmt == PF_SPLIT) pl[pe + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+}
+static inline float host_take(const std::vector<bf16_bits> &pl, size_t pe, size_t off, int fmt) {
+    if (fmt == PF_F16) {
+        __half h;
+        memcpy(&h, &pl[off], 2);
+        return __half2float(h);
+    }
+    float v = host_bf16_to_f32(pl[off]);
+    if (fmt == PF_SPLIT) v += host_bf16_to_f32(pl[pe + off]);
+    return v;
+}
+static inline size_t plane_count(int fmt) { return fmt == PF_SPLIT ? 2 : 1; }
 
 // Shape test for the tensor-core convolution: 64-channel granularity on both sides and one of
 // the four geometries it implements as row-shifted GEMMs.
@@ -701,10 +737,11 @@ int finalize_model(gpx_model &m) {
             int H = s.rank == 4 ? (int)s.dims[2] : 1, W = s.rank == 4 ? (int)s.dims[3] : 1;
             GPX_REQUIRE(C % 8 == 0, GPX_FAIL, "%s: %d channels, need a multiple of 8", s.name.c_str(), C);
             s.layout = make_layout(N, H, W, C, order[i]);
+            s.layout.fmt = m.fmt;
             s.plane_elems = (size_t)s.layout.rows * C;
-            GPX_CUDA(cudaMalloc((void **)&s.hi, 2 * s.plane_elems * sizeof(bf16_bits)));
-            GPX_CUDA(cudaMemset(s.hi, 0, 2 * s.plane_elems * sizeof(bf16_bits)));
-            s.lo = s.hi + s.plane_elems;
+            GPX_CUDA(cudaMalloc((void **)&s.hi, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
+            GPX_CUDA(cudaMemset(s.hi, 0, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
+            s.lo = m.fmt == PF_SPLIT ? s.hi + s.plane_elems : nullptr;
         } else {
             // Rounded up to 512 bytes so a kernel may read a bias in whole 128-channel tiles.
             size_t alloc = (s.bytes + 511) / 512 * 512;
@@ -715,9 +752,9 @@ int finalize_model(gpx_model &m) {
             GPX_CUDA(cudaMemset(s.dptr, 0, alloc));
             if (s.kind == Storage::Weight && s.wants_split) {
                 s.plane_elems = (size_t)s.cout_pad * s.split_k;
-                GPX_CUDA(cudaMalloc((void **)&s.hi, 2 * s.plane_elems * sizeof(bf16_bits)));
-                GPX_CUDA(cudaMemset(s.hi, 0, 2 * s.plane_elems * sizeof(bf16_bits)));
-                s.lo = s.hi + s.plane_elems;
+                GPX_CUDA(cudaMalloc((void **)&s.hi, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
+                GPX_CUDA(cudaMemset(s.hi, 0, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
+                s.lo = m.fmt == PF_SPLIT ? s.hi + s.plane_elems : nullptr;
             }
         }
     }
@@ -730,7 +767,7 @@ int finalize_model(gpx_model &m) {
         s.layout = par.layout;
         s.plane_elems = par.plane_elems;
         s.hi = par.hi + s.ch_off;
-        s.lo = par.lo + s.ch_off;
+        s.lo = par.lo ? par.lo + s.ch_off : nullptr;
     }
     GPX_CUDA(cgemm_prepare(d.device));
 
@@ -797,6 +834,7 @@ int finalize_model(gpx_model &m) {
                 q.in_hi = in.hi;
                 q.in_lo = in.lo;
             }
+            q.fmt = m.fmt;
             q.gamma = m.storages[n.weight].dptr;
             q.beta = m.storages[n.bias].dptr;
             if (out.kind == Storage::OutputF32) {
@@ -828,6 +866,7 @@ int finalize_model(gpx_model &m) {
             const Storage &sk = m.storages[m.nodes[n.inputs[1]].storage];
             const Storage &sv = m.storages[m.nodes[n.inputs[2]].storage];
             GPX_REQUIRE(n.heads > 0 && n.C == n.heads * 64, GPX_FAIL, "%s: head dimension must be 64", n.name.c_str());
+            q.fmt = m.fmt;
             q.q_hi = sq.hi;
             q.q_lo = sq.lo;
             q.k_hi = sk.hi;
@@ -947,6 +986,7 @@ int finalize_model(gpx_model &m) {
             q.in = view_of(m, src);
             q.out_hi = pm.hi;
             q.out_lo = pm.lo;
+            q.fmt = m.fmt;
             q.Cin = src.C;
             q.Ho = n.H;
             q.Wo = n.W;
@@ -1026,9 +1066,10 @@ int finalize_model(gpx_model &m) {
             p.out = out.layout;
         }
         GPX_TRY(make_tmap_2d_bf16(&p.a_hi, in->hi, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
-        GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
+        if (in->lo) GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
         GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));
-        GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));
+        if (w.lo) GPX_TRY(make_tmap_2d_bf16(&p.w_lo, w.lo, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));
+        p.fmt = m.fmt;
         // Split K when the output alone cannot fill the GPU: each split gets at least four K
         // blocks, the finishing kernel adds the splits in order.
         const int all_kb = p.taps * p.cin_blocks;
@@ -1141,17 +1182,16 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
         GPX_CUDA(cudaStreamSynchronize(st));
         if (s.wants_split) {
             // [Cout][tap][Cin] hi/lo planes for the tensor-core kernel
-            std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
+            const int fmt = m->fmt;
+            std::vector<bf16_bits> planes(plane_count(fmt) * s.plane_elems, 0);
             const size_t K = (size_t)s.split_k;  // rows are zero-padded to a multiple of 64
             for (int o = 0; o < O; ++o)
                 for (int h = 0; h < KH; ++h)
                     for (int w = 0; w < KW; ++w)
                         for (int i = 0; i < I; ++i) {
                             float v = src[(((size_t)o * I + i) * KH + h) * KW + w];
-                            bf16_bits hi = host_f32_to_bf16(v);
                             size_t off = (size_t)o * K + ((size_t)h * KW + w) * s.cin_pad + i;
-                            planes[off] = hi;
-                            planes[s.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                            host_put(planes, s.plane_elems, off, v, fmt);
                         }
             GPX_CUDA(cudaMemcpyAsync(s.hi, planes.data(), planes.size() * sizeof(bf16_bits),
                                      cudaMemcpyHostToDevice, st));
@@ -1164,7 +1204,7 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
     if (s.parent >= 0) {
         // A channel slice: patch the owning tensor's planes.
         Storage &par = m->storages[s.parent];
-        std::vector<bf16_bits> pl(2 * par.plane_elems);
+        std::vector<bf16_bits> pl(plane_count(l.fmt) * par.plane_elems);
         GPX_CUDA(cudaMemcpyAsync(pl.data(), par.hi, pl.size() * sizeof(bf16_bits), cudaMemcpyDeviceToHost, st));
         GPX_CUDA(cudaStreamSynchronize(st));
         const int C = (int)s.dims[1];
@@ -1173,33 +1213,25 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
                 for (int h = 0; h < l.H; ++h)
                     for (int w = 0; w < l.W; ++w) {
                         float v = src[(((size_t)n * C + c) * l.H + h) * l.W + w];
-                        bf16_bits hi = host_f32_to_bf16(v);
                         size_t off = (size_t)layout_row(l, n, h, w) * l.C + s.ch_off + c;
-                        pl[off] = hi;
-                        pl[par.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                        host_put(pl, par.plane_elems, off, v, l.fmt);
                     }
         GPX_CUDA(cudaMemcpyAsync(par.hi, pl.data(), pl.size() * sizeof(bf16_bits), cudaMemcpyHostToDevice, st));
         GPX_CUDA(cudaStreamSynchronize(st));
         return GPX_SUCC;
     }
-    std::vector<bf16_bits> planes(2 * s.plane_elems, 0);
+    std::vector<bf16_bits> planes(plane_count(l.fmt) * s.plane_elems, 0);
     if (s.token_major) {
         const size_t total = (size_t)l.N * l.W * l.C;
-        for (size_t i = 0; i < total; ++i) {
-            bf16_bits hi = host_f32_to_bf16(src[i]);
-            planes[i] = hi;
-            planes[s.plane_elems + i] = host_f32_to_bf16(src[i] - host_bf16_to_f32(hi));
-        }
+        for (size_t i = 0; i < total; ++i) host_put(planes, s.plane_elems, i, src[i], l.fmt);
     } else
     for (int n = 0; n < l.N; ++n)
         for (int c = 0; c < (int)s.dims[1]; ++c)  // logical channels; stored padding stays zero
             for (int h = 0; h < l.H; ++h)
                 for (int w = 0; w < l.W; ++w) {
                     float v = src[(((size_t)n * s.dims[1] + c) * l.H + h) * l.W + w];
-                    bf16_bits hi = host_f32_to_bf16(v);
                     size_t off = (size_t)layout_row(l, n, h, w) * l.C + c;
-                    planes[off] = hi;
-                    planes[s.plane_elems + off] = host_f32_to_bf16(v - host_bf16_to_f32(hi));
+                    host_put(planes, s.plane_elems, off, v, l.fmt);
                 }
     GPX_CUDA(cudaMemcpyAsync(s.hi, planes.data(), planes.size() * sizeof(bf16_bits),
                              cudaMemcpyHostToDevice, st));
@@ -1236,7 +1268,7 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
     const ActLayout &l = s.layout;
     const Storage &own = s.parent >= 0 ? m->storages[s.parent] : s;  // who holds the planes
     const int coff = s.parent >= 0 ? s.ch_off : 0;
-    std::vector<bf16_bits> planes(2 * s.plane_elems);
+    std::vector<bf16_bits> planes(plane_count(l.fmt) * s.plane_elems);
     GPX_CUDA(cudaMemcpyAsync(planes.data(), own.hi, planes.size() * sizeof(bf16_bits),
                              cudaMemcpyDeviceToHost, st));
     GPX_CUDA(cudaStreamSynchronize(st));
@@ -1244,7 +1276,7 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
         // [N][S][C]: the stored rows in order
         const size_t total = (size_t)l.N * l.W * l.C;
         for (size_t i = 0; i < total; ++i)
-            dst[i] = host_bf16_to_f32(planes[i]) + host_bf16_to_f32(planes[s.plane_elems + i]);
+            dst[i] = host_take(planes, s.plane_elems, i, l.fmt);
         return GPX_SUCC;
     }
     for (int n = 0; n < l.N; ++n)
@@ -1253,7 +1285,7 @@ static int storage_get(gpx_model *m, Storage &s, void *host, size_t len, cudaStr
                 size_t row = (size_t)layout_row(l, n, h, w) * l.C + coff;
                 for (int c = 0; c < (int)s.dims[1]; ++c)
                     dst[(((size_t)n * s.dims[1] + c) * l.H + h) * l.W + w] =
-                        host_bf16_to_f32(planes[row + c]) + host_bf16_to_f32(planes[s.plane_elems + row + c]);
+                        host_take(planes, s.plane_elems, row + c, l.fmt);
             }
     return GPX_SUCC;
 }

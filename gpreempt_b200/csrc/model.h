@@ -114,6 +114,7 @@ struct gpx_model {
     int max_cgemm_grid = 0;
     size_t max_partial_floats = 0;  // split-K workspace an executor must provide
     bool pad_channels = false;      // store activations with channels padded to a multiple of 64
+    int fmt = 0;                    // PlaneFmt of activations and tensor-core weights (dtype option)
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;

@@ -761,7 +761,10 @@ static int run_suite(Suite &s, Json *report) {
     // One thread per task (benchmark.cpp:325-328).
     s.run_begin = now_ns() + 50000000ull;
     s.run_end = s.run_begin + (uint64_t)(s.time_s * 1e9);
-    std::atomic<int> core{0};
+    // Cores are handed out in arrival order (bind_core(cores.fetch_add(1)), src/util/util.cpp:3-11);
+    // GPX_CORE_BASE moves the first one so that several processes on one host do not share cores.
+    const char *core_base = getenv("GPX_CORE_BASE");
+    std::atomic<int> core{core_base ? atoi(core_base) : 0};
     std::atomic<int> errors{0};
     std::string first_error;
     std::vector<std::thread> threads;

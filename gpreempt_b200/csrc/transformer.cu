@@ -13,35 +13,6 @@ namespace gpx {
 
 constexpr int kTfThreads = 256;
 
-__device__ __forceinline__ void unpack8(uint4 hi, uint4 lo, float (&x)[8]) {
-    const unsigned h[4] = {hi.x, hi.y, hi.z, hi.w}, l[4] = {lo.x, lo.y, lo.z, lo.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        x[2 * q] = __uint_as_float(h[q] << 16) + __uint_as_float(l[q] << 16);
-        x[2 * q + 1] = __uint_as_float(h[q] & 0xffff0000u) + __uint_as_float(l[q] & 0xffff0000u);
-    }
-}
-
-__device__ __forceinline__ unsigned short tf_bf16(float f) {
-    unsigned u = __float_as_uint(f);
-    u += 0x7fffu + ((u >> 16) & 1u);
-    return (unsigned short)(u >> 16);
-}
-
-__device__ __forceinline__ void pack8(const float (&x)[8], uint4 &hi, uint4 &lo) {
-    unsigned h[4], l[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        unsigned short h0 = tf_bf16(x[2 * q]), h1 = tf_bf16(x[2 * q + 1]);
-        unsigned short l0 = tf_bf16(x[2 * q] - __uint_as_float((unsigned)h0 << 16));
-        unsigned short l1 = tf_bf16(x[2 * q + 1] - __uint_as_float((unsigned)h1 << 16));
-        h[q] = (unsigned)h0 | ((unsigned)h1 << 16);
-        l[q] = (unsigned)l0 | ((unsigned)l1 << 16);
-    }
-    hi = make_uint4(h[0], h[1], h[2], h[3]);
-    lo = make_uint4(l[0], l[1], l[2], l[3]);
-}
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int sh = 16; sh >= 1; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
@@ -126,8 +97,7 @@ layernorm_kernel(const __grid_constant__ LayerNormParams p, BlpArgs blp) {
                         x[i][7] = a1.w + b1.w + c1.w;
                     } else {
                         const size_t off = (size_t)row * p.H + v * 8;
-                        unpack8(*reinterpret_cast<const uint4 *>(p.in_hi + off),
-                                *reinterpret_cast<const uint4 *>(p.in_lo + off), x[i]);
+                        planes_load8(p.in_hi, p.in_lo, off, p.fmt, x[i]);
                     }
                 } else {
 #pragma unroll
@@ -145,10 +115,7 @@ layernorm_kernel(const __grid_constant__ LayerNormParams p, BlpArgs blp) {
                         o[0] = make_float4(x[i][0], x[i][1], x[i][2], x[i][3]);
                         o[1] = make_float4(x[i][4], x[i][5], x[i][6], x[i][7]);
                     } else {
-                        uint4 hi, lo;
-                        pack8(x[i], hi, lo);
-                        *reinterpret_cast<uint4 *>(p.out_hi + off) = hi;
-                        *reinterpret_cast<uint4 *>(p.out_lo + off) = lo;
+                        planes_store8(p.out_hi, p.out_lo, off, p.fmt, x[i]);
                     }
                 }
             }
@@ -210,8 +177,7 @@ attention_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
 #pragma unroll
             for (int v = 0; v < kAttnDh / 8; ++v) {
                 float x[8];
-                unpack8(*reinterpret_cast<const uint4 *>(p.q_hi + off + v * 8),
-                        *reinterpret_cast<const uint4 *>(p.q_lo + off + v * 8), x);
+                planes_load8(p.q_hi, p.q_lo, off + v * 8, p.fmt, x);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[v * 8 + j] = x[j] * p.scale;
             }
@@ -224,10 +190,8 @@ attention_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
                 float kx[8], vx[8];
                 if (k0 + kr < p.S) {
                     const size_t off = ((size_t)b * p.S + k0 + kr) * p.ld + col + v * 8;
-                    unpack8(*reinterpret_cast<const uint4 *>(p.k_hi + off),
-                            *reinterpret_cast<const uint4 *>(p.k_lo + off), kx);
-                    unpack8(*reinterpret_cast<const uint4 *>(p.v_hi + off),
-                            *reinterpret_cast<const uint4 *>(p.v_lo + off), vx);
+                    planes_load8(p.k_hi, p.k_lo, off, p.fmt, kx);
+                    planes_load8(p.v_hi, p.v_lo, off, p.fmt, vx);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) kx[j] = vx[j] = 0.f;
@@ -293,10 +257,7 @@ attention_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
                 float x[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) x[j] = mine[v * 8 + j];
-                uint4 hi, lo;
-                pack8(x, hi, lo);
-                *reinterpret_cast<uint4 *>(p.out_hi + off + v * 8) = hi;
-                *reinterpret_cast<uint4 *>(p.out_lo + off + v * 8) = lo;
+                planes_store8(p.out_hi, p.out_lo, off + v * 8, p.fmt, x);
             }
         }
         ++iter;

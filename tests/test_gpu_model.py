@@ -382,3 +382,99 @@ def test_bert_preempt_resume_bit_identical(gpx):
         assert np.array_equal(ex.get_output("heads"), want), f"trial {trial}"
     assert stops > 0
     base.clear(), ex.clear(), word.destroy(), s.destroy()
+
+
+RTOL_16BIT = 2e-2  # the bf16 / fp16 tolerance of the parity contract
+
+
+@pytest.mark.parametrize("model,batch,dtype", [("resnet_tiny", 2, "bfloat16"), ("resnet_tiny", 2, "float16"),
+                                               ("resnet50", 1, "bfloat16"), ("resnet50", 2, "float16"),
+                                               ("vgg16", 1, "float16"), ("mobilenet_v2", 1, "bfloat16"),
+                                               ("densenet_tiny", 2, "bfloat16"), ("densenet201", 1, "float16")])
+def test_reduced_precision_forward_matches_fp32_oracle(gpx, oracle, model, batch, dtype):
+    """One 16-bit plane between layers, one tensor-core product per K step, fp32 accumulation:
+    `heads` against the float64-accumulating oracle on the same seeded weights and input."""
+    ex = gpx.BaseExecutor()
+    ex.init(model, batch=batch, seed=1, dtype=dtype)
+    data = _data(gpx, batch)
+    ex.set_input("data", data)
+    ex.execute()
+    assert ex.error() == (0, 0)
+    got = ex.get_output("heads")
+    ex.execute()
+    assert np.array_equal(got, ex.get_output("heads"))
+    want = oracle.forward(model, ex.model.params(), data)
+    assert _rel(got, want) <= RTOL_16BIT, f"{model} {dtype}"
+    ex.clear()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_reduced_precision_bert_matches_oracle(gpx, oracle, dtype):
+    ex = gpx.BaseExecutor()
+    ex.init("bert_base", batch=1, seed=7, seq_len=128, dtype=dtype)
+    ids = _ids(1, 128, 30522)
+    ex.set_input("data", ids)
+    ex.execute()
+    assert ex.error() == (0, 0)
+    got = ex.get_output("heads")
+    params = {k: v.reshape(v.shape[0], -1) if v.ndim == 4 else v for k, v in ex.model.params().items()}
+    want = oracle.bert_forward(params, ids, layers=12, heads=12)
+    assert _rel(got, want) <= RTOL_16BIT
+    ex.clear()
+
+
+def test_reduced_precision_preempt_resume_bit_identical(gpx):
+    base = gpx.BaseExecutor()
+    base.init("resnet50", batch=8, seed=1, dtype="float16")
+    data = _data(gpx, 8)
+    base.set_input("data", data)
+    base.execute()
+    want = _all_activations(base)
+    word = gpx.PreemptWord(1)
+    ex = gpx.BLPExecutor()
+    ex.init("resnet50", batch=8, dtype="float16")
+    for k, v in base.model.params().items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.set_input("data", data)
+    s = gpx.Stream(1)
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    rng = np.random.default_rng(4)
+    stops = 0
+    for trial in range(8):
+        ex.set_input("data", data * 0.0)
+        ex.execute(s)
+        s.sync()
+        ex.set_input("data", data)
+        word.clear()
+        time.sleep(0.001)
+        ex.execute(s)
+        rounds = 0
+        while True:
+            if rounds < 4:
+                delay = float(rng.uniform(0, run_us / 2))
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < delay:
+                    pass
+                word.raise_()
+            s.sync()
+            word.clear()
+            time.sleep(0.0005)
+            stop = ex.resume(s)
+            rounds += 1
+            if stop == -1:
+                break
+            stops += 1
+            assert rounds < 60
+        s.sync()
+        got = _all_activations(ex)
+        for k in want:
+            assert np.array_equal(got[k], want[k]), f"trial {trial}: {k} differs after resume"
+    assert stops > 0
+    assert ex.error() == (0, 0)
+    ex.clear()
+    base.clear()
+    s.destroy()
