@@ -44,25 +44,29 @@ struct CgemmCfg {
     static constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kWBytes;
     static constexpr int kStages = BN == 128 ? 3 : 4;
     // ring + alignment slack + control block + one staging buffer per epilogue warp
-    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + 256 + 8 * 32 * kCStageRowBytes;
+    // ring + alignment slack + 64x64 identity tile + control block + one staging buffer per
+    // epilogue warp
+    static constexpr uint32_t kIdentBytes = 64 * kCBK * 2;
+    static constexpr size_t kSmem =
+        (size_t)kStages * kStageBytes + 1024 + kIdentBytes + 256 + 8 * 32 * kCStageRowBytes;
     // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
     // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
     static constexpr int kAccs = 4;
     static constexpr int kTmemCols = kAccs * BN;
 };
 
-enum : int { CMSG_DATA = 0, CMSG_STOP = 1, CMSG_EXIT = 2 };
+enum : int { CMSG_DATA = 0, CMSG_STOP = 1, CMSG_EXIT = 2, CMSG_RES = 3 };
 enum : int { CEPI_COMPLETE = 0, CEPI_PARTIAL = 1, CEPI_EXIT = 2 };
 
 struct CgemmControl {
     unsigned long long full[4];
     unsigned long long empty[4];
-    unsigned long long tmem_full;
-    unsigned long long tmem_empty;
+    unsigned long long tmem_full[2];   // one per accumulator buffer
+    unsigned long long tmem_empty[2];
     uint32_t tmem_base;
     int stage_msg[4];
-    int epi_kind;
-    int epi_k_done;
+    int epi_kind[2];
+    int epi_k_done[2];
     int epi_go;
     int abort_flag;
 };
@@ -85,9 +89,11 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     uint32_t raw_addr = smem_u32(smem_raw);
     uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     unsigned char *smem = smem_raw + pad;
-    CgemmControl *ctl = reinterpret_cast<CgemmControl *>(smem + (size_t)kStages * Cfg::kStageBytes);
+    // The identity tile follows the ring (1024-byte aligned, as its swizzled layout needs).
+    const uint32_t ident_off = kStages * Cfg::kStageBytes;
+    CgemmControl *ctl = reinterpret_cast<CgemmControl *>(smem + ident_off + Cfg::kIdentBytes);
     const uint32_t smem_base = smem_u32(smem);
-    unsigned char *epi_stage = smem + (size_t)kStages * Cfg::kStageBytes + 256;
+    unsigned char *epi_stage = smem + ident_off + Cfg::kIdentBytes + 256;
     volatile int *abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -104,6 +110,12 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     const bool resumable = blp.preempted != nullptr;
     // Two-plane operands (float32 models) or one 16-bit plane (reduced-precision models).
     const bool two_plane = p.fmt == PF_SPLIT;
+    // Accumulator plan.  dual: two accumulators per tile (BN columns each) in two buffers, so the
+    // epilogue of one tile overlaps the K loop of the next; used when the K range is short or the
+    // operands are single-plane.  Otherwise four accumulators in one buffer (see the MMA issuer).
+    const bool dual = p.dual != 0;
+    const int nbuf = dual ? 2 : 1;
+    const int buf_cols = dual ? 2 * BN : Cfg::kTmemCols;
 
     CgemmSlot *slot = p.slots + blockIdx.x;
     float *spill = p.spill + (size_t)blockIdx.x * (kCBM * Cfg::kTmemCols);
@@ -139,11 +151,13 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
-        mbar_init(smem_u32(&ctl->tmem_full), 2);
-        mbar_init(smem_u32(&ctl->tmem_empty), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl->tmem_full[b]), 2);
+            mbar_init(smem_u32(&ctl->tmem_empty[b]), 1);
+            ctl->epi_kind[b] = CEPI_EXIT;
+            ctl->epi_k_done[b] = 0;
+        }
         ctl->abort_flag = 0;
-        ctl->epi_kind = CEPI_EXIT;
-        ctl->epi_k_done = 0;
         ctl->epi_go = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -171,6 +185,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             int flag = resumable ? load_word(blp.preempted) : 0;
             int msg = CMSG_EXIT;
             bool ok = true;
+            // The identity tile travels with the first stage this CTA fills.
+            uint32_t ident_bytes = p.res_kb ? Cfg::kIdentBytes : 0u;
             for (int it = first_iter; ok; ++it) {
                 int tile = blockIdx.x + it * gridDim.x;
                 if (tile >= total_tiles) break;
@@ -178,7 +194,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 const int n_blk = (tile / p.k_splits) % p.tiles_n;
                 const int m_blk = (tile / p.k_splits) / p.tiles_n;
                 const int kb0 = it == first_iter ? first_k : 0;
-                const int num_kb = tile_kb_count(tile);
+                const int main_kb = tile_kb_count(tile);
+                const int num_kb = main_kb + p.res_kb;  // the residual rides along as extra K blocks
                 const int kb_base = tile_kb_begin(tile);
                 for (int kb = kb0; kb < num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs)) {
@@ -194,11 +211,31 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                         flag = load_word(blp.preempted);
                     }
+                    const uint32_t bar = smem_u32(&ctl->full[stage]);
+                    if (kb >= main_kb) {
+                        // Residual block: A = 64 channels of the residual rows of this tile; the W
+                        // operand is the 64x64 identity that stays in shared memory, applied to the
+                        // matching 64 accumulator columns, so the tensor core adds the residual.
+                        const int rb = kb - main_kb;
+                        ctl->stage_msg[stage] = CMSG_RES + rb;
+                        mbar_arrive_expect_tx(bar, (two_plane ? 2 : 1) * Cfg::kABytes + ident_bytes);
+                        const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
+                        tma_load_2d(dst, &p.r_hi, bar, n_blk * BN + rb * kCBK, m_blk * kCBM);
+                        if (two_plane) tma_load_2d(dst + Cfg::kABytes, &p.r_lo, bar, n_blk * BN + rb * kCBK, m_blk * kCBM);
+                        if (ident_bytes) tma_load_2d(smem_base + ident_off, &p.ident, bar, 0, 0);
+                        ident_bytes = 0;
+                        if (++stage == kStages) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                        continue;
+                    }
                     const int tap = (kb_base + kb) / p.cin_blocks;
                     const int cb = (kb_base + kb) - tap * p.cin_blocks;
                     ctl->stage_msg[stage] = CMSG_DATA;
-                    const uint32_t bar = smem_u32(&ctl->full[stage]);
-                    mbar_arrive_expect_tx(bar, two_plane ? Cfg::kStageBytes : Cfg::kABytes + Cfg::kWBytes);
+                    mbar_arrive_expect_tx(bar, (two_plane ? Cfg::kStageBytes : Cfg::kABytes + Cfg::kWBytes) + ident_bytes);
+                    if (ident_bytes) tma_load_2d(smem_base + ident_off, &p.ident, bar, 0, 0);
+                    ident_bytes = 0;
                     const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
                     const int a_row = m_blk * kCBM + p.tap_shift[tap];
                     const int w_col = tap * p.cin + cb * kCBK;
@@ -231,12 +268,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, BN) : make_idesc_bf16_f32(kCBM, BN);
+            const uint32_t idesc64 = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, 64) : make_idesc_bf16_f32(kCBM, 64);
+            const uint64_t eye = make_smem_desc_sw128(smem_base + ident_off);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t seg = 0;
             int kb = first_k;
             int it = first_iter;
-            int num_kb = tile_kb_count(blockIdx.x + it * gridDim.x);
+            int num_kb = tile_kb_count(blockIdx.x + it * gridDim.x) + p.res_kb;
             bool seg_open = false;
             for (;;) {
                 if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, kCWaitLimitNs)) {
@@ -245,19 +284,21 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 }
                 tc_fence_after_sync();
                 const int msg = ctl->stage_msg[stage];
+                const int buf = (int)(seg % nbuf);
+                const uint32_t acc0 = tmem_base + buf * buf_cols;
                 if (!seg_open) {
-                    if (!mbar_wait(smem_u32(&ctl->tmem_empty), seg & 1, abort_flag, kCWaitLimitNs)) {
+                    if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), (seg / nbuf) & 1, abort_flag, kCWaitLimitNs)) {
                         fail(202);
                         break;
                     }
                     tc_fence_after_sync();
                     seg_open = true;
                 }
-                if (msg != CMSG_DATA) {
-                    ctl->epi_kind = msg == CMSG_STOP ? CEPI_PARTIAL : CEPI_EXIT;
-                    ctl->epi_k_done = kb;
-                    mma_commit(smem_u32(&ctl->tmem_full));
-                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                if (msg != CMSG_DATA && msg < CMSG_RES) {
+                    ctl->epi_kind[buf] = msg == CMSG_STOP ? CEPI_PARTIAL : CEPI_EXIT;
+                    ctl->epi_k_done[buf] = kb;
+                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
                     break;
                 }
                 const uint32_t base = smem_base + stage * Cfg::kStageBytes;
@@ -275,11 +316,30 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     // order is fixed, so a resumed tile replays exactly the instruction sequence
                     // of an uninterrupted one.
                     const uint32_t first = kb > 0 ? 1u : 0u;
-                    mma_f16_ss(tmem_base + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc,
-                               (first || k > 1) ? 1u : 0u);
-                    if (two_plane) {
-                        mma_f16_ss(tmem_base + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
-                        mma_f16_ss(tmem_base + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                    if (msg >= CMSG_RES) {
+                        // residual x identity on 64 accumulator columns: the hi plane into a hi*hi
+                        // accumulator, the lo plane into a cross-term accumulator (exact products,
+                        // added like any other)
+                        const uint32_t col = (uint32_t)(msg - CMSG_RES) * 64;
+                        if (dual && two_plane) {
+                            mma_f16_ss(acc0 + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
+                            mma_f16_ss(acc0 + BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
+                        } else {
+                            mma_f16_ss(acc0 + (k & 1) * BN + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
+                            if (two_plane) mma_f16_ss(acc0 + 3 * BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
+                        }
+                    } else if (dual && two_plane) {
+                        // short K: hi*hi in one accumulator, both cross terms in the other
+                        mma_f16_ss(acc0, a_hi + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                        mma_f16_ss(acc0 + BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                        mma_f16_ss(acc0 + BN, a_lo + 2 * k, w_hi + 2 * k, idesc, 1u);
+                    } else {
+                        mma_f16_ss(acc0 + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc,
+                                   (first || k > 1) ? 1u : 0u);
+                        if (two_plane) {
+                            mma_f16_ss(acc0 + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                            mma_f16_ss(acc0 + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                        }
                     }
                 }
                 mma_commit(smem_u32(&ctl->empty[stage]));
@@ -288,13 +348,13 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     phase ^= 1;
                 }
                 if (++kb == num_kb) {
-                    ctl->epi_kind = CEPI_COMPLETE;
-                    ctl->epi_k_done = num_kb;
-                    mma_commit(smem_u32(&ctl->tmem_full));
-                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                    ctl->epi_kind[buf] = CEPI_COMPLETE;
+                    ctl->epi_k_done[buf] = num_kb;
+                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
                     ++seg;
                     ++it;
-                    num_kb = tile_kb_count(blockIdx.x + it * gridDim.x);
+                    num_kb = tile_kb_count(blockIdx.x + it * gridDim.x) + p.res_kb;
                     kb = 0;
                     seg_open = false;
                 }
@@ -305,7 +365,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;                 // which half of the columns
         const int c_lo = half * (BN / 2), c_hi = c_lo + BN / 2;
-        const int s_lo = half * (Cfg::kTmemCols / 2), s_hi = s_lo + Cfg::kTmemCols / 2;
+        // this warp's share of the columns of one accumulator buffer, for spill and restore
+        const int s_lo = half * (buf_cols / 2), s_hi = s_lo + buf_cols / 2;
         const int row = quarter * 32 + lane;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const bool leader = threadIdx.x == 64;
@@ -327,23 +388,26 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         }
         tc_fence_before_sync();
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (leader) mbar_arrive(smem_u32(&ctl->tmem_empty));
+        if (leader)
+            for (int b = 0; b < nbuf; ++b) mbar_arrive(smem_u32(&ctl->tmem_empty[b]));
 
         int it = first_iter;
         int seg_k0 = first_k;
         int tiles_done = 0;
         const int img = p.in_hs * p.in_ws;
         for (uint32_t seg = 0;; ++seg) {
+            const int buf = (int)(seg % nbuf);
+            const uint32_t t_acc = t_lane + buf * buf_cols;
             if (leader) {
-                bool ok = mbar_wait(smem_u32(&ctl->tmem_full), seg & 1, abort_flag, kCWaitLimitNs);
+                bool ok = mbar_wait(smem_u32(&ctl->tmem_full[buf]), (seg / nbuf) & 1, abort_flag, kCWaitLimitNs);
                 if (!ok) fail(301);
                 ctl->epi_go = ok ? 1 : 0;
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (!ctl->epi_go) break;
             tc_fence_after_sync();
-            const int kind = ctl->epi_kind;
-            const int k_done = ctl->epi_k_done;
+            const int kind = ctl->epi_kind[buf];
+            const int k_done = ctl->epi_k_done[buf];
             if (kind == CEPI_EXIT) {
                 if (leader && resumable) {
                     slot->next_iter = it;
@@ -429,7 +493,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     __syncwarp();
                 };
                 for (int c = c_lo; c < c_hi; c += 32) {
-                    float f[32], g[32];
+                    float f[32];
                     // The residual is requested first so its latency overlaps the TMEM reads.
                     uint4 rh4[4], rl4[4];
                     const bool use_res = staged && p.res_hi;
@@ -438,23 +502,23 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         load_plane(p.res_hi, c, gh);  // both planes are in flight together
                         if (two_plane) load_plane(p.res_lo, c, gl);
                     }
-                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    tmem_ld_32x32(t_lane + BN + c, v);
+                    tmem_ld_32x32(t_acc + BN + c, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
-                    if (two_plane) {
-                        tmem_ld_32x32(t_lane + 2 * BN + c, v);
+                    if (two_plane && !dual) {
+                        tmem_ld_32x32(t_acc + 2 * BN + c, v);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(v[j]);
-                        tmem_ld_32x32(t_lane + 3 * BN + c, v);
+                        for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
+                        tmem_ld_32x32(t_acc + 3 * BN + c, v);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] += g[j] + __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
                     }
                     if (p.partial) {
                         // Split K: the raw fp32 sum of this K range goes to the workspace; the
@@ -555,7 +619,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 tc_fence_before_sync();
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (leader) {
-                    mbar_arrive(smem_u32(&ctl->tmem_empty));
+                    mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
                     if (blp.executed) atomicAdd(blp.executed, 1);
                 }
                 continue;
@@ -563,7 +627,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             // CEPI_PARTIAL
             if (k_done > seg_k0) {
                 for (int c = s_lo; c < s_hi; c += 32) {
-                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
                     uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
 #pragma unroll

@@ -52,6 +52,13 @@ struct CgemmParams {
     int cout_valid;          // real output channels (the last column tile may be partly padding)
     int fmt;                 // PlaneFmt of operands, residual and output: PF_SPLIT issues three
                              // products per K step (hi*hi, hi*lo, lo*hi), the others one
+    // Residual by tensor core (1x1 stride-1 convolutions on plain rows, no split K): res_kb = BN/64
+    // extra K blocks per tile whose A operand is the residual tile and whose W operand is the
+    // identity; res_hi/res_lo are then null and the epilogue adds nothing.
+    CUtensorMap r_hi, r_lo, ident;
+    int res_kb;
+    int dual;                // 1: two accumulators per tile in two TMEM buffers (short K ranges and
+                             // single-plane operands), 0: four accumulators in one buffer
     int k_splits;            // >= 1: the K range is cut into this many tiles per output block
     int kb_per_split;        // K blocks per split (the last split may be shorter)
     float *partial;          // k_splits > 1: fp32 workspace [split][partial_rows][partial_ld]

@@ -739,6 +739,8 @@ int finalize_model(gpx_model &m) {
             s.layout = make_layout(N, H, W, C, order[i]);
             s.layout.fmt = m.fmt;
             s.plane_elems = (size_t)s.layout.rows * C;
+            GPX_REQUIRE(s.plane_elems < 0xffffffffull, GPX_OUT_OF_RANGE, "%s: %zu elements per plane, the kernels index with 32 bits",
+                        s.name.c_str(), s.plane_elems);
             GPX_CUDA(cudaMalloc((void **)&s.hi, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
             GPX_CUDA(cudaMemset(s.hi, 0, plane_count(m.fmt) * s.plane_elems * sizeof(bf16_bits)));
             s.lo = m.fmt == PF_SPLIT ? s.hi + s.plane_elems : nullptr;
@@ -768,6 +770,14 @@ int finalize_model(gpx_model &m) {
         s.plane_elems = par.plane_elems;
         s.hi = par.hi + s.ch_off;
         s.lo = par.lo ? par.lo + s.ch_off : nullptr;
+    }
+    {
+        // 128 x 128 identity in the plane format: the W operand of residual K blocks.
+        std::vector<bf16_bits> eye(128 * 128, 0);
+        const bf16_bits one = m.fmt == PF_F16 ? 0x3C00 : 0x3F80;
+        for (int i = 0; i < 128; ++i) eye[i * 128 + i] = one;
+        GPX_CUDA(cudaMalloc((void **)&m.identity, eye.size() * sizeof(bf16_bits)));
+        GPX_CUDA(cudaMemcpy(m.identity, eye.data(), eye.size() * sizeof(bf16_bits), cudaMemcpyHostToDevice));
     }
     GPX_CUDA(cgemm_prepare(d.device));
 
@@ -1083,6 +1093,24 @@ int finalize_model(gpx_model &m) {
                 p.k_splits = (all_kb + p.kb_per_split - 1) / p.kb_per_split;
             }
         }
+        // Accumulation chains of at most 1024 products keep one hi*hi accumulator within the fp32
+        // parity bound, which frees tensor memory for a second buffer (see cgemm_tcgen05.cu).
+        p.dual = (m.fmt != PF_SPLIT || p.kb_per_split * 64 <= 1024) ? 1 : 0;
+        if (const char *e = getenv("GPX_CGEMM_DUAL")) p.dual = atoi(e) ? p.dual : 0;
+        // The residual of a 1x1 stride-1 convolution on plain rows has the rows of the GEMM itself:
+        // it is then added by the tensor core as identity K blocks instead of by the epilogue.
+        p.res_kb = 0;
+        if (n.residual >= 0 && p.k_splits == 1 && eff_k == 1 && !n.via_im2col && in == &m.storages[src.storage] &&
+            il.order == ACT_PLAIN && !getenv("GPX_CGEMM_RES_EPILOGUE")) {
+            const Storage &r = m.storages[m.nodes[n.residual].storage];
+            if (r.layout.order == ACT_PLAIN && r.layout.rows == il.rows && r.parent < 0 && r.layout.C % 64 == 0) {
+                GPX_TRY(make_tmap_2d_bf16(&p.r_hi, r.hi, (uint64_t)r.layout.rows, (uint64_t)r.layout.C, 128, 64));
+                if (r.lo) GPX_TRY(make_tmap_2d_bf16(&p.r_lo, r.lo, (uint64_t)r.layout.rows, (uint64_t)r.layout.C, 128, 64));
+                GPX_TRY(make_tmap_2d_bf16(&p.ident, m.identity, 128, 128, 64, 64));
+                p.res_kb = bn / 64;
+                p.res_hi = p.res_lo = nullptr;
+            }
+        }
         kn.total_tiles = out_tiles * p.k_splits;
         kn.grid = std::min(kn.total_tiles, m.sm_count);
         m.max_cgemm_grid = std::max(m.max_cgemm_grid, kn.grid);
@@ -1333,6 +1361,7 @@ int gpx_model_close(gpx_model *m) {
         if (s.dptr) cudaFree(s.dptr);
         if (s.hi && s.parent < 0) cudaFree(s.hi);  // lo lives in the same allocation; slices own nothing
     }
+    if (m->identity) cudaFree(m->identity);
     delete m;
     return GPX_SUCC;
 }

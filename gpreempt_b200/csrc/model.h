@@ -114,6 +114,7 @@ struct gpx_model {
     int max_cgemm_grid = 0;
     size_t max_partial_floats = 0;  // split-K workspace an executor must provide
     bool pad_channels = false;      // store activations with channels padded to a multiple of 64
+    gpx::bf16_bits *identity = nullptr;  // 128 x 128 identity matrix in the plane format
     int fmt = 0;                    // PlaneFmt of activations and tensor-core weights (dtype option)
 
     int add_storage(const gpx::Storage &s);

@@ -10,6 +10,7 @@
 
 #include "act_layout.h"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace gpx {
@@ -39,7 +40,8 @@ __device__ __forceinline__ unsigned pf_pack2(float a, float b, int fmt) {
         __half2 h = __floats2half2_rn(a, b);
         return *reinterpret_cast<unsigned *>(&h);
     }
-    return (unsigned)pf_bf16_bits(a) | ((unsigned)pf_bf16_bits(b) << 16);
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);  // one cvt.rn.bf16x2.f32
+    return *reinterpret_cast<unsigned *>(&v);
 }
 
 __device__ __forceinline__ void planes_load8(const plane_bits *hi, const plane_bits *lo, size_t off, int fmt,
