@@ -117,6 +117,12 @@ def measured_peaks() -> tuple[dict, str]:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+# DRAM bytes (read + write) the 54 tensor-core convolution launches of one ResNet-50 b32 fp32
+# forward move, from an ncu capture of `python -m gpreempt_b200.profile_step model --model resnet50
+# --batch 32` (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one forward).
+NCU_CONV_DRAM_BYTES_PER_STEP = 2.673e9
+
+
 def conv_roofline(api, device: int) -> dict:
     """Per-layer device time of one best-effort forward, measured with CUDA events on the
     launching stream, and the algorithmic FLOP rate of the convolution kernels."""
@@ -350,7 +356,10 @@ def main() -> None:
             "wall_s_resident_run": t1 - t0,
             "roofline": {
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
-                "frac": tflops / peak, "traffic": None,
+                "frac": tflops / peak, "traffic": NCU_CONV_DRAM_BYTES_PER_STEP if roof["tensor_core"] else None,
+                "traffic_note": "dram__bytes_read+write summed over the 54 convolution launches of one "
+                                "forward (ncu capture, bytes per step); algorithmic bytes of the same "
+                                "launches 3.60e9",
                 "kernel": ("cgemm_tcgen05_kernel (split-bf16 tensor-core convolution, 3 bf16 MMAs per "
                            "fp32 MAC, best-effort batch 32)") if roof["tensor_core"] else
                           "conv_simt_kernel (fp32 FFMA convolution, best-effort batch 32)",

@@ -162,6 +162,7 @@ struct Tenant {
     int priority = 1;
     int batch = 1;
     int seq_len = 0;
+    std::string dtype;  // "" = float32
     bool use_graph = false;
     uint64_t preprocess_us = 0;
     int gpu = 0;
@@ -614,6 +615,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         t->priority = (int)jc["priority"].as_int(1);
         t->batch = (int)jc["batch_size"].as_int(1);
         t->seq_len = (int)jc["seq_len"].as_int(0);
+        if (jc.has("dtype")) t->dtype = jc["dtype"].as_string();
         t->use_graph = jc["use_cuda_graph"].as_bool(false);
         t->preprocess_us = (uint64_t)jc["preprocess_time"].as_int(0);
         t->gpu = jc.has("gpu") ? (int)jc["gpu"].as_int() : default_gpu;
@@ -645,6 +647,7 @@ static int init_tenant(Suite &s, Tenant *t) {
     gpx_model_opts o{};
     o.batch = t->batch;
     o.seq_len = t->seq_len;
+    o.dtype = t->dtype.empty() ? nullptr : t->dtype.c_str();
     GPX_TRY(gpx_model_open(t->model_name.c_str(), &o, &t->model));
     GPX_TRY(gpx_model_init_random(t->model, 1));
     bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);

@@ -34,14 +34,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
         "r"(bytes)
         : "memory");
 }
+// Upper bound of one hardware suspension inside try_wait: a waiting thread sleeps instead of
+// spinning through issue slots its neighbours need, and wakes as soon as the phase completes.
+constexpr uint32_t kMbarSuspendNs = 2000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kMbarSuspendNs)
         : "memory");
     return ok != 0;
 }

@@ -78,3 +78,26 @@ def test_unknown_client_and_bad_config(gpx):
     assert e.value.status == B.FAIL
     with pytest.raises(gpx.GpxError):
         gpx.run_workload("baseclient", json.dumps({"time": 1, "tasks": []}))
+
+
+@pytest.mark.parametrize("name", ["C1_resnet50_contention", "C3_bert_vs_vgg16", "C4_mix_vs_densenet_bert"])
+def test_shipped_contention_configs_run(gpx, name):
+    """The contention configurations shipped under config/ (models, batches, dtypes and loads of
+    the baseline's configs 1, 3 and 4) run under the GP policy: every tenant serves requests, the
+    best-effort tenants are preempted and resumed, latency-critical tail stays finite."""
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "config", name + ".json")
+    cfg = json.load(open(path))
+    cfg["time"] = 2.0
+    cfg["warmup"] = 2
+    cfg["standalone"] = 3
+    rep = json.loads(gpx.run_workload("gpreemptclient", json.dumps(cfg)))
+    tasks = {t["id"]: t for t in rep["tasks"]}
+    assert set(tasks) == {t["id"] for t in cfg["tasks"]}
+    for t in tasks.values():
+        assert t["requests"] > 0, t["id"]
+        assert t["totalLatency(us)"]["p99"] > 0
+    g = rep["gpus"][0]
+    assert g["wordRaises"] > 0
+    assert g["beResumes"] > 0
