@@ -82,6 +82,23 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == ACT_RELU6) return fminf(fmaxf(v, 0.f), 6.f);
     return v;
 }
+
+// The same over a register array, with the (warp-uniform) choice made once outside the element
+// loop: inside it the compiler would otherwise evaluate the erf of GELU for every element of every
+// layer and select afterwards.
+template <int N>
+__device__ __forceinline__ void apply_act_n(float (&f)[N], int act) {
+    if (act == ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) f[j] = fmaxf(f[j], 0.f);
+    } else if (act == ACT_RELU6) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) f[j] = fminf(fmaxf(f[j], 0.f), 6.f);
+    } else if (act == ACT_GELU) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) f[j] = 0.5f * f[j] * (1.0f + erff(f[j] * 0.70710678118654752440f));
+    }
+}
 #endif
 
 }  // namespace gpx

@@ -9,6 +9,7 @@
 #pragma once
 
 #include <cstdint>
+#include <cstdlib>
 
 namespace gpx {
 
@@ -35,6 +36,18 @@ __device__ __forceinline__ int load_word(const int *p) {
     int v;
     asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+// Programmatic dependent launch.  The layer kernels of a model are launched with programmatic
+// stream serialization: a kernel may become resident while its predecessor in the stream is
+// still draining, so launch latency and the scheduling of its CTAs overlap the predecessor's
+// tail (batch-1 forwards are ~90 kernels of a few microseconds each).  Every such kernel calls
+// pdl_enter() before it touches global memory: it lets its own successor start launching, then
+// waits until the predecessor grid has completed and its writes are visible.  Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ void trace_begin(const BlpArgs &b) {
@@ -66,5 +79,33 @@ __device__ __forceinline__ int blp_claim(const BlpArgs &b, int iter) {
     int idx = atomicAdd(b.executed, 1);
     return idx < b.total_tiles ? idx : -1;
 }
+
+#if defined(__CUDACC__)
+// Launch of a layer kernel with the programmatic-serialization attribute (GPX_PDL=0 turns it off).
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("GPX_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_layer(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t s,
+                                Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 }  // namespace gpx

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kCgemmThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     using Cfg = CgemmCfg<BN>;
     constexpr int kStages = Cfg::kStages;
+    pdl_enter();
     extern __shared__ unsigned char smem_raw[];
     uint32_t raw_addr = smem_u32(smem_raw);
     uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -571,10 +572,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                             }
                         }
                     }
-                    if (p.relu) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.relu);
-                    }
+                    apply_act_n(f, p.relu);
                     if (p.out_f32) {
                         const int col0 = n_blk * BN + c;
                         if (valid) {
@@ -675,9 +673,9 @@ cudaError_t cgemm_prepare(int device) {
 
 cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s) {
     if (bn == 128)
-        cgemm_tcgen05_kernel<128><<<grid, kCgemmThreads, CgemmCfg<128>::kSmem, s>>>(p, blp);
+        launch_layer(cgemm_tcgen05_kernel<128>, grid, kCgemmThreads, CgemmCfg<128>::kSmem, s, p, blp);
     else
-        cgemm_tcgen05_kernel<64><<<grid, kCgemmThreads, CgemmCfg<64>::kSmem, s>>>(p, blp);
+        launch_layer(cgemm_tcgen05_kernel<64>, grid, kCgemmThreads, CgemmCfg<64>::kSmem, s, p, blp);
     return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ __device__ __forceinline__ float view_load(const ActView &v, int n, int h, int w
 template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__(kConvThreads)
 conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
+    pdl_enter();
     constexpr int BK = kConvBK;
     static_assert((BM / TM) * (BN / TN) == kConvThreads, "thread layout");
     constexpr int SB = (BN * 4 + kConvThreads - 1) / kConvThreads;  // float4 slots of B per thread
@@ -244,13 +245,13 @@ cudaError_t conv_launch(const ConvParams &p, int tile, int grid, const BlpArgs &
                         cudaStream_t s) {
     switch (tile) {
         case CONV_TILE_128:
-            conv_simt_kernel<128, 128, 8, 8><<<grid, kConvThreads, 0, s>>>(p, blp);
+            launch_layer(conv_simt_kernel<128, 128, 8, 8>, grid, kConvThreads, 0, s, p, blp);
             break;
         case CONV_TILE_64:
-            conv_simt_kernel<64, 64, 4, 4><<<grid, kConvThreads, 0, s>>>(p, blp);
+            launch_layer(conv_simt_kernel<64, 64, 4, 4>, grid, kConvThreads, 0, s, p, blp);
             break;
         default:
-            conv_simt_kernel<32, 32, 2, 2><<<grid, kConvThreads, 0, s>>>(p, blp);
+            launch_layer(conv_simt_kernel<32, 32, 2, 2>, grid, kConvThreads, 0, s, p, blp);
             break;
     }
     return cudaGetLastError();
@@ -271,7 +272,8 @@ __device__ __forceinline__ void pool_load8(const PoolParams &p, size_t off, int 
         const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
         const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = apply_act(fmaf(x[j], sv[j], hv[j]), p.act);
+        for (int j = 0; j < 8; ++j) x[j] = fmaf(x[j], sv[j], hv[j]);
+        apply_act_n(x, p.act);
     }
 }
 
@@ -284,6 +286,7 @@ __device__ __forceinline__ void pool_store8(const PoolParams &p, size_t off, con
 // vectors in (n, ho, wo, c/8) order.
 __global__ void __launch_bounds__(kPoolThreads)
 pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -400,6 +403,7 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
 // (one 16-byte vector per plane) of one row.
 __global__ void __launch_bounds__(kPoolThreads)
 im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -464,7 +468,7 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
 }
 
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    im2col_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    launch_layer(im2col_kernel, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
@@ -473,6 +477,7 @@ cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, c
 // not depend on which CTA produced which split or in which order they finished.
 __global__ void __launch_bounds__(kPoolThreads)
 splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -523,10 +528,7 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] += r[j];
             }
-            if (p.relu) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = apply_act(f[j], p.relu);
-            }
+            apply_act_n(f, p.relu);
             if (p.out_f32) {
                 size_t off = ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid;
 #pragma unroll
@@ -544,7 +546,7 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
 }
 
 cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    splitk_finish_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    launch_layer(splitk_finish_kernel, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
@@ -552,6 +554,7 @@ cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, c
 // taps walked in (fh, fw) order with one FFMA each, so the result is independent of the tiling.
 __global__ void __launch_bounds__(kPoolThreads)
 dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -603,8 +606,7 @@ dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] += p.bias[c8 * 8 + j];
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = apply_act(acc[j], p.act);
+            apply_act_n(acc, p.act);
             planes_store8(p.out_hi, p.out_lo, (size_t)layout_row(p.out, n, ho, wo) * C + c8 * 8, p.out.fmt, acc);
         }
         ++iter;
@@ -614,7 +616,7 @@ dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
 }
 
 cudaError_t dwconv_launch(const DwConvParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    dwconv_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    launch_layer(dwconv_kernel, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
@@ -626,7 +628,7 @@ int pool_grid(const PoolParams &p, int sm_count) {
 }
 
 cudaError_t pool_launch(const PoolParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    pool_kernel<<<grid, kPoolThreads, 0, s>>>(p, blp);
+    launch_layer(pool_kernel, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 

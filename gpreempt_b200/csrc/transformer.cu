@@ -54,6 +54,7 @@ __device__ __forceinline__ void layer_norm_row(float (&x)[kLnMaxVec][8], int nve
 // Rows of a [rows][H] matrix, one warp per row, eight rows per tile.
 __global__ void __launch_bounds__(kTfThreads)
 layernorm_kernel(const __grid_constant__ LayerNormParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -127,7 +128,7 @@ layernorm_kernel(const __grid_constant__ LayerNormParams p, BlpArgs blp) {
 }
 
 cudaError_t layernorm_launch(const LayerNormParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    layernorm_kernel<<<grid, kTfThreads, 0, s>>>(p, blp);
+    launch_layer(layernorm_kernel, grid, kTfThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
@@ -144,6 +145,7 @@ constexpr int kAttnLd = kAttnDh + 4;
 // in a fixed order by shuffles.
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
+    pdl_enter();
     __shared__ int s_tile;
     __shared__ __align__(16) float Ks[kAttnKeys][kAttnLd];
     __shared__ __align__(16) float Vs[kAttnKeys][kAttnLd];
@@ -266,7 +268,7 @@ attention_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
 }
 
 cudaError_t attention_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    attention_kernel<<<grid, kAttnThreads, 0, s>>>(p, blp);
+    launch_layer(attention_kernel, grid, kAttnThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
