@@ -31,9 +31,6 @@ constexpr int kCBM = 128, kCBK = 64, kCUmmaK = 16;
 // while a tile is drained (the epilogue, not the tensor pipe, bounds the small-K layers).
 constexpr int kCgemmThreads = 320;
 constexpr int kCEpiThreads = 256;
-// Epilogue staging: 32 rows of 64 data bytes per warp, padded to 80 bytes so that the row-wise
-// and the four-lanes-per-row access patterns both spread over the shared-memory banks.
-constexpr int kCStageRowBytes = 80;
 constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
 constexpr int kCPollEvery = 2;
 
@@ -43,12 +40,10 @@ struct CgemmCfg {
     static constexpr uint32_t kWBytes = BN * kCBK * 2;          // one plane of W
     static constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kWBytes;
     static constexpr int kStages = BN == 128 ? 3 : 4;
-    // ring + alignment slack + control block + one staging buffer per epilogue warp
-    // ring + alignment slack + 64x64 identity tile + control block + one staging buffer per
-    // epilogue warp
+    // ring + alignment slack + 64x64 identity tile + control block
     static constexpr uint32_t kIdentBytes = 64 * kCBK * 2;
     static constexpr size_t kSmem =
-        (size_t)kStages * kStageBytes + 1024 + kIdentBytes + 256 + 8 * 32 * kCStageRowBytes;
+        (size_t)kStages * kStageBytes + 1024 + kIdentBytes + 256;
     // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
     // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
     static constexpr int kAccs = 4;
@@ -75,6 +70,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&p);
 }
+// 256-bit global accesses (32-byte aligned): one whole sector per lane.
+__device__ __forceinline__ void ld_global_v8(const void *ptr, uint32_t *r) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(ptr));
+}
+__device__ __forceinline__ void st_global_v8(void *ptr, const uint32_t *r) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi_to_f32(uint32_t packed) {
     return __uint_as_float(packed & 0xffff0000u);
@@ -94,7 +100,6 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     const uint32_t ident_off = kStages * Cfg::kStageBytes;
     CgemmControl *ctl = reinterpret_cast<CgemmControl *>(smem + ident_off + Cfg::kIdentBytes);
     const uint32_t smem_base = smem_u32(smem);
-    unsigned char *epi_stage = smem + ident_off + Cfg::kIdentBytes + 256;
     volatile int *abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -441,67 +446,22 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                                         : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
                     if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
                 }
-                // Rows whose planes this lane moves in the coalesced phases: row (lane/4 + 8i) of the
-                // warp's 32, 16 bytes at column group (lane%4).  ~0 marks a row that is not an
-                // output pixel.
-                const bool staged = !p.partial && !p.out_f32;
-                unsigned long long my_out = valid ? (unsigned long long)out_off : ~0ull;
-                unsigned long long my_res = (valid && p.res_hi) ? (unsigned long long)res_off : ~0ull;
-                unsigned long long row_out[4], row_res[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    row_out[i] = __shfl_sync(0xffffffffu, my_out, (lane >> 2) + 8 * i);
-                    row_res[i] = __shfl_sync(0xffffffffu, my_res, (lane >> 2) + 8 * i);
-                }
-                unsigned char *stg = epi_stage + (size_t)(warp - 2) * kCStageRowBytes * 32;
-                const int seg = lane & 3;
+                // Every lane owns one row of the tile (its TMEM lane): 32 columns of a plane are 64
+                // contiguous bytes of that row, moved as two 256-bit accesses, each a whole sector.
+                const bool planes_out = !p.partial && !p.out_f32;
                 const int col_lim = p.cout_valid - n_blk * BN;
-                // One plane of a 32-row x 32-column piece: global -> shared with full 64-byte row
-                // pieces per four lanes, then every lane picks up its own row.
-                auto load_plane = [&](const bf16_bits *base, int c, uint4 (&q)[4]) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        q[i] = make_uint4(0u, 0u, 0u, 0u);
-                        if (row_res[i] != ~0ull)
-                            q[i] = *reinterpret_cast<const uint4 *>(base + row_res[i] + c + seg * 8);
-                    }
-                };
-                auto transpose_plane = [&](const uint4 (&q)[4], uint4 (&dst)[4]) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = (lane >> 2) + 8 * i;
-                        *reinterpret_cast<uint4 *>(stg + r * kCStageRowBytes + seg * 16) = q[i];
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        dst[j] = *reinterpret_cast<const uint4 *>(stg + lane * kCStageRowBytes + j * 16);
-                    __syncwarp();
-                };
-                auto flush_plane = [&](bf16_bits *base, int c, const uint4 (&src)[4]) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4 *>(stg + lane * kCStageRowBytes + j * 16) = src[j];
-                    __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = (lane >> 2) + 8 * i;
-                        uint4 q = *reinterpret_cast<const uint4 *>(stg + r * kCStageRowBytes + seg * 16);
-                        // The output may be a channel slice: nothing is stored past cout_valid.
-                        if (row_out[i] != ~0ull && c + seg * 8 < col_lim)
-                            *reinterpret_cast<uint4 *>(base + row_out[i] + c + seg * 8) = q;
-                    }
-                    __syncwarp();
-                };
                 for (int c = c_lo; c < c_hi; c += 32) {
                     float f[32];
                     // The residual is requested first so its latency overlaps the TMEM reads.
-                    uint4 rh4[4], rl4[4];
-                    const bool use_res = staged && p.res_hi;
-                    uint4 gh[4], gl[4];
+                    const bool use_res = planes_out && p.res_hi && valid;
+                    uint32_t rh[16], rl[16];
                     if (use_res) {
-                        load_plane(p.res_hi, c, gh);  // both planes are in flight together
-                        if (two_plane) load_plane(p.res_lo, c, gl);
+                        ld_global_v8(p.res_hi + res_off + c, rh);
+                        ld_global_v8(p.res_hi + res_off + c + 16, rh + 8);
+                        if (two_plane) {
+                            ld_global_v8(p.res_lo + res_off + c, rl);
+                            ld_global_v8(p.res_lo + res_off + c + 16, rl + 8);
+                        }
                     }
                     tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
@@ -545,30 +505,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                     }
                     if (use_res) {
-                        transpose_plane(gh, rh4);
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) {
+                            float2 r = pf_unpack2(rh[q], p.fmt);
+                            f[2 * q] += r.x;
+                            f[2 * q + 1] += r.y;
+                        }
                         if (two_plane) {
-                            transpose_plane(gl, rl4);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 a = rh4[j], b = rl4[j];
-                                const uint32_t ah[4] = {a.x, a.y, a.z, a.w}, bl[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    f[8 * j + 2 * q + 0] += bf16_lo_to_f32(ah[q]) + bf16_lo_to_f32(bl[q]);
-                                    f[8 * j + 2 * q + 1] += bf16_hi_to_f32(ah[q]) + bf16_hi_to_f32(bl[q]);
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 a = rh4[j];
-                                const uint32_t ah[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    float2 r = pf_unpack2(ah[q], p.fmt);
-                                    f[8 * j + 2 * q + 0] += r.x;
-                                    f[8 * j + 2 * q + 1] += r.y;
-                                }
+                            for (int q = 0; q < 16; ++q) {
+                                f[2 * q] += bf16_lo_to_f32(rl[q]);
+                                f[2 * q + 1] += bf16_hi_to_f32(rl[q]);
                             }
                         }
                     }
@@ -582,33 +529,23 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         }
                         continue;
                     }
-                    uint4 hi4[4], lo4[4];
+                    uint32_t hi[16];
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) hi[q] = pf_pack2(f[2 * q], f[2 * q + 1], p.fmt);
+                    if (valid) {
+                        // The output may be a channel slice: nothing is stored past cout_valid.
+                        if (c < col_lim) st_global_v8(p.out_hi + out_off + c, hi);
+                        if (c + 16 < col_lim) st_global_v8(p.out_hi + out_off + c + 16, hi + 8);
+                    }
                     if (two_plane) {
+                        uint32_t lo[16];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t hi[4], lo[4];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                float x0 = f[8 * j + 2 * q], x1 = f[8 * j + 2 * q + 1];
-                                uint32_t ph = pack_bf16(x0, x1);
-                                hi[q] = ph;
-                                lo[q] = pack_bf16(x0 - bf16_lo_to_f32(ph), x1 - bf16_hi_to_f32(ph));
-                            }
-                            hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                            lo4[j] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        for (int q = 0; q < 16; ++q)
+                            lo[q] = pack_bf16(f[2 * q] - bf16_lo_to_f32(hi[q]), f[2 * q + 1] - bf16_hi_to_f32(hi[q]));
+                        if (valid) {
+                            if (c < col_lim) st_global_v8(p.out_lo + out_off + c, lo);
+                            if (c + 16 < col_lim) st_global_v8(p.out_lo + out_off + c + 16, lo + 8);
                         }
-                        flush_plane(p.out_hi, c, hi4);
-                        flush_plane(p.out_lo, c, lo4);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t hi[4];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                hi[q] = pf_pack2(f[8 * j + 2 * q], f[8 * j + 2 * q + 1], p.fmt);
-                            hi4[j] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        }
-                        flush_plane(p.out_hi, c, hi4);
                     }
                 }
                 ++it;

@@ -542,8 +542,9 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         const int cfg[4] = {6, 12, 48, 32};
         build_densenet(m, batch, cfg, 32, 64);
     } else if (name == "densenet_tiny") {
-        // Same structure with two or three layers per block, for fast tests.
-        const int cfg[4] = {2, 3, 2, 2};
+        // Same structure with a few layers per block (channel counts stay multiples of 32), for
+        // fast tests.
+        const int cfg[4] = {2, 2, 4, 2};
         build_densenet(m, batch, cfg, 32, 64);
     } else if (name == "bert_base" || name == "bert") {
         int seq = opts.seq_len > 0 ? opts.seq_len : 128;
@@ -1075,6 +1076,9 @@ int finalize_model(gpx_model &m) {
             p.out_lo = out.lo;
             p.out = out.layout;
         }
+        // The epilogue moves 32 bytes per access: 16-channel granularity of rows and slices.
+        GPX_REQUIRE(head || (out.layout.C % 16 == 0 && out.ch_off % 16 == 0), GPX_FAIL,
+                    "%s: output channels %d (+%d) not in whole 16-channel groups", n.name.c_str(), out.layout.C, out.ch_off);
         GPX_TRY(make_tmap_2d_bf16(&p.a_hi, in->hi, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
         if (in->lo) GPX_TRY(make_tmap_2d_bf16(&p.a_lo, in->lo, (uint64_t)il.rows, (uint64_t)eff_cin, 128, 64));
         GPX_TRY(make_tmap_2d_bf16(&p.w_hi, w.hi, (uint64_t)w.cout_pad, (uint64_t)w.split_k, bn, 64));

@@ -310,7 +310,7 @@ def mobilenet_v2_forward(params, data, fast=False, taps=None):
     return keep("heads", x.reshape(x.shape[0], -1))
 
 
-DENSENET_CFG = {"densenet201": (6, 12, 48, 32), "densenet_tiny": (2, 3, 2, 2)}
+DENSENET_CFG = {"densenet201": (6, 12, 48, 32), "densenet_tiny": (2, 2, 4, 2)}
 
 
 def densenet_param_shapes(cfg="densenet201", growth=32, init_features=64, num_classes=1000):
