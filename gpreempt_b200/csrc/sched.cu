@@ -203,6 +203,7 @@ struct Dispatcher {
     int device = 0;
     Policy policy = POLICY_YIELD;
     bool hint = true;
+    uint64_t hint_lead_us = 0;
     std::vector<Tenant *> hp, be;
     gpx_word *word = nullptr;
     cudaEvent_t clear_event = nullptr;
@@ -474,6 +475,7 @@ struct Suite {
     int warmup = 5, standalone = 20;
     uint64_t seed = 0;
     bool hint = true;
+    uint64_t hint_lead_us = 0;
     int word_transport = GPX_WORD_DEVICE;
     size_t copy_chunk = 2u << 20;  // best-effort input copies are issued in pieces of this size
     bool resident = false;  // inputs stay in HBM: no per-request host<->device copies
@@ -494,10 +496,19 @@ struct Suite {
         uint64_t t1 = now_ns();  // prepareInput: inputs are pre-generated
         bool hinting = d->hint && t->priority == 0 && d->policy == POLICY_YIELD;
         if (t->preprocess_us) {
-            // The pre-preemption hint of the reference fires ~100 us before the data-prepare
-            // phase ends (gpreemptclient.cpp:203-219); here the word is raised when copyInput
-            // begins, which hides the drain behind the input copy.
-            usleep((useconds_t)t->preprocess_us);
+            // The pre-preemption hint of the reference fires SWITCH_TIME (100 us) before the
+            // data-prepare phase ends (gpreemptclient.cpp:21,203-219).  Here the word is raised
+            // `hint_lead_us` before the end of the phase; with the default 0 it is raised when
+            // copyInput begins, which already hides the drain behind the input copy.  A longer
+            // lead reserves the GPU earlier and costs the best-effort tenants that time.
+            uint64_t lead = hinting ? std::min<uint64_t>(hint_lead_us, t->preprocess_us) : 0;
+            usleep((useconds_t)(t->preprocess_us - lead));
+            if (lead) {
+                t->state.store(ST_HINTED, std::memory_order_release);
+                uint64_t until = now_ns() + lead * 1000;
+                while (now_ns() < until) {
+                }
+            }
         }
         uint64_t t2 = now_ns();
         if (hinting) t->state.store(ST_HINTED, std::memory_order_release);
@@ -590,6 +601,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
     bool rt_only = false, hint = true;
     GPX_TRY(parse_policy(client, &s.policy, &rt_only, &hint));
     s.hint = cfg.has("preempt_hint") ? cfg["preempt_hint"].as_bool() : hint;
+    s.hint_lead_us = (uint64_t)cfg["hint_lead_us"].as_int(0);
     s.time_s = cfg["time"].as_double(1.0);
     if (cfg.has("warmup")) s.warmup = (int)cfg["warmup"].as_int();
     if (cfg.has("standalone")) s.standalone = (int)cfg["standalone"].as_int();
@@ -900,6 +912,7 @@ static int run_suite(Suite &s, Json *report) {
                                                    : "base";
     root.set("policy", pn);
     root.set("preempt_hint", Json(s.hint));
+    root.set("hint_lead_us", Json((int)s.hint_lead_us));
     root.set("resident_inputs", Json(s.resident));
     *report = root;
     return GPX_SUCC;
