@@ -50,6 +50,12 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         err = layernorm_launch(k.ln, k.grid, b, s);
     } else if (k.type == KernelType::Attention) {
         err = attention_launch(k.attn, k.grid, b, s);
+    } else if (k.type == KernelType::AttentionTc) {
+        AttnParams p = k.attn;
+        p.error = e->d_error;
+        err = attention_tc_launch(p, k.grid, b, s);
+    } else if (k.type == KernelType::TransposeV) {
+        err = transpose_v_launch(k.attn, k.grid, b, s);
     } else if (k.type == KernelType::Im2col) {
         err = im2col_launch(k.im2col, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {

@@ -172,8 +172,17 @@ struct AttnParams {
     int fmt;                // PlaneFmt of all four matrices
     float scale;
     int total_tiles;
+    // Tensor-core path (single-plane formats, attention_tcgen05.cu): TMA maps of Q and K
+    // ([B*S][ld], boxes of 128 rows x 64 columns) and of the transposed values
+    // ([B*heads*64][S], boxes of 64 x 64), the transposed-value scratch and the error word.
+    CUtensorMap tq, tk, tvt;
+    bf16_bits *vt;
+    int *error;
 };
 cudaError_t attention_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+cudaError_t attention_tc_prepare();
+cudaError_t attention_tc_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+cudaError_t transpose_v_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
 // Depthwise k x k convolution + bias + activation over split-plane activations; the filter is
 // stored [kh*kw][C] so that eight channels of one tap are one 32-byte load.

@@ -891,11 +891,41 @@ int finalize_model(gpx_model &m) {
             q.heads = n.heads;
             q.ld = n.C;
             q.scale = 0.125f;  // 1 / sqrt(64)
+            kn.flops = 4.0 * n.N * n.heads * (double)n.W * n.W * 64;
+            kn.bytes = 4.0 * 4 * (double)n.N * n.W * n.C;
+            const char *force_simt = getenv("GPX_ATTN");
+            if (m.fmt != PF_SPLIT && !(force_simt && std::string(force_simt) == "simt")) {
+                // Single-plane models: both products on the tensor cores.  The values are first
+                // written with keys contiguous (the B operand of the second product).
+                const size_t vt_elems = (size_t)n.N * n.heads * 64 * n.W;
+                GPX_CUDA(cudaMalloc((void **)&q.vt, vt_elems * sizeof(bf16_bits)));
+                GPX_CUDA(cudaMemset(q.vt, 0, vt_elems * sizeof(bf16_bits)));
+                m.scratch.push_back(q.vt);
+                const uint64_t rows = (uint64_t)n.N * n.W;
+                GPX_TRY(make_tmap_2d_bf16(&q.tq, sq.hi, rows, (uint64_t)n.C, 128, 64));
+                GPX_TRY(make_tmap_2d_bf16(&q.tk, sk.hi, rows, (uint64_t)n.C, 128, 64));
+                GPX_TRY(make_tmap_2d_bf16(&q.tvt, q.vt, (uint64_t)n.N * n.heads * 64, (uint64_t)n.W, 64, 64));
+                GPX_CUDA(attention_tc_prepare());
+                Kernel kt = kn;
+                kt.name = n.name + ".vt";
+                kt.type = KernelType::TransposeV;
+                kt.threads = 256;
+                kt.total_tiles = n.N * n.heads * ((n.W + 63) / 64);
+                kt.grid = (int)std::min<long long>((long long)m.sm_count * 8, kt.total_tiles);
+                kt.flops = 0;
+                kt.bytes = 2.0 * 2 * (double)n.N * n.W * n.C;
+                kt.attn.total_tiles = kt.total_tiles;
+                m.kernels.push_back(kt);
+                kn.type = KernelType::AttentionTc;
+                q.total_tiles = n.N * n.heads * ((n.W + 127) / 128);
+                kn.total_tiles = q.total_tiles;
+                kn.grid = (int)std::min<long long>((long long)m.sm_count * 2, q.total_tiles);
+                m.kernels.push_back(kn);
+                continue;
+            }
             q.total_tiles = n.N * n.heads * ((n.W + 31) / 32);
             kn.total_tiles = q.total_tiles;
             kn.grid = (int)std::min<long long>((long long)m.sm_count * 4, q.total_tiles);
-            kn.flops = 4.0 * n.N * n.heads * (double)n.W * n.W * 64;
-            kn.bytes = 4.0 * 4 * (double)n.N * n.W * n.C;
             m.kernels.push_back(kn);
             continue;
         }
@@ -1366,6 +1396,7 @@ int gpx_model_close(gpx_model *m) {
         if (s.hi && s.parent < 0) cudaFree(s.hi);  // lo lives in the same allocation; slices own nothing
     }
     if (m->identity) cudaFree(m->identity);
+    for (void *ptr : m->scratch) cudaFree(ptr);
     delete m;
     return GPX_SUCC;
 }

@@ -75,7 +75,7 @@ struct Node {
     int scale = -1, shift = -1;    // Affine, or a pooling node that normalises its input: Vec storages
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV };
 
 struct Kernel {
     std::string name;
@@ -114,6 +114,7 @@ struct gpx_model {
     int max_cgemm_grid = 0;
     size_t max_partial_floats = 0;  // split-K workspace an executor must provide
     bool pad_channels = false;      // store activations with channels padded to a multiple of 64
+    std::vector<void *> scratch;         // device buffers owned by the model besides the storages
     gpx::bf16_bits *identity = nullptr;  // 128 x 128 identity matrix in the plane format
     int fmt = 0;                    // PlaneFmt of activations and tensor-core weights (dtype option)
 

@@ -333,16 +333,17 @@ def test_bert_matches_oracle(gpx, oracle, model, batch, seq, layers, heads, voca
     ex.clear()
 
 
-def test_bert_preempt_resume_bit_identical(gpx):
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+def test_bert_preempt_resume_bit_identical(gpx, dtype):
     base = gpx.BaseExecutor()
-    base.init("bert_tiny", batch=8, seed=7, seq_len=128)
+    base.init("bert_tiny", batch=8, seed=7, seq_len=128, dtype=dtype)
     ids = _ids(8, 128, 1000)
     base.set_input("data", ids)
     base.execute()
     want = base.get_output("heads")
     word = gpx.PreemptWord(1)
     ex = gpx.BLPExecutor()
-    ex.init("bert_tiny", batch=8, seq_len=128)
+    ex.init("bert_tiny", batch=8, seq_len=128, dtype=dtype)
     for k, v in base.model.params().items():
         ex.model.set(k, v)
     ex.set_word(word)
@@ -408,17 +409,30 @@ def test_reduced_precision_forward_matches_fp32_oracle(gpx, oracle, model, batch
     ex.clear()
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-def test_reduced_precision_bert_matches_oracle(gpx, oracle, dtype):
+@pytest.mark.parametrize("model,batch,seq,layers,heads,vocab,dtype", [
+    ("bert_base", 1, 128, 12, 12, 30522, "bfloat16"), ("bert_base", 1, 128, 12, 12, 30522, "float16"),
+    ("bert_tiny", 2, 40, 2, 2, 1000, "float16"), ("bert_tiny", 3, 200, 2, 2, 1000, "bfloat16"),
+    ("bert_base", 2, 512, 12, 12, 30522, "float16")])
+def test_reduced_precision_bert_matches_oracle(gpx, oracle, model, batch, seq, layers, heads, vocab, dtype):
+    """Single-plane BERT: dense layers and both attention products on the tensor cores (sequence
+    lengths that are and are not multiples of the 128-key block), against the float64 oracle; the
+    attention context is also checked on its own."""
     ex = gpx.BaseExecutor()
-    ex.init("bert_base", batch=1, seed=7, seq_len=128, dtype=dtype)
-    ids = _ids(1, 128, 30522)
+    ex.init(model, batch=batch, seed=7, seq_len=seq, dtype=dtype)
+    names = [ex.model.get_kernel_info(i)["name"] for i in range(ex.get_kernel_num())]
+    assert any(n.endswith(".vt") for n in names), "tensor-core attention not selected"
+    ids = _ids(batch, seq, vocab)
     ex.set_input("data", ids)
     ex.execute()
     assert ex.error() == (0, 0)
     got = ex.get_output("heads")
+    ex.execute()
+    assert np.array_equal(got, ex.get_output("heads"))
     params = {k: v.reshape(v.shape[0], -1) if v.ndim == 4 else v for k, v in ex.model.params().items()}
-    want = oracle.bert_forward(params, ids, layers=12, heads=12)
+    taps = {}
+    want = oracle.bert_forward(params, ids, layers=layers, heads=heads, taps=taps)
+    ctx = ex.model.get("encoder.layer.0.attention.context").reshape(taps["encoder.layer.0.attention.context"].shape)
+    assert _rel(ctx, taps["encoder.layer.0.attention.context"]) <= RTOL_16BIT
     assert _rel(got, want) <= RTOL_16BIT
     ex.clear()
 
