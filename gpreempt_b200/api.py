@@ -428,6 +428,9 @@ class Executor:
         check(B.load().gpx_exec_error(self.handle, ctypes.byref(code), ctypes.byref(where)))
         return code.value, where.value
 
+    def set_restart_policy(self, drop_tile_in_flight: bool) -> None:
+        check(B.load().gpx_exec_set_restart_policy(self.handle, 1 if drop_tile_in_flight else 0))
+
     def reset_cursors(self, stream=None) -> None:
         check(B.load().gpx_exec_reset_cursors(self.handle, _h(stream)))
 

@@ -134,6 +134,7 @@ _SIGS = {
     "gpx_exec_cursor_dptr": [vp, P(vp)],
     "gpx_exec_error": [vp, P(ci), P(ci)],
     "gpx_exec_reset_cursors": [vp, vp],
+    "gpx_exec_set_restart_policy": [vp, ctypes.c_int],
     "gpx_exec_read_cursors": [vp, P(ci), sz, P(sz)],
     "gpx_run_workload": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, sz, P(sz)],
     "gpx_clock_offset_ns": [P(i64), P(i64)],

@@ -32,7 +32,7 @@ constexpr int kCBM = 128, kCBK = 64, kCUmmaK = 16;
 constexpr int kCgemmThreads = 320;
 constexpr int kCEpiThreads = 256;
 constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
-constexpr int kCPollEvery = 2;
+constexpr int kCPollEvery = 1;
 
 template <int BN>
 struct CgemmCfg {
@@ -560,7 +560,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 continue;
             }
             // CEPI_PARTIAL
-            if (k_done > seg_k0) {
+            const int keep_k = p.drop_on_stop ? 0 : k_done;
+            if (keep_k > seg_k0) {
                 for (int c = s_lo; c < s_hi; c += 32) {
                     tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
@@ -572,7 +573,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
             if (leader) {
                 slot->next_iter = it;
-                slot->k_done = k_done;
+                slot->k_done = keep_k;
                 slot->grid = gridDim.x;
                 if (blp.stop_index) atomicCAS(blp.stop_index, -1, blp.kernel_id);
             }

@@ -39,6 +39,7 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         p.spill = e->d_spill;
         p.error = e->d_error;
         if (p.k_splits > 1) p.partial = e->d_partial;
+        p.drop_on_stop = e->drop_tile_in_flight ? 1 : 0;
         err = cgemm_launch(p, k.tile, k.grid, b, s);
     } else if (k.type == KernelType::SplitK) {
         SplitKParams p = k.splitk;
@@ -247,6 +248,12 @@ int gpx_exec_error(gpx_exec *e, int *code, int *where) {
     GPX_CUDA(cudaMemcpy(h, e->d_error, sizeof(h), cudaMemcpyDeviceToHost));
     *code = h[0];
     if (where) *where = h[1];
+    return GPX_SUCC;
+}
+
+int gpx_exec_set_restart_policy(gpx_exec *e, int drop_tile_in_flight) {
+    GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
+    e->drop_tile_in_flight = drop_tile_in_flight != 0;
     return GPX_SUCC;
 }
 

@@ -21,6 +21,7 @@ struct gpx_exec {
     unsigned long long *h_trace = nullptr;  // pinned landing area for asynchronous trace read-back
     int stop_index = -1;
     bool trace_on = false;
+    bool drop_tile_in_flight = false;  // restart policy of the tensor-core kernels (gpx_exec_set_restart_policy)
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
 };

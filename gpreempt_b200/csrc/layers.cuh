@@ -57,6 +57,8 @@ struct CgemmParams {
     // identity; res_hi/res_lo are then null and the epilogue adds nothing.
     CUtensorMap r_hi, r_lo, ident;
     int res_kb;
+    int drop_on_stop;        // 1: a tile interrupted by the word is recomputed from K block 0 after the
+                             // resume instead of being saved (no spill on the way out)
     int dual;                // 1: two accumulators per tile in two TMEM buffers (short K ranges and
                              // single-plane operands), 0: four accumulators in one buffer
     int k_splits;            // >= 1: the K range is cut into this many tiles per output block

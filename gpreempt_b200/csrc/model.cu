@@ -645,6 +645,11 @@ static ActView view_of(const gpx_model &m, const Node &node) {
     return v;
 }
 
+// Largest tile of the memory-bound kernels, in 8-channel vectors.  A claimed tile always completes
+// (scripts/compile/convert_to_blp.py:39-70), so the tile bounds the drain after a preemption: 2048
+// vectors of the stem's 3x3 max pooling took 86 us, 256 keep every such kernel under ~10 us.
+constexpr long long kMaxTileVectors = 256;
+
 int finalize_model(gpx_model &m) {
     const DeviceInfo &d = device_info();
     GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
@@ -815,7 +820,7 @@ int finalize_model(gpx_model &m) {
             // Enough tiles to fill the GPU even when the tensor is small (global average pool).
             long long want_tiles = 4LL * m.sm_count;
             p.tile_elems = (int)std::max<long long>(mode == 1 && k * k >= 16 ? 8 : 64,
-                                                    std::min<long long>(2048, total / want_tiles / 8 * 8));
+                                                    std::min<long long>(kMaxTileVectors, total / want_tiles / 8 * 8));
             p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
             kn.total_tiles = p.total_tiles;
             kn.grid = pool_grid(p, m.sm_count);
@@ -949,7 +954,7 @@ int finalize_model(gpx_model &m) {
             q.pad = n.pad;
             q.act = n.act;
             long long total = (long long)n.N * n.H * n.W * (q.out.C / 8);
-            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2048, total / (8LL * m.sm_count) / 32 * 32));
+            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(kMaxTileVectors, total / (8LL * m.sm_count) / 32 * 32));
             q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
             kn.total_tiles = q.total_tiles;
             kn.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
@@ -1038,7 +1043,8 @@ int finalize_model(gpx_model &m) {
             q.Kp = (int)pm.dims[1];
             q.M = n.N * n.H * n.W;
             long long total = (long long)q.M * (q.Kp / 8);
-            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2048, total / (8LL * m.sm_count) / 32 * 32));
+            // (twice the usual cap: a patch-matrix tile re-reads its lookup table, ~5 us per 256 vectors)
+            q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2 * kMaxTileVectors, total / (8LL * m.sm_count) / 32 * 32));
             q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
             ki.total_tiles = q.total_tiles;
             ki.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);

@@ -476,6 +476,7 @@ struct Suite {
     uint64_t seed = 0;
     bool hint = true;
     uint64_t hint_lead_us = 0;
+    bool drop_tile = false;
     int word_transport = GPX_WORD_DEVICE;
     size_t copy_chunk = 2u << 20;  // best-effort input copies are issued in pieces of this size
     bool resident = false;  // inputs stay in HBM: no per-request host<->device copies
@@ -584,7 +585,7 @@ static Json summarize(const std::vector<double> &v) {
 static int parse_policy(const std::string &client, Policy *p, bool *rt_only, bool *hint) {
     *rt_only = false;
     *hint = true;
-    if (client == "gpreemptclient") *p = POLICY_YIELD;
+    if (client == "gpreemptclient" || client == "reefclient") *p = POLICY_YIELD;
     else if (client == "gpreemptclient_wo") { *p = POLICY_YIELD; *hint = false; }
     else if (client == "blpclient") *p = POLICY_BLP_WAIT;
     else if (client == "baseclient") *p = POLICY_BASE;
@@ -600,6 +601,9 @@ static int parse_policy(const std::string &client, Policy *p, bool *rt_only, boo
 static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
     bool rt_only = false, hint = true;
     GPX_TRY(parse_policy(client, &s.policy, &rt_only, &hint));
+    // "reefclient": the GP policy with REEF's reset-and-restart treatment of the interrupted tile
+    // (gpx_exec_set_restart_policy); the key overrides it for any client.
+    s.drop_tile = cfg.has("drop_tile_in_flight") ? cfg["drop_tile_in_flight"].as_bool() : client == "reefclient";
     s.hint = cfg.has("preempt_hint") ? cfg["preempt_hint"].as_bool() : hint;
     s.hint_lead_us = (uint64_t)cfg["hint_lead_us"].as_int(0);
     s.time_s = cfg["time"].as_double(1.0);
@@ -665,6 +669,7 @@ static int init_tenant(Suite &s, Tenant *t) {
     bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);
     GPX_TRY(gpx_exec_create(t->model, blp ? GPX_EXEC_BLP : GPX_EXEC_BASE, &t->exec));
     if (blp) GPX_TRY(gpx_exec_enable_trace(t->exec, 1));
+    if (blp && s.drop_tile) GPX_TRY(gpx_exec_set_restart_policy(t->exec, 1));
     Dispatcher *d = s.dispatcher_for(t->gpu);
     if (blp) GPX_TRY(gpx_exec_set_word(t->exec, d->word));
     gpx_stream st;
@@ -912,6 +917,7 @@ static int run_suite(Suite &s, Json *report) {
                                                    : "base";
     root.set("policy", pn);
     root.set("preempt_hint", Json(s.hint));
+    root.set("drop_tile_in_flight", Json(s.drop_tile));
     root.set("hint_lead_us", Json((int)s.hint_lead_us));
     root.set("resident_inputs", Json(s.resident));
     *report = root;

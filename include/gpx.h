@@ -292,6 +292,14 @@ int gpx_exec_error(gpx_exec *e, int *code, int *where);
 /* Zeroes every kernel's tile cursor and progress slot on `s`, as BLPExecutor::execute does
  * before launching (src/executor.cpp:212-214); lets kernels be relaunched one by one. */
 int gpx_exec_reset_cursors(gpx_exec *e, gpx_stream s);
+/* What a tensor-core kernel does with the output tile it is accumulating when the word is raised.
+ * 0 (default): the accumulators and the K position are saved and the tile continues after the
+ * resume.  1: the tile is dropped and computed again from its first K block after the resume -
+ * REEF's reset-and-restart (src/reef-client/reef_scheduler.cpp:316-357,460-510: kill the
+ * best-effort kernels, restart from kernel_offset; its kernels are idempotent, as these tiles are)
+ * at tile granularity: nothing is written on the way out, so the drain is shorter, at the cost of
+ * repeating up to one tile of work per CTA.  Either way the result is bit-identical. */
+int gpx_exec_set_restart_policy(gpx_exec *e, int drop_tile_in_flight);
 /* Device address of the executed[] cursor array (one int per kernel); zeroing it re-arms every
  * kernel for a full run, as BLPExecutor::execute does (src/executor.cpp:212-214). */
 int gpx_exec_cursor_dptr(gpx_exec *e, void **dptr);

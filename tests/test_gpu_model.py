@@ -437,16 +437,20 @@ def test_reduced_precision_bert_matches_oracle(gpx, oracle, model, batch, seq, l
     ex.clear()
 
 
-def test_reduced_precision_preempt_resume_bit_identical(gpx):
+@pytest.mark.parametrize("dtype,drop", [("float16", False), ("float32", True), ("float16", True)])
+def test_reduced_precision_preempt_resume_bit_identical(gpx, dtype, drop):
+    """Preempt and resume in the single-plane format, and with the restart policy that drops the
+    tile in flight (REEF's reset-and-restart at tile granularity) instead of saving it."""
     base = gpx.BaseExecutor()
-    base.init("resnet50", batch=8, seed=1, dtype="float16")
+    base.init("resnet50", batch=8, seed=1, dtype=dtype)
     data = _data(gpx, 8)
     base.set_input("data", data)
     base.execute()
     want = _all_activations(base)
     word = gpx.PreemptWord(1)
     ex = gpx.BLPExecutor()
-    ex.init("resnet50", batch=8, dtype="float16")
+    ex.init("resnet50", batch=8, dtype=dtype)
+    ex.set_restart_policy(drop)
     for k, v in base.model.params().items():
         ex.model.set(k, v)
     ex.set_word(word)

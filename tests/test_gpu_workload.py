@@ -33,7 +33,7 @@ REPORT_KEYS = ["avgThroughput(req/s)", "standAloneTotalLatency(us)", "avgPrepare
 
 
 @pytest.mark.parametrize("client", ["gpreemptclient", "gpreemptclient_wo", "blpclient",
-                                    "baseclient", "seqclient"])
+                                    "baseclient", "seqclient", "reefclient"])
 def test_policy_runs_and_reports(gpx, client):
     rep = json.loads(gpx.run_workload(client, json.dumps(_config())))
     tasks = {t["id"]: t for t in rep["tasks"]}
@@ -47,7 +47,8 @@ def test_policy_runs_and_reports(gpx, client):
     assert 100 <= tasks["tiny_rt"]["requests"] <= 300
     assert tasks["tiny_rt"]["avgPreprocessLatency(us)"] >= 50
     g = rep["gpus"][0]
-    if client in ("gpreemptclient", "gpreemptclient_wo", "blpclient"):
+    assert rep["drop_tile_in_flight"] is (client == "reefclient")
+    if client in ("gpreemptclient", "gpreemptclient_wo", "blpclient", "reefclient"):
         assert g["wordRaises"] > 0
         assert g["beResumes"] >= 0
     else:
