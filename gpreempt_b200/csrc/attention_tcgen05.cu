@@ -41,7 +41,6 @@ __device__ __forceinline__ void fa_st_v8(void *ptr, const uint32_t *r) {
 
 __global__ void __launch_bounds__(kFaThreads)
 attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
-    pdl_enter();
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     unsigned char *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -60,12 +59,14 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
         ctl->abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
-        trace_begin(blp);
     }
     if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem_base), kFaTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    pdl_wait();  // the prologue above overlapped the predecessor's tail
+    pdl_launch_dependents();
+    if (tid == 0) trace_begin(blp);
     const uint32_t tmem = ctl->tmem_base;
     const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
     const uint32_t idesc_s = p.fmt == PF_F16 ? make_idesc_f16_f32(128, 128) : make_idesc_bf16_f32(128, 128);

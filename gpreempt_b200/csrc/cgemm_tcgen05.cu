@@ -63,12 +63,17 @@ struct CgemmControl {
     int epi_kind[2];
     int epi_k_done[2];
     int epi_go;
+    int raised;  // the word was up when this CTA started
     int abort_flag;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&p);
+}
+// Pulls a TMA descriptor (kernel parameter) into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const void *tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 // 256-bit global accesses (32-byte aligned): one whole sector per lane.
 __device__ __forceinline__ void ld_global_v8(const void *ptr, uint32_t *r) {
@@ -91,7 +96,8 @@ __global__ void __launch_bounds__(kCgemmThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     using Cfg = CgemmCfg<BN>;
     constexpr int kStages = Cfg::kStages;
-    pdl_enter();
+    // The prologue below (barriers, tensor memory, descriptor prefetch) touches nothing a
+    // predecessor kernel writes, so it runs while that kernel drains; pdl_wait() comes after it.
     extern __shared__ unsigned char smem_raw[];
     uint32_t raw_addr = smem_u32(smem_raw);
     uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -125,32 +131,6 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
 
     CgemmSlot *slot = p.slots + blockIdx.x;
     float *spill = p.spill + (size_t)blockIdx.x * (kCBM * Cfg::kTmemCols);
-    // A non-preemptible launch never stops early, so it neither reads nor writes the cursor.
-    const int first_iter = resumable ? slot->next_iter : 0;
-    const int first_k = resumable ? slot->k_done : 0;
-    const int slot_grid = resumable ? slot->grid : 0;
-
-    // A kernel that starts while the word is raised (it was queued behind the stop point) leaves
-    // at once, before it allocates tensor memory or touches a barrier: the cursor is unchanged,
-    // the stop point is recorded if this CTA still has work (kernel_transform_be.py:10-12).
-    if (resumable) {
-        __shared__ int s_raised;
-        if (threadIdx.x == 0) {
-            s_raised = load_word(blp.preempted);
-            if (s_raised) {
-                if ((int)blockIdx.x + first_iter * (int)gridDim.x < total_tiles && blp.stop_index)
-                    atomicCAS(blp.stop_index, -1, blp.kernel_id);
-                if (blp.trace) {
-                    unsigned long long t = globaltimer_ns();
-                    atomicMin(blp.trace + 0, t);
-                    atomicMin(blp.trace + 2, t);
-                    atomicMax(blp.trace + 1, t);
-                }
-            }
-        }
-        __syncthreads();
-        if (s_raised) return;
-    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -165,15 +145,59 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         }
         ctl->abort_flag = 0;
         ctl->epi_go = 0;
+        ctl->raised = 0;
         fence_barrier_init();
         fence_proxy_async();
-        trace_begin(blp);
+        prefetch_tensormap(&p.a_hi);
+        prefetch_tensormap(&p.w_hi);
+        if (two_plane) {
+            prefetch_tensormap(&p.a_lo);
+            prefetch_tensormap(&p.w_lo);
+        }
     }
     if (warp == 1) tmem_alloc(smem_u32(&ctl->tmem_base), Cfg::kTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
+
+    pdl_wait();  // from here on the predecessor's results (and this executor's slots) are visible
+    pdl_launch_dependents();
+
+    // A non-preemptible launch never stops early, so it neither reads nor writes the cursor.
+    const int first_iter = resumable ? slot->next_iter : 0;
+    const int first_k = resumable ? slot->k_done : 0;
+    const int slot_grid = resumable ? slot->grid : 0;
+
+    // A kernel that starts while the word is raised (it was queued behind the stop point) leaves
+    // at once: the cursor is unchanged, the stop point is recorded if this CTA still has work
+    // (kernel_transform_be.py:10-12).
+    if (resumable) {
+        if (threadIdx.x == 0) {
+            const int raised = load_word(blp.preempted);
+            if (raised) {
+                if ((int)blockIdx.x + first_iter * (int)gridDim.x < total_tiles && blp.stop_index)
+                    atomicCAS(blp.stop_index, -1, blp.kernel_id);
+                if (blp.trace) {
+                    unsigned long long t = globaltimer_ns();
+                    atomicMin(blp.trace + 0, t);
+                    atomicMin(blp.trace + 2, t);
+                    atomicMax(blp.trace + 1, t);
+                }
+            }
+            ctl->raised = raised;
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (ctl->raised) {
+            if (warp == 1) {
+                tc_fence_after_sync();
+                tmem_dealloc(tmem_base, Cfg::kTmemCols);
+            }
+            return;
+        }
+    }
+    if (threadIdx.x == 0) trace_begin(blp);
 
     const bool grid_ok = slot_grid == 0 || slot_grid == (int)gridDim.x;
     auto fail = [&](int code) {
