@@ -122,7 +122,7 @@ def measured_peaks() -> tuple[dict, str]:
 # DRAM bytes (read + write) the 54 tensor-core convolution launches of one ResNet-50 b32 fp32
 # forward move, from an ncu capture of `python -m gpreempt_b200.profile_step model --model resnet50
 # --batch 32` (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one forward).
-NCU_CONV_DRAM_BYTES_PER_STEP = 2.673e9
+NCU_CONV_DRAM_BYTES_PER_STEP = 2.684e9
 
 
 def conv_roofline(api, device: int) -> dict:
