@@ -54,12 +54,12 @@ enum : int { CMSG_DATA = 0, CMSG_STOP = 1, CMSG_EXIT = 2, CMSG_RES = 3 };
 enum : int { CEPI_COMPLETE = 0, CEPI_PARTIAL = 1, CEPI_EXIT = 2 };
 
 struct CgemmControl {
-    unsigned long long full[4];
-    unsigned long long empty[4];
+    unsigned long long full[8];
+    unsigned long long empty[8];
     unsigned long long tmem_full[2];   // one per accumulator buffer
     unsigned long long tmem_empty[2];
     uint32_t tmem_base;
-    int stage_msg[4];
+    int stage_msg[8];
     int epi_kind[2];
     int epi_k_done[2];
     int epi_go;
@@ -122,6 +122,12 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     const bool resumable = blp.preempted != nullptr;
     // Two-plane operands (float32 models) or one 16-bit plane (reduced-precision models).
     const bool two_plane = p.fmt == PF_SPLIT;
+    // A ring stage holds the A and W tiles of one K block: hi and lo planes of both for float32
+    // models; single-plane models use half of that per stage and get twice as many stages, which
+    // doubles the bytes TMA keeps in flight.
+    const int nst = two_plane ? kStages : 2 * kStages;
+    const uint32_t stage_bytes = two_plane ? Cfg::kStageBytes : Cfg::kStageBytes / 2;
+    const uint32_t w_off = two_plane ? 2 * Cfg::kABytes : Cfg::kABytes;  // W (hi) tile inside a stage
     // Accumulator plan.  dual: two accumulators per tile (BN columns each) in two buffers, so the
     // epilogue of one tile overlaps the K loop of the next; used when the K range is short or the
     // operands are single-plane.  Otherwise four accumulators in one buffer (see the MMA issuer).
@@ -133,7 +139,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     float *spill = p.spill + (size_t)blockIdx.x * (kCBM * Cfg::kTmemCols);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < nst; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
@@ -249,12 +255,12 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         const int rb = kb - main_kb;
                         ctl->stage_msg[stage] = CMSG_RES + rb;
                         mbar_arrive_expect_tx(bar, (two_plane ? 2 : 1) * Cfg::kABytes + ident_bytes);
-                        const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
+                        const uint32_t dst = smem_base + stage * stage_bytes;
                         tma_load_2d(dst, &p.r_hi, bar, n_blk * BN + rb * kCBK, m_blk * kCBM);
                         if (two_plane) tma_load_2d(dst + Cfg::kABytes, &p.r_lo, bar, n_blk * BN + rb * kCBK, m_blk * kCBM);
                         if (ident_bytes) tma_load_2d(smem_base + ident_off, &p.ident, bar, 0, 0);
                         ident_bytes = 0;
-                        if (++stage == kStages) {
+                        if (++stage == nst) {
                             stage = 0;
                             phase ^= 1;
                         }
@@ -266,16 +272,16 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     mbar_arrive_expect_tx(bar, (two_plane ? Cfg::kStageBytes : Cfg::kABytes + Cfg::kWBytes) + ident_bytes);
                     if (ident_bytes) tma_load_2d(smem_base + ident_off, &p.ident, bar, 0, 0);
                     ident_bytes = 0;
-                    const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t dst = smem_base + stage * stage_bytes;
                     const int a_row = m_blk * kCBM + p.tap_shift[tap];
                     const int w_col = tap * p.cin + cb * kCBK;
                     tma_load_2d(dst, &p.a_hi, bar, cb * kCBK, a_row);
-                    tma_load_2d(dst + 2 * Cfg::kABytes, &p.w_hi, bar, w_col, n_blk * BN);
+                    tma_load_2d(dst + w_off, &p.w_hi, bar, w_col, n_blk * BN);
                     if (two_plane) {
                         tma_load_2d(dst + Cfg::kABytes, &p.a_lo, bar, cb * kCBK, a_row);
                         tma_load_2d(dst + 2 * Cfg::kABytes + Cfg::kWBytes, &p.w_lo, bar, w_col, n_blk * BN);
                     }
-                    if (++stage == kStages) {
+                    if (++stage == nst) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -331,10 +337,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
                     break;
                 }
-                const uint32_t base = smem_base + stage * Cfg::kStageBytes;
+                const uint32_t base = smem_base + stage * stage_bytes;
                 const uint64_t a_hi = make_smem_desc_sw128(base);
                 const uint64_t a_lo = make_smem_desc_sw128(base + Cfg::kABytes);
-                const uint64_t w_hi = make_smem_desc_sw128(base + 2 * Cfg::kABytes);
+                const uint64_t w_hi = make_smem_desc_sw128(base + w_off);
                 const uint64_t w_lo = make_smem_desc_sw128(base + 2 * Cfg::kABytes + Cfg::kWBytes);
 #pragma unroll
                 for (int k = 0; k < kCBK / kCUmmaK; ++k) {
@@ -373,7 +379,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                 }
                 mma_commit(smem_u32(&ctl->empty[stage]));
-                if (++stage == kStages) {
+                if (++stage == nst) {
                     stage = 0;
                     phase ^= 1;
                 }

@@ -613,6 +613,10 @@ static int stored_c(const gpx_model &m, const Node &n) {
     return s.cs ? s.cs : n.C;
 }
 
+static bool full_map_dense(const Node &n, const Node &src) {
+    return n.op == Op::Conv && n.k > 1 && n.k == src.H && n.k == src.W && n.pad == 0 && n.stride == 1;
+}
+
 static bool tensor_core_shape(const gpx_model &m, const Node &n, const Node &src) {
     if (n.op != Op::Conv) return false;
     // Input channels in whole 64-wide K blocks; output channels in 16-byte vectors (the epilogue
@@ -622,6 +626,9 @@ static bool tensor_core_shape(const gpx_model &m, const Node &n, const Node &src
     if (n.k == 1 && n.pad == 0 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
     if (n.k == 3 && n.pad == 1 && n.stride == 1) return true;
     if (n.k == 3 && n.pad == 1 && n.stride == 2) return src.H % 2 == 0 && src.W % 2 == 0;
+    // A filter that covers the whole feature map (the first dense layer of VGG): with plain rows
+    // the (h, w, c) values of one image are contiguous, so the layer is a GEMM over [N][H*W*C].
+    if (full_map_dense(n, src)) return (long long)n.k * n.k * stored_c(m, src) % 64 == 0;
     return false;
 }
 
@@ -683,6 +690,7 @@ int finalize_model(gpx_model &m) {
     std::vector<bool> conflict(m.storages.size(), false);
     for (auto &n : m.nodes) {
         if (n.op != Op::Conv || !n.tensor_core || n.k != 3 || n.via_im2col) continue;
+        if (full_map_dense(n, m.nodes[n.inputs[0]])) continue;
         int st = m.nodes[n.inputs[0]].storage;
         int want = wanted_order(n);
         if (votes[st] >= 0 && votes[st] != want) conflict[st] = true;
@@ -694,9 +702,10 @@ int finalize_model(gpx_model &m) {
     for (auto &n : m.nodes) {
         if (n.op != Op::Conv || !n.tensor_core || n.via_im2col) continue;
         int st = m.nodes[n.inputs[0]].storage;
-        if (n.k == 3 && order[st] != wanted_order(n)) n.tensor_core = false;
+        if (n.k == 3 && !full_map_dense(n, m.nodes[n.inputs[0]]) && order[st] != wanted_order(n)) n.tensor_core = false;
         if (n.k == 1 && order[st] == ACT_PHASED) n.tensor_core = false;
         if (n.k == 1 && n.stride == 2 && order[st] != ACT_PLAIN) n.tensor_core = false;
+        if (full_map_dense(n, m.nodes[n.inputs[0]]) && order[st] != ACT_PLAIN) n.tensor_core = false;
         if (n.residual >= 0 && m.storages[m.nodes[n.residual].storage].kind != Storage::ActSplit)
             n.tensor_core = false;
     }
@@ -1065,13 +1074,19 @@ int finalize_model(gpx_model &m) {
         kn.type = KernelType::Cgemm;
         kn.threads = 320;
         CgemmParams &p = kn.cgemm;
-        const ActLayout &il = in->layout;
+        ActLayout il = in->layout;
+        if (full_map_dense(n, src) && !n.via_im2col) {
+            // one GEMM row per image, K = (h, w, c) in the stored order
+            eff_cin = n.k * n.k * stored_c(m, src);
+            eff_k = 1;
+            il = make_layout(n.N, 1, 1, eff_cin, ACT_PLAIN);
+        }
         const bool head = out.kind == Storage::OutputF32;
         const int cout_st = head ? n.C : stored_c(m, n);  // output channels as stored
         int bn = (cout_st % 128 == 0 || head) ? 128 : 64;
         {
             // Few output tiles (batch 1, late stages): narrower column tiles expose more CTAs.
-            long long tiles128 = (long long)((in->layout.plane + 127) / 128) * ((cout_st + 127) / 128);
+            long long tiles128 = (long long)((il.plane + 127) / 128) * ((cout_st + 127) / 128);
             if (tiles128 * 2 <= m.sm_count) bn = 64;
         }
         kn.tile = bn;
