@@ -294,7 +294,7 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
     const int C8 = p.channels / 8;
     const int Ho = p.out.H, Wo = p.out.W;
     const int H = p.in.l.H, W = p.in.l.W;
-    const long long total = (long long)p.out.N * Ho * Wo * C8;
+    const unsigned total = (unsigned)p.out.N * Ho * Wo * C8;  // < 2^31, checked when the model is built
     int iter = 0;
     for (;;) {
         int tile;
@@ -306,16 +306,16 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        long long begin = (long long)tile * p.tile_elems;
-        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        const unsigned begin = (unsigned)tile * p.tile_elems;
+        const unsigned end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
         if (p.mode == 1 && p.k * p.k >= 16) {
             // Large averaging window (global average pool): one warp per output vector, lanes
             // take taps lane, lane+32, ...; a fixed shuffle tree adds the lane sums, so the
             // result is the same on every run.
             const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-            for (long long e = begin + wid; e < end; e += kPoolThreads / 32) {
+            for (unsigned e = begin + wid; e < end; e += kPoolThreads / 32) {
                 int c8 = (int)(e % C8);
-                long long t = e / C8;
+                unsigned t = e / C8;
                 int wo = (int)(t % Wo);
                 t /= Wo;
                 int ho = (int)(t % Ho);
@@ -354,9 +354,9 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
             if (dynamic) __syncthreads();
             continue;
         }
-        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+        for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
             int c8 = (int)(e % C8);
-            long long t = e / C8;
+            unsigned t = e / C8;
             int wo = (int)(t % Wo);
             t /= Wo;
             int ho = (int)(t % Ho);
@@ -408,7 +408,7 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
     const int K8 = p.Kp / 8;
-    const long long total = (long long)p.M * K8;
+    const unsigned total = (unsigned)p.M * K8;
     const int H = p.in.l.H, W = p.in.l.W;
     // Column k of the patch matrix is filter tap (fh, fw) of channel ci; the decomposition and,
     // for an fp32 NCHW input, the element offset relative to the window origin are tabulated
@@ -437,9 +437,9 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        long long begin = (long long)tile * p.tile_elems;
-        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
-        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+        const unsigned begin = (unsigned)tile * p.tile_elems;
+        const unsigned end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
             int k8 = (int)(e % K8);
             int m = (int)(e / K8);
             int wo = m % p.Wo;
@@ -482,7 +482,7 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
     const int C8 = p.cout_padded / 8;
-    const long long total = (long long)p.m_rows * C8;
+    const unsigned total = (unsigned)p.m_rows * C8;
     const int img = p.in_hs * p.in_ws;
     int iter = 0;
     for (;;) {
@@ -495,9 +495,9 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        long long begin = (long long)tile * p.tile_elems;
-        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
-        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+        const unsigned begin = (unsigned)tile * p.tile_elems;
+        const unsigned end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
             const int c8 = (int)(e % C8);
             const int vrow = (int)(e / C8);
             const int n_img = vrow / img;
@@ -562,7 +562,7 @@ dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
     const int C8 = C / 8;
     const int Ho = p.out.H, Wo = p.out.W;
     const int H = p.in.l.H, W = p.in.l.W;
-    const long long total = (long long)p.out.N * Ho * Wo * C8;
+    const unsigned total = (unsigned)p.out.N * Ho * Wo * C8;  // < 2^31, checked when the model is built
     int iter = 0;
     for (;;) {
         int tile;
@@ -574,11 +574,11 @@ dwconv_kernel(const __grid_constant__ DwConvParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        long long begin = (long long)tile * p.tile_elems;
-        long long end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
-        for (long long e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+        const unsigned begin = (unsigned)tile * p.tile_elems;
+        const unsigned end = begin + p.tile_elems < total ? begin + p.tile_elems : total;
+        for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
             int c8 = (int)(e % C8);
-            long long t = e / C8;
+            unsigned t = e / C8;
             int wo = (int)(t % Wo);
             t /= Wo;
             int ho = (int)(t % Ho);

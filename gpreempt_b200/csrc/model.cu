@@ -828,8 +828,12 @@ int finalize_model(gpx_model &m) {
             long long total = (long long)dst.layout.N * dst.layout.H * dst.layout.W * (p.channels / 8);
             // Enough tiles to fill the GPU even when the tensor is small (global average pool).
             long long want_tiles = 4LL * m.sm_count;
+            // the cap is per unit of work: a copy or an affine map reads one tap per vector, a 3x3
+            // pooling nine
+            const int taps_per_vec = mode == 2 ? 1 : k * k;
+            const long long tile_cap = std::min<long long>(2048, std::max<long long>(kMaxTileVectors, 9 * kMaxTileVectors / taps_per_vec));
             p.tile_elems = (int)std::max<long long>(mode == 1 && k * k >= 16 ? 8 : 64,
-                                                    std::min<long long>(kMaxTileVectors, total / want_tiles / 8 * 8));
+                                                    std::min<long long>(tile_cap, total / want_tiles / 8 * 8));
             p.total_tiles = (int)((total + p.tile_elems - 1) / p.tile_elems);
             kn.total_tiles = p.total_tiles;
             kn.grid = pool_grid(p, m.sm_count);
