@@ -154,8 +154,8 @@ def conv_roofline(api, device: int) -> dict:
         for i in range(nk):
             per_kernel[i] += events[i].elapsed_ms(events[i + 1]) / reps
     assert ex.error() == (0, 0), ex.error()
-    # tensor-core convolutions run 320-thread CTAs; everything else is a CUDA-core kernel
-    tc = [i for i in range(nk) if infos[i]["launch_params"][3] == 320]
+    # tensor-core convolutions run CTAs of more than 256 threads; everything else is a CUDA-core kernel
+    tc = [i for i in range(nk) if infos[i]["launch_params"][3] > 256]
     dominant = tc if tc else [i for i in range(nk) if "pool" not in infos[i]["name"]]
     flops = sum(infos[i]["flops"] for i in dominant)
     ms = sum(per_kernel[i] for i in dominant)

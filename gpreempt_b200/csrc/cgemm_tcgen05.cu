@@ -26,11 +26,13 @@ namespace gpx {
 using namespace sm100;
 
 constexpr int kCBM = 128, kCBK = 64, kCUmmaK = 16;
-// Warp 0 feeds TMA, warp 1 issues MMAs, warps 2-9 are the epilogue: two warps per TMEM lane
-// quarter, each taking half of the columns, so twice as many loads and stores are in flight
-// while a tile is drained (the epilogue, not the tensor pipe, bounds the small-K layers).
-constexpr int kCgemmThreads = 320;
-constexpr int kCEpiThreads = 256;
+// Warp 0 feeds TMA, warp 1 issues MMAs, the other warps are the epilogue: kCEpiParts warps per
+// TMEM lane quarter, each taking an equal share of the columns in 16-column pieces, so that
+// enough independent TMEM loads, conversions and stores are in flight while a tile is drained
+// (the epilogue, not the tensor pipe, bounds the small-K layers).
+constexpr int kCEpiParts = 2;                       // epilogue warps per TMEM lane quarter
+constexpr int kCEpiThreads = 128 * kCEpiParts;
+constexpr int kCgemmThreads = 64 + kCEpiThreads;
 constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
 constexpr int kCPollEvery = 1;
 
@@ -397,12 +399,12 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (8 warps)
+        // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;                 // which half of the columns
-        const int c_lo = half * (BN / 2), c_hi = c_lo + BN / 2;
+        const int part = (warp - 2) >> 2;                 // which share of the columns
+        const int c_lo = part * (BN / kCEpiParts), c_hi = c_lo + BN / kCEpiParts;
         // this warp's share of the columns of one accumulator buffer, for spill and restore
-        const int s_lo = half * (buf_cols / 2), s_hi = s_lo + buf_cols / 2;
+        const int s_lo = part * (buf_cols / kCEpiParts), s_hi = s_lo + buf_cols / kCEpiParts;
         const int row = quarter * 32 + lane;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const bool leader = threadIdx.x == 64;
@@ -423,7 +425,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             tmem_st_wait();
         }
         tc_fence_before_sync();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kCEpiThreads) : "memory");
         if (leader)
             for (int b = 0; b < nbuf; ++b) mbar_arrive(smem_u32(&ctl->tmem_empty[b]));
 
@@ -439,7 +441,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 if (!ok) fail(301);
                 ctl->epi_go = ok ? 1 : 0;
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kCEpiThreads) : "memory");
             if (!ctl->epi_go) break;
             tc_fence_after_sync();
             const int kind = ctl->epi_kind[buf];
@@ -476,40 +478,37 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                                         : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
                     if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
                 }
-                // Every lane owns one row of the tile (its TMEM lane): 32 columns of a plane are 64
-                // contiguous bytes of that row, moved as two 256-bit accesses, each a whole sector.
+                // Every lane owns one row of the tile (its TMEM lane): 16 columns of a plane are 32
+                // contiguous bytes of that row, one 256-bit access, a whole sector.
                 const bool planes_out = !p.partial && !p.out_f32;
                 const int col_lim = p.cout_valid - n_blk * BN;
-                for (int c = c_lo; c < c_hi; c += 32) {
-                    float f[32];
+                for (int c = c_lo; c < c_hi; c += 16) {
+                    float f[16];
+                    uint32_t t16[16];
                     // The residual is requested first so its latency overlaps the TMEM reads.
                     const bool use_res = planes_out && p.res_hi && valid;
-                    uint32_t rh[16], rl[16];
+                    uint32_t rh[8], rl[8];
                     if (use_res) {
                         ld_global_v8(p.res_hi + res_off + c, rh);
-                        ld_global_v8(p.res_hi + res_off + c + 16, rh + 8);
-                        if (two_plane) {
-                            ld_global_v8(p.res_lo + res_off + c, rl);
-                            ld_global_v8(p.res_lo + res_off + c + 16, rl + 8);
-                        }
+                        if (two_plane) ld_global_v8(p.res_lo + res_off + c, rl);
                     }
-                    tmem_ld_32x32(t_acc + c, v);
+                    tmem_ld_32x16(t_acc + c, t16);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    tmem_ld_32x32(t_acc + BN + c, v);
+                    for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(t16[j]);
+                    tmem_ld_32x16(t_acc + BN + c, t16);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
+                    for (int j = 0; j < 16; ++j) f[j] += __uint_as_float(t16[j]);
                     if (two_plane && !dual) {
-                        tmem_ld_32x32(t_acc + 2 * BN + c, v);
+                        tmem_ld_32x16(t_acc + 2 * BN + c, t16);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
-                        tmem_ld_32x32(t_acc + 3 * BN + c, v);
+                        for (int j = 0; j < 16; ++j) f[j] += __uint_as_float(t16[j]);
+                        tmem_ld_32x16(t_acc + 3 * BN + c, t16);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
+                        for (int j = 0; j < 16; ++j) f[j] += __uint_as_float(t16[j]);
                     }
                     if (p.partial) {
                         // Split K: the raw fp32 sum of this K range goes to the workspace; the
@@ -518,7 +517,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                             float4 *dst = reinterpret_cast<float4 *>(
                                 p.partial + ((size_t)split * p.partial_rows + vrow) * p.partial_ld + n_blk * BN + c);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
+                            for (int j = 0; j < 4; ++j)
                                 dst[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
                         }
                         continue;
@@ -526,7 +525,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     if (p.bias) {
                         const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + n_blk * BN + c);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < 4; ++j) {
                             float4 b = __ldg(b4 + j);
                             f[4 * j + 0] += b.x;
                             f[4 * j + 1] += b.y;
@@ -536,14 +535,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                     if (use_res) {
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) {
+                        for (int q = 0; q < 8; ++q) {
                             float2 r = pf_unpack2(rh[q], p.fmt);
                             f[2 * q] += r.x;
                             f[2 * q + 1] += r.y;
                         }
                         if (two_plane) {
 #pragma unroll
-                            for (int q = 0; q < 16; ++q) {
+                            for (int q = 0; q < 8; ++q) {
                                 f[2 * q] += bf16_lo_to_f32(rl[q]);
                                 f[2 * q + 1] += bf16_hi_to_f32(rl[q]);
                             }
@@ -554,35 +553,30 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         const int col0 = n_blk * BN + c;
                         if (valid) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
+                            for (int j = 0; j < 16; ++j)
                                 if (col0 + j < p.cout_valid) p.out_f32[out_off + col0 + j] = f[j];
                         }
                         continue;
                     }
-                    uint32_t hi[16];
+                    uint32_t hi[8];
 #pragma unroll
-                    for (int q = 0; q < 16; ++q) hi[q] = pf_pack2(f[2 * q], f[2 * q + 1], p.fmt);
-                    if (valid) {
-                        // The output may be a channel slice: nothing is stored past cout_valid.
-                        if (c < col_lim) st_global_v8(p.out_hi + out_off + c, hi);
-                        if (c + 16 < col_lim) st_global_v8(p.out_hi + out_off + c + 16, hi + 8);
-                    }
+                    for (int q = 0; q < 8; ++q) hi[q] = pf_pack2(f[2 * q], f[2 * q + 1], p.fmt);
+                    // The output may be a channel slice: nothing is stored past cout_valid.
+                    const bool store = valid && c < col_lim;
+                    if (store) st_global_v8(p.out_hi + out_off + c, hi);
                     if (two_plane) {
-                        uint32_t lo[16];
+                        uint32_t lo[8];
 #pragma unroll
-                        for (int q = 0; q < 16; ++q)
+                        for (int q = 0; q < 8; ++q)
                             lo[q] = pack_bf16(f[2 * q] - bf16_lo_to_f32(hi[q]), f[2 * q + 1] - bf16_hi_to_f32(hi[q]));
-                        if (valid) {
-                            if (c < col_lim) st_global_v8(p.out_lo + out_off + c, lo);
-                            if (c + 16 < col_lim) st_global_v8(p.out_lo + out_off + c + 16, lo + 8);
-                        }
+                        if (store) st_global_v8(p.out_lo + out_off + c, lo);
                     }
                 }
                 ++it;
                 ++tiles_done;
                 seg_k0 = 0;
                 tc_fence_before_sync();
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kCEpiThreads) : "memory");
                 if (leader) {
                     mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
                     if (blp.executed) atomicAdd(blp.executed, 1);
@@ -646,6 +640,8 @@ cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &
         launch_layer(cgemm_tcgen05_kernel<64>, grid, kCgemmThreads, CgemmCfg<64>::kSmem, s, p, blp);
     return cudaGetLastError();
 }
+
+int cgemm_threads() { return kCgemmThreads; }
 
 size_t cgemm_spill_floats_per_cta() { return (size_t)kCBM * CgemmCfg<128>::kTmemCols; }
 

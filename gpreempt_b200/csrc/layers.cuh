@@ -73,6 +73,7 @@ struct CgemmParams {
 cudaError_t cgemm_prepare(int device);
 cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s);
 size_t cgemm_spill_floats_per_cta();
+int cgemm_threads();
 
 // ---- CUDA-core convolution / dense (conv_simt.cu) --------------------------------------------
 

@@ -1076,7 +1076,7 @@ int finalize_model(gpx_model &m) {
         kn.name = n.name;
         kn.node = (int)ni;
         kn.type = KernelType::Cgemm;
-        kn.threads = 320;
+        kn.threads = cgemm_threads();
         CgemmParams &p = kn.cgemm;
         ActLayout il = in->layout;
         if (full_map_dense(n, src) && !n.via_im2col) {

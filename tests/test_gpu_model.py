@@ -278,7 +278,7 @@ def test_cuda_core_convolution_path_matches_oracle(gpx, oracle, monkeypatch):
     assert _rel(simt, want) <= RTOL_FP32
     tc = gpx.BaseExecutor()
     tc.init("resnet_tiny", batch=2, seed=1)
-    assert 320 in {tc.model.get_kernel_info(i)["launch_params"][3] for i in range(tc.get_kernel_num())}
+    assert max(tc.model.get_kernel_info(i)["launch_params"][3] for i in range(tc.get_kernel_num())) > 256
     tc.set_input("data", data)
     tc.execute()
     assert tc.error() == (0, 0)
