@@ -73,6 +73,20 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
     return GPX_SUCC;
 }
 
+int exec_prologue(gpx_exec *e, cudaStream_t s) {
+    size_t nk = e->model->kernels.size();
+    if (e->kind == GPX_EXEC_BLP) {
+        GPX_REQUIRE(e->word_dptr, GPX_FAIL, "BLP executor has no preempt word (gpx_exec_set_word)");
+        // BLPExecutor::execute zeroes executed[] first (src/executor.cpp:212-214).
+        GPX_CUDA(cudaMemsetAsync(e->d_executed, 0, sizeof(int) * nk, s));
+        GPX_CUDA(cudaMemsetAsync(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * nk, s));
+    }
+    if (e->trace_on)
+        GPX_CUDA(cudaMemcpyAsync(e->d_trace, e->h_trace_init, sizeof(uint64_t) * 4 * nk,
+                                 cudaMemcpyHostToDevice, s));
+    return GPX_SUCC;
+}
+
 }  // namespace gpx
 
 extern "C" {
@@ -152,20 +166,6 @@ int gpx_exec_enable_trace(gpx_exec *e, int on) {
     GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
     GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "enable tracing before capturing the graph");
     e->trace_on = on != 0;
-    return GPX_SUCC;
-}
-
-static int exec_prologue(gpx_exec *e, cudaStream_t s) {
-    size_t nk = e->model->kernels.size();
-    if (e->kind == GPX_EXEC_BLP) {
-        GPX_REQUIRE(e->word_dptr, GPX_FAIL, "BLP executor has no preempt word (gpx_exec_set_word)");
-        // BLPExecutor::execute zeroes executed[] first (src/executor.cpp:212-214).
-        GPX_CUDA(cudaMemsetAsync(e->d_executed, 0, sizeof(int) * nk, s));
-        GPX_CUDA(cudaMemsetAsync(e->d_slots, 0, sizeof(CgemmSlot) * kSlotsPerKernel * nk, s));
-    }
-    if (e->trace_on)
-        GPX_CUDA(cudaMemcpyAsync(e->d_trace, e->h_trace_init, sizeof(uint64_t) * 4 * nk,
-                                 cudaMemcpyHostToDevice, s));
     return GPX_SUCC;
 }
 

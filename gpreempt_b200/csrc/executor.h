@@ -30,4 +30,6 @@ namespace gpx {
 constexpr size_t kSlotsPerKernel = 256;
 BlpArgs exec_blp_args(gpx_exec *e, size_t idx);
 int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s);
+// Re-arms cursors, progress slots and trace for a run from kernel 0 (what execute does first).
+int exec_prologue(gpx_exec *e, cudaStream_t s);
 }  // namespace gpx
