@@ -33,6 +33,13 @@ struct FaControl {
     int abort_flag;
 };
 
+// 2^x, the hardware approximation (relative error ~2^-22; -inf gives 0).
+__device__ __forceinline__ float fa_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void fa_st_v8(void *ptr, const uint32_t *r) {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]),
                  "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -138,17 +145,24 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
             // ---- online softmax of this thread's row over the 128 keys of the block
             const int key0 = kb * kFaKeys;
             uint32_t v[32];
-            float bmax = -INFINITY;
+            // Whole blocks (all 128 keys inside the sequence) skip the per-key bound test.
+            const bool whole = key0 + kFaKeys <= p.S;
+            float bmax = -INFINITY;  // of the raw scores: the scale is positive
 #pragma unroll
             for (int c = 0; c < kFaKeys; c += 32) {
                 tmem_ld_32x32(t_lane + c, v);
                 tmem_ld_wait();
+                if (whole) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (key0 + c + j < p.S) bmax = fmaxf(bmax, __uint_as_float(v[j]) * scale_log2);
+                    for (int j = 0; j < 32; ++j) bmax = fmaxf(bmax, __uint_as_float(v[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (key0 + c + j < p.S) bmax = fmaxf(bmax, __uint_as_float(v[j]));
+                }
             }
-            const float m_new = fmaxf(m, bmax);
-            const float alpha = exp2f(m - m_new);
+            const float m_new = fmaxf(m, bmax * scale_log2);
+            const float alpha = fa_ex2(m - m_new);
             float lsum = 0.f;
             const int r8 = tid & 7;
             unsigned char *prow = pP + (tid >> 3) * 1024 + r8 * 128;
@@ -159,12 +173,14 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
-                    float e0 = key0 + c + j < p.S ? exp2f(__uint_as_float(v[j]) * scale_log2 - m_new) : 0.f;
-                    float e1 = key0 + c + j + 1 < p.S ? exp2f(__uint_as_float(v[j + 1]) * scale_log2 - m_new) : 0.f;
+                    float e0 = fa_ex2(fmaf(__uint_as_float(v[j]), scale_log2, -m_new));
+                    float e1 = fa_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, -m_new));
+                    if (!whole) {
+                        if (key0 + c + j >= p.S) e0 = 0.f;
+                        if (key0 + c + j + 1 >= p.S) e1 = 0.f;
+                    }
+                    lsum += e0 + e1;
                     pk[j >> 1] = pf_pack2(e0, e1, p.fmt);
-                    // the normaliser sums what the second product will see: the rounded values
-                    float2 rr = pf_unpack2(pk[j >> 1], p.fmt);
-                    lsum += rr.x + rr.y;
                 }
                 // 32 keys = four 16-byte pieces of this row, in the 128-byte swizzled layout of
                 // an A tile: piece index XOR (row mod 8); keys 64..127 form the second tile.

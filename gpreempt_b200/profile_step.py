@@ -2,7 +2,8 @@
 
     python -m gpreempt_b200.profile_step gemm  [--size 8192] [--iters 2]
     python -m gpreempt_b200.profile_step axpy  [--size 268435456] [--iters 2]
-    python -m gpreempt_b200.profile_step model [--model resnet50] [--batch 32] [--iters 2]
+    python -m gpreempt_b200.profile_step model [--model resnet50] [--batch 32] [--dtype float32]
+                                               [--seq-len 0] [--iters 2]
 
 Each run launches the kernels of interest `iters` times with preemption armed (the word stays
 clear) and exits; inputs are larger than L2 so DRAM counters are meaningful, and at most a few
@@ -22,6 +23,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--model", default="resnet50")
     ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--seq-len", type=int, default=0)
     a = ap.parse_args()
     api.init_cuda(0)
     s = api.Stream(1)
@@ -51,9 +54,15 @@ def main() -> None:
             s.sync()
     else:
         ex = api.BLPExecutor()
-        ex.init(a.model, batch=a.batch, seed=1)
+        ex.init(a.model, batch=a.batch, seed=1, dtype=a.dtype, seq_len=a.seq_len)
         ex.set_word(word)
-        data = api.synth_normal(a.batch * 3 * 224 * 224, 0).reshape(a.batch, 3, 224, 224)
+        if a.model.startswith("bert"):
+            import numpy as np
+
+            vocab = 30522 if a.model == "bert_base" else 1000
+            data = np.random.default_rng(6).integers(0, vocab, (a.batch, a.seq_len or 128)).astype(np.int64)
+        else:
+            data = api.synth_normal(a.batch * 3 * 224 * 224, 0).reshape(a.batch, 3, 224, 224)
         ex.set_input("data", data)
         for _ in range(a.iters):
             ex.execute(s)
