@@ -262,8 +262,10 @@ def main() -> None:
 
     group = dist.init(world, rank)
     device = local_rank if world > 1 else 0
-    # each rank's client threads get their own cores
-    os.environ.setdefault("GPX_CORE_BASE", str(4 * local_rank))
+    # Each rank's dispatcher and two client threads get cores of their own when the host has
+    # enough of them; otherwise nothing is pinned (two ranks pinned to one core stall each other).
+    per_rank = (os.cpu_count() or 1) // max(world, 1)
+    os.environ.setdefault("GPX_CORE_BASE", str(min(4, per_rank) * local_rank) if per_rank >= 3 else "-1")
     api.init_cuda(device)
 
     def launches() -> int:

@@ -812,7 +812,8 @@ static int run_suite(Suite &s, Json *report) {
     // host do not share cores.
     const char *core_base_env = getenv("GPX_CORE_BASE");
     const int core_base = core_base_env ? atoi(core_base_env) : 0;
-    for (size_t i = 0; i < s.dispatchers.size(); ++i) s.dispatchers[i]->core = core_base + (int)i;
+    // (a negative base leaves every thread to the OS scheduler: fewer cores than threads)
+    for (size_t i = 0; i < s.dispatchers.size(); ++i) s.dispatchers[i]->core = core_base < 0 ? -1 : core_base + (int)i;
     for (auto &d : s.dispatchers) d->thread = std::thread([dp = d.get()] { dp->run(); });
 
     // Warm-up, then stand-alone latency of each client (benchmark.cpp:221-299).
@@ -856,7 +857,7 @@ static int run_suite(Suite &s, Json *report) {
         t->load.start(s.run_begin, s.run_end, s.seed * 7919 + 2 + i);
         t->records.reserve(1 << 16);
         threads.emplace_back([&, t] {
-            gpx_bind_core(core.fetch_add(1) + 1);
+            if (core_base >= 0) gpx_bind_core(core.fetch_add(1) + 1);
             if (gpx_init(t->gpu) != GPX_SUCC) {
                 errors.fetch_add(1);
                 return;
