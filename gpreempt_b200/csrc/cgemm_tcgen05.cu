@@ -13,9 +13,16 @@
 // matrix [Cout][taps*Cin].  Rows that are not real output pixels (image borders of the padded
 // layouts) are computed and dropped by the epilogue.
 //
+// Single-plane models (bf16 / fp16 storage) use the same kernel with one product per K step and
+// twice as many ring stages.
+//
 // CTA roles, ring, messages and the preempt / spill / resume protocol are those of
-// gemm_tcgen05.cu; the epilogue additionally adds the bias and the residual, applies ReLU,
-// splits the fp32 result into hi/lo planes and scatters rows into the consumer's layout.
+// gemm_tcgen05.cu, with two accumulator buffers in tensor memory so that the epilogue of one
+// tile overlaps the K loop of the next.  The epilogue adds the bias, applies the activation,
+// splits the fp32 result into the plane format and writes each row into the consumer's layout
+// with 256-bit stores.  The residual of a 1x1 convolution on plain rows is added by the tensor
+// core itself: extra K blocks whose A operand is the residual tile and whose B operand is a
+// 64x64 identity tile kept in shared memory; other residuals are added by the epilogue.
 #include "layers.cuh"
 #include "sm100.cuh"
 
