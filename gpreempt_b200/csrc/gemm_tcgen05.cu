@@ -11,7 +11,7 @@
 //   warps 2-5          epilogue: tcgen05.ld the accumulator, convert to bf16, store C.
 //
 // Preemption is K-block granular, not tile granular (a whole 128x256x8192 tile takes ~50 us,
-// far above the drain budget): when the producer sees the word raised it sends a STOP message
+// far above the 20 us drain target): when the producer sees the word raised it sends a STOP message
 // down the ring; the MMA issuer commits what it has accumulated, the epilogue spills the fp32
 // accumulator and the {iteration, K block} cursor of this CTA to the context buffer, and the
 // CTA returns.  A relaunch with the same context reloads the accumulator into TMEM and
