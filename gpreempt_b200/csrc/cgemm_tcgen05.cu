@@ -48,14 +48,15 @@ struct CgemmCfg {
     static constexpr uint32_t kABytes = kCBM * kCBK * 2;        // one plane of A: 16 KiB
     static constexpr uint32_t kWBytes = BN * kCBK * 2;          // one plane of W
     static constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kWBytes;
-    static constexpr int kStages = BN == 128 ? 3 : 4;
+    static constexpr int kStages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
     // ring + alignment slack + 64x64 identity tile + control block
     static constexpr uint32_t kIdentBytes = 64 * kCBK * 2;
     static constexpr size_t kSmem =
         (size_t)kStages * kStageBytes + 1024 + kIdentBytes + 256;
     // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
     // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
-    static constexpr int kAccs = 4;
+    // (256-column tiles exist for the two-accumulator plan only: 2 x 256 columns, one buffer.)
+    static constexpr int kAccs = BN == 256 ? 2 : 4;
     static constexpr int kTmemCols = kAccs * BN;
 };
 
@@ -141,7 +142,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     // epilogue of one tile overlaps the K loop of the next; used when the K range is short or the
     // operands are single-plane.  Otherwise four accumulators in one buffer (see the MMA issuer).
     const bool dual = p.dual != 0;
-    const int nbuf = dual ? 2 : 1;
+    const int nbuf = (dual && 4 * BN <= 512) ? 2 : 1;
     const int buf_cols = dual ? 2 * BN : Cfg::kTmemCols;
 
     CgemmSlot *slot = p.slots + blockIdx.x;
@@ -633,6 +634,9 @@ cudaError_t cgemm_prepare(int device) {
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)CgemmCfg<128>::kSmem);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(cgemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)CgemmCfg<256>::kSmem);
+    if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(cgemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)CgemmCfg<64>::kSmem);
     if (e != cudaSuccess) return e;
@@ -641,7 +645,9 @@ cudaError_t cgemm_prepare(int device) {
 }
 
 cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s) {
-    if (bn == 128)
+    if (bn == 256)
+        launch_layer(cgemm_tcgen05_kernel<256>, grid, kCgemmThreads, CgemmCfg<256>::kSmem, s, p, blp);
+    else if (bn == 128)
         launch_layer(cgemm_tcgen05_kernel<128>, grid, kCgemmThreads, CgemmCfg<128>::kSmem, s, p, blp);
     else
         launch_layer(cgemm_tcgen05_kernel<64>, grid, kCgemmThreads, CgemmCfg<64>::kSmem, s, p, blp);

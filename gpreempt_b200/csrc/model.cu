@@ -1092,6 +1092,17 @@ int finalize_model(gpx_model &m) {
             // Few output tiles (batch 1, late stages): narrower column tiles expose more CTAs.
             long long tiles128 = (long long)((il.plane + 127) / 128) * ((cout_st + 127) / 128);
             if (tiles128 * 2 <= m.sm_count) bn = 64;
+            // Single-plane operands do one product per K step, so a 128x128 tile cannot be fed
+            // fast enough (32 KB of TMA fill per 0.13 us of products): 256-column tiles halve the
+            // activation bytes per product, as the stand-alone GEMM's 128x256 tiles do, wherever
+            // they still fill the GPU and the K loop is long enough to outweigh the second
+            // accumulator buffer they give up (ResNet-50's 1x1 convolutions with K <= 512 lose 6 %,
+            // BERT's dense layers and VGG's 3x3 convolutions gain 17-19 %).
+            const char *wide = getenv("GPX_CGEMM_BN256");
+            if (m.fmt != PF_SPLIT && !head && cout_st % 256 == 0 && tiles128 / 2 >= m.sm_count &&
+                (long long)eff_k * eff_k * eff_cin >= 768 &&
+                !(wide && wide[0] == '0'))
+                bn = 256;
         }
         kn.tile = bn;
         p.taps = eff_k * eff_k;
@@ -1162,6 +1173,7 @@ int finalize_model(gpx_model &m) {
             if (atoi(e) == 0) p.dual = 0;
             if (atoi(e) == 1) p.dual = (m.fmt != PF_SPLIT || p.kb_per_split * 64 <= 1024) ? 1 : 0;
         }
+        if (bn == 256) p.dual = 1;  // the only plan that fits 256-column tiles in tensor memory
         // The residual of a 1x1 stride-1 convolution on plain rows has the rows of the GEMM itself:
         // it is then added by the tensor core as identity K blocks instead of by the epilogue.
         p.res_kb = 0;
