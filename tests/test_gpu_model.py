@@ -496,3 +496,58 @@ def test_reduced_precision_preempt_resume_bit_identical(gpx, dtype, drop):
     ex.clear()
     base.clear()
     s.destroy()
+
+
+def test_wide_tile_layers_preempt_resume_bit_identical(gpx):
+    """VGG-16 at batch 8 in fp16 runs its 256- and 512-channel convolutions on 128x256 tiles
+    (one accumulator buffer); preempting and resuming them leaves every checked tensor bit-identical."""
+    base = gpx.BaseExecutor()
+    base.init("vgg16", batch=8, seed=2, dtype="float16")
+    data = _data(gpx, 8, seed=3)
+    base.set_input("data", data)
+    base.execute()
+    names = ["features.5", "features.9", "features.12", "heads"]
+    want = {n: base.model.get(n) for n in names}
+    word = gpx.PreemptWord(1)
+    ex = gpx.BLPExecutor()
+    ex.init("vgg16", batch=8, dtype="float16")
+    for k, v in base.model.params().items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.set_input("data", data)
+    s = gpx.Stream(1)
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    rng = np.random.default_rng(5)
+    stops = 0
+    for trial in range(6):
+        word.clear()
+        time.sleep(0.001)
+        ex.execute(s)
+        rounds = 0
+        while True:
+            if rounds < 5:
+                delay = float(rng.uniform(0, run_us / 3))
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < delay:
+                    pass
+                word.raise_()
+            s.sync()
+            word.clear()
+            time.sleep(0.0005)
+            stop = ex.resume(s)
+            rounds += 1
+            if stop == -1:
+                break
+            stops += 1
+            assert rounds < 80
+        s.sync()
+        for n in names:
+            assert np.array_equal(ex.model.get(n), want[n]), f"trial {trial}: {n} differs after resume"
+    assert stops > 0
+    assert ex.error() == (0, 0)
+    ex.clear()
+    base.clear()
+    s.destroy()
