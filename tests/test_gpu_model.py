@@ -551,3 +551,63 @@ def test_wide_tile_layers_preempt_resume_bit_identical(gpx):
     ex.clear()
     base.clear()
     s.destroy()
+
+
+def test_schedule_order_from_device_timestamps(gpx):
+    """Raise the word in the middle of a best-effort forward and read the per-kernel %globaltimer
+    trace: kernels before the stop point ran all their tiles in stream order; the stopped kernel
+    saw the word after the host wrote it and left within the drain bound; no kernel behind it did
+    any tile; after the resume every kernel has run exactly its tiles."""
+    ex = gpx.BLPExecutor()
+    ex.init("resnet50", batch=16, seed=1)
+    word = gpx.PreemptWord(1)
+    ex.set_word(word)
+    ex.enable_trace(True)
+    ex.set_input("data", _data(gpx, 16))
+    s = gpx.Stream(1)
+    nk = ex.get_kernel_num()
+    tiles = np.array([ex.model.get_kernel_info(i)["total_tiles"] for i in range(nk)], np.int64)
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    NONE = np.uint64(0xFFFFFFFFFFFFFFFF)
+    checked = 0
+    for trial, frac in enumerate((0.2, 0.35, 0.5, 0.65, 0.8)):
+        word.clear()
+        time.sleep(0.001)
+        off, unc = gpx.clock_offset_ns()  # host clock minus device clock, and its uncertainty
+        ex.execute(s)
+        t0 = time.perf_counter()
+        while (time.perf_counter() - t0) * 1e6 < run_us * frac:
+            pass
+        t_raise_dev = gpx.host_now_ns() - off
+        word.raise_()
+        s.sync()
+        tr = ex.read_trace()
+        begin, end, seen, done = tr[:, 0], tr[:, 1], tr[:, 2], tr[:, 3].astype(np.int64)
+        unfinished = np.nonzero(done < tiles)[0]
+        if unfinished.size == 0:
+            continue  # the forward had already finished
+        stop = int(unfinished[0])
+        assert np.array_equal(done[:stop], tiles[:stop]), "a kernel before the stop point is incomplete"
+        assert np.all(np.diff(begin[: stop + 1].astype(np.int64)) >= 0), "kernels started out of stream order"
+        assert done[stop] < tiles[stop], "the stop point is a kernel that finished"
+        assert seen[stop] != NONE
+        slack = unc + 20_000  # clock correlation plus the raise call itself
+        assert int(seen[stop]) + slack >= t_raise_dev, "the kernel saw the word before it was written"
+        assert int(end[stop]) - int(seen[stop]) < 100_000, "drain of the stopped kernel above 100 us"
+        assert np.all(done[stop + 1:] == 0), "a kernel behind the stop point ran a tile"
+        later = begin[stop + 1:]
+        started = later[later != NONE].astype(np.int64)
+        assert np.all(started + slack >= t_raise_dev), "a kernel behind the stop point started before the raise"
+        word.clear()
+        time.sleep(0.0005)
+        assert ex.resume(s) == stop, "the recorded stop point is not the first unfinished kernel"
+        s.sync()
+        assert ex.resume(s) == -1
+        assert np.all(ex.read_cursors() >= tiles)
+        checked += 1
+    assert checked >= 3
+    assert ex.error() == (0, 0)
+    ex.clear(), word.destroy(), s.destroy()
