@@ -1156,8 +1156,13 @@ int finalize_model(gpx_model &m) {
         const int out_tiles = p.tiles_m * p.tiles_n;
         p.k_splits = 1;
         p.kb_per_split = all_kb;
-        if (out_tiles * 2 <= m.sm_count && all_kb >= 8) {
-            int s_want = std::min(all_kb / 4, m.sm_count / out_tiles);
+        // (GPX_SPLITK_MIN_KB: fewest K blocks per split, default 4; GPX_SPLITK_ALLKB: shortest K loop
+        // that is split at all, default 8 - tuning knobs for the batch-1 latency.)
+        const char *e_min = getenv("GPX_SPLITK_MIN_KB"), *e_all = getenv("GPX_SPLITK_ALLKB");
+        const int min_kb = e_min ? std::max(1, atoi(e_min)) : 4;
+        const int split_from = e_all ? atoi(e_all) : 8;
+        if (out_tiles * 2 <= m.sm_count && all_kb >= split_from) {
+            int s_want = std::min(all_kb / min_kb, m.sm_count / out_tiles);
             if (s_want >= 2) {
                 p.kb_per_split = (all_kb + s_want - 1) / s_want;
                 p.k_splits = (all_kb + p.kb_per_split - 1) / p.kb_per_split;
