@@ -102,3 +102,19 @@ def test_shipped_contention_configs_run(gpx, name):
     g = rep["gpus"][0]
     assert g["wordRaises"] > 0
     assert g["beResumes"] > 0
+
+
+def test_input_double_buffering_keeps_results_and_counts(gpx):
+    """`prefetch_inputs`: the best-effort tenant stages its next input while a request runs; the
+    run serves the same number of step-bounded requests and reports the shorter copy phase."""
+    base = _config(be_requests=30)
+    rep0 = json.loads(gpx.run_workload("gpreemptclient", json.dumps(base)))
+    cfg = _config(be_requests=30)
+    cfg["prefetch_inputs"] = True
+    rep1 = json.loads(gpx.run_workload("gpreemptclient", json.dumps(cfg)))
+    assert rep1["prefetch_inputs"] is True and rep0["prefetch_inputs"] is False
+    t0 = {t["id"]: t for t in rep0["tasks"]}
+    t1 = {t["id"]: t for t in rep1["tasks"]}
+    assert t1["tiny_be"]["requests"] == t0["tiny_be"]["requests"] == 30
+    assert t1["tiny_be"]["avgCopyInputLatency(us)"] < t0["tiny_be"]["avgCopyInputLatency(us)"]
+    assert t1["tiny_rt"]["requests"] > 0
