@@ -479,9 +479,76 @@ def run_workload(client: str, config_json: str) -> str:
     need = ctypes.c_size_t()
     cap = 1 << 20
     buf = ctypes.create_string_buffer(cap)
-    check(B.load().gpx_run_workload(client.encode(), config_json.encode(), buf, cap,
-                                    ctypes.byref(need)))
+    st = B.load().gpx_run_workload(client.encode(), config_json.encode(), buf, cap, ctypes.byref(need))
+    if st == B.OUT_OF_RANGE and need.value > cap:
+        # the run completed; only the buffer was too small: fetch the kept report
+        buf = ctypes.create_string_buffer(need.value)
+        check(B.load().gpx_workload_report(buf, need.value, ctypes.byref(need)))
+        return buf.value.decode()
+    check(st)
     return buf.value.decode()
+
+
+class _BorrowedStream:
+    """A stream owned by the scheduler, usable wherever a Stream is (never destroyed here)."""
+
+    def __init__(self, handle):
+        self.handle = ctypes.c_void_p(handle)
+
+    def sync(self) -> None:
+        check(B.load().gpx_stream_sync(self.handle))
+
+
+class Scheduler:
+    """reef::executor::REEFScheduler (include/reef_scheduler.h:61-109): the per-GPU dispatch loop,
+    for clients that bring their own request loop."""
+
+    def __init__(self, device: int = 0, policy: str = "gpreemptclient"):
+        self.handle = ctypes.c_void_p()
+        check(B.load().gpx_sched_create(device, policy.encode(), ctypes.byref(self.handle)))
+
+    def attach(self, executor: "Executor | None", priority: int) -> int:
+        """create_queue + bind_model_queue: returns the client index."""
+        c = ctypes.c_int()
+        check(B.load().gpx_sched_attach(self.handle, executor.handle if executor is not None else None,
+                                        priority, ctypes.byref(c)))
+        return c.value
+
+    def client_stream(self, client: int) -> _BorrowedStream:
+        h = ctypes.c_void_p()
+        check(B.load().gpx_sched_client_stream(self.handle, client, ctypes.byref(h)))
+        return _BorrowedStream(h.value)
+
+    def run(self) -> None:
+        check(B.load().gpx_sched_run(self.handle))
+
+    def shutdown(self) -> None:
+        check(B.load().gpx_sched_shutdown(self.handle))
+
+    def new_task(self, client: int) -> int:
+        t = ctypes.c_uint64()
+        check(B.load().gpx_sched_enqueue(self.handle, client, ctypes.byref(t)))
+        return t.value
+
+    def wait_task(self, client: int, ticket: int, timeout_s: float = 30.0) -> None:
+        check(B.load().gpx_wait(self.handle, client, ticket, int(timeout_s * 1e9)))
+
+    def hint(self, client: int, on: bool = True) -> None:
+        check(B.load().gpx_sched_hint(self.handle, client, int(on)))
+
+    def stats(self) -> dict:
+        import json
+
+        need = ctypes.c_size_t()
+        check(B.load().gpx_sched_stats(self.handle, None, 0, ctypes.byref(need)))
+        buf = ctypes.create_string_buffer(need.value)
+        check(B.load().gpx_sched_stats(self.handle, buf, need.value, ctypes.byref(need)))
+        return json.loads(buf.value.decode())
+
+    def destroy(self) -> None:
+        if self.handle:
+            B.load().gpx_sched_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
 
 
 def fill_uniform(buf: DeviceBuffer, n: int, bf16: bool, seed: int, stream_id: int = 0,

@@ -137,6 +137,17 @@ _SIGS = {
     "gpx_exec_set_restart_policy": [vp, ctypes.c_int],
     "gpx_exec_read_cursors": [vp, P(ci), sz, P(sz)],
     "gpx_run_workload": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, sz, P(sz)],
+    "gpx_workload_report": [ctypes.c_char_p, sz, P(sz)],
+    "gpx_sched_create": [ci, ctypes.c_char_p, P(vp)],
+    "gpx_sched_attach": [vp, vp, ci, P(ci)],
+    "gpx_sched_client_stream": [vp, ci, P(vp)],
+    "gpx_sched_run": [vp],
+    "gpx_sched_shutdown": [vp],
+    "gpx_sched_destroy": [vp],
+    "gpx_sched_enqueue": [vp, ci, P(u64)],
+    "gpx_wait": [vp, ci, u64, u64],
+    "gpx_sched_hint": [vp, ci, ci],
+    "gpx_sched_stats": [vp, ctypes.c_char_p, sz, P(sz)],
     "gpx_clock_offset_ns": [P(i64), P(i64)],
 }
 

@@ -509,9 +509,21 @@ static __device__ __align__(256) unsigned char g_gemm_static_ctx[kStaticCtxBytes
 static unsigned char *g_static_ctx_addr[64] = {nullptr};
 
 static int static_ctx_address(int device, unsigned char **out) {
+    // cudaGetSymbolAddress answers for the device that is current in the CUDA runtime, which is
+    // not necessarily the one this thread bound with gpx_init (another library may have called
+    // cudaSetDevice since): a pointer cached under the wrong index would send every later call on
+    // that device to another GPU's array.
+    int current = -1;
+    cudaError_t err = cudaGetDevice(&current);
+    if (err != cudaSuccess || current != device || device < 0 || device >= 64) {
+        set_error("gpx_gemm_bf16_static: the CUDA current device is %d but this thread was bound to device %d "
+                  "by gpx_init; make device %d current (or call gpx_init again) before the call",
+                  current, device, device);
+        return GPX_FAIL;
+    }
     if (!g_static_ctx_addr[device]) {
         void *p = nullptr;
-        cudaError_t err = cudaGetSymbolAddress(&p, g_gemm_static_ctx);
+        err = cudaGetSymbolAddress(&p, g_gemm_static_ctx);
         if (err != cudaSuccess || !p) {
             set_error("cudaGetSymbolAddress(g_gemm_static_ctx) failed on device %d: %s", device,
                       cudaGetErrorString(err));

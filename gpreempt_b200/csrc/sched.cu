@@ -157,31 +157,15 @@ struct Record {
     uint64_t total() const { return prepare + preprocess + copy_in + infer + copy_out + postprocess; }
 };
 
-struct Tenant {
-    std::string id, name, model_name;
+// What the dispatcher knows about one request source: an executor bound to a stream and a
+// priority class (REEFScheduler::create_queue + bind_model_queue, include/reef_scheduler.h:67-75).
+// One request is in flight per client at a time; further submissions queue behind it.
+struct Client {
     int priority = 1;
-    int batch = 1;
-    int seq_len = 0;
-    std::string dtype;  // "" = float32
-    bool use_graph = false;
-    uint64_t preprocess_us = 0;
     int gpu = 0;
-    uint64_t seed = 0;
-    Load load;
-    gpx_model *model = nullptr;
-    gpx_exec *exec = nullptr;
+    gpx_exec *exec = nullptr;  // null: a client without GPU work, its requests complete when seen
     cudaStream_t stream = nullptr;
     cudaEvent_t done = nullptr;
-    void *h_in = nullptr, *h_out = nullptr;
-    // Input double buffering (best-effort tenants, `prefetch_inputs`): while a request runs, the
-    // next one's input is copied, chunk by chunk, into a staging buffer on a stream of its own;
-    // copyInput then is a device-to-device copy.
-    void *d_stage = nullptr;
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t consumed = nullptr;  // the staging buffer has been copied into the model input
-    size_t staged_off = 0;           // bytes of the next input already issued
-    bool staging = false;            // a prefetch is in progress or complete
-    size_t in_bytes = 0, out_bytes = 0;
     std::atomic<int> state{ST_IDLE};
     std::atomic<uint64_t> ticket{0};
     uint64_t submit_ns = 0;
@@ -193,6 +177,38 @@ struct Tenant {
     size_t seg_recorded = 0, seg_done = 0;
     int unlaunched_from = -1; // first kernel a cut-short resume never launched (-1: none)
     int resumes = 0;
+    // Clients of the scheduler API (gpx_sched_enqueue / gpx_wait): requests are counted, not
+    // queued as objects, because every request of a client runs the same executor.  `submitted`
+    // is advanced by the client thread, `started` and `completed` by the dispatcher.
+    bool external = false;
+    std::atomic<uint64_t> submitted{0}, completed{0};
+    uint64_t started = 0;
+    std::atomic<int> hint{0};        // gpx_sched_hint: raise the word ahead of the next submission
+    std::atomic<uint64_t> last_queue_ns{0}, last_run_ns{0};
+    uint64_t launch_ns = 0;
+    virtual ~Client() {}
+};
+
+struct Tenant : Client {
+    std::string id, name, model_name;
+    int batch = 1;
+    int seq_len = 0;
+    std::string dtype;  // "" = float32
+    bool use_graph = false;
+    uint64_t preprocess_us = 0;
+    uint64_t seed = 0;
+    Load load;
+    gpx_model *model = nullptr;
+    void *h_in = nullptr, *h_out = nullptr;
+    // Input double buffering (best-effort tenants, `prefetch_inputs`): while a request runs, the
+    // next one's input is copied, chunk by chunk, into a staging buffer on a stream of its own;
+    // copyInput then is a device-to-device copy.
+    void *d_stage = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t consumed = nullptr;  // the staging buffer has been copied into the model input
+    size_t staged_off = 0;           // bytes of the next input already issued
+    bool staging = false;            // a prefetch is in progress or complete
+    size_t in_bytes = 0, out_bytes = 0;
     std::vector<Record> records;
     Record standalone{};
     uint64_t first_ns = 0, last_ns = 0;
@@ -215,16 +231,23 @@ struct Dispatcher {
     int device = 0;
     Policy policy = POLICY_YIELD;
     bool hint = true;
-    uint64_t hint_lead_us = 0;
     int core = -1;  // host core of the dispatcher thread
-    std::vector<Tenant *> hp, be;
+    std::vector<Client *> hp, be;
     gpx_word *word = nullptr;
     cudaEvent_t clear_event = nullptr;
     std::atomic<bool> stop{false};
     std::atomic<bool> failed{false};
     std::thread thread;
     Stats stats;
+    std::atomic_flag stats_busy = ATOMIC_FLAG_INIT;  // held for the few stores of a sample, and by readers
     std::string error;
+    std::atomic<uint64_t> beat_ns{0};  // host time of the dispatcher's latest pass
+
+    void stats_lock() {
+        while (stats_busy.test_and_set(std::memory_order_acquire)) {
+        }
+    }
+    void stats_unlock() { stats_busy.clear(std::memory_order_release); }
 
     bool word_raised = false;
     uint64_t t_raise = 0;
@@ -236,8 +259,11 @@ struct Dispatcher {
         return GPX_FAIL;
     }
 
-    int launch_full(Tenant *t) {
+    int launch_full(Client *t) {
         gpx_exec *e = t->exec;
+        t->launch_ns = now_ns();
+        t->last_queue_ns.store(t->launch_ns - t->submit_ns, std::memory_order_relaxed);
+        if (!e) return GPX_SUCC;  // nothing to run: the request completes at the next pass
         if (e->kind == GPX_EXEC_BLP && word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
         GPX_TRY(gpx_exec_execute(e, t->stream));
@@ -250,7 +276,7 @@ struct Dispatcher {
         return GPX_SUCC;
     }
 
-    int read_trace_async(Tenant *t) {
+    int read_trace_async(Client *t) {
         gpx_exec *e = t->exec;
         if (!e->trace_on) return GPX_SUCC;
         GPX_CUDA(cudaMemcpyAsync(e->h_trace, e->d_trace, sizeof(uint64_t) * 4 * e->model->kernels.size(),
@@ -278,7 +304,7 @@ struct Dispatcher {
     size_t be_window_min_kernels = 64;
 
     // A fresh best-effort run under the window: like a resume from kernel 0 with new cursors.
-    int windowed_begin(Tenant *t) {
+    int windowed_begin(Client *t) {
         gpx_exec *e = t->exec;
         if (word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
@@ -289,7 +315,7 @@ struct Dispatcher {
         return GPX_SUCC;
     }
 
-    int resume_begin(Tenant *t) {
+    int resume_begin(Client *t) {
         gpx_exec *e = t->exec;
         if (word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
@@ -308,7 +334,7 @@ struct Dispatcher {
         return GPX_SUCC;
     }
 
-    int resume_finish(Tenant *t) {
+    int resume_finish(Client *t) {
         gpx_exec *e = t->exec;
         GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
                                  cudaMemcpyDeviceToHost, t->stream));
@@ -318,7 +344,7 @@ struct Dispatcher {
     }
 
     // Returns with the tenant RUNNING once everything is enqueued, or still RESUMING.
-    int resume_continue(Tenant *t, bool cut_short) {
+    int resume_continue(Client *t, bool cut_short) {
         gpx_exec *e = t->exec;
         const size_t nk = e->model->kernels.size();
         if (cut_short) {
@@ -352,9 +378,11 @@ struct Dispatcher {
         GPX_TRY(gpx_word_raise(word));
         word_raised = true;
         t_raise = now_ns();
+        stats_lock();
         ++stats.raises;
+        stats_unlock();
         drain_pending = false;
-        for (Tenant *t : be)
+        for (Client *t : be)
             if (t->state.load(std::memory_order_relaxed) == ST_RUNNING ||
                 t->state.load(std::memory_order_relaxed) == ST_RESUMING)
                 drain_pending = true;
@@ -369,11 +397,38 @@ struct Dispatcher {
         return GPX_SUCC;
     }
 
+    // Clients of the scheduler API: the next counted request of an idle client becomes its
+    // submission; a finished one is counted and the client goes back to idle.
+    void admit_external(Client *t) {
+        if (!t->external) return;
+        int st = t->state.load(std::memory_order_acquire);
+        if (st == ST_DONE) {
+            t->last_run_ns.store(now_ns() - t->launch_ns, std::memory_order_relaxed);
+            t->state.store(ST_IDLE, std::memory_order_relaxed);
+            t->completed.fetch_add(1, std::memory_order_release);
+            st = ST_IDLE;
+        }
+        if (st == ST_IDLE || st == ST_HINTED) {
+            if (t->submitted.load(std::memory_order_acquire) > t->started) {
+                ++t->started;
+                t->submit_ns = now_ns();
+                t->hint.store(0, std::memory_order_relaxed);
+                t->state.store(ST_SUBMITTED, std::memory_order_release);
+            } else if (st == ST_IDLE && t->hint.load(std::memory_order_acquire)) {
+                t->state.store(ST_HINTED, std::memory_order_release);
+            } else if (st == ST_HINTED && !t->hint.load(std::memory_order_acquire)) {
+                t->state.store(ST_IDLE, std::memory_order_release);  // the hint was withdrawn
+            }
+        }
+    }
+
     int step() {
+        for (Client *t : hp) admit_external(t);
+        for (Client *t : be) admit_external(t);
         // 1. latency-critical: hints raise the word early, submissions are launched at once.
         int hp_active = 0;
         bool hp_launched_this_step = false;
-        for (Tenant *t : hp) {
+        for (Client *t : hp) {
             int st = t->state.load(std::memory_order_acquire);
             if (st == ST_HINTED) {
                 ++hp_active;
@@ -385,7 +440,7 @@ struct Dispatcher {
                 if (policy == POLICY_BLP_WAIT) {
                     // Wait-based: the latency-critical kernels are only launched once every
                     // best-effort executor has drained (blpclient.cpp:185-191).
-                    for (Tenant *b : be)
+                    for (Client *b : be)
                         if (b->state.load(std::memory_order_relaxed) == ST_RUNNING ||
                             b->state.load(std::memory_order_relaxed) == ST_RESUMING)
                             may_launch = false;
@@ -393,13 +448,15 @@ struct Dispatcher {
                     may_launch = seq_turn(t);
                 }
                 if (may_launch) {
+                    stats_lock();
                     stats.hp_queue_us.push_back((now_ns() - t->submit_ns) / 1e3);
+                    stats_unlock();
                     GPX_TRY(launch_full(t));
                     t->state.store(ST_RUNNING, std::memory_order_release);
                     hp_launched_this_step = true;
                 }
             } else if (st == ST_RUNNING) {
-                cudaError_t q = cudaEventQuery(t->done);
+                cudaError_t q = t->exec ? cudaEventQuery(t->done) : cudaSuccess;
                 if (q == cudaSuccess) {
                     t->state.store(ST_DONE, std::memory_order_release);
                     seq_release(t);
@@ -414,12 +471,12 @@ struct Dispatcher {
         (void)hp_launched_this_step;
         // 2. best-effort progress.
         int be_running = 0;
-        for (Tenant *t : be) {
+        for (Client *t : be) {
             int st = t->state.load(std::memory_order_acquire);
             if (st == ST_RUNNING) {
-                cudaError_t q = cudaEventQuery(t->done);
+                cudaError_t q = t->exec ? cudaEventQuery(t->done) : cudaSuccess;
                 if (q == cudaSuccess) {
-                    int stop = t->exec->kind == GPX_EXEC_BLP ? *t->exec->h_stop_index : -1;
+                    int stop = (t->exec && t->exec->kind == GPX_EXEC_BLP) ? *t->exec->h_stop_index : -1;
                     if (stop == -1 && t->unlaunched_from >= 0) stop = t->unlaunched_from;
                     t->unlaunched_from = -1;
                     if (stop == -1) {
@@ -427,10 +484,13 @@ struct Dispatcher {
                         seq_release(t);
                     } else {
                         t->stop_index = stop;
-                        if (t->exec->trace_on && (size_t)stop < t->exec->model->kernels.size()) {
+                        if (t->exec && t->exec->trace_on && (size_t)stop < t->exec->model->kernels.size()) {
                             const unsigned long long *tr = t->exec->h_trace + 4 * (size_t)stop;
-                            if (tr[2] != ~0ull && tr[1] >= tr[2])
+                            if (tr[2] != ~0ull && tr[1] >= tr[2]) {
+                                stats_lock();
                                 stats.kernel_drain_us.push_back((double)(tr[1] - tr[2]) / 1e3);
+                                stats_unlock();
+                            }
                         }
                         t->state.store(ST_SUSPENDED, std::memory_order_release);
                     }
@@ -446,7 +506,9 @@ struct Dispatcher {
             }
         }
         if (word_raised && drain_pending && be_running == 0) {
+            stats_lock();
             stats.drain_us.push_back((now_ns() - t_raise) / 1e3);
+            stats_unlock();
             drain_pending = false;
         }
         // 3. the word is cleared only when no latency-critical request is in the system and
@@ -455,12 +517,14 @@ struct Dispatcher {
         if (word_raised && hp_active == 0 && be_running == 0) GPX_TRY(clear());
         // 4. best-effort launches and resumes while the word is clear.
         if (!word_raised) {
-            for (Tenant *t : be) {
+            for (Client *t : be) {
                 int st = t->state.load(std::memory_order_acquire);
                 if (st == ST_SUBMITTED) {
                     if (policy == POLICY_SEQ && !seq_turn(t)) continue;
+                    stats_lock();
                     ++stats.be_launches;
-                    if (be_window && t->exec->kind == GPX_EXEC_BLP &&
+                    stats_unlock();
+                    if (be_window && t->exec && t->exec->kind == GPX_EXEC_BLP &&
                         t->exec->model->kernels.size() > be_window_min_kernels) {
                         GPX_TRY(windowed_begin(t));
                         t->state.store(ST_RESUMING, std::memory_order_release);
@@ -471,7 +535,9 @@ struct Dispatcher {
                     t->state.store(ST_RUNNING, std::memory_order_release);
                 } else if (st == ST_SUSPENDED) {
                     GPX_TRY(resume_begin(t));
+                    stats_lock();
                     ++stats.be_resumes;
+                    stats_unlock();
                     ++t->resumes;
                     t->state.store(ST_RESUMING, std::memory_order_release);
                     GPX_TRY(resume_continue(t, false));
@@ -485,16 +551,16 @@ struct Dispatcher {
 
     // Strict serialisation (src/common-clients/seqclient.cpp:82-102): one request on the GPU
     // at a time, in submission order.
-    Tenant *seq_owner = nullptr;
-    bool seq_turn(Tenant *t) {
+    Client *seq_owner = nullptr;
+    bool seq_turn(Client *t) {
         if (seq_owner && seq_owner != t) return false;
         if (!seq_owner) {
             uint64_t mine = t->ticket.load(std::memory_order_relaxed);
-            for (Tenant *o : hp)
+            for (Client *o : hp)
                 if (o != t && o->state.load(std::memory_order_relaxed) == ST_SUBMITTED &&
                     o->ticket.load(std::memory_order_relaxed) < mine)
                     return false;
-            for (Tenant *o : be)
+            for (Client *o : be)
                 if (o != t && o->state.load(std::memory_order_relaxed) == ST_SUBMITTED &&
                     o->ticket.load(std::memory_order_relaxed) < mine)
                     return false;
@@ -502,7 +568,7 @@ struct Dispatcher {
         }
         return true;
     }
-    void seq_release(Tenant *t) {
+    void seq_release(Client *t) {
         if (seq_owner == t) seq_owner = nullptr;
     }
 
@@ -519,6 +585,7 @@ struct Dispatcher {
                 fail("dispatcher step");
                 return;
             }
+            beat_ns.store(now_ns(), std::memory_order_relaxed);
         }
     }
 };
@@ -539,6 +606,7 @@ struct Suite {
     bool drop_tile = false;
     size_t be_window = 16, be_window_min_kernels = 64;
     int word_transport = GPX_WORD_DEVICE;
+    uint64_t request_timeout_ms = 60000;  // a request the dispatcher has not completed by then fails the run
     size_t copy_chunk = 2u << 20;  // best-effort input copies are issued in pieces of this size
     bool resident = false;  // inputs stay in HBM: no per-request host<->device copies
     bool prefetch_inputs = false;  // best-effort tenants stage the next input while a request runs
@@ -620,9 +688,17 @@ struct Suite {
             t->staged_off = 0;
             GPX_CUDA(cudaStreamWaitEvent(t->copy_stream, t->consumed, 0));
         }
-        // Spin for the dispatcher's DONE; best-effort clients back off between polls.
+        // Spin for the dispatcher's DONE; best-effort clients back off between polls.  The wait has a
+        // deadline: a dispatcher that stopped making progress fails the request (and with it the
+        // run) instead of hanging the client for ever.
+        const uint64_t deadline = t3 + request_timeout_ms * 1000000ull;
         for (uint32_t spin = 0;; ++spin) {
             if (t->state.load(std::memory_order_acquire) == ST_DONE) break;
+            if ((spin & 255) == 255 && now_ns() > deadline) {
+                set_error("task %s: request not completed within %llu ms (dispatcher stalled?)", t->id.c_str(),
+                          (unsigned long long)request_timeout_ms);
+                return GPX_TIMEOUT;
+            }
             if (prefetch && t->staged_off < t->in_bytes && cudaStreamQuery(t->copy_stream) == cudaSuccess)
                 GPX_TRY(stage_next_chunk(t));
             if (d->failed.load(std::memory_order_relaxed)) {
@@ -701,7 +777,15 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
     s.hint = cfg.has("preempt_hint") ? cfg["preempt_hint"].as_bool() : hint;
     s.hint_lead_us = (uint64_t)cfg["hint_lead_us"].as_int(0);
     s.prefetch_inputs = cfg["prefetch_inputs"].as_bool(false);
-    if (cfg.has("be_window")) s.be_window = (size_t)cfg["be_window"].as_int(16);
+    if (cfg.has("be_window")) {
+        // The window is counted in segments of kSegKernels launches tracked by a ring of eight
+        // events: 0 (no window) or kSegKernels .. 8 * kSegKernels kernels.
+        const long long w = cfg["be_window"].as_int(16);
+        const long long lo = (long long)Dispatcher::kSegKernels, hi = 8 * lo;
+        GPX_REQUIRE(w == 0 || (w >= lo && w <= hi), GPX_OUT_OF_RANGE,
+                    "be_window %lld: must be 0 (whole runs are enqueued) or between %lld and %lld kernels", w, lo, hi);
+        s.be_window = (size_t)w;
+    }
     if (cfg.has("be_window_min_kernels")) s.be_window_min_kernels = (size_t)cfg["be_window_min_kernels"].as_int(64);
     s.time_s = cfg["time"].as_double(1.0);
     if (cfg.has("warmup")) s.warmup = (int)cfg["warmup"].as_int();
@@ -712,6 +796,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
     s.end_when = cfg["end_when"].as_string();
     s.resident = cfg["resident_inputs"].as_bool(false);
     if (cfg.has("copy_chunk_bytes")) s.copy_chunk = (size_t)cfg["copy_chunk_bytes"].as_int(0);
+    if (cfg.has("request_timeout_ms")) s.request_timeout_ms = (uint64_t)std::max<long long>(1, cfg["request_timeout_ms"].as_int(60000));
     int default_gpu = (int)cfg["device"].as_int(0);
     const Json &tasks = cfg["tasks"];
     GPX_REQUIRE(tasks.is_array() && tasks.size() > 0, GPX_FAIL, "config has no tasks");
@@ -1044,6 +1129,8 @@ static int run_suite(Suite &s, Json *report) {
 
 using namespace gpx;
 
+static thread_local std::string g_last_report;
+
 extern "C" int gpx_run_workload(const char *client, const char *config_json, char *report,
                                 size_t cap, size_t *needed) {
     GPX_REQUIRE(client && config_json, GPX_FAIL, "NULL argument");
@@ -1064,12 +1151,230 @@ extern "C" int gpx_run_workload(const char *client, const char *config_json, cha
         set_error("%s", saved.c_str());
         return st;
     }
-    std::string text = rep.dump(1);
+    // The rendered report is kept (per calling thread) so a caller whose buffer was too small can
+    // fetch it with gpx_workload_report instead of running the workload again.
+    g_last_report = rep.dump(1);
+    const std::string &text = g_last_report;
+    if (needed) *needed = text.size() + 1;
+    if (!report || cap < text.size() + 1) {
+        set_error("report needs %zu bytes; fetch it with gpx_workload_report", text.size() + 1);
+        return report ? GPX_OUT_OF_RANGE : GPX_SUCC;
+    }
+    memcpy(report, text.c_str(), text.size() + 1);
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_workload_report(char *report, size_t cap, size_t *needed) {
+    const std::string &text = g_last_report;
+    GPX_REQUIRE(!text.empty(), GPX_NOT_FOUND, "no workload has completed on this thread");
     if (needed) *needed = text.size() + 1;
     if (!report || cap < text.size() + 1) {
         set_error("report needs %zu bytes", text.size() + 1);
         return report ? GPX_OUT_OF_RANGE : GPX_SUCC;
     }
     memcpy(report, text.c_str(), text.size() + 1);
+    return GPX_SUCC;
+}
+
+// ---- scheduler API ------------------------------------------------------------------------------
+//
+// The dispatcher behind gpx_run_workload, for clients that bring their own request loop: the
+// counterpart of REEFScheduler's public interface (include/reef_scheduler.h:61-109: create_queue,
+// bind_model_queue, new_task, wait_task, run, shutdown).
+
+struct gpx_sched {
+    Dispatcher d;
+    std::vector<std::unique_ptr<Client>> clients;
+    bool running = false;
+    bool gpu_ready = false;
+    std::string policy_name;
+};
+
+static int sched_gpu_setup(gpx_sched *s) {
+    if (s->gpu_ready) return GPX_SUCC;
+    GPX_TRY(gpx_init(s->d.device));
+    if (s->d.policy == POLICY_YIELD || s->d.policy == POLICY_BLP_WAIT) {
+        GPX_TRY(gpx_word_create(&s->d.word, GPX_WORD_DEVICE));
+        GPX_CUDA(cudaEventCreateWithFlags(&s->d.clear_event, cudaEventDisableTiming));
+        GPX_CUDA(cudaEventRecord(s->d.clear_event, s->d.word->wstream));
+    }
+    s->gpu_ready = true;
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_create(int device, const char *client_policy, gpx_sched **out) {
+    GPX_REQUIRE(out, GPX_FAIL, "NULL argument");
+    std::unique_ptr<gpx_sched> s(new gpx_sched());
+    bool rt_only = false, hint = true;
+    s->policy_name = client_policy && client_policy[0] ? client_policy : "gpreemptclient";
+    GPX_TRY(parse_policy(s->policy_name, &s->d.policy, &rt_only, &hint));
+    s->d.device = device;
+    s->d.hint = hint;
+    *out = s.release();
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_attach(gpx_sched *s, gpx_exec *exec, int priority, int *client) {
+    GPX_REQUIRE(s && client, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(!s->running, GPX_FAIL, "clients are attached before gpx_sched_run");
+    GPX_REQUIRE(priority == 0 || priority == 1, GPX_OUT_OF_RANGE, "priority %d: 0 = latency-critical, 1 = best-effort", priority);
+    std::unique_ptr<Client> c(new Client());
+    c->priority = priority;
+    c->gpu = s->d.device;
+    c->exec = exec;
+    c->external = true;
+    if (exec) {
+        GPX_TRY(sched_gpu_setup(s));
+        GPX_REQUIRE(exec->model->device == s->d.device, GPX_FAIL, "the executor's model lives on device %d, the scheduler on %d",
+                    exec->model->device, s->d.device);
+        if (exec->kind == GPX_EXEC_BLP) {
+            GPX_REQUIRE(s->d.word, GPX_FAIL, "policy '%s' has no preempt word; attach a base executor", s->policy_name.c_str());
+            GPX_TRY(gpx_exec_set_word(exec, s->d.word));
+            GPX_TRY(gpx_exec_enable_trace(exec, 1));
+        }
+        gpx_stream st;
+        GPX_TRY(gpx_stream_create(&st, priority == 0 ? 0 : 1));
+        c->stream = as_stream(st);
+        GPX_CUDA(cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming));
+        for (auto &ev : c->seg_ev) GPX_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    }
+    *client = (int)s->clients.size();
+    (priority == 0 ? s->d.hp : s->d.be).push_back(c.get());
+    s->clients.push_back(std::move(c));
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_client_stream(gpx_sched *s, int client, gpx_stream *stream) {
+    GPX_REQUIRE(s && stream, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(client >= 0 && (size_t)client < s->clients.size(), GPX_OUT_OF_RANGE, "client %d does not exist", client);
+    *stream = (gpx_stream)s->clients[client]->stream;
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_run(gpx_sched *s) {
+    GPX_REQUIRE(s, GPX_FAIL, "NULL scheduler");
+    GPX_REQUIRE(!s->running, GPX_FAIL, "the scheduler is already running");
+    const char *core_base_env = getenv("GPX_CORE_BASE");
+    s->d.core = core_base_env ? atoi(core_base_env) : -1;
+    s->d.stop.store(false);
+    s->d.beat_ns.store(now_ns());
+    s->d.thread = std::thread([dp = &s->d] { dp->run(); });
+    s->running = true;
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_enqueue(gpx_sched *s, int client, uint64_t *ticket) {
+    GPX_REQUIRE(s && ticket, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(client >= 0 && (size_t)client < s->clients.size(), GPX_OUT_OF_RANGE, "client %d does not exist", client);
+    Client *c = s->clients[client].get();
+    const uint64_t pending = c->submitted.load(std::memory_order_relaxed) - c->completed.load(std::memory_order_acquire);
+    // (capacity of the reference's task queues, include/threadsafe_queue.h:14)
+    GPX_REQUIRE(pending < 10000, GPX_FULL, "client %d has %llu requests outstanding", client, (unsigned long long)pending);
+    *ticket = c->submitted.fetch_add(1, std::memory_order_release) + 1;
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_hint(gpx_sched *s, int client, int on) {
+    GPX_REQUIRE(s, GPX_FAIL, "NULL scheduler");
+    GPX_REQUIRE(client >= 0 && (size_t)client < s->clients.size(), GPX_OUT_OF_RANGE, "client %d does not exist", client);
+    s->clients[client]->hint.store(on ? 1 : 0, std::memory_order_release);
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_wait(gpx_sched *s, int client, uint64_t ticket, uint64_t timeout_ns) {
+    GPX_REQUIRE(s, GPX_FAIL, "NULL scheduler");
+    GPX_REQUIRE(client >= 0 && (size_t)client < s->clients.size(), GPX_OUT_OF_RANGE, "client %d does not exist", client);
+    Client *c = s->clients[client].get();
+    GPX_REQUIRE(ticket >= 1 && ticket <= c->submitted.load(std::memory_order_acquire), GPX_NOT_FOUND,
+                "client %d has issued no ticket %llu", client, (unsigned long long)ticket);
+    const uint64_t t0 = now_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        if (c->completed.load(std::memory_order_acquire) >= ticket) return GPX_SUCC;
+        if (s->d.failed.load(std::memory_order_acquire)) {
+            set_error("dispatcher failed: %s", s->d.error.c_str());
+            return GPX_FAIL;
+        }
+        if ((spin & 63) == 63) {
+            if (now_ns() - t0 > timeout_ns) {
+                set_error("ticket %llu of client %d not completed within %llu ns%s", (unsigned long long)ticket, client,
+                          (unsigned long long)timeout_ns, s->running ? "" : " (the scheduler is not running)");
+                return GPX_TIMEOUT;
+            }
+            if (c->priority != 0) usleep(20);
+        }
+    }
+}
+
+extern "C" int gpx_sched_shutdown(gpx_sched *s) {
+    GPX_REQUIRE(s, GPX_FAIL, "NULL scheduler");
+    if (s->running) {
+        s->d.stop.store(true);
+        if (s->d.thread.joinable()) s->d.thread.join();
+        s->running = false;
+    }
+    // Whatever state the dispatcher stopped in, no kernel may find the word raised afterwards.
+    if (s->d.word && s->d.word_raised) {
+        gpx_word_clear(s->d.word);
+        s->d.word_raised = false;
+    }
+    if (s->d.failed.load()) {
+        set_error("dispatcher failed: %s", s->d.error.c_str());
+        return GPX_FAIL;
+    }
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_destroy(gpx_sched *s) {
+    if (!s) return GPX_SUCC;
+    gpx_sched_shutdown(s);
+    if (s->gpu_ready) cudaSetDevice(s->d.device);
+    for (auto &cp : s->clients) {
+        Client *c = cp.get();
+        if (c->stream) cudaStreamSynchronize(c->stream);
+        if (c->done) cudaEventDestroy(c->done);
+        for (auto &ev : c->seg_ev)
+            if (ev) cudaEventDestroy(ev);
+        if (c->stream) cudaStreamDestroy(c->stream);
+    }
+    if (s->d.clear_event) cudaEventDestroy(s->d.clear_event);
+    if (s->d.word) gpx_word_destroy(s->d.word);
+    delete s;
+    return GPX_SUCC;
+}
+
+extern "C" int gpx_sched_stats(gpx_sched *s, char *json, size_t cap, size_t *needed) {
+    GPX_REQUIRE(s, GPX_FAIL, "NULL scheduler");
+    s->d.stats_lock();
+    Stats st = s->d.stats;
+    s->d.stats_unlock();
+    Json root = Json::object();
+    root.set("policy", s->policy_name);
+    root.set("running", Json(s->running));
+    root.set("failed", Json(s->d.failed.load()));
+    root.set("wordRaises", Json(st.raises));
+    root.set("beLaunches", Json(st.be_launches));
+    root.set("beResumes", Json(st.be_resumes));
+    root.set("preemptLatency(us)", summarize(st.drain_us));
+    root.set("kernelDrain(us)", summarize(st.kernel_drain_us));
+    root.set("hpDispatchDelay(us)", summarize(st.hp_queue_us));
+    Json jc = Json::array();
+    for (auto &cp : s->clients) {
+        Json j = Json::object();
+        j.set("priority", Json(cp->priority));
+        j.set("submitted", Json((long long)cp->submitted.load()));
+        j.set("completed", Json((long long)cp->completed.load()));
+        j.set("resumes", Json(cp->resumes));
+        j.set("lastQueue(us)", Json(cp->last_queue_ns.load() / 1e3));
+        j.set("lastRun(us)", Json(cp->last_run_ns.load() / 1e3));
+        jc.push(j);
+    }
+    root.set("clients", jc);
+    std::string text = root.dump(1);
+    if (needed) *needed = text.size() + 1;
+    if (!json || cap < text.size() + 1) {
+        if (json) set_error("statistics need %zu bytes", text.size() + 1);
+        return json ? GPX_OUT_OF_RANGE : GPX_SUCC;
+    }
+    memcpy(json, text.c_str(), text.size() + 1);
     return GPX_SUCC;
 }

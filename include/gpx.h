@@ -324,6 +324,58 @@ int gpx_exec_read_cursors(gpx_exec *e, int *out, size_t cap, size_t *n);
  * written to `report`; *needed receives its length including NUL. */
 int gpx_run_workload(const char *client, const char *config_json, char *report, size_t cap,
                      size_t *needed);
+/* The report of the last workload this thread completed (BenchmarkSuite::generateReport can be
+ * called again after run, third_party/disb/src/benchmark.cpp:340-354): when gpx_run_workload
+ * returned GPX_OUT_OF_RANGE because `cap` was too small, the run is not lost; call this with a
+ * buffer of *needed bytes.  NULL `report` only queries the size. */
+int gpx_workload_report(char *report, size_t cap, size_t *needed);
+
+/* ---- scheduler ---------------------------------------------------------------------- */
+
+/* The per-GPU dispatch loop behind gpx_run_workload, for clients that bring their own request
+ * loop.  Counterpart of reef::executor::REEFScheduler (include/reef_scheduler.h:61-109,
+ * src/reef-client/reef_scheduler.cpp:35-260): one scheduler thread per GPU that launches
+ * latency-critical requests the moment it sees them, raises the preempt word so that running
+ * best-effort kernels drain, and resumes them from their stop point afterwards.  Clients talk to
+ * it through per-client atomic counters (no mutex, no condition variable).
+ *
+ * `client_policy` is one of the names gpx_run_workload takes ("gpreemptclient", "blpclient",
+ * "baseclient", "seqclient", "reefclient", ...); NULL = "gpreemptclient".  Creating a scheduler
+ * touches no GPU; the first attached executor does. */
+typedef struct gpx_sched gpx_sched;
+int gpx_sched_create(int device, const char *client_policy, gpx_sched **s);
+/* REEFScheduler::create_queue + bind_model_queue (include/reef_scheduler.h:67-75): registers an
+ * executor as a request source of the given priority (0 = latency-critical: real-time queue,
+ * 1 = best-effort) and returns its client index.  The scheduler creates the stream the executor
+ * runs on; a BLP executor is bound to the scheduler's preempt word here, so attach it before
+ * capturing its graph.  `exec` may be NULL: such a client's requests complete as soon as the
+ * dispatcher sees them (dispatch-latency probe, the gpu_noop of the scheduler).  Attach every
+ * client before gpx_sched_run. */
+int gpx_sched_attach(gpx_sched *s, gpx_exec *exec, int priority, int *client);
+/* The stream a client's executor is launched on (for input copies and graph capture). */
+int gpx_sched_client_stream(gpx_sched *s, int client, gpx_stream *stream);
+/* REEFScheduler::run / shutdown (include/reef_scheduler.h:101-102): start and stop the
+ * dispatcher thread.  Shutdown clears the preempt word if it was left raised. */
+int gpx_sched_run(gpx_sched *s);
+int gpx_sched_shutdown(gpx_sched *s);
+int gpx_sched_destroy(gpx_sched *s);
+/* REEFScheduler::new_task (include/reef_scheduler.h:85-88): one more execution of the client's
+ * executor; *ticket identifies it (1, 2, 3, ... per client).  Requests of one client run in
+ * order, one at a time.  GPX_FULL when 10 000 are outstanding (the reference's queue capacity,
+ * include/threadsafe_queue.h:14). */
+int gpx_sched_enqueue(gpx_sched *s, int client, uint64_t *ticket);
+/* REEFScheduler::wait_task (include/reef_scheduler.h:90-92), with a deadline: GPX_SUCC once the
+ * request completed, GPX_TIMEOUT after `timeout_ns` (the request stays queued), GPX_FAIL when the
+ * dispatcher stopped on an error. */
+int gpx_wait(gpx_sched *s, int client, uint64_t ticket, uint64_t timeout_ns);
+/* Pre-preemption hint (DeamonHint, src/cuda-clients/gpreemptclient.cpp:51-60,203-219): a
+ * latency-critical client announces that a request is about to be submitted; the dispatcher
+ * raises the preempt word now, so best-effort kernels have drained when the request arrives.
+ * `on` = 0 withdraws the hint. */
+int gpx_sched_hint(gpx_sched *s, int client, int on);
+/* Counters and latency summaries as JSON (REEFScheduler::avg_preempt_latency,
+ * include/reef_scheduler.h:104-106, and the per-GPU section of the workload report). */
+int gpx_sched_stats(gpx_sched *s, char *json, size_t cap, size_t *needed);
 
 /* Host-clock (CLOCK_MONOTONIC ns) minus device %globaltimer offset, measured by a bounded
  * ping kernel; used to place host events on the device timeline. */

@@ -81,6 +81,85 @@ def test_static_scratch_gemm_resumes_after_a_raised_word(gpx, oracle):
         (o.free if hasattr(o, "free") else o.destroy)()
 
 
+def test_static_scratch_gemm_spills_and_reloads_accumulators_mid_tile(gpx, oracle):
+    """The path that makes the static array matter: the word goes up while every CTA is in the
+    middle of its only tile, so each one saves its fp32 accumulators and K position into the
+    array and a `resume=1` call reloads them.  The product sits at the 64-tile limit with a long
+    K, so a tile takes the whole kernel; afterwards a fresh product of another shape (resume=0)
+    must not be disturbed by what the first one left in the array."""
+    import time
+
+    m, n, k = 2048, 1024, 16384
+    a, b = _operands(gpx, oracle, m, n, k, 24)
+    da, db = gpx.DeviceBuffer.from_numpy(a), gpx.DeviceBuffer.from_numpy(b)
+    want_buf, got_buf = gpx.DeviceBuffer(m * n * 2), gpx.DeviceBuffer(m * n * 2)
+    s = gpx.Stream(1)
+    ctx = gpx.GemmContext()
+    tiles = gpx.gemm_tiles(m, n)
+    assert tiles == 64
+    gpx.gemm_bf16(da, db, want_buf, m, n, k, ctx, None, s)
+    s.sync()
+    t0 = time.perf_counter()
+    ctx.reset()
+    gpx.gemm_bf16(da, db, want_buf, m, n, k, ctx, None, s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    assert ctx.status() == (0, 0)
+    want = want_buf.download(np.uint16, m * n)
+
+    word = gpx.PreemptWord(1)
+    blp = gpx.BlpContext(word, kernel_id=6)
+    mid_tile_stops = 0
+    for trial, frac in enumerate((0.3, 0.5, 0.2, 0.6)):
+        got_buf.zero()
+        blp.reset()
+        word.clear()
+        gpx.device_sync()
+        resume = False
+        rounds = 0
+        while True:
+            gpx.gemm_bf16_static(da, db, got_buf, m, n, k, resume, blp, s)
+            if rounds < 3:
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < run_us * frac:
+                    pass
+                word.raise_()
+            s.sync()
+            word.clear()
+            gpx.device_sync()
+            st = blp.read()
+            assert gpx.gemm_static_status() == (0, 0)
+            rounds += 1
+            if st["stop_index"] == -1:
+                break
+            assert st["stop_index"] == 6
+            # One tile per CTA: a launch that ran for a while and completed no tile can only have
+            # left its progress in the accumulators it saved.
+            if st["cursor"] < tiles and st["t_seen"] - st["t_start"] > 5_000:
+                mid_tile_stops += 1
+            blp.rearm()
+            resume = True
+            assert rounds < 20
+        st = blp.read()
+        assert st["cursor"] == tiles
+        assert np.array_equal(got_buf.download(np.uint16, m * n), want), f"trial {trial}: resumed result differs"
+    assert mid_tile_stops > 0, "no launch was ever stopped in the middle of its tiles"
+
+    # a fresh product of another shape right after: the header-only clear of resume=0 must do
+    m2, n2, k2 = 1024, 512, 320
+    a2, b2 = _operands(gpx, oracle, m2, n2, k2, 25)
+    da2, db2 = gpx.DeviceBuffer.from_numpy(a2), gpx.DeviceBuffer.from_numpy(b2)
+    want2, got2 = gpx.DeviceBuffer(m2 * n2 * 2), gpx.DeviceBuffer(m2 * n2 * 2)
+    ctx.reset()
+    gpx.gemm_bf16(da2, db2, want2, m2, n2, k2, ctx, None, s)
+    gpx.gemm_bf16_static(da2, db2, got2, m2, n2, k2, False, None, s)
+    s.sync()
+    assert gpx.gemm_static_status() == (0, 0)
+    assert np.array_equal(got2.download(np.uint16, m2 * n2), want2.download(np.uint16, m2 * n2))
+    for o in (da, db, want_buf, got_buf, da2, db2, want2, got2, ctx, blp, word, s):
+        (o.free if hasattr(o, "free") else o.destroy)()
+
+
 def test_static_scratch_gemm_rejects_products_beyond_its_limit(gpx):
     from gpreempt_b200 import binding as B
 
