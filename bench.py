@@ -3,17 +3,20 @@
 
 Workload (the reference's A-type contention config, config/A.json, at the sizes the baseline
 names): a latency-critical ResNet-50 batch-1 fp32 client with Poisson arrivals at 100 req/s and
-a best-effort ResNet-50 batch-32 fp32 client that resubmits continuously.  A "step" is one
-best-effort batch (32 inferences) executed while the latency-critical load keeps arriving.
+a best-effort ResNet-50 batch-32 fp32 client that resubmits continuously.  A "step" is 50
+best-effort batches (1 600 inferences, about 0.1 s) executed while the latency-critical load keeps
+arriving, so that any number of steps spans real contention (about ten latency-critical arrivals
+and preemptions per step).
 
     python bench.py --gpus N --steps K --warmup W          # this library, one rank per GPU
     python bench.py --impl reference --steps K --warmup W  # CPU port of the same forward
 
 Rank 0 prints ONE JSON line.  `value` is the whole-job best-effort throughput (inf/s) under
 contention with inputs resident in HBM; `e2e` is the same with every request's input copied
-from pinned host memory and its result copied back inside the timed region; `hp` carries the
-latency-critical p50/p99 under contention and solo, `preempt_us` the word-raise -> drained
-latency.  No number here is produced on the CPU oracle except the `cpu_baseline` object.
+from pinned host memory and its result copied back inside the timed region; `e2e` also carries
+the rest of the metric: latency-critical p50/p99 under contention (the 10 s run the baseline
+configuration names) and alone, best-effort throughput alone, and the preemption latencies.  No
+number here is produced on the CPU oracle except the `cpu_baseline` object.
 """
 from __future__ import annotations
 
@@ -29,8 +32,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 BE_BATCH = 32
-LATENCY_RUN_S = 4.0
+BATCHES_PER_STEP = 50
+LATENCY_RUN_S = 10.0
 HP_RATE = 100.0
+WORKLOAD = ("configs[1]: HP ResNet-50 b1 fp32 Poisson 100 req/s vs BE ResNet-50 b32 fp32 closed loop, "
+            "one scheduler per GPU (replicas)")
+REF_IMAGES_PER_STEP = 8      # bounded sample of a step for the CPU arm
+MICROBENCH_TRIGGERS = 1000
+MICROBENCH_AXPY_ELEMS = 1 << 30
 
 
 def workload_config(device: int, steps: int, warmup: int, resident: bool, hp: bool = True,
@@ -121,10 +130,19 @@ def measured_peaks() -> tuple[dict, str]:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-# DRAM bytes (read + write) the 54 tensor-core convolution launches of one ResNet-50 b32 fp32
-# forward move, from an ncu capture of `python -m gpreempt_b200.profile_step model --model resnet50
-# --batch 32` (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one forward).
-NCU_CONV_DRAM_BYTES_PER_STEP = 2.684e9
+def ncu_traffic_bytes() -> tuple[float | None, str]:
+    """DRAM read + write bytes of the convolution launches of one best-effort forward, from the
+    committed ncu summary (the `dram_bytes_per_step:` line that its capture command produced).
+    None when the summary is absent; the number is a capture, not measured by this run."""
+    path = os.path.join(ROOT, "profiles", "cgemm_tcgen05_resnet50_b32_dram_traffic.md")
+    try:
+        with open(path) as fp:
+            for line in fp:
+                if line.startswith("dram_bytes_per_step:"):
+                    return float(line.split(":", 1)[1].split()[0]), os.path.relpath(path, ROOT)
+    except OSError:
+        pass
+    return None, ""
 
 
 def conv_roofline(api, device: int) -> dict:
@@ -168,33 +186,71 @@ def conv_roofline(api, device: int) -> dict:
         e.destroy()
     return {"conv_flops_per_step": flops, "conv_ms_per_step": ms, "all_kernels_ms_per_step": total_ms,
             "conv_launches_per_step": len(dominant), "tensor_core": bool(tc),
+            "conv_bytes_per_step": sum(infos[i]["bytes"] for i in dominant),
             "share_of_step": ms / total_ms if total_ms else 0.0,
+            "layers": [(infos[i]["flops"], infos[i]["bytes"]) for i in range(nk)],
             "top": [[round(t, 4), n] for t, n in top]}
 
 
-def cpu_baseline(images: int = 100) -> dict:
-    """The oracle's fp32 forward (a port, not the reference's TVM build) timed on host cores."""
+def _seeded_params(orc, shapes, std=None):
+    import numpy as np
+
+    rng = np.random.default_rng(1)
+    params = {}
+    for name, shape in shapes.items():
+        if name.endswith("weight") and len(shape) > 1:
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * (std or np.sqrt(2.0 / fan_in))).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    return params
+
+
+def cpu_baseline(seconds: float = 10.0) -> dict:
+    """The oracle's fp32 forward (a port, not the reference's TVM build) timed on host cores: the
+    benchmark's model for about `seconds`, then one-thread and other-model figures on short samples."""
     import numpy as np
     from oracle import oracle as orc
 
     orc.build()
     rng = np.random.default_rng(1)
-    params = {}
-    for name, shape in orc.resnet_param_shapes().items():
-        if name.endswith("weight"):
-            fan_in = int(np.prod(shape[1:]))
-            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
-        else:
-            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    params = _seeded_params(orc, orc.resnet_param_shapes())
     data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
     orc.forward("resnet50", params, data, fast=True)  # warm-up
     t0 = time.perf_counter()
-    for _ in range(images):
+    images = 0
+    while time.perf_counter() - t0 < seconds:
         orc.forward("resnet50", params, data, fast=True)
+        images += 1
     dt = time.perf_counter() - t0
+    others = {}
+
+    def timed(fn, reps):
+        fn()
+        t = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        return (time.perf_counter() - t) / reps
+
+    try:
+        others["mobilenet_v2_b1_inf_s"] = 1.0 / timed(lambda: orc.forward(
+            "mobilenet_v2", _seeded_params(orc, orc.mobilenet_v2_param_shapes()), data, fast=True), 5)
+        dn = _seeded_params(orc, orc.densenet_param_shapes())
+        others["densenet201_b1_inf_s"] = 1.0 / timed(lambda: orc.forward("densenet201", dn, data, fast=True), 3)
+        bp = _seeded_params(orc, orc.bert_param_shapes(), 0.02)
+        ids = rng.integers(0, 30522, (1, 128)).astype(np.int64)
+        others["bert_base_s128_b1_inf_s"] = 1.0 / timed(lambda: orc.bert_forward(bp, ids), 2)
+        x = rng.standard_normal(1 << 26).astype(np.float32)
+        y = rng.standard_normal(1 << 26).astype(np.float32)
+        others["axpy_2p26_gb_s"] = 12.0 * (1 << 26) / timed(lambda: orc.axpy(1.0009765625, x, y), 3) / 1e9
+        a = orc.f32_to_bf16(rng.uniform(-1, 1, (1024, 1024)).astype(np.float32))
+        others["gemm_bf16_1024_gflop_s"] = 2.0 * 1024 ** 3 / timed(lambda: orc.gemm_bf16_nt_fast(a, a), 2) / 1e9
+    except Exception as e:  # noqa: BLE001 - the side figures must not cost the run its line
+        others["error"] = repr(e)
     return {"value": images / dt, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
             "sample": f"{images} ResNet-50 fp32 batch-1 forwards of the CPU oracle "
-                      f"(fp32 accumulate, OpenMP), {dt:.1f} s"}
+                      f"(fp32 accumulate, OpenMP, every core), {dt:.1f} s",
+            "other_samples": others}
 
 
 def run_reference(args, rank: int) -> None:
@@ -209,29 +265,23 @@ def run_reference(args, rank: int) -> None:
 
     orc.build()
     rng = np.random.default_rng(1)
-    params = {}
-    for name, shape in orc.resnet_param_shapes().items():
-        if name.endswith("weight"):
-            fan_in = int(np.prod(shape[1:]))
-            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
-        else:
-            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    params = _seeded_params(orc, orc.resnet_param_shapes())
     data = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
     for _ in range(max(1, min(args.warmup, 3))):
         orc.forward("resnet50", params, data, fast=True)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(args.steps * REF_IMAGES_PER_STEP):
         orc.forward("resnet50", params, data, fast=True)
     dt = time.perf_counter() - t0
-    value = args.steps / dt
-    sample = "each step = 1 of the 32 images of a best-effort batch (ResNet-50 fp32 forward on the CPU)"
+    value = args.steps * REF_IMAGES_PER_STEP / dt
+    sample = (f"each step = {REF_IMAGES_PER_STEP} of the {BATCHES_PER_STEP * BE_BATCH} images of a step "
+              "(ResNet-50 fp32 forward on the CPU, every host core)")
     line = {
         "impl": "reference", "metric": "be_throughput_under_hp_contention", "value": value,
         "unit": "inf/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: HP ResNet-50 b1 Poisson 100 req/s vs BE ResNet-50 b32 "
-                               "closed loop, fp32", "note": sample},
+        "config": {"workload": WORKLOAD, "be_batch": BE_BATCH, "hp_rate_hz": HP_RATE, "note": sample},
         "cpu_baseline": {"value": value, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "inf/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -240,13 +290,20 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def model_roofline_ms(layers, peak_tflops: float, hbm_gbs: float) -> float:
+    """Sum over the kernels of one forward of max(FLOP / tensor peak, bytes / HBM bandwidth)."""
+    return sum(max(f / (peak_tflops * 1e12), b / (hbm_gbs * 1e9)) for f, b in layers) * 1e3
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="gpx", choices=["gpx", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--latency-seconds", type=float, default=LATENCY_RUN_S)
+    ap.add_argument("--triggers", type=int, default=MICROBENCH_TRIGGERS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -275,11 +332,13 @@ def main() -> None:
         B.check(B.load().gpx_launch_count(ctypes.byref(c)))
         return c.value
 
+    batches = args.steps * BATCHES_PER_STEP          # best-effort batches of the timed region
+    warm_batches = args.warmup * BATCHES_PER_STEP    # untimed: the driver's warm-up steps
     # solo runs: latency-critical alone (rtonlyclient) and best-effort alone
     hp_solo = json.loads(api.run_workload(
-        "rtonlyclient", json.dumps(workload_config(device, 0, args.warmup, False, be=False, seconds=2.0))))
+        "rtonlyclient", json.dumps(workload_config(device, 0, 5, False, be=False, seconds=5.0))))
     be_solo = json.loads(api.run_workload(
-        "baseclient", json.dumps(workload_config(device, max(20, args.steps // 4), args.warmup, True, hp=False))))
+        "baseclient", json.dumps(workload_config(device, max(200, batches // 4), warm_batches, True, hp=False))))
 
     sampler = ClockSampler(device)
     dist.barrier(group)
@@ -288,47 +347,59 @@ def main() -> None:
     l0 = launches()
     t0 = time.perf_counter()
     resident = json.loads(api.run_workload(
-        "gpreemptclient", json.dumps(workload_config(device, args.steps, args.warmup, True))))
+        "gpreemptclient", json.dumps(workload_config(device, batches, warm_batches, True))))
     api.device_sync()
     t1 = time.perf_counter()
     l1 = launches()
     e2e = json.loads(api.run_workload(
-        "gpreemptclient", json.dumps(workload_config(device, args.steps, args.warmup, False))))
+        "gpreemptclient", json.dumps(workload_config(device, batches, warm_batches, False))))
     api.device_sync()
     dist.barrier(group)
     clocks = sampler.stop()
-    # Latency statistics need more latency-critical requests than a few hundred best-effort steps
-    # contain (100 req/s): a time-bounded run of the same contention workload, host copies included.
+    # The latency statistics of the configuration: the same contention workload for the 10 s it
+    # names (about 1000 latency-critical requests), host copies included.
     lat = json.loads(api.run_workload(
-        "gpreemptclient", json.dumps(workload_config(device, 0, args.warmup, False, seconds=LATENCY_RUN_S))))
+        "gpreemptclient", json.dumps(workload_config(device, 0, 5, False, seconds=args.latency_seconds))))
 
     def task(rep, tid):
         return next(t for t in rep["tasks"] if t["id"] == tid)
 
     be_r, be_e = task(resident, "resnet50_be"), task(e2e, "resnet50_be")
     hp_r, hp_e = task(resident, "resnet50_rt"), task(e2e, "resnet50_rt")
-    # device-timed span of exactly K best-effort steps (CUDA events on the best-effort stream)
+    # device-timed span of exactly K steps (CUDA events on the best-effort stream)
     ms_resident = be_r["deviceSpan(ms)"]
     ms_e2e = be_e["deviceSpan(ms)"]
     worst_resident = dist.max_over_ranks(group, ms_resident)
     worst_e2e = dist.max_over_ranks(group, ms_e2e)
-    total_inf = world * args.steps * BE_BATCH
+    total_inf = world * batches * BE_BATCH
 
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         roof = conv_roofline(api, device)
-        # flag-to-drain latency and bit-exact resume of the stand-alone best-effort kernels
+        # flag-to-drain latency and bit-exact resume of the stand-alone best-effort kernels, at the
+        # sizes the microbenchmark configuration names (GEMM 8192^3; axpy over 4 GiB vectors)
         microbench = {}
-        for kind, size in (("gemm", 8192), ("axpy", 1 << 28)):
-            r = api.preempt_microbench(kind, size, 200, seed=5)
+        for kind, size in (("gemm", 8192), ("axpy", MICROBENCH_AXPY_ELEMS)):
+            r = api.preempt_microbench(kind, size, args.triggers, seed=5)
             microbench[kind] = {k: r[k] for k in ("triggers", "preempted", "mismatches", "kernel_ms",
                                                   "drain_us_p50", "drain_us_p99", "drain_us_max",
-                                                  "seen_us_p50")}
+                                                  "seen_us_p50", "raise_call_us_max",
+                                                  "drain_after_return_us_max")}
         tflops = roof["conv_flops_per_step"] / (roof["conv_ms_per_step"] * 1e-3) / 1e12
         peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        hbm = peaks["hbm_gbs"]
+        batch_ms = worst_resident / batches
+        model_ms = model_roofline_ms(roof["layers"], peak, hbm)
+        traffic, traffic_src = ncu_traffic_bytes()
+        lat_hp, lat_be = task(lat, "resnet50_rt"), task(lat, "resnet50_be")
+        solo_hp = task(hp_solo, "resnet50_rt")
+        hp_p99 = lat_hp["totalLatency(us)"].get("p99", 0) / 1e3
+        hp_solo_p99 = solo_hp["totalLatency(us)"].get("p99", 0) / 1e3
+        be_solo_inf = task(be_solo, "resnet50_be")["throughput(inf/s)"]
+        value = total_inf / (worst_resident * 1e-3)
         line = {
             "metric": "be_throughput_under_hp_contention",
-            "value": total_inf / (worst_resident * 1e-3),
+            "value": value,
             "unit": "inf/s",
             "n_gpus": world,
             "steps": args.steps,
@@ -339,55 +410,67 @@ def main() -> None:
             "vs_baseline": None,
             "dtype": "f32",
             "data": "synthetic",
+            "gpu_launches": l1 - l0,
             "config": {
-                "workload": "configs[1]: HP ResNet-50 b1 fp32 Poisson 100 req/s vs BE ResNet-50 b32 "
-                            "fp32 closed loop, one scheduler per GPU (replicas)",
+                "workload": WORKLOAD,
                 "be_batch": BE_BATCH, "hp_rate_hz": HP_RATE, "policy": "gpreemptclient (in-kernel yield)",
-                "l2": "every step streams 3 GB of layer traffic (weights + activations), larger than L2",
-                "step": "one best-effort batch under latency-critical load",
+                "step": f"{BATCHES_PER_STEP} best-effort batches ({BATCHES_PER_STEP * BE_BATCH} inferences) "
+                        "under latency-critical Poisson load",
+                "l2": "every batch streams 3 GB of layer traffic (weights + activations), larger than L2",
                 "e2e": "pinned host input copied in and result copied out on every request; the "
                        "best-effort tenant stages its next input while the current batch runs",
+                "latency_run": f"{args.latency_seconds:g} s of the same workload with host copies",
+                "microbench": f"configs[2]: {args.triggers} triggers each, bf16 GEMM 8192^3 and fp32 axpy over "
+                              f"{MICROBENCH_AXPY_ELEMS * 4 // (1 << 30)} GiB vectors",
             },
-            "e2e": {"value": total_inf / (worst_e2e * 1e-3), "unit": "inf/s",
-                    "h2d_bytes_per_step": be_e["in_bytes"], "d2h_bytes_per_step": be_e["out_bytes"],
-                    "ms_per_step": worst_e2e / args.steps},
-            "hp": {
-                "p50_ms": task(lat, "resnet50_rt")["totalLatency(us)"].get("p50", 0) / 1e3,
-                "p99_ms": task(lat, "resnet50_rt")["totalLatency(us)"].get("p99", 0) / 1e3,
-                "requests": task(lat, "resnet50_rt")["requests"],
-                "run": f"{LATENCY_RUN_S:g} s time-bounded contention run, host copies included",
-                "be_inf_s_in_that_run": task(lat, "resnet50_be")["throughput(inf/s)"],
-                "kernel_drain_us_in_that_run": lat["gpus"][0]["kernelDrain(us)"],
-                "step_run_p50_ms": hp_e["totalLatency(us)"].get("p50", 0) / 1e3,
-                "step_run_p99_ms": hp_e["totalLatency(us)"].get("p99", 0) / 1e3,
-                "step_run_requests": hp_e["requests"],
-                "solo_p50_ms": task(hp_solo, "resnet50_rt")["totalLatency(us)"].get("p50", 0) / 1e3,
-                "solo_p99_ms": task(hp_solo, "resnet50_rt")["totalLatency(us)"].get("p99", 0) / 1e3,
-                "resident_p99_ms": hp_r["totalLatency(us)"].get("p99", 0) / 1e3,
-            },
-            "be_solo_inf_s": task(be_solo, "resnet50_be")["throughput(inf/s)"],
-            "preempt_us": e2e["gpus"][0]["preemptLatency(us)"],
-            "kernel_drain_us": e2e["gpus"][0]["kernelDrain(us)"],
-            "preempt_flag_to_drain_us": microbench,
-            "be_resumes": e2e["gpus"][0]["beResumes"],
-            "gpu_launches": l1 - l0,
-            "wall_s_resident_run": t1 - t0,
             "roofline": {
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
-                "frac": tflops / peak, "traffic": NCU_CONV_DRAM_BYTES_PER_STEP if roof["tensor_core"] else None,
-                "traffic_note": "dram__bytes_read+write summed over the 54 convolution launches of one "
-                                "forward (ncu capture, bytes per step); algorithmic bytes of the same "
-                                "launches 3.60e9",
+                "frac": tflops / peak,
+                "traffic": traffic if roof["tensor_core"] else None,
+                "traffic_source": f"ncu capture summarised in {traffic_src} (not measured by this run)" if traffic else None,
+                "algorithmic_bytes": roof["conv_bytes_per_step"],
                 "kernel": ("cgemm_tcgen05_kernel (split-bf16 tensor-core convolution, 3 bf16 MMAs per "
                            "fp32 MAC, best-effort batch 32)") if roof["tensor_core"] else
                           "conv_simt_kernel (fp32 FFMA convolution, best-effort batch 32)",
                 "share_of_step": roof["share_of_step"],
-                "peak_source": f"bf16_tflops_sustained of {peak_kind} peaks",
-                "launches_per_step": roof["conv_launches_per_step"],
-                "ms_per_step_all_kernels": roof["all_kernels_ms_per_step"],
+                "peak_source": f"bf16_tflops_sustained of {peak_kind} peaks; fp32 work is counted once (2 FLOP "
+                               "per multiply-add) against the bf16 peak although it costs three bf16 "
+                               "products, the stricter choice (no TF32 peak is measured)",
+                "launches_per_step": roof["conv_launches_per_step"] * BATCHES_PER_STEP,
+                "ms_per_batch_all_kernels": roof["all_kernels_ms_per_step"],
                 "top_kernels_ms": roof["top"],
+                "model_roofline_ms_per_batch": model_ms,
+                "model_frac": model_ms / batch_ms,
+                "model_frac_note": "sum over the kernels of one batch of max(FLOP / peak, bytes / measured HBM "
+                                   f"bandwidth {hbm:g} GB/s), divided by the measured time per batch under contention",
             },
             "clocks": clocks,
+            "e2e": {
+                "value": total_inf / (worst_e2e * 1e-3), "unit": "inf/s",
+                "h2d_bytes_per_step": be_e["in_bytes"] * BATCHES_PER_STEP,
+                "d2h_bytes_per_step": be_e["out_bytes"] * BATCHES_PER_STEP,
+                "ms_per_step": worst_e2e / args.steps,
+                # the rest of the metric, measured with host copies
+                "hp_p50_ms": lat_hp["totalLatency(us)"].get("p50", 0) / 1e3,
+                "hp_p99_ms": hp_p99,
+                "hp_requests": lat_hp["requests"],
+                "hp_solo_p50_ms": solo_hp["totalLatency(us)"].get("p50", 0) / 1e3,
+                "hp_solo_p99_ms": hp_solo_p99,
+                "hp_p99_over_solo": hp_p99 / hp_solo_p99 if hp_solo_p99 else None,
+                "hp_p99_ms_in_timed_region": hp_e["totalLatency(us)"].get("p99", 0) / 1e3,
+                "hp_requests_in_timed_region": hp_e["requests"],
+                "be_solo_inf_s": be_solo_inf,
+                "be_over_solo": value / world / be_solo_inf if be_solo_inf else None,
+                "be_inf_s_in_latency_run": lat_be["throughput(inf/s)"],
+                "be_resumes_in_timed_region": e2e["gpus"][0]["beResumes"],
+                "preempt_flag_to_drain_p99_us": {k: v["drain_us_p99"] for k, v in microbench.items()},
+                "kernel_drain_p99_us": lat["gpus"][0]["kernelDrain(us)"].get("p99"),
+                "kernel_drain_p50_us": lat["gpus"][0]["kernelDrain(us)"].get("p50"),
+                "host_observed_preempt_p99_us": lat["gpus"][0]["preemptLatency(us)"].get("p99"),
+                "resume_mismatches": sum(v["mismatches"] for v in microbench.values()),
+            },
+            "preempt_microbench": microbench,
+            "wall_s_resident_run": t1 - t0,
         }
         if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
             line["cpu_baseline"] = cpu_baseline()

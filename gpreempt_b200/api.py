@@ -63,7 +63,7 @@ class Stream:
 def _h(stream) -> ctypes.c_void_p:
     if stream is None:
         return ctypes.c_void_p()
-    return stream.handle if isinstance(stream, Stream) else stream
+    return stream.handle if hasattr(stream, "handle") else stream
 
 
 class Event:
@@ -277,7 +277,9 @@ def synth_uniform(n: int, seed: int, stream: int = 0, lo: float = -1.0, hi: floa
 class Model:
     """foo::Model (include/model.h:32-93)."""
 
-    def __init__(self, name: str, batch: int = 1, dtype: str = "float32", seq_len: int = 0):
+    def __init__(self, name: str, batch: int = 0, dtype: str = "", seq_len: int = 0):
+        """`name` is a built-in graph (batch 1 and float32 unless given) or a directory holding
+        mod.json + host.json (+ mod.params), whose batch and storage format are the exported ones."""
         self.handle = ctypes.c_void_p()
         opts = B.ModelOpts(batch, dtype.encode(), seq_len)
         check(B.load().gpx_model_open(name.encode(), ctypes.byref(opts), ctypes.byref(self.handle)))
@@ -359,6 +361,10 @@ class Model:
         buf = ctypes.create_string_buffer(need.value)
         check(B.load().gpx_model_export_json(self.handle, buf, need.value, ctypes.byref(need)))
         return buf.value.decode()
+
+    def export_dir(self, path: str) -> None:
+        """Writes mod.json, host.json and mod.params into `path`; Model(path) loads them back."""
+        check(B.load().gpx_model_export_dir(self.handle, path.encode()))
 
     def clear(self) -> None:
         if self.handle:

@@ -6,7 +6,9 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libgpx.so")
+# GPX_LIB selects another build of the library (a development variant made with
+# `python -m gpreempt_b200.build --define ... --out DIR`).
+LIB_PATH = os.environ.get("GPX_LIB") or os.path.join(HERE, "lib", "libgpx.so")
 HEADER = os.path.join(HERE, "..", "include", "gpx.h")
 
 SUCC, FAIL, TIMEOUT, NOT_FOUND, OUT_OF_RANGE, FULL = range(6)
@@ -38,6 +40,8 @@ class MicrobenchSummary(ctypes.Structure):
         ("drain_us_max", ctypes.c_double), ("drain_us_mean", ctypes.c_double),
         ("seen_us_p50", ctypes.c_double), ("seen_us_p99", ctypes.c_double),
         ("clock_uncertainty_ns", ctypes.c_double),
+        ("raise_call_us_p50", ctypes.c_double), ("raise_call_us_max", ctypes.c_double),
+        ("drain_after_return_us_max", ctypes.c_double),
     ]
 
 
@@ -120,9 +124,11 @@ _SIGS = {
     "gpx_model_kernel_info": [vp, sz, ctypes.c_char_p, sz, P(ctypes.c_uint32), P(ci),
                               P(ctypes.c_double), P(ctypes.c_double)],
     "gpx_model_export_json": [vp, ctypes.c_char_p, sz, P(sz)],
+    "gpx_model_export_dir": [vp, ctypes.c_char_p],
     "gpx_exec_create": [vp, ci, P(vp)],
     "gpx_exec_destroy": [vp],
     "gpx_exec_set_word": [vp, vp],
+    "gpx_exec_set_word_dptr": [vp, vp],
     "gpx_exec_execute": [vp, vp],
     "gpx_exec_launch_kernel": [vp, sz, vp],
     "gpx_exec_capture_graph": [vp, vp],

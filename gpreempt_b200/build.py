@@ -63,19 +63,26 @@ def _digest() -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJDIR, exist_ok=True)
-    stamp = os.path.join(LIBDIR, "libgpx.digest")
-    digest = _digest()
-    if not force and os.path.exists(LIB) and os.path.exists(stamp):
+def build(force: bool = False, verbose: bool = False, defines: list[str] | None = None,
+          out_dir: str | None = None) -> str:
+    """Builds the library.  `defines` adds -D macros (development variants such as
+    GPX_CGEMM_TIMING) and `out_dir` places that variant elsewhere; GPX_LIB selects it at load time."""
+    libdir = os.path.abspath(out_dir) if out_dir else LIBDIR
+    objdir = os.path.join(libdir, "obj")
+    lib = os.path.join(libdir, "libgpx.so")
+    dflags = [f"-D{d}" for d in (defines or [])]
+    os.makedirs(objdir, exist_ok=True)
+    stamp = os.path.join(libdir, "libgpx.digest")
+    digest = _digest() + "|" + " ".join(dflags)
+    if not force and os.path.exists(lib) and os.path.exists(stamp):
         with open(stamp) as fp:
             if fp.read().strip() == digest:
-                return LIB
+                return lib
     exe = nvcc()
 
     def compile_one(src: str) -> str:
-        obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + ".o")
-        cmd = [exe, *NVCC_FLAGS, "-c", src, "-o", obj]
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        cmd = [exe, *NVCC_FLAGS, *dflags, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -88,19 +95,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, sources()))
-    cmd = [exe, "-shared", "-o", LIB, *objs, "-cudart", "static",
+    cmd = [exe, "-shared", "-o", lib, *objs, "-cudart", "static",
            "-gencode", "arch=compute_100a,code=sm_100a", "-lpthread", "-ldl", "-lrt"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     with open(stamp, "w") as fp:
         fp.write(digest)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="extra -D macro (repeatable)")
+    ap.add_argument("--out", default=None, help="directory for this variant (default: the package's lib/)")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, defines=a.define, out_dir=a.out))

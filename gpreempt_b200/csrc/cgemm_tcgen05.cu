@@ -43,6 +43,10 @@ constexpr int kCgemmThreads = 64 + kCEpiThreads;
 constexpr unsigned long long kCWaitLimitNs = 2000000000ull;
 constexpr int kCPollEvery = 1;
 
+struct CgemmControlSize {
+    unsigned char bytes[2560];  // room for CgemmControl (checked below)
+};
+
 template <int BN>
 struct CgemmCfg {
     static constexpr uint32_t kABytes = kCBM * kCBK * 2;        // one plane of A: 16 KiB
@@ -52,7 +56,7 @@ struct CgemmCfg {
     // ring + alignment slack + 64x64 identity tile + control block
     static constexpr uint32_t kIdentBytes = 64 * kCBK * 2;
     static constexpr size_t kSmem =
-        (size_t)kStages * kStageBytes + 1024 + kIdentBytes + 256;
+        (size_t)kStages * kStageBytes + 1024 + kIdentBytes + sizeof(CgemmControlSize);
     // Four fp32 accumulators per tile (see the MMA issuer): hi*hi of even K steps, hi*hi of odd
     // K steps, hi*lo, lo*hi.  256 or 512 TMEM columns, both powers of two.
     // (256-column tiles exist for the two-accumulator plan only: 2 x 256 columns, one buffer.)
@@ -75,7 +79,10 @@ struct CgemmControl {
     int epi_go;
     int raised;  // the word was up when this CTA started
     int abort_flag;
+    float bias_s[2][256];  // bias of the tile each accumulator buffer holds, staged by the epilogue
 };
+
+static_assert(sizeof(CgemmControl) <= sizeof(CgemmControlSize), "control block outgrew its shared-memory budget");
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
@@ -101,11 +108,23 @@ __device__ __forceinline__ float bf16_hi_to_f32(uint32_t packed) {
     return __uint_as_float(packed & 0xffff0000u);
 }
 
+// Phase timers of a development build (-DGPX_CGEMM_TIMING): clock64 deltas summed over CTAs into a
+// device array that gpx_debug_cgemm_timing reads.  Compiled out otherwise.
+#ifdef GPX_CGEMM_TIMING
+__device__ unsigned long long g_cgemm_timing[32];
+#define TCK(var) long long var = clock64()
+#define TADD(slot, val) atomicAdd(&g_cgemm_timing[slot], (unsigned long long)(val))
+#else
+#define TCK(var)
+#define TADD(slot, val)
+#endif
+
 template <int BN>
 __global__ void __launch_bounds__(kCgemmThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     using Cfg = CgemmCfg<BN>;
     constexpr int kStages = Cfg::kStages;
+    TCK(t_start);
     // The prologue below (barriers, tensor memory, descriptor prefetch) touches nothing a
     // predecessor kernel writes, so it runs while that kernel drains; pdl_wait() comes after it.
     extern __shared__ unsigned char smem_raw[];
@@ -214,6 +233,9 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         }
     }
     if (threadIdx.x == 0) trace_begin(blp);
+#ifdef GPX_CGEMM_TIMING
+    if (threadIdx.x == 0) TADD(14, clock64() - t_start);
+#endif
 
     const bool grid_ok = slot_grid == 0 || slot_grid == (int)gridDim.x;
     auto fail = [&](int code) {
@@ -233,6 +255,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             bool ok = true;
             // The identity tile travels with the first stage this CTA fills.
             uint32_t ident_bytes = p.res_kb ? Cfg::kIdentBytes : 0u;
+            TCK(t_prod0);
+#ifdef GPX_CGEMM_TIMING
+            long long prod_wait = 0;
+#endif
             for (int it = first_iter; ok; ++it) {
                 int tile = blockIdx.x + it * gridDim.x;
                 if (tile >= total_tiles) break;
@@ -244,11 +270,15 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 const int num_kb = main_kb + p.res_kb;  // the residual rides along as extra K blocks
                 const int kb_base = tile_kb_begin(tile);
                 for (int kb = kb0; kb < num_kb; ++kb) {
+                    TCK(t_w0);
                     if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs)) {
                         fail(101);
                         ok = false;
                         break;
                     }
+#ifdef GPX_CGEMM_TIMING
+                    prod_wait += clock64() - t_w0;
+#endif
                     if (resumable && ((kb - kb0) % kCPollEvery) == 0) {
                         if (flag != 0) {
                             msg = CMSG_STOP;
@@ -297,6 +327,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     }
                 }
             }
+#ifdef GPX_CGEMM_TIMING
+            TADD(0, prod_wait);
+            TADD(1, clock64() - t_prod0);
+#endif
             if (!*abort_flag) {
                 bool have_slot = msg == CMSG_STOP;
                 if (!have_slot)
@@ -312,10 +346,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp walks the K loop in lock step and one lane issues the tensor-core
+        // instructions.  With the loop inside an `if (lane == 0)` the compiler has to treat every
+        // address and descriptor as a per-thread value and moves each operand of each
+        // tcgen05.mma into the uniform registers the instruction reads, ~100 cycles of a lone
+        // thread's issue time per instruction, more than a 128x128x16 product takes (64 cycles);
+        // warp-uniform control flow keeps that arithmetic on the uniform datapath.
+        {
             const uint32_t idesc = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, BN) : make_idesc_bf16_f32(kCBM, BN);
             const uint32_t idesc64 = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, 64) : make_idesc_bf16_f32(kCBM, 64);
             const uint64_t eye = make_smem_desc_sw128(smem_base + ident_off);
+            const bool issuer = lane == 0;
             int stage = 0;
             uint32_t phase = 0;
             uint32_t seg = 0;
@@ -323,28 +364,45 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             int it = first_iter;
             int num_kb = tile_kb_count(blockIdx.x + it * gridDim.x) + p.res_kb;
             bool seg_open = false;
+            TCK(t_mma0);
+#ifdef GPX_CGEMM_TIMING
+            long long mma_wait_full = 0, mma_wait_tmem = 0, mma_kb = 0;
+#endif
             for (;;) {
-                if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, kCWaitLimitNs)) {
-                    fail(201);
+                TCK(t_f0);
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, kCWaitLimitNs))) {
+                    if (issuer) fail(201);
                     break;
                 }
+#ifdef GPX_CGEMM_TIMING
+                mma_wait_full += clock64() - t_f0;
+                ++mma_kb;
+#endif
                 tc_fence_after_sync();
-                const int msg = ctl->stage_msg[stage];
+                const int msg = __shfl_sync(0xffffffffu, ctl->stage_msg[stage], 0);
                 const int buf = (int)(seg % nbuf);
                 const uint32_t acc0 = tmem_base + buf * buf_cols;
                 if (!seg_open) {
-                    if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), (seg / nbuf) & 1, abort_flag, kCWaitLimitNs)) {
-                        fail(202);
+                    TCK(t_e0);
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->tmem_empty[buf]), (seg / nbuf) & 1, abort_flag,
+                                                           kCWaitLimitNs))) {
+                        if (issuer) fail(202);
                         break;
                     }
+#ifdef GPX_CGEMM_TIMING
+                    mma_wait_tmem += clock64() - t_e0;
+#endif
                     tc_fence_after_sync();
                     seg_open = true;
                 }
                 if (msg != CMSG_DATA && msg < CMSG_RES) {
-                    ctl->epi_kind[buf] = msg == CMSG_STOP ? CEPI_PARTIAL : CEPI_EXIT;
-                    ctl->epi_k_done[buf] = kb;
-                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
-                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
+                    if (issuer) {
+                        ctl->epi_kind[buf] = msg == CMSG_STOP ? CEPI_PARTIAL : CEPI_EXIT;
+                        ctl->epi_k_done[buf] = kb;
+                        mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                        mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
+                    }
+                    __syncwarp();
                     break;
                 }
                 const uint32_t base = smem_base + stage * stage_bytes;
@@ -352,52 +410,63 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 const uint64_t a_lo = make_smem_desc_sw128(base + Cfg::kABytes);
                 const uint64_t w_hi = make_smem_desc_sw128(base + w_off);
                 const uint64_t w_lo = make_smem_desc_sw128(base + 2 * Cfg::kABytes + Cfg::kWBytes);
-#pragma unroll
-                for (int k = 0; k < kCBK / kCUmmaK; ++k) {
-                    // fp32 product from three bf16 products.  The tensor core truncates when it
-                    // adds into the fp32 accumulator, a bias that grows with the length of the
-                    // accumulation chain, so the chain is split over four accumulators that the
-                    // epilogue adds with round-to-nearest: the dominant hi*hi terms alternate
-                    // between two of them, the small hi*lo and lo*hi terms get one each.  The
-                    // order is fixed, so a resumed tile replays exactly the instruction sequence
-                    // of an uninterrupted one.
-                    const uint32_t first = kb > 0 ? 1u : 0u;
+                // fp32 product from three bf16 products.  The tensor core truncates when it adds
+                // into the fp32 accumulator, a bias that grows with the length of the accumulation
+                // chain, so the chain is split over several accumulators that the epilogue adds with
+                // round-to-nearest.  The order is fixed, so a resumed tile replays exactly the
+                // instruction sequence of an uninterrupted one.
+                const uint32_t first = kb > 0 ? 1u : 0u;
+                if (issuer) {
                     if (msg >= CMSG_RES) {
                         // residual x identity on 64 accumulator columns: the hi plane into a hi*hi
                         // accumulator, the lo plane into a cross-term accumulator (exact products,
                         // added like any other)
                         const uint32_t col = (uint32_t)(msg - CMSG_RES) * 64;
-                        if (dual && two_plane) {
-                            mma_f16_ss(acc0 + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
-                            mma_f16_ss(acc0 + BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
-                        } else {
-                            mma_f16_ss(acc0 + (k & 1) * BN + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
-                            if (two_plane) mma_f16_ss(acc0 + 3 * BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
+#pragma unroll
+                        for (int k = 0; k < kCBK / kCUmmaK; ++k) {
+                            if (dual && two_plane) {
+                                mma_f16_ss(acc0 + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
+                                mma_f16_ss(acc0 + BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
+                            } else {
+                                mma_f16_ss(acc0 + (k & 1) * BN + col, a_hi + 2 * k, eye + 2 * k, idesc64, 1u);
+                                if (two_plane) mma_f16_ss(acc0 + 3 * BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
+                            }
                         }
                     } else if (dual && two_plane) {
-                        // short K: hi*hi in one accumulator, both cross terms in the other
-                        mma_f16_ss(acc0, a_hi + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
-                        mma_f16_ss(acc0 + BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
-                        mma_f16_ss(acc0 + BN, a_lo + 2 * k, w_hi + 2 * k, idesc, 1u);
+                        // hi*hi in one accumulator, both cross terms in the other
+#pragma unroll
+                        for (int k = 0; k < kCBK / kCUmmaK; ++k) {
+                            mma_f16_ss(acc0, a_hi + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                            mma_f16_ss(acc0 + BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                            mma_f16_ss(acc0 + BN, a_lo + 2 * k, w_hi + 2 * k, idesc, 1u);
+                        }
                     } else {
-                        mma_f16_ss(acc0 + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc,
-                                   (first || k > 1) ? 1u : 0u);
-                        if (two_plane) {
-                            mma_f16_ss(acc0 + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
-                            mma_f16_ss(acc0 + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                        // hi*hi terms alternate between two accumulators (even / odd K steps); the
+                        // small hi*lo and lo*hi terms get one each
+#pragma unroll
+                        for (int k = 0; k < kCBK / kCUmmaK; ++k) {
+                            mma_f16_ss(acc0 + (k & 1) * BN, a_hi + 2 * k, w_hi + 2 * k, idesc, (first || k > 1) ? 1u : 0u);
+                            if (two_plane) {
+                                mma_f16_ss(acc0 + 2 * BN, a_hi + 2 * k, w_lo + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                                mma_f16_ss(acc0 + 3 * BN, a_lo + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);
+                            }
                         }
                     }
+                    mma_commit(smem_u32(&ctl->empty[stage]));
                 }
-                mma_commit(smem_u32(&ctl->empty[stage]));
+                __syncwarp();
                 if (++stage == nst) {
                     stage = 0;
                     phase ^= 1;
                 }
                 if (++kb == num_kb) {
-                    ctl->epi_kind[buf] = CEPI_COMPLETE;
-                    ctl->epi_k_done[buf] = num_kb;
-                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
-                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
+                    if (issuer) {
+                        ctl->epi_kind[buf] = CEPI_COMPLETE;
+                        ctl->epi_k_done[buf] = num_kb;
+                        mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                        mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
+                    }
+                    __syncwarp();
                     ++seg;
                     ++it;
                     num_kb = tile_kb_count(blockIdx.x + it * gridDim.x) + p.res_kb;
@@ -405,6 +474,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     seg_open = false;
                 }
             }
+#ifdef GPX_CGEMM_TIMING
+            if (issuer) {
+                TADD(2, mma_wait_full);
+                TADD(3, mma_wait_tmem);
+                TADD(4, clock64() - t_mma0);
+                TADD(12, mma_kb);
+            }
+#endif
         }
     } else {
         // ------------------------------------------------------------------ epilogue
@@ -441,15 +518,32 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         int seg_k0 = first_k;
         int tiles_done = 0;
         const int img = p.in_hs * p.in_ws;
+        TCK(t_epi0);
+#ifdef GPX_CGEMM_TIMING
+        long long e_wait = 0, e_tmem = 0, e_math = 0, e_store = 0, e_bar = 0;
+#endif
         for (uint32_t seg = 0;; ++seg) {
             const int buf = (int)(seg % nbuf);
             const uint32_t t_acc = t_lane + buf * buf_cols;
+            TCK(t_wait0);
+            // The bias of the tile this buffer is being filled with goes to shared memory while
+            // the tile is still accumulating: read from global memory inside the drain loop, its
+            // latency (an L2 round trip under load) was paid once per 16-column piece.
+            if (p.bias && !p.partial) {
+                const int next_tile = blockIdx.x + it * gridDim.x;
+                const int t = (int)threadIdx.x - 64;
+                if (next_tile < total_tiles && t < BN)
+                    ctl->bias_s[buf][t] = __ldg(p.bias + ((next_tile / p.k_splits) % p.tiles_n) * BN + t);
+            }
             if (leader) {
                 bool ok = mbar_wait(smem_u32(&ctl->tmem_full[buf]), (seg / nbuf) & 1, abort_flag, kCWaitLimitNs);
                 if (!ok) fail(301);
                 ctl->epi_go = ok ? 1 : 0;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kCEpiThreads) : "memory");
+#ifdef GPX_CGEMM_TIMING
+            e_wait += clock64() - t_wait0;
+#endif
             if (!ctl->epi_go) break;
             tc_fence_after_sync();
             const int kind = ctl->epi_kind[buf];
@@ -495,19 +589,20 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     uint32_t t16[16];
                     // The residual is requested first so its latency overlaps the TMEM reads.
                     const bool use_res = planes_out && p.res_hi && valid;
+                    TCK(t_p0);
                     uint32_t rh[8], rl[8];
                     if (use_res) {
                         ld_global_v8(p.res_hi + res_off + c, rh);
                         if (two_plane) ld_global_v8(p.res_lo + res_off + c, rl);
                     }
-                    tmem_ld_32x16(t_acc + c, t16);
-                    tmem_ld_wait();
+                    {
+                        uint32_t u16[16];
+                        tmem_ld_32x16(t_acc + c, t16);
+                        tmem_ld_32x16(t_acc + BN + c, u16);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(t16[j]);
-                    tmem_ld_32x16(t_acc + BN + c, t16);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) f[j] += __uint_as_float(t16[j]);
+                        for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(t16[j]) + __uint_as_float(u16[j]);
+                    }
                     if (two_plane && !dual) {
                         tmem_ld_32x16(t_acc + 2 * BN + c, t16);
                         tmem_ld_wait();
@@ -518,6 +613,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) f[j] += __uint_as_float(t16[j]);
                     }
+#ifdef GPX_CGEMM_TIMING
+                    long long t_p1 = clock64();
+                    e_tmem += t_p1 - t_p0;
+#endif
                     if (p.partial) {
                         // Split K: the raw fp32 sum of this K range goes to the workspace; the
                         // finishing kernel adds the ranges in split order and applies the rest.
@@ -531,10 +630,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                         continue;
                     }
                     if (p.bias) {
-                        const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + n_blk * BN + c);
+                        const float4 *b4 = reinterpret_cast<const float4 *>(&ctl->bias_s[buf][c]);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            float4 b = __ldg(b4 + j);
+                            float4 b = b4[j];
                             f[4 * j + 0] += b.x;
                             f[4 * j + 1] += b.y;
                             f[4 * j + 2] += b.z;
@@ -571,6 +670,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     for (int q = 0; q < 8; ++q) hi[q] = pf_pack2(f[2 * q], f[2 * q + 1], p.fmt);
                     // The output may be a channel slice: nothing is stored past cout_valid.
                     const bool store = valid && c < col_lim;
+#ifdef GPX_CGEMM_TIMING
+                    long long t_p2 = clock64();
+                    e_math += t_p2 - t_p1;
+#endif
                     if (store) st_global_v8(p.out_hi + out_off + c, hi);
                     if (two_plane) {
                         uint32_t lo[8];
@@ -579,12 +682,19 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                             lo[q] = pack_bf16(f[2 * q] - bf16_lo_to_f32(hi[q]), f[2 * q + 1] - bf16_hi_to_f32(hi[q]));
                         if (store) st_global_v8(p.out_lo + out_off + c, lo);
                     }
+#ifdef GPX_CGEMM_TIMING
+                    e_store += clock64() - t_p2;
+#endif
                 }
                 ++it;
                 ++tiles_done;
                 seg_k0 = 0;
                 tc_fence_before_sync();
+                TCK(t_b0);
                 asm volatile("bar.sync 1, %0;" ::"n"(kCEpiThreads) : "memory");
+#ifdef GPX_CGEMM_TIMING
+                e_bar += clock64() - t_b0;
+#endif
                 if (leader) {
                     mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
                     if (blp.executed) atomicAdd(blp.executed, 1);
@@ -612,6 +722,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             break;
         }
         if (leader && blp.trace && tiles_done) atomicAdd(blp.trace + 3, (unsigned long long)tiles_done);
+#ifdef GPX_CGEMM_TIMING
+        if (lane == 0) {
+            TADD(5, e_wait);
+            TADD(6, e_tmem);
+            TADD(7, e_math);
+            TADD(8, e_store);
+            TADD(9, e_bar);
+            TADD(10, clock64() - t_epi0);
+        }
+        if (leader) TADD(11, tiles_done);
+#endif
     }
 
     tc_fence_before_sync();
@@ -625,7 +746,25 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
     if (threadIdx.x == 0 && blp.trace) atomicMax(blp.trace + 1, globaltimer_ns());
+#ifdef GPX_CGEMM_TIMING
+    if (threadIdx.x == 0) {
+        TADD(13, clock64() - t_start);
+        TADD(15, 1);
+    }
+#endif
 }
+
+#ifdef GPX_CGEMM_TIMING
+// Development build only: copies the phase timers to the host and optionally clears them.
+extern "C" int gpx_debug_cgemm_timing(unsigned long long *out, int reset) {
+    if (cudaMemcpyFromSymbol(out, g_cgemm_timing, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+    if (reset) {
+        static unsigned long long zeros[32] = {0};
+        if (cudaMemcpyToSymbol(g_cgemm_timing, zeros, sizeof(zeros)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
 
 cudaError_t cgemm_prepare(int device) {
     static bool done[64] = {false};

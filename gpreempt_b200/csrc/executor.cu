@@ -162,6 +162,15 @@ int gpx_exec_set_word(gpx_exec *e, gpx_word *w) {
     return GPX_SUCC;
 }
 
+int gpx_exec_set_word_dptr(gpx_exec *e, const void *dptr) {
+    GPX_REQUIRE(e && dptr, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(((uintptr_t)dptr % 4) == 0, GPX_FAIL, "the preempt word must be 4-byte aligned");
+    GPX_REQUIRE(!e->graph_exec || e->word_dptr == (const int *)dptr, GPX_FAIL,
+                "set the preempt word before capturing the graph");
+    e->word_dptr = (const int *)dptr;
+    return GPX_SUCC;
+}
+
 int gpx_exec_enable_trace(gpx_exec *e, int on) {
     GPX_REQUIRE(e, GPX_FAIL, "NULL executor");
     GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "enable tracing before capturing the graph");

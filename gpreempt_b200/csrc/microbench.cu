@@ -228,7 +228,8 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
 
     std::mt19937_64 rng(seed * 31 + 5);
     std::uniform_real_distribution<double> uni(0.0, 1.0);
-    std::vector<double> drains, seens;
+    std::vector<double> drains, seens, raise_calls;
+    double drain_after_return_max = 0;
     int mismatches = 0, preempted = 0, resumes_total = 0;
     for (int t = 0; t < triggers; ++t) {
         GPX_TRY(prepare());
@@ -239,11 +240,20 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
         unc_sum += (double)unc;
         GPX_TRY(launch());
         spin_ns(delay_ns);
+        // Two host stamps around the raise.  The latency is counted from the first (before the
+        // write is issued), so it includes the write's own way to the GPU and is an upper bound;
+        // a host thread that is descheduled inside the call (seen once as a 0.9 ms "drain" among
+        // 1000 triggers of 17 us) shows up as a long call, and the drain counted from the second
+        // stamp tells such a host delay from a kernel that was slow to leave.
         uint64_t t_raise = now_ns();
         GPX_TRY(gpx_word_raise(word));
+        uint64_t t_raised = now_ns();
         GPX_TRY(read());
+        raise_calls.push_back((double)(t_raised - t_raise) / 1e3);
         if (snap.stop != -1) {
             ++preempted;
+            drain_after_return_max = std::max(
+                drain_after_return_max, ((double)((int64_t)snap.trace[1] + offset) - (double)t_raised) / 1e3);
             // last CTA exit on the device clock, moved to the host clock
             double drain = ((double)((int64_t)snap.trace[1] + offset) - (double)t_raise) / 1e3;
             double seen = ((double)((int64_t)snap.trace[2] + offset) - (double)t_raise) / 1e3;
@@ -295,6 +305,9 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
     out->drain_us_mean = drains.empty() ? 0 : sum / drains.size();
     out->seen_us_p50 = pct(seens, 0.5);
     out->seen_us_p99 = pct(seens, 0.99);
+    out->raise_call_us_p50 = pct(raise_calls, 0.5);
+    out->raise_call_us_max = raise_calls.empty() ? 0 : *std::max_element(raise_calls.begin(), raise_calls.end());
+    out->drain_after_return_us_max = drain_after_return_max;
 
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);

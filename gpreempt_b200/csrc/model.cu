@@ -2,6 +2,7 @@
 // the kernel list.  Counterpart of src/model.cpp in the reference (Model::load_model :79-125,
 // load_from_json :128-235, load_param :263-282, get/set :288-321, ModelParamParser :15-55).
 #include "model.h"
+#include "graph_builder.h"
 #include "json.h"
 
 #include <algorithm>
@@ -57,298 +58,7 @@ void uniform_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float lo
     }
 }
 
-// ---- graph construction ---------------------------------------------------------------------
-
-struct GraphBuilder {
-    gpx_model &m;
-    explicit GraphBuilder(gpx_model &model) : m(model) {}
-
-    int add_act(const std::string &name, int N, int C, int H, int W, Storage::Kind kind) {
-        Storage s;
-        s.name = name;
-        s.kind = kind;
-        if (H == 1 && W == 1) {
-            s.rank = 2;
-            s.dims[0] = N;
-            s.dims[1] = C;
-        } else {
-            s.rank = 4;
-            s.dims[0] = N;
-            s.dims[1] = C;
-            s.dims[2] = H;
-            s.dims[3] = W;
-        }
-        s.bytes = (size_t)N * C * H * W * sizeof(float);
-        // Models with channel counts that are not multiples of 64 keep their activations padded
-        // with zero channels, so every convolution still fits the tensor-core tile shapes.
-        if (kind == Storage::ActSplit && m.pad_channels) s.cs = (C + 63) / 64 * 64;
-        return m.add_storage(s);
-    }
-
-    // Depthwise k x k convolution + bias + activation (MobileNet's spatial filter).
-    int dwconv(const std::string &name, int in, int k, int stride, int pad, int act) {
-        const Node &src = m.nodes[in];
-        Node n;
-        n.name = name;
-        n.op = Op::DwConv;
-        n.inputs.push_back(in);
-        n.k = k;
-        n.stride = stride;
-        n.pad = pad;
-        n.act = act;
-        n.N = src.N;
-        n.C = src.C;
-        n.H = (src.H + 2 * pad - k) / stride + 1;
-        n.W = (src.W + 2 * pad - k) / stride + 1;
-        Storage w;
-        w.name = name + ".weight";
-        w.kind = Storage::Weight;
-        w.is_param = true;
-        w.depthwise = true;
-        w.rank = 4;
-        w.dims[0] = src.C;
-        w.dims[1] = 1;
-        w.dims[2] = k;
-        w.dims[3] = k;
-        w.bytes = (size_t)src.C * k * k * sizeof(float);
-        w.fan_in = k * k;
-        n.weight = m.add_storage(w);
-        n.bias = add_vec(name + ".bias", src.C, 0.f, 0.f);
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    int input(const std::string &name, int N, int C, int H, int W) {
-        Node n;
-        n.name = name;
-        n.op = Op::Input;
-        n.N = N;
-        n.H = H;
-        n.W = W;
-        n.C = C;
-        n.storage = add_act(name, N, C, H, W, Storage::InputF32);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    int conv(const std::string &name, int in, int cout, int k, int stride, int pad, bool relu,
-             int residual = -1, const std::string &param_prefix = "", bool is_head = false) {
-        const Node &src = m.nodes[in];
-        Node n;
-        n.name = name;
-        n.op = Op::Conv;
-        n.inputs.push_back(in);
-        if (residual >= 0) n.inputs.push_back(residual);
-        n.residual = residual;
-        n.k = k;
-        n.stride = stride;
-        n.pad = pad;
-        n.act = relu ? ACT_RELU : ACT_NONE;
-        n.N = src.N;
-        n.H = (src.H + 2 * pad - k) / stride + 1;
-        n.W = (src.W + 2 * pad - k) / stride + 1;
-        n.C = cout;
-        const std::string pp = param_prefix.empty() ? name : param_prefix;
-        Storage w;
-        w.name = pp + ".weight";
-        w.kind = Storage::Weight;
-        w.is_param = true;
-        w.rank = 4;
-        w.dims[0] = cout;
-        w.dims[1] = src.C;
-        w.dims[2] = k;
-        w.dims[3] = k;
-        w.bytes = (size_t)cout * src.C * k * k * sizeof(float);
-        w.fan_in = src.C * k * k;
-        n.weight = m.add_storage(w);
-        Storage b;
-        b.name = pp + ".bias";
-        b.kind = Storage::Vec;
-        b.is_param = true;
-        b.rank = 1;
-        b.dims[0] = cout;
-        b.bytes = (size_t)cout * sizeof(float);
-        n.bias = m.add_storage(b);
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, is_head ? Storage::OutputF32 : Storage::ActSplit);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    // Fully connected layer over the flattened (C, H, W) input: a convolution whose filter
-    // covers the whole feature map, so the canonical weight [out][C*H*W] is its OIHW filter.
-    int dense(const std::string &name, int in, int cout, bool relu) {
-        const Node &src = m.nodes[in];
-        return conv(name, in, cout, src.H, 1, 0, relu);
-    }
-
-    // Token ids [N][S] (int64), the "data" input of sequence models.
-    int input_ids(const std::string &name, int N, int S) {
-        Node n;
-        n.name = name;
-        n.op = Op::Input;
-        n.N = N;
-        n.H = 1;
-        n.W = S;
-        n.C = 1;
-        Storage s;
-        s.name = name;
-        s.kind = Storage::InputI64;
-        s.stype = "int64";
-        s.rank = 2;
-        s.dims[0] = N;
-        s.dims[1] = S;
-        s.bytes = (size_t)N * S * sizeof(long long);
-        n.storage = m.add_storage(s);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    int add_vec(const std::string &name, int n, float mean, float std) {
-        Storage s;
-        s.name = name;
-        s.kind = Storage::Vec;
-        s.is_param = true;
-        s.rank = 1;
-        s.dims[0] = n;
-        s.bytes = (size_t)n * sizeof(float);
-        s.init_mean = mean;
-        s.init_std = std;
-        return m.add_storage(s);
-    }
-
-    int add_table(const std::string &name, int rows, int cols, float std) {
-        Storage s;
-        s.name = name;
-        s.kind = Storage::Table;
-        s.is_param = true;
-        s.rank = 2;
-        s.dims[0] = rows;
-        s.dims[1] = cols;
-        s.bytes = (size_t)rows * cols * sizeof(float);
-        s.init_std = std;
-        return m.add_storage(s);
-    }
-
-    // LayerNorm over channels.  `in` is an activation, or the token-id input when `tables` names
-    // the word / position / token-type embedding tables (the sum is formed on the fly).
-    int layer_norm(const std::string &name, int in, int C, const std::string &param_prefix,
-                   const int *tables = nullptr, bool is_head = false) {
-        const Node &src = m.nodes[in];
-        Node n;
-        n.name = name;
-        n.op = Op::LayerNorm;
-        n.inputs.push_back(in);
-        n.N = src.N;
-        n.H = src.H;
-        n.W = src.W;
-        n.C = C;
-        n.weight = add_vec(param_prefix + ".weight", C, 1.0f, 0.02f);
-        n.bias = add_vec(param_prefix + ".bias", C, 0.0f, 0.02f);
-        if (tables)
-            for (int i = 0; i < 3; ++i) n.tables[i] = tables[i];
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, is_head ? Storage::OutputF32 : Storage::ActSplit);
-        m.storages[n.storage].token_major = true;
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    int attention(const std::string &name, int q, int k, int v, int heads) {
-        const Node &src = m.nodes[q];
-        Node n;
-        n.name = name;
-        n.op = Op::Attention;
-        n.inputs = {q, k, v};
-        n.N = src.N;
-        n.H = src.H;
-        n.W = src.W;
-        n.C = src.C;
-        n.heads = heads;
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
-        m.storages[n.storage].token_major = true;
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    // Dense layer of a sequence model: a 1x1 convolution over [N][1][S][C] with N(0, 0.02) weights.
-    int linear(const std::string &name, int in, int cout, int act, int residual = -1) {
-        int id = conv(name + ".out", in, cout, 1, 1, 0, false, residual, name);
-        m.nodes[id].act = act;
-        m.storages[m.nodes[id].storage].token_major = true;
-        m.storages[m.nodes[id].weight].init_std = 0.02f;
-        m.storages[m.nodes[id].bias].init_std = 0.02f;
-        return id;
-    }
-
-    // Pooling; with `norm_prefix` the input first goes through a per-channel affine + ReLU (a
-    // batch norm that sits between the producer and the pooling, as DenseNet's last one does).
-    int pool(const std::string &name, int in, Op op, int k, int stride, int pad,
-             const std::string &norm_prefix = "") {
-        const Node &src = m.nodes[in];
-        Node n;
-        n.name = name;
-        n.op = op;
-        n.inputs.push_back(in);
-        n.k = k;
-        n.stride = stride;
-        n.pad = pad;
-        n.N = src.N;
-        n.C = src.C;
-        n.H = (src.H + 2 * pad - k) / stride + 1;
-        n.W = (src.W + 2 * pad - k) / stride + 1;
-        if (!norm_prefix.empty()) {
-            n.scale = add_vec(norm_prefix + ".weight", src.C, 1.0f, 0.02f);
-            n.shift = add_vec(norm_prefix + ".bias", src.C, 0.0f, 0.02f);
-            n.act = ACT_RELU;
-        }
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    // A tensor that other nodes fill slice by slice: concatenation along channels by placement.
-    int buffer(const std::string &name, int N, int C, int H, int W) {
-        Node n;
-        n.name = name;
-        n.op = Op::Buffer;
-        n.N = N;
-        n.C = C;
-        n.H = H;
-        n.W = W;
-        n.storage = add_act(name, N, C, H, W, Storage::ActSplit);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-
-    // Makes the output of node `id` the channels [off, off + C) of the buffer node `buf`.
-    void place(int id, int buf, int off) {
-        Storage &s = m.storages[m.nodes[id].storage];
-        s.parent = m.nodes[buf].storage;
-        s.ch_off = off;
-        s.cs = 0;
-    }
-
-    // act(x * scale + shift) over the first `in_c` channels of `in` (a batch norm ahead of its
-    // convolution, folded to an affine map), written as a tensor of its own.
-    int affine(const std::string &name, int in, int in_c, int act) {
-        const Node &src = m.nodes[in];
-        Node n;
-        n.name = name;
-        n.op = Op::Affine;
-        n.inputs.push_back(in);
-        n.in_c = in_c;
-        n.act = act;
-        n.N = src.N;
-        n.C = in_c;
-        n.H = src.H;
-        n.W = src.W;
-        n.scale = add_vec(name + ".weight", in_c, 1.0f, 0.02f);
-        n.shift = add_vec(name + ".bias", in_c, 0.0f, 0.02f);
-        n.storage = add_act(name, n.N, n.C, n.H, n.W, Storage::ActSplit);
-        m.nodes.push_back(n);
-        return (int)m.nodes.size() - 1;
-    }
-};
+// ---- built-in graphs ------------------------------------------------------------------------
 
 // ResNet v1.5 with bottleneck blocks (stride on the 3x3 convolution), batch norm folded into
 // each convolution's bias.  layers = {3,4,6,3} gives ResNet-50, {3,8,36,3} ResNet-152.
@@ -499,6 +209,35 @@ static void build_bert(gpx_model &m, int batch, int seq, int layers, int hidden,
     m.head_node = x;
 }
 
+// DistilBERT (Sanh et al. 2019; the Hugging Face DistilBertModel layout and parameter names): the
+// BERT encoder without token-type embeddings, 6 layers for distilbert-base.  This is the sequence
+// model the reference compiles (scripts/compile/compile-bert.py:33-52, traced on a 6-token input);
+// "heads" is the last hidden state.
+static void build_distilbert(gpx_model &m, int batch, int seq, int layers, int hidden, int heads, int ffn,
+                             int vocab, int max_pos) {
+    GraphBuilder g(m);
+    int ids = g.input_ids("data", batch, seq);
+    int tables[3];
+    tables[0] = g.add_table("embeddings.word_embeddings.weight", vocab, hidden, 0.02f);
+    tables[1] = g.add_table("embeddings.position_embeddings.weight", max_pos, hidden, 0.02f);
+    tables[2] = -1;
+    int x = g.layer_norm("embeddings", ids, hidden, "embeddings.LayerNorm", tables);
+    for (int l = 0; l < layers; ++l) {
+        const std::string p = "transformer.layer." + std::to_string(l);
+        int q = g.linear(p + ".attention.q_lin", x, hidden, ACT_NONE);
+        int k = g.linear(p + ".attention.k_lin", x, hidden, ACT_NONE);
+        int v = g.linear(p + ".attention.v_lin", x, hidden, ACT_NONE);
+        int ctx = g.attention(p + ".attention.context", q, k, v, heads);
+        int a = g.linear(p + ".attention.out_lin", ctx, hidden, ACT_NONE, x);
+        x = g.layer_norm(p + ".sa_output", a, hidden, p + ".sa_layer_norm");
+        int h = g.linear(p + ".ffn.lin1", x, ffn, ACT_GELU);
+        int o = g.linear(p + ".ffn.lin2", h, hidden, ACT_NONE, x);
+        bool last = l == layers - 1;
+        x = g.layer_norm(last ? "heads" : p + ".output", o, hidden, p + ".output_layer_norm", nullptr, last);
+    }
+    m.head_node = x;
+}
+
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts) {
     int batch = opts.batch > 0 ? opts.batch : 1;
     m.batch = batch;
@@ -546,7 +285,19 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         // fast tests.
         const int cfg[4] = {2, 2, 4, 2};
         build_densenet(m, batch, cfg, 32, 64);
-    } else if (name == "bert_base" || name == "bert") {
+    } else if (name == "distilbert" || name == "bert") {
+        // "bert" is what the reference's task configs call its DistilBERT build (config/C.json); its
+        // sequence length is the 6 tokens the model was traced on unless the client gives one.
+        int seq = opts.seq_len > 0 ? opts.seq_len : 6;
+        if (seq > 512 || (m.fmt != PF_SPLIT && seq % 8 != 0)) {
+            set_error("distilbert: seq_len %d must be at most 512 (and a multiple of 8 in the 16-bit formats)", seq);
+            return GPX_OUT_OF_RANGE;
+        }
+        build_distilbert(m, batch, seq, 6, 768, 12, 3072, 30522, 512);
+    } else if (name == "distilbert_tiny") {
+        int seq = opts.seq_len > 0 ? opts.seq_len : 6;
+        build_distilbert(m, batch, seq, 2, 128, 2, 256, 1000, 512);
+    } else if (name == "bert_base") {
         int seq = opts.seq_len > 0 ? opts.seq_len : 128;
         if (seq > 512 || seq % 8 != 0) {
             set_error("bert_base: seq_len %d must be a multiple of 8 and at most 512", seq);
@@ -859,7 +610,7 @@ int finalize_model(gpx_model &m) {
                 q.ids = reinterpret_cast<const long long *>(in.dptr);
                 q.word = m.storages[n.tables[0]].dptr;
                 q.pos = m.storages[n.tables[1]].dptr;
-                q.type = m.storages[n.tables[2]].dptr;
+                q.type = n.tables[2] >= 0 ? m.storages[n.tables[2]].dptr : nullptr;
             } else {
                 GPX_REQUIRE(in.kind == Storage::ActSplit && in.layout.order == ACT_PLAIN, GPX_FAIL,
                             "%s: LayerNorm needs a plain activation", n.name.c_str());
@@ -1428,12 +1179,30 @@ int gpx_model_open(const char *name, const gpx_model_opts *opts, gpx_model **out
     if (opts) o = *opts;
     std::unique_ptr<gpx_model> m(new gpx_model());
     std::string nm(name);
-    // Aliases for the model names the reference's task configs use (config/A.json, C.json).
-    if (nm == "resnet") nm = "resnet152";
-    GPX_TRY(build_builtin_graph(*m, nm, o));
+    // A directory holding mod.json + host.json (+ mod.params), the layout the reference loads
+    // (MODEL_PATH/<workload>/..., src/executor.cpp:110-117), or the name of a built-in graph.
+    const bool from_dir = model_dir_exists(nm);
+    if (from_dir) {
+        GPX_TRY(build_graph_from_dir(*m, nm, o));
+    } else {
+        // Aliases for the model names the reference's task configs use (config/A.json, C.json).
+        if (nm == "resnet") nm = "resnet152";
+        GPX_TRY(build_builtin_graph(*m, nm, o));
+    }
     int st = finalize_model(*m);
+    if (st == GPX_SUCC && from_dir) st = check_host_json(*m, nm);
+    if (st == GPX_SUCC && from_dir) {
+        // Parameters travel with the directory (Executor::load_param, src/executor.cpp:115-117).
+        const std::string params = nm + "/mod.params";
+        if (FILE *fp = fopen(params.c_str(), "rb")) {
+            fclose(fp);
+            st = gpx_model_load_params(m.get(), params.c_str());
+        }
+    }
     if (st != GPX_SUCC) {
+        std::string saved = last_error();
         gpx_model_close(m.release());
+        set_error("%s", saved.c_str());
         return st;
     }
     *out = m.release();
@@ -1641,119 +1410,6 @@ int gpx_model_kernel_info(gpx_model *m, size_t idx, char *name, size_t name_cap,
     if (total_tiles) *total_tiles = k.total_tiles;
     if (flops) *flops = k.flops;
     if (bytes) *bytes = k.bytes;
-    return GPX_SUCC;
-}
-
-int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
-    GPX_REQUIRE(m, GPX_FAIL, "NULL model");
-    // Same skeleton as the TVM graph JSON Model::load_from_json walks (src/model.cpp:157-197):
-    // parameters and inputs are "null" nodes listed in arg_nodes; compute nodes are "tvm_op"
-    // with attrs.func_name; attrs.dltype / attrs.shape hold one entry per node; heads names
-    // the output.  Layer hyper-parameters ride in each node's attrs.
-    Json nodes = Json::array(), arg_nodes = Json::array(), dltype = Json::array(),
-         shapes = Json::array(), row_ptr = Json::array();
-    std::unordered_map<int, int> storage_to_json;  // storage index -> json node id
-    int jid = 0;
-    auto shape_of = [&](const Storage &s) {
-        Json sh = Json::array();
-        for (int d = 0; d < s.rank; ++d) sh.push(Json((long long)s.dims[d]));
-        return sh;
-    };
-    auto add_null = [&](int storage) {
-        const Storage &s = m->storages[storage];
-        Json n = Json::object();
-        n.set("op", "null");
-        n.set("name", s.name);
-        n.set("inputs", Json::array());
-        nodes.push(n);
-        arg_nodes.push(Json(jid));
-        dltype.push(Json(s.stype));
-        shapes.push(shape_of(s));
-        row_ptr.push(Json(jid));
-        storage_to_json[storage] = jid++;
-    };
-    int head_json = -1;
-    for (size_t ni = 0; ni < m->nodes.size(); ++ni) {
-        const Node &n = m->nodes[ni];
-        if (n.op == Op::Input) {
-            add_null(n.storage);
-            continue;
-        }
-        if (n.weight >= 0) add_null(n.weight);
-        if (n.bias >= 0) add_null(n.bias);
-        Json jn = Json::object();
-        jn.set("op", "tvm_op");
-        jn.set("name", n.name);
-        Json attrs = Json::object();
-        const char *fn = n.op == Op::Conv        ? "gpx_conv2d"
-                         : n.op == Op::MaxPool   ? "gpx_max_pool2d"
-                         : n.op == Op::AvgPool   ? "gpx_avg_pool2d"
-                         : n.op == Op::LayerNorm ? "gpx_layer_norm"
-                                                 : "gpx_attention";
-        attrs.set("func_name", fn);
-        attrs.set("flatten_data", "0");
-        attrs.set("num_outputs", "1");
-        attrs.set("kernel", Json(n.k));
-        attrs.set("stride", Json(n.stride));
-        attrs.set("padding", Json(n.pad));
-        attrs.set("relu", Json(n.act == ACT_RELU));
-        attrs.set("activation", Json(n.act));
-        attrs.set("channels", Json(n.C));
-        Json inputs = Json::array();
-        auto ref = [&](int storage) {
-            Json r = Json::array();
-            r.push(Json(storage_to_json[storage]));
-            r.push(Json(0));
-            r.push(Json(0));
-            inputs.push(r);
-        };
-        ref(m->nodes[n.inputs[0]].storage);
-        if (n.weight >= 0) ref(n.weight);
-        if (n.bias >= 0) ref(n.bias);
-        if (n.residual >= 0) {
-            ref(m->nodes[n.residual].storage);
-            attrs.set("residual", Json(true));
-        }
-        attrs.set("num_inputs", std::to_string(inputs.size()));
-        jn.set("attrs", attrs);
-        jn.set("inputs", inputs);
-        nodes.push(jn);
-        const Storage &s = m->storages[n.storage];
-        dltype.push(Json(s.stype));
-        shapes.push(shape_of(s));
-        row_ptr.push(Json(jid));
-        if ((int)ni == m->head_node) head_json = jid;
-        storage_to_json[n.storage] = jid++;
-    }
-    row_ptr.push(Json(jid));
-    Json root = Json::object();
-    root.set("nodes", nodes);
-    root.set("arg_nodes", arg_nodes);
-    Json heads = Json::array(), h = Json::array();
-    h.push(Json(head_json));
-    h.push(Json(0));
-    h.push(Json(0));
-    heads.push(h);
-    root.set("heads", heads);
-    Json attrs = Json::object();
-    Json dl = Json::array();
-    dl.push("list_str");
-    dl.push(dltype);
-    attrs.set("dltype", dl);
-    Json sh = Json::array();
-    sh.push("list_shape");
-    sh.push(shapes);
-    attrs.set("shape", sh);
-    root.set("attrs", attrs);
-    root.set("node_row_ptr", row_ptr);
-    Json meta = Json::object();
-    meta.set("model", m->name);
-    meta.set("batch", Json(m->batch));
-    root.set("gpx", meta);
-    std::string text = root.dump(1);
-    if (needed) *needed = text.size() + 1;
-    if (!buf || cap < text.size() + 1) return buf ? GPX_OUT_OF_RANGE : GPX_SUCC;
-    memcpy(buf, text.c_str(), text.size() + 1);
     return GPX_SUCC;
 }
 

@@ -125,6 +125,10 @@ struct gpx_model {
 namespace gpx {
 
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts);
+// Model directories (artifacts.cu): mod.json + host.json (+ mod.params).
+bool model_dir_exists(const std::string &dir);
+int build_graph_from_dir(gpx_model &m, const std::string &dir, const gpx_model_opts &opts);
+int check_host_json(const gpx_model &m, const std::string &dir);
 int finalize_model(gpx_model &m);
 void normal_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std);
 void uniform_fill(float *dst, size_t n, uint64_t seed, uint64_t stream, float lo, float hi);

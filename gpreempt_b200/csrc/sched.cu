@@ -32,8 +32,16 @@ enum Policy { POLICY_BASE, POLICY_SEQ, POLICY_BLP_WAIT, POLICY_YIELD };
 // ---- loads (third_party/disb/src/load.cpp) ----------------------------------------------------
 
 struct Load {
-    enum Type { Continuous, Periodic, Poisson, Trace, Burst } type = Continuous;
+    enum Type { Continuous, Periodic, Poisson, Trace, Burst, Dependent } type = Continuous;
     double frequency = 0;
+    int priority = -1;             // the load's own priority key (config/A.json:8); -1 = not given
+    uint64_t launch_delay_ns = 0;  // periodic: offset of the first launch, set by the load coordinator
+    long long dropped = 0;         // arrivals given up because their successor had already arrived
+    // Dependent (load.cpp:299-361): a request starts once every predecessor task has delivered its
+    // result with the same serial number; the predecessors' completion counters are read here.
+    std::vector<const std::atomic<uint64_t> *> prev_done;
+    std::vector<std::string> prev_task_ids;
+    uint64_t consumed = 0;
     std::vector<double> trace_ms;
     double on_s = 1.0, off_s = 1.0;  // burst: Poisson arrivals during `on`, silence during `off`
     long long max_requests = -1;
@@ -47,7 +55,7 @@ struct Load {
     void start(uint64_t begin, uint64_t end, uint64_t seed) {
         begin_ns = begin;
         end_ns = end;
-        next_ns = begin;
+        next_ns = begin + (type == Periodic ? launch_delay_ns : 0);
         rng.seed(seed);
         if (type == Periodic && frequency > 0) interval_ns = (uint64_t)(1e9 / frequency);
         if (type == Burst) next_ns = begin + exp_interval();
@@ -96,6 +104,7 @@ struct Load {
                 while (nn < now) {
                     next_ns = nn;
                     nn = next_ns + interval_ns;
+                    ++dropped;
                 }
                 if (next_ns >= end_ns) return false;
                 sleep_until(next_ns);
@@ -108,6 +117,7 @@ struct Load {
                 while (nn < now) {
                     next_ns = nn;
                     nn = next_ns + exp_interval();
+                    ++dropped;
                 }
                 if (next_ns >= end_ns) return false;
                 sleep_until(next_ns);
@@ -120,6 +130,7 @@ struct Load {
                 while (nn < now) {
                     next_ns = nn;
                     nn = burst_next(next_ns);
+                    ++dropped;
                 }
                 if (next_ns >= end_ns) return false;
                 sleep_until(next_ns);
@@ -135,10 +146,26 @@ struct Load {
                     if (t >= now) break;
                     launch = t;
                     ++nn;
+                    ++dropped;
                 }
                 next_trace = nn;
                 if (launch >= end_ns) return false;
                 sleep_until(launch);
+                break;
+            }
+            case Dependent: {
+                // every predecessor has finished request number consumed + 1
+                for (;;) {
+                    bool ready = !prev_done.empty();
+                    for (const std::atomic<uint64_t> *c : prev_done)
+                        if (c->load(std::memory_order_acquire) <= consumed) ready = false;
+                    if (ready) break;
+                    if (stop.load(std::memory_order_relaxed) || now_ns() >= end_ns) return false;
+                    timespec ts{0, 20000};
+                    nanosleep(&ts, nullptr);
+                }
+                ++consumed;
+                if (now_ns() >= end_ns) return false;
                 break;
             }
         }
@@ -186,6 +213,11 @@ struct Client {
     std::atomic<int> hint{0};        // gpx_sched_hint: raise the word ahead of the next submission
     std::atomic<uint64_t> last_queue_ns{0}, last_run_ns{0};
     uint64_t launch_ns = 0;
+    // schedule log: tiles run per kernel summed over the launches of one request, first kernel of
+    // the launch in flight
+    std::vector<long long> tiles_sum;
+    int seg_from = 0;
+    int log_index = -1;
     virtual ~Client() {}
 };
 
@@ -210,10 +242,21 @@ struct Tenant : Client {
     bool staging = false;            // a prefetch is in progress or complete
     size_t in_bytes = 0, out_bytes = 0;
     std::vector<Record> records;
+    std::atomic<uint64_t> results{0};  // requests completed in the run (what dependent tasks wait for)
     Record standalone{};
     uint64_t first_ns = 0, last_ns = 0;
     cudaEvent_t ev_first = nullptr, ev_last = nullptr;
     bool ev_first_recorded = false;
+};
+
+// One line of the schedule log (config key "schedule_log"): what the dispatcher did and what the
+// device-side %globaltimer trace of the executors says about it.  Host stamps are CLOCK_MONOTONIC
+// ns, device stamps %globaltimer ns; the report carries the clock offset measured before and after
+// the run so a reader can put both on one timeline.
+struct LogEntry {
+    int kind;     // 0 raise, 1 clear, 2 hp done, 3 be start, 4 be stopped, 5 be done
+    int client;   // index of the tenant on its GPU list (hp or be), -1 for word events
+    long long a, b, c, d;
 };
 
 struct Stats {
@@ -223,6 +266,7 @@ struct Stats {
     long long raises = 0;
     long long be_resumes = 0;
     long long be_launches = 0;
+    std::vector<LogEntry> log;
 };
 
 // ---- dispatcher -------------------------------------------------------------------------------
@@ -252,6 +296,22 @@ struct Dispatcher {
     bool word_raised = false;
     uint64_t t_raise = 0;
     bool drain_pending = false;
+    bool schedule_log = false;
+    static constexpr size_t kMaxLog = 200000;
+
+    void log(int kind, int client, long long a = 0, long long b = 0, long long c = 0, long long d = 0) {
+        if (!schedule_log || stats.log.size() >= kMaxLog) return;
+        stats_lock();
+        stats.log.push_back(LogEntry{kind, client, a, b, c, d});
+        stats_unlock();
+    }
+    // Adds the tiles the kernels from `from` on ran in the launch that just ended (h_trace is current).
+    void account_tiles(Client *t, size_t from) {
+        if (!schedule_log || !t->exec || !t->exec->trace_on) return;
+        const size_t nk = t->exec->model->kernels.size();
+        if (t->tiles_sum.size() != nk) t->tiles_sum.assign(nk, 0);
+        for (size_t k = from; k < nk; ++k) t->tiles_sum[k] += (long long)t->exec->h_trace[4 * k + 3];
+    }
 
     int fail(const char *what) {
         error = std::string(what) + ": " + last_error();
@@ -267,12 +327,16 @@ struct Dispatcher {
         if (e->kind == GPX_EXEC_BLP && word && word->transport == GPX_WORD_DEVICE && clear_event)
             GPX_CUDA(cudaStreamWaitEvent(t->stream, clear_event, 0));
         GPX_TRY(gpx_exec_execute(e, t->stream));
-        if (e->kind == GPX_EXEC_BLP) {
+        if (e->kind == GPX_EXEC_BLP)
             GPX_CUDA(cudaMemcpyAsync(e->h_stop_index, e->d_stop_index, sizeof(int),
                                      cudaMemcpyDeviceToHost, t->stream));
-            GPX_TRY(read_trace_async(t));
-        }
+        GPX_TRY(read_trace_async(t));
         GPX_CUDA(cudaEventRecord(t->done, t->stream));
+        if (t->priority != 0) {
+            t->seg_from = 0;
+            if (schedule_log) t->tiles_sum.assign(e->model->kernels.size(), 0);
+            log(3, t->log_index, (long long)now_ns(), 0);
+        }
         return GPX_SUCC;
     }
 
@@ -312,6 +376,9 @@ struct Dispatcher {
         t->resume_next = 0;
         t->unlaunched_from = -1;
         t->seg_recorded = t->seg_done = 0;
+        t->seg_from = 0;
+        if (schedule_log) t->tiles_sum.assign(e->model->kernels.size(), 0);
+        log(3, t->log_index, (long long)now_ns(), 0);
         return GPX_SUCC;
     }
 
@@ -331,6 +398,8 @@ struct Dispatcher {
         t->resume_next = (size_t)t->stop_index;
         t->unlaunched_from = -1;
         t->seg_recorded = t->seg_done = 0;
+        t->seg_from = t->stop_index;
+        log(3, t->log_index, (long long)now_ns(), t->stop_index);
         return GPX_SUCC;
     }
 
@@ -378,6 +447,7 @@ struct Dispatcher {
         GPX_TRY(gpx_word_raise(word));
         word_raised = true;
         t_raise = now_ns();
+        log(0, -1, (long long)t_raise);
         stats_lock();
         ++stats.raises;
         stats_unlock();
@@ -391,6 +461,7 @@ struct Dispatcher {
 
     int clear() {
         if (!word || !word_raised) return GPX_SUCC;
+        log(1, -1, (long long)now_ns());
         GPX_TRY(gpx_word_clear(word));
         if (word->transport == GPX_WORD_DEVICE) GPX_CUDA(cudaEventRecord(clear_event, word->wstream));
         word_raised = false;
@@ -458,6 +529,16 @@ struct Dispatcher {
             } else if (st == ST_RUNNING) {
                 cudaError_t q = t->exec ? cudaEventQuery(t->done) : cudaSuccess;
                 if (q == cudaSuccess) {
+                    if (schedule_log && t->exec && t->exec->trace_on) {
+                        // first CTA start and last CTA exit of the request on the device clock
+                        const size_t nk = t->exec->model->kernels.size();
+                        unsigned long long first = ~0ull, last = 0;
+                        for (size_t k = 0; k < nk; ++k) {
+                            first = std::min(first, t->exec->h_trace[4 * k + 0]);
+                            last = std::max(last, t->exec->h_trace[4 * k + 1]);
+                        }
+                        log(2, t->log_index, (long long)first, (long long)last, (long long)t->submit_ns, (long long)t->launch_ns);
+                    }
                     t->state.store(ST_DONE, std::memory_order_release);
                     seq_release(t);
                 } else if (q != cudaErrorNotReady) {
@@ -479,6 +560,26 @@ struct Dispatcher {
                     int stop = (t->exec && t->exec->kind == GPX_EXEC_BLP) ? *t->exec->h_stop_index : -1;
                     if (stop == -1 && t->unlaunched_from >= 0) stop = t->unlaunched_from;
                     t->unlaunched_from = -1;
+                    account_tiles(t, (size_t)t->seg_from);
+                    if (schedule_log && t->exec && t->exec->trace_on) {
+                        const size_t nk = t->exec->model->kernels.size();
+                        const unsigned long long *tr = t->exec->h_trace;
+                        // first CTA start of this launch, and tiles run behind the stop point
+                        unsigned long long first = ~0ull;
+                        long long behind = 0;
+                        for (size_t k = (size_t)t->seg_from; k < nk; ++k) first = std::min(first, tr[4 * k + 0]);
+                        if (stop >= 0)
+                            for (size_t k = (size_t)stop + 1; k < nk; ++k) behind += (long long)tr[4 * k + 3];
+                        if (stop == -1) {
+                            long long wrong = 0;
+                            for (size_t k = 0; k < nk; ++k)
+                                wrong += t->tiles_sum[k] != t->exec->model->kernels[k].total_tiles ? 1 : 0;
+                            log(5, t->log_index, (long long)first, wrong);
+                        } else {
+                            log(4, t->log_index, (long long)first, stop,
+                                (size_t)stop < nk ? (long long)tr[4 * (size_t)stop + 2] : -1, behind);
+                        }
+                    }
                     if (stop == -1) {
                         t->state.store(ST_DONE, std::memory_order_release);
                         seq_release(t);
@@ -608,6 +709,9 @@ struct Suite {
     int word_transport = GPX_WORD_DEVICE;
     uint64_t request_timeout_ms = 60000;  // a request the dispatcher has not completed by then fails the run
     size_t copy_chunk = 2u << 20;  // best-effort input copies are issued in pieces of this size
+    bool schedule_log = false;  // record raise / clear / start / stop events and trace every executor
+    int64_t clock_off0 = 0, clock_off1 = 0, clock_unc = 0;
+    uint64_t clock_t0 = 0, clock_t1 = 0;
     bool resident = false;  // inputs stay in HBM: no per-request host<->device copies
     bool prefetch_inputs = false;  // best-effort tenants stage the next input while a request runs
     std::string end_when;  // "" = time; otherwise run ends when this task hits max_requests
@@ -795,6 +899,7 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         s.word_transport = cfg["word_transport"].as_string() == "mapped" ? GPX_WORD_MAPPED : GPX_WORD_DEVICE;
     s.end_when = cfg["end_when"].as_string();
     s.resident = cfg["resident_inputs"].as_bool(false);
+    s.schedule_log = cfg["schedule_log"].as_bool(false);
     if (cfg.has("copy_chunk_bytes")) s.copy_chunk = (size_t)cfg["copy_chunk_bytes"].as_int(0);
     if (cfg.has("request_timeout_ms")) s.request_timeout_ms = (uint64_t)std::max<long long>(1, cfg["request_timeout_ms"].as_int(60000));
     int default_gpu = (int)cfg["device"].as_int(0);
@@ -824,19 +929,34 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         else if (lt == "poisson") t->load.type = Load::Poisson;
         else if (lt == "trace") t->load.type = Load::Trace;
         else if (lt == "burst") t->load.type = Load::Burst;
+        else if (lt == "dependent") t->load.type = Load::Dependent;
         else {
             set_error("task %s: unknown load type '%s'", id.c_str(), lt.c_str());
             return GPX_NOT_FOUND;
         }
         t->load.frequency = jl["frequency"].as_double(0);
+        if (jl.has("priority")) t->load.priority = (int)jl["priority"].as_int(0);
         if (jl.has("on")) t->load.on_s = jl["on"].as_double(1.0);
         if (jl.has("off")) t->load.off_s = jl["off"].as_double(1.0);
         if (jl.has("max_requests")) t->load.max_requests = jl["max_requests"].as_int(-1);
+        const Json &prev = jl["prev_task_ids"];
+        for (size_t k = 0; k < prev.size(); ++k) t->load.prev_task_ids.push_back(prev[k].as_string());
         const Json &tr = jl["trace"];
         for (size_t k = 0; k < tr.size(); ++k) t->load.trace_ms.push_back(tr[k].as_double());
         s.tenants.push_back(std::move(t));
     }
     GPX_REQUIRE(!s.tenants.empty(), GPX_FAIL, "no task left after filtering");
+    for (auto &t : s.tenants) {
+        if (t->load.type != Load::Dependent) continue;
+        GPX_REQUIRE(!t->load.prev_task_ids.empty(), GPX_FAIL, "task %s: a dependent load needs prev_task_ids", t->id.c_str());
+        for (const std::string &pid : t->load.prev_task_ids) {
+            const Tenant *found = nullptr;
+            for (auto &o : s.tenants)
+                if (o->id == pid && o.get() != t.get()) found = o.get();
+            GPX_REQUIRE(found, GPX_NOT_FOUND, "task %s depends on task '%s', which is not in the run", t->id.c_str(), pid.c_str());
+            t->load.prev_done.push_back(&found->results);
+        }
+    }
     return GPX_SUCC;
 }
 
@@ -850,7 +970,7 @@ static int init_tenant(Suite &s, Tenant *t) {
     GPX_TRY(gpx_model_init_random(t->model, 1));
     bool blp = t->priority != 0 && (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT);
     GPX_TRY(gpx_exec_create(t->model, blp ? GPX_EXEC_BLP : GPX_EXEC_BASE, &t->exec));
-    if (blp) GPX_TRY(gpx_exec_enable_trace(t->exec, 1));
+    if (blp || s.schedule_log) GPX_TRY(gpx_exec_enable_trace(t->exec, 1));
     if (blp && s.drop_tile) GPX_TRY(gpx_exec_set_restart_policy(t->exec, 1));
     Dispatcher *d = s.dispatcher_for(t->gpu);
     if (blp) GPX_TRY(gpx_exec_set_word(t->exec, d->word));
@@ -928,6 +1048,7 @@ static int run_suite(Suite &s, Json *report) {
         d->hint = s.hint;
         d->be_window = s.be_window;
         d->be_window_min_kernels = s.be_window_min_kernels;
+        d->schedule_log = s.schedule_log;
         GPX_TRY(gpx_init(d->device));
         if (s.policy == POLICY_YIELD || s.policy == POLICY_BLP_WAIT) {
             GPX_TRY(gpx_word_create(&d->word, s.word_transport));
@@ -940,6 +1061,7 @@ static int run_suite(Suite &s, Json *report) {
     for (auto &tp : s.tenants) {
         GPX_TRY(init_tenant(s, tp.get()));
         Dispatcher *d = s.dispatcher_for(tp->gpu);
+        tp->log_index = (int)(tp->priority == 0 ? d->hp : d->be).size();
         (tp->priority == 0 ? d->hp : d->be).push_back(tp.get());
     }
     // Cores: dispatchers first, then one per client thread in arrival order (bind_core(cores.fetch_add(1)),
@@ -979,7 +1101,31 @@ static int run_suite(Suite &s, Json *report) {
     for (auto &d : s.dispatchers) {
         d->stats = Stats();
     }
+    // builtinLoadCoordinator (load.cpp:47-69): periodic latency-critical loads of equal frequency
+    // are staggered by the stand-alone latencies of the ones before them, so they do not all
+    // arrive at the same instant.
+    {
+        std::vector<std::pair<double, uint64_t>> delay_of;  // frequency -> accumulated delay
+        for (auto &tp : s.tenants) {
+            Tenant *t = tp.get();
+            // (the load's priority key decides, as in the reference; the client's when it is absent)
+            const int lp = t->load.priority >= 0 ? t->load.priority : t->priority;
+            if (t->load.type != Load::Periodic || lp > 0) continue;
+            size_t k = 0;
+            while (k < delay_of.size() && delay_of[k].first != t->load.frequency) ++k;
+            if (k == delay_of.size()) delay_of.push_back({t->load.frequency, 0});
+            t->load.launch_delay_ns = delay_of[k].second;
+            delay_of[k].second += t->standalone.total();
+        }
+    }
 
+    if (s.schedule_log) {
+        int64_t unc = 0;
+        GPX_TRY(gpx_init(s.dispatchers[0]->device));
+        GPX_TRY(gpx_clock_offset_ns(&s.clock_off0, &unc));
+        s.clock_t0 = now_ns();
+        s.clock_unc = unc;
+    }
     // One thread per task (benchmark.cpp:325-328).
     s.run_begin = now_ns() + 50000000ull;
     s.run_end = s.run_begin + (uint64_t)(s.time_s * 1e9);
@@ -1012,6 +1158,7 @@ static int run_suite(Suite &s, Json *report) {
                 }
                 t->last_ns = now_ns();
                 t->records.push_back(r);
+                t->results.fetch_add(1, std::memory_order_release);
             }
             cudaEventRecord(t->ev_last, t->stream);
             cudaStreamSynchronize(t->stream);
@@ -1020,6 +1167,13 @@ static int run_suite(Suite &s, Json *report) {
     }
     for (auto &th : threads) th.join();
     uint64_t t_end = now_ns();
+    if (s.schedule_log) {
+        int64_t unc = 0;
+        if (gpx_init(s.dispatchers[0]->device) == GPX_SUCC && gpx_clock_offset_ns(&s.clock_off1, &unc) == GPX_SUCC) {
+            s.clock_t1 = now_ns();
+            s.clock_unc = std::max<int64_t>(s.clock_unc, unc);
+        }
+    }
     for (auto &d : s.dispatchers) {
         d->stop.store(true);
         if (d->thread.joinable()) d->thread.join();
@@ -1047,6 +1201,9 @@ static int run_suite(Suite &s, Json *report) {
         j.set("gpu", Json(t->gpu));
         size_t n = t->records.size();
         j.set("requests", Json((long long)n));
+        j.set("droppedArrivals", Json(t->load.dropped));
+        j.set("launchDelay(us)", Json((long long)(t->load.launch_delay_ns / 1000)));
+        if (n) j.set("firstLaunchOffset(us)", Json((long long)((t->records[0].arrive - s.run_begin) / 1000)));
         double span_s = n ? (t->last_ns - s.run_begin) / 1e9 : 0;
         if (t->load.type == Load::Continuous && !s.end_when.empty() && n)
             span_s = (t->last_ns - t->first_ns) / 1e9;
@@ -1106,6 +1263,62 @@ static int run_suite(Suite &s, Json *report) {
         j.set("preemptLatency(us)", summarize(d->stats.drain_us));
         j.set("kernelDrain(us)", summarize(d->stats.kernel_drain_us));
         j.set("hpDispatchDelay(us)", summarize(d->stats.hp_queue_us));
+        if (s.schedule_log) {
+            // kinds: 0 raise [host ns]; 1 clear [host ns]; 2 latency-critical request done [first CTA
+            // start, last CTA exit (device ns), submit, launch (host ns)]; 3 best-effort launch [host ns,
+            // first kernel]; 4 best-effort launch stopped [first CTA start (device ns), stop kernel, word
+            // first seen (device ns), tiles run behind the stop point]; 5 best-effort request done [first
+            // CTA start of the last launch (device ns), kernels whose tiles were not run exactly once]
+            // Stamps are written relative to the start of the run (host clock) and to the device
+            // clock at the first offset measurement, so they stay exact as JSON numbers:
+            //   host_rel = device_rel + offset_rel, with offset_rel measured before and after the run.
+            const long long host_base = (long long)s.run_begin;
+            const long long dev_base = (long long)s.clock_t0 - (long long)s.clock_off0;
+            auto host_rel = [&](long long v) { return Json(v - host_base); };
+            auto dev_rel = [&](long long v) { return (v == -1 || (unsigned long long)v == ~0ull) ? Json(-1) : Json(v - dev_base); };
+            Json ev = Json::array();
+            for (const LogEntry &e : d->stats.log) {
+                Json r = Json::array();
+                r.push(Json(e.kind));
+                r.push(Json(e.client));
+                switch (e.kind) {
+                    case 0:
+                    case 1:
+                        r.push(host_rel(e.a));
+                        break;
+                    case 2:
+                        r.push(dev_rel(e.a));
+                        r.push(dev_rel(e.b));
+                        r.push(host_rel(e.c));
+                        r.push(host_rel(e.d));
+                        break;
+                    case 3:
+                        r.push(host_rel(e.a));
+                        r.push(Json(e.b));
+                        break;
+                    case 4:
+                        r.push(dev_rel(e.a));
+                        r.push(Json(e.b));
+                        r.push(dev_rel(e.c));
+                        r.push(Json(e.d));
+                        break;
+                    default:
+                        r.push(dev_rel(e.a));
+                        r.push(Json(e.b));
+                        break;
+                }
+                ev.push(r);
+            }
+            Json lg = Json::object();
+            lg.set("events", ev);
+            lg.set("clock", "host_rel_ns = device_rel_ns + offset_rel_ns (interpolate between the two measurements)");
+            lg.set("offset_before_rel_ns", Json((long long)s.clock_off0 + dev_base - host_base));
+            lg.set("offset_after_rel_ns", Json((long long)s.clock_off1 + dev_base - host_base));
+            lg.set("offset_before_at_rel_ns", Json((long long)s.clock_t0 - host_base));
+            lg.set("offset_after_at_rel_ns", Json((long long)s.clock_t1 - host_base));
+            lg.set("uncertainty_ns", Json((long long)s.clock_unc));
+            j.set("scheduleLog", lg);
+        }
         jd.push(j);
     }
     root.set("gpus", jd);

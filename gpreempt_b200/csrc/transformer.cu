@@ -81,13 +81,18 @@ layernorm_kernel(const __grid_constant__ LayerNormParams p, BlpArgs blp) {
                 if (v < V) {
                     nvec = i + 1;
                     if (p.ids) {
-                        // embedding row: word + position + token type 0
+                        // embedding row: word + position (+ token type 0 where the model has that table)
                         const long long id = p.ids[row];
                         const int pos = row % p.S;
                         const float4 *w = reinterpret_cast<const float4 *>(p.word + (size_t)id * p.H + v * 8);
                         const float4 *q = reinterpret_cast<const float4 *>(p.pos + (size_t)pos * p.H + v * 8);
-                        const float4 *t = reinterpret_cast<const float4 *>(p.type + v * 8);
-                        float4 a0 = w[0], a1 = w[1], b0 = q[0], b1 = q[1], c0 = t[0], c1 = t[1];
+                        float4 a0 = w[0], a1 = w[1], b0 = q[0], b1 = q[1];
+                        float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
+                        if (p.type) {
+                            const float4 *t = reinterpret_cast<const float4 *>(p.type + v * 8);
+                            c0 = t[0];
+                            c1 = t[1];
+                        }
                         x[i][0] = a0.x + b0.x + c0.x;
                         x[i][1] = a0.y + b0.y + c0.y;
                         x[i][2] = a0.z + b0.z + c0.z;

@@ -200,6 +200,11 @@ typedef struct gpx_microbench_summary {
     double drain_us_p50, drain_us_p99, drain_us_max, drain_us_mean;
     double seen_us_p50, seen_us_p99; /* raise -> first CTA observed the word */
     double clock_uncertainty_ns;
+    /* Host time spent inside the raise call itself, and the longest drain counted from the call's
+     * return instead of its start: a large drain_us_max with a small drain_after_return_us_max is
+     * a host thread that was delayed while issuing the write, not a kernel that was slow to leave. */
+    double raise_call_us_p50, raise_call_us_max;
+    double drain_after_return_us_max;
 } gpx_microbench_summary;
 int gpx_preempt_microbench(int kind, size_t size, int triggers, uint64_t seed, int transport,
                            double *drain_us, double *seen_us, gpx_microbench_summary *out);
@@ -226,8 +231,13 @@ typedef struct gpx_model_opts {
     int seq_len;        /* transformer graphs only */
 } gpx_model_opts;
 
-/* Model::load_model, src/model.cpp:79-125.  `name` is a built-in graph name (resnet50,
- * vgg16, ... and the reference's aliases) or a directory holding mod.json (+ mod.params). */
+/* Model::load_model, src/model.cpp:79-125.  `name` is a built-in graph name (resnet50, vgg16,
+ * mobilenet_v2, densenet201, bert_base, ... and the reference's aliases) or a directory holding
+ * mod.json + host.json (+ mod.params) in the reference's formats (src/model.cpp:128-235), as
+ * gpx_model_export_dir writes them: the graph is rebuilt from the nodes of mod.json, host.json
+ * must list the same functions in order (the reference's "Function name mismatch" check), and
+ * the parameters are loaded when the file is there.  A mod.json written by TVM is rejected: its
+ * nodes only name generated functions whose arithmetic lives in mod.cu. */
 int gpx_model_open(const char *name, const gpx_model_opts *opts, gpx_model **m);
 int gpx_model_close(gpx_model *m); /* Model::clear, src/model.cpp:238-260 */
 /* Model::load_param, src/model.cpp:263-282; file format of ModelParamParser::parse_from_file
@@ -260,6 +270,11 @@ int gpx_model_kernel_info(gpx_model *m, size_t idx, char *name, size_t name_cap,
  * (src/model.cpp:128-235: nodes / arg_nodes / heads / attrs.{dltype,shape}); returns the
  * number of bytes needed (including NUL) when buf is NULL or too small. */
 int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed);
+/* Writes `dir`/mod.json, host.json and mod.params: the three files the reference's model
+ * directory holds (patch/tvm.patch:296-329 emits host.json: temp_args in bytes and, per fused
+ * function, its kernels with launch_params[6] and argument indices; scripts/compile/compile.py:
+ * 73-85 writes mod.params).  gpx_model_open(dir) loads it back. */
+int gpx_model_export_dir(gpx_model *m, const char *dir);
 
 /* ---- executor ----------------------------------------------------------------------- */
 
@@ -271,6 +286,11 @@ enum gpx_exec_kind { GPX_EXEC_BASE = 0, GPX_EXEC_BLP = 1 };
 int gpx_exec_create(gpx_model *m, int kind, gpx_exec **e);
 int gpx_exec_destroy(gpx_exec *e);
 int gpx_exec_set_word(gpx_exec *e, gpx_word *w); /* blp_executor->dpStop = g_stop.d */
+/* The same with a raw address, for callers that own the flag memory themselves as the reference's
+ * test does (executor.dpStop = p1 with p1 from GPUMallocManaged, src/tests/test-dnn-blp.cpp:18-22):
+ * any 4-byte word the device can read - device memory, or pinned host memory, which the kernels
+ * then poll across the bus. */
+int gpx_exec_set_word_dptr(gpx_exec *e, const void *dptr);
 /* Executor::execute (src/executor.cpp:119-134) / BLPExecutor::execute (:211-232). */
 int gpx_exec_execute(gpx_exec *e, gpx_stream s);
 /* Executor::launch_kernel, src/executor.cpp:136-164. */

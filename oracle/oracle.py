@@ -521,3 +521,66 @@ def bert_forward(params, ids, layers=12, heads=12, taps=None):
     if taps is not None:
         taps["heads"] = out
     return out
+
+
+# ---- DistilBERT -------------------------------------------------------------------------------
+# The sequence model the reference compiles (scripts/compile/compile-bert.py:33-52: Hugging Face
+# DistilBertModel, last hidden state, traced on a 6-token input).  Same post-LayerNorm encoder as
+# BERT without token-type embeddings; parameter names follow the DistilBertModel state dict.
+
+def distilbert_param_shapes(layers=6, hidden=768, heads=12, ffn=3072, vocab=30522, max_pos=512):
+    s = {
+        "embeddings.word_embeddings.weight": (vocab, hidden),
+        "embeddings.position_embeddings.weight": (max_pos, hidden),
+        "embeddings.LayerNorm.weight": (hidden,),
+        "embeddings.LayerNorm.bias": (hidden,),
+    }
+    for i in range(layers):
+        p = f"transformer.layer.{i}"
+        for nm in ("q_lin", "k_lin", "v_lin", "out_lin"):
+            s[f"{p}.attention.{nm}.weight"] = (hidden, hidden)
+            s[f"{p}.attention.{nm}.bias"] = (hidden,)
+        s[f"{p}.sa_layer_norm.weight"] = (hidden,)
+        s[f"{p}.sa_layer_norm.bias"] = (hidden,)
+        s[f"{p}.ffn.lin1.weight"] = (ffn, hidden)
+        s[f"{p}.ffn.lin1.bias"] = (ffn,)
+        s[f"{p}.ffn.lin2.weight"] = (hidden, ffn)
+        s[f"{p}.ffn.lin2.bias"] = (hidden,)
+        s[f"{p}.output_layer_norm.weight"] = (hidden,)
+        s[f"{p}.output_layer_norm.bias"] = (hidden,)
+    return s
+
+
+def distilbert_forward(params, ids, layers=6, heads=12, taps=None):
+    """ids: int64 [B][S]; returns the last hidden state [B][S][H] as float32 (numpy float64 inside)."""
+    P = {k: np.asarray(v, np.float64).reshape(v.shape[0], -1) if np.ndim(v) > 1 else np.asarray(v, np.float64)
+         for k, v in params.items()}
+    ids = np.asarray(ids, np.int64)
+    B, S = ids.shape
+    x = P["embeddings.word_embeddings.weight"][ids] + P["embeddings.position_embeddings.weight"][np.arange(S)][None, :, :]
+    x = _layer_norm(x, P["embeddings.LayerNorm.weight"], P["embeddings.LayerNorm.bias"])
+    if taps is not None:
+        taps["embeddings"] = x.astype(np.float32)
+    H = x.shape[-1]
+    dh = H // heads
+    for i in range(layers):
+        p = f"transformer.layer.{i}"
+        lin = lambda name, t: t @ P[f"{p}.{name}.weight"].T + P[f"{p}.{name}.bias"]  # noqa: E731
+        split = lambda t: t.reshape(B, S, heads, dh).transpose(0, 2, 1, 3)  # noqa: E731
+        qh, kh, vh = split(lin("attention.q_lin", x)), split(lin("attention.k_lin", x)), split(lin("attention.v_lin", x))
+        sc = qh @ kh.transpose(0, 1, 3, 2) / np.sqrt(dh)
+        sc = sc - sc.max(-1, keepdims=True)
+        pr = np.exp(sc)
+        pr = pr / pr.sum(-1, keepdims=True)
+        ctx = (pr @ vh).transpose(0, 2, 1, 3).reshape(B, S, H)
+        if taps is not None:
+            taps[f"{p}.attention.context"] = ctx.astype(np.float32)
+        x = _layer_norm(lin("attention.out_lin", ctx) + x, P[f"{p}.sa_layer_norm.weight"], P[f"{p}.sa_layer_norm.bias"])
+        o = lin("ffn.lin2", _gelu(lin("ffn.lin1", x)))
+        x = _layer_norm(o + x, P[f"{p}.output_layer_norm.weight"], P[f"{p}.output_layer_norm.bias"])
+        if taps is not None and i != layers - 1:
+            taps[f"{p}.output"] = x.astype(np.float32)
+    out = x.astype(np.float32)
+    if taps is not None:
+        taps["heads"] = out
+    return out

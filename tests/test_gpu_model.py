@@ -611,3 +611,34 @@ def test_schedule_order_from_device_timestamps(gpx):
     assert checked >= 3
     assert ex.error() == (0, 0)
     ex.clear(), word.destroy(), s.destroy()
+
+
+@pytest.mark.parametrize("model,batch,seq,layers,heads,vocab", [("distilbert_tiny", 2, 6, 2, 2, 1000),
+                                                                ("distilbert", 1, 6, 6, 12, 30522),
+                                                                ("bert", 2, 40, 6, 12, 30522)])
+def test_distilbert_matches_oracle(gpx, oracle, model, batch, seq, layers, heads, vocab):
+    """The reference's sequence model (DistilBERT, 6 layers, traced on a 6-token input:
+    scripts/compile/compile-bert.py:33-52; "bert" is its name in the task configs): last hidden
+    state against the float64 oracle with the fp32 bound, including the reference test's own
+    token ids (src/tests/test-dnn.cpp:21-23)."""
+    ex = gpx.BaseExecutor()
+    ex.init(model, batch=batch, seed=7, seq_len=seq)
+    if batch == 1 and seq == 6:
+        ids = np.array([[101, 7592, 1010, 2088, 999, 102]], np.int64)
+    else:
+        ids = _ids(batch, seq, vocab)
+    ex.set_input("data", ids)
+    ex.execute()
+    assert ex.error() == (0, 0)
+    got = ex.get_output("heads")
+    assert got.shape == (batch, seq, ex.model.shape("heads")[2])
+    params = {k: v.reshape(v.shape[0], -1) if v.ndim == 4 else v for k, v in ex.model.params().items()}
+    assert "embeddings.token_type_embeddings.weight" not in params
+    taps = {}
+    want = oracle.distilbert_forward(params, ids, layers=layers, heads=heads, taps=taps)
+    for name, ref in taps.items():
+        if name == "heads":
+            continue
+        assert _rel(ex.model.get(name).reshape(ref.shape), ref) <= RTOL_FP32, f"{model} node {name}"
+    assert _rel(got, want) <= RTOL_FP32
+    ex.clear()

@@ -64,7 +64,7 @@ def test_two_client_threads_share_one_gpu_through_the_scheduler(gpx):
     def be_client():
         try:
             gpx.init_cuda(0)
-            for _ in range(25):
+            for _ in range(40):
                 t = sched.new_task(c_be)
                 sched.wait_task(c_be, t, 20.0)
                 if not np.array_equal(be.get_output("heads"), be_want):
@@ -83,10 +83,10 @@ def test_two_client_threads_share_one_gpu_through_the_scheduler(gpx):
     st = sched.stats()
     sched.shutdown()
     assert not errors, errors[:3]
-    assert be_done[0] == 25 and hp_done[0] > 20
+    assert be_done[0] == 40 and hp_done[0] > 5
     assert st["wordRaises"] > 0 and st["beResumes"] > 0
     assert st["clients"][c_hp]["completed"] == hp_done[0]
-    assert st["clients"][c_be]["completed"] == 25
+    assert st["clients"][c_be]["completed"] == 40
     assert st["kernelDrain(us)"]["count"] > 0 and st["kernelDrain(us)"]["p99"] < 100.0
     assert be.error() == (0, 0)
     sched.destroy()

@@ -300,3 +300,21 @@ def test_bert_restatement_matches_huggingface_bert(oracle):
     got = oracle.bert_forward(params, ids, layers=2, heads=4)
     assert got.shape == ref.shape
     assert _rel(got, ref) < 2e-6
+
+
+def test_distilbert_restatement_matches_huggingface_distilbert(oracle):
+    """The oracle's DistilBERT encoder (the sequence model the reference compiles,
+    scripts/compile/compile-bert.py:33-52) against transformers.DistilBertModel on a 6-token input."""
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.DistilBertConfig(dim=128, n_layers=2, n_heads=4, hidden_dim=256, vocab_size=1000,
+                                        max_position_embeddings=64, dropout=0.0, attention_dropout=0.0)
+    torch.manual_seed(0)
+    net = transformers.DistilBertModel(cfg).double().eval()
+    params = {k: v.detach().numpy() for k, v in net.state_dict().items() if "position_ids" not in k}
+    assert set(params) == set(oracle.distilbert_param_shapes(layers=2, hidden=128, heads=4, ffn=256, vocab=1000, max_pos=64))
+    ids = np.random.default_rng(6).integers(0, 1000, (2, 6))
+    with torch.no_grad():
+        ref = net(input_ids=torch.from_numpy(ids)).last_hidden_state.numpy()
+    got = oracle.distilbert_forward(params, ids, layers=2, heads=4)
+    assert got.shape == ref.shape
+    assert _rel(got, ref) < 2e-6
