@@ -141,6 +141,9 @@ static void render_graph(const gpx_model *m, Json *graph, Json *host) {
         attrs.set("kernel", Json(n.k));
         attrs.set("stride", Json(n.stride));
         attrs.set("padding", Json(n.pad));
+        if (n.kw) attrs.set("kernel_w", Json(n.kw));
+        if (n.pad_w >= 0) attrs.set("padding_w", Json(n.pad_w));
+        if (n.count_pad) attrs.set("count_include_pad", Json(true));
         attrs.set("relu", Json(n.act == ACT_RELU));
         attrs.set("activation", Json(n.act));
         attrs.set("channels", Json(n.C));
@@ -340,7 +343,12 @@ int build_graph_from_dir(gpx_model &m, const std::string &dir, const gpx_model_o
             const bool tm = a["token_major"].as_bool(false);
             const int cout = tm ? dim(i, 2) : dim(i, 1);
             int res = a["residual"].as_bool(false) ? act_in(3) : -1;
-            id = g.conv(name, src, cout, k, stride, pad, false, res, "", is_head);
+            if (a.has("kernel_w") || a.has("padding_w")) {
+                GPX_REQUIRE(res < 0 && !is_head, GPX_FAIL, "%s: a one-sided filter takes no residual and is no graph output", name.c_str());
+                id = g.conv_rect(name, src, cout, k, (int)a["kernel_w"].as_int(k), stride, pad, (int)a["padding_w"].as_int(pad), false);
+            } else {
+                id = g.conv(name, src, cout, k, stride, pad, false, res, "", is_head);
+            }
             m.nodes[id].act = act;
             if (tm) m.storages[m.nodes[id].storage].token_major = true;
         } else if (fn == "gpx_depthwise_conv2d") {
@@ -352,6 +360,7 @@ int build_graph_from_dir(gpx_model &m, const std::string &dir, const gpx_model_o
                 if (prefix.size() > 7 && prefix.compare(prefix.size() - 7, 7, ".weight") == 0) prefix.erase(prefix.size() - 7);
             }
             id = g.pool(name, src, fn == "gpx_max_pool2d" ? Op::MaxPool : Op::AvgPool, k, stride, pad, prefix);
+            m.nodes[id].count_pad = a["count_include_pad"].as_bool(false);
         } else if (fn == "gpx_affine") {
             id = g.affine(name, src, (int)a["in_channels"].as_int(0), act);
         } else if (fn == "gpx_layer_norm") {

@@ -355,6 +355,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         {
             const uint32_t idesc = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, BN) : make_idesc_bf16_f32(kCBM, BN);
             const uint32_t idesc64 = p.fmt == PF_F16 ? make_idesc_f16_f32(kCBM, 64) : make_idesc_bf16_f32(kCBM, 64);
+            constexpr int kWide = 2 * BN <= 256 ? 2 * BN : BN;  // (256-column tiles never take the packed path)
+            const uint32_t idesc_wide = make_idesc_bf16_f32(kCBM, kWide);
             const uint64_t eye = make_smem_desc_sw128(smem_base + ident_off);
             const bool issuer = lane == 0;
             int stage = 0;
@@ -432,8 +434,19 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                                 if (two_plane) mma_f16_ss(acc0 + 3 * BN + col, a_lo + 2 * k, eye + 2 * k, idesc64, 1u);
                             }
                         }
+                    } else if (dual && two_plane && p.packed) {
+                        // hi*hi in one accumulator, both cross terms in the other.  The W_lo tile
+                        // follows the W_hi tile in the stage and the two accumulators are adjacent
+                        // columns, so A_hi x [W_hi; W_lo] is ONE instruction of width 2*BN: the
+                        // kernel is bound by shared-memory bandwidth (operand reads plus the TMA
+                        // fill), and this reads the A_hi tile once instead of twice.  Every
+                        // accumulator element still receives the same additions in the same order.
+#pragma unroll
+                        for (int k = 0; k < kCBK / kCUmmaK; ++k) {
+                            mma_f16_ss(acc0, a_hi + 2 * k, w_hi + 2 * k, idesc_wide, (first || k > 0) ? 1u : 0u);
+                            mma_f16_ss(acc0 + BN, a_lo + 2 * k, w_hi + 2 * k, idesc, 1u);
+                        }
                     } else if (dual && two_plane) {
-                        // hi*hi in one accumulator, both cross terms in the other
 #pragma unroll
                         for (int k = 0; k < kCBK / kCUmmaK; ++k) {
                             mma_f16_ss(acc0, a_hi + 2 * k, w_hi + 2 * k, idesc, (first || k > 0) ? 1u : 0u);

@@ -76,7 +76,7 @@ conv_simt_kernel(const __grid_constant__ ConvParams p, BlpArgs blp) {
             int ho = t % p.Ho;
             row_n = ok ? t / p.Ho : -1;
             row_h = ho * p.stride - p.pad;
-            row_w = wo * p.stride - p.pad;
+            row_w = wo * p.stride - p.pad_w;
         }
 
         float ra[EA];
@@ -386,8 +386,8 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
                     }
                 }
             }
-            if (p.mode == 1) {
-                float inv = 1.0f / (float)cnt;
+            if (p.mode == 1 || p.mode == 3) {
+                float inv = 1.0f / (float)(p.mode == 1 ? cnt : p.k * p.k);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] *= inv;
             }

@@ -9,6 +9,8 @@
 //                      through a 4-stage shared-memory ring and polls the preempt word,
 //   warp 1 (one lane)  MMA issuer: four tcgen05.mma (128x256x16) per K block into TMEM,
 //   warps 2-5          epilogue: tcgen05.ld the accumulator, convert to bf16, store C.
+// The accumulator is double-buffered (2 x 256 of the 512 tensor-memory columns): while the
+// epilogue drains one tile the MMA issuer already accumulates the next one in the other buffer.
 //
 // Preemption is K-block granular, not tile granular (a whole 128x256x8192 tile takes ~50 us,
 // far above the 20 us drain target): when the producer sees the word raised it sends a STOP message
@@ -36,7 +38,7 @@ using namespace sm100;
 
 constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4, kUmmaK = 16;
 constexpr int kGemmThreads = 192;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;  // two accumulator buffers of 256 columns
 constexpr int kMaxGemmCtas = 256;
 constexpr uint32_t kABytes = kBM * kBK * 2;           // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;           // 32 KiB
@@ -69,12 +71,12 @@ enum : int { EPI_COMPLETE = 0, EPI_PARTIAL = 1, EPI_EXIT = 2 };
 struct GemmControl {
     unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    unsigned long long tmem_full;
-    unsigned long long tmem_empty;
+    unsigned long long tmem_full[2];   // one per accumulator buffer
+    unsigned long long tmem_empty[2];
     uint32_t tmem_base;
     int stage_msg[kStages];
-    int epi_kind;
-    int epi_k_done;
+    int epi_kind[2];
+    int epi_k_done[2];
     int epi_go;
     int abort_flag;
 };
@@ -125,11 +127,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
-        mbar_init(smem_u32(&ctl->tmem_full), 2);   // tcgen05.commit + the issuer's own arrive
-        mbar_init(smem_u32(&ctl->tmem_empty), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl->tmem_full[b]), 2);   // tcgen05.commit + the issuer's own arrive
+            mbar_init(smem_u32(&ctl->tmem_empty[b]), 1);
+            ctl->epi_kind[b] = EPI_EXIT;
+            ctl->epi_k_done[b] = 0;
+        }
         ctl->abort_flag = 0;
-        ctl->epi_kind = EPI_EXIT;
-        ctl->epi_k_done = 0;
         fence_barrier_init();
         fence_proxy_async();
         trace_begin(blp);
@@ -223,10 +227,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 tc_fence_after_sync();
                 int msg = ctl->stage_msg[stage];
+                // Segments alternate between the two accumulator buffers, so the epilogue of one
+                // tile runs while the next tile accumulates in the other buffer.
+                const int buf = (int)(seg & 1);
+                const uint32_t acc = tmem_base + buf * kBN;
                 if (!seg_open) {
-                    // The accumulator is free (or restored) once the epilogue arrived for the
-                    // previous segment; completion number `seg` has parity seg & 1.
-                    if (!mbar_wait(smem_u32(&ctl->tmem_empty), seg & 1, abort_flag, kWaitLimitNs)) {
+                    // The buffer is free (or restored) once the epilogue arrived for the segment
+                    // that used it last; its completion number seg / 2 has parity (seg >> 1) & 1.
+                    if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), (seg >> 1) & 1, abort_flag, kWaitLimitNs)) {
                         fail(202);
                         break;
                     }
@@ -234,10 +242,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     seg_open = true;
                 }
                 if (msg != MSG_DATA) {
-                    ctl->epi_kind = msg == MSG_STOP ? EPI_PARTIAL : EPI_EXIT;
-                    ctl->epi_k_done = kb;
-                    mma_commit(smem_u32(&ctl->tmem_full));
-                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                    ctl->epi_kind[buf] = msg == MSG_STOP ? EPI_PARTIAL : EPI_EXIT;
+                    ctl->epi_k_done[buf] = kb;
+                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
                     break;
                 }
                 uint32_t a_addr = smem_base + stage * kStageBytes;
@@ -247,7 +255,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (int k = 0; k < kBK / kUmmaK; ++k) {
                     // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the
                     // descriptor's 16-byte address units.
-                    mma_f16_ss(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                    mma_f16_ss(acc, a_desc + 2 * k, b_desc + 2 * k, idesc,
                                (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 mma_commit(smem_u32(&ctl->empty[stage]));  // ring slot reusable once these retire
@@ -256,10 +264,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     phase ^= 1;
                 }
                 if (++kb == num_kb) {
-                    ctl->epi_kind = EPI_COMPLETE;
-                    ctl->epi_k_done = num_kb;
-                    mma_commit(smem_u32(&ctl->tmem_full));
-                    mbar_arrive(smem_u32(&ctl->tmem_full));
+                    ctl->epi_kind[buf] = EPI_COMPLETE;
+                    ctl->epi_k_done[buf] = num_kb;
+                    mma_commit(smem_u32(&ctl->tmem_full[buf]));
+                    mbar_arrive(smem_u32(&ctl->tmem_full[buf]));
                     ++seg;
                     ++it;
                     kb = 0;
@@ -292,24 +300,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_before_sync();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (leader) mbar_arrive(smem_u32(&ctl->tmem_empty));
+        if (leader) {
+            mbar_arrive(smem_u32(&ctl->tmem_empty[0]));  // a restored tile sits in buffer 0: segment 0 uses it
+            mbar_arrive(smem_u32(&ctl->tmem_empty[1]));
+        }
 
         int it = first_iter;
         int seg_k0 = first_k;
         int tiles_done = 0;
         for (uint32_t seg = 0;; ++seg) {
+            const int buf = (int)(seg & 1);
+            const uint32_t t_acc = t_lane + buf * kBN;
             // One thread waits on the mbarrier and publishes the outcome, so the 128 epilogue
             // threads always take the same branch and never strand one another at bar.sync.
             if (leader) {
-                bool ok = mbar_wait(smem_u32(&ctl->tmem_full), seg & 1, abort_flag, kWaitLimitNs);
+                bool ok = mbar_wait(smem_u32(&ctl->tmem_full[buf]), (seg >> 1) & 1, abort_flag, kWaitLimitNs);
                 if (!ok) fail(301);
                 ctl->epi_go = ok ? 1 : 0;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (!ctl->epi_go) break;
             tc_fence_after_sync();
-            const int kind = ctl->epi_kind;
-            const int k_done = ctl->epi_k_done;
+            const int kind = ctl->epi_kind[buf];
+            const int k_done = ctl->epi_k_done[buf];
             if (kind == EPI_EXIT) {
                 if (leader) {
                     slot->next_iter = it;
@@ -324,7 +337,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
                 __nv_bfloat16 *crow = C + (size_t)(m_blk * kBM + row) * N + (size_t)n_blk * kBN;
                 for (int c = 0; c < kBN; c += 32) {
-                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
                     uint4 *dst = reinterpret_cast<uint4 *>(crow + c);
 #pragma unroll
@@ -352,7 +365,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tc_fence_before_sync();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (leader) {
-                    mbar_arrive(smem_u32(&ctl->tmem_empty));
+                    mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
                     if (blp.executed) atomicAdd(blp.executed, 1);
                 }
                 continue;
@@ -360,7 +373,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // EPI_PARTIAL: spill the accumulator if this launch added to it, record the cursor.
             if (k_done > seg_k0) {
                 for (int c = 0; c < kBN; c += 32) {
-                    tmem_ld_32x32(t_lane + c, v);
+                    tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
                     uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * kBN + c);
 #pragma unroll

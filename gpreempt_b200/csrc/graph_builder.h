@@ -123,6 +123,27 @@ struct GraphBuilder {
         return (int)m.nodes.size() - 1;
     }
 
+    // Convolution with a kh x kw filter and separate vertical / horizontal padding (the factorised
+    // 1x7 / 7x1 / 1x3 / 3x1 convolutions of Inception-v3), + bias + ReLU.
+    int conv_rect(const std::string &name, int in, int cout, int kh, int kw, int stride, int ph, int pw,
+                  bool relu) {
+        int id = conv(name, in, cout, kh, stride, ph, relu);
+        if (kh == kw && ph == pw) return id;
+        Node &n = m.nodes[id];
+        const Node &src = m.nodes[in];
+        n.kw = kw;
+        n.pad_w = pw;
+        n.W = (src.W + 2 * pw - kw) / stride + 1;
+        Storage &w = m.storages[n.weight];
+        w.dims[3] = kw;
+        w.bytes = (size_t)cout * src.C * kh * kw * sizeof(float);
+        w.fan_in = src.C * kh * kw;
+        Storage &out = m.storages[n.storage];
+        out.dims[3] = n.W;
+        out.bytes = (size_t)n.N * n.C * n.H * n.W * sizeof(float);
+        return id;
+    }
+
     // Fully connected layer over the flattened (C, H, W) input: a convolution whose filter
     // covers the whole feature map, so the canonical weight [out][C*H*W] is its OIHW filter.
     int dense(const std::string &name, int in, int cout, bool relu) {

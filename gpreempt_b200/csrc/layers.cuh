@@ -59,6 +59,8 @@ struct CgemmParams {
     int res_kb;
     int drop_on_stop;        // 1: a tile interrupted by the word is recomputed from K block 0 after the
                              // resume instead of being saved (no spill on the way out)
+    int packed;              // 1 (two-plane operands, dual plan): hi*hi and hi*lo issued as one product of
+                             // width 2*BN against the adjacent W_hi / W_lo tiles
     int dual;                // 1: two accumulators per tile in two TMEM buffers (short K ranges and
                              // single-plane operands), 0: four accumulators in one buffer
     int k_splits;            // >= 1: the K range is cut into this many tiles per output block
@@ -89,7 +91,8 @@ struct ConvParams {
     bf16_bits *out_hi, *out_lo;
     ActLayout out;
     int Cin, Ho, Wo, Cout;
-    int kh, kw, stride, pad;
+    int kh, kw, stride, pad;  // pad: vertical padding
+    int pad_w;                // horizontal padding (one-sided filters pad one direction only)
     int M, K;
     int relu;
     int tiles_m, tiles_n;
@@ -100,7 +103,8 @@ struct PoolParams {
     bf16_bits *out_hi, *out_lo;
     ActLayout out;
     int k, stride, pad;
-    int mode;         // 0 = max, 1 = average over valid taps, 2 = copy of the tap (0,0) (subsample)
+    int mode;         // 0 = max, 1 = average over valid taps, 2 = copy of the tap (0,0) (subsample),
+                      // 3 = average with the whole window as divisor (padding counts as zeros)
     int total_tiles;
     int tile_elems;   // output 8-channel vectors per tile
     // The output may be a channel slice of a wider tensor and the input a channel prefix of one:

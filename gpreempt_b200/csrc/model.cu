@@ -209,6 +209,109 @@ static void build_bert(gpx_model &m, int batch, int seq, int layers, int hidden,
     m.head_node = x;
 }
 
+// Inception-v3 (Szegedy et al. 2016) in the torchvision layer schedule and parameter names: one
+// of the models the reference compiles (scripts/compile/compile.py:27-36, 3x299x299 input; its
+// relay.testing definition pools the last block's pooling branch with max where this one
+// averages).  Every convolution carries its folded batch norm as a bias and a ReLU; a block's
+// concatenation is one buffer its branches write channel slices of.  The 1x1 and padded 3x3
+// convolutions run on the tensor cores, the one-sided (1x7, 7x1, 1x3, 3x1), 5x5 and unpadded
+// stride-2 filters on the CUDA-core kernel.
+static void build_inception_v3(gpx_model &m, int batch) {
+    m.pad_channels = true;
+    GraphBuilder g(m);
+    auto cv = [&](const std::string &name, int in, int cout, int kh, int kw, int stride, int ph, int pw) {
+        return g.conv_rect(name, in, cout, kh, kw, stride, ph, pw, true);
+    };
+    auto avg3 = [&](const std::string &name, int in) {
+        int id = g.pool(name, in, Op::AvgPool, 3, 1, 1);
+        m.nodes[id].count_pad = true;
+        return id;
+    };
+    int x = g.input("data", batch, 3, 299, 299);
+    x = cv("Conv2d_1a_3x3", x, 32, 3, 3, 2, 0, 0);
+    x = cv("Conv2d_2a_3x3", x, 32, 3, 3, 1, 0, 0);
+    x = cv("Conv2d_2b_3x3", x, 64, 3, 3, 1, 1, 1);
+    x = g.pool("maxpool1", x, Op::MaxPool, 3, 2, 0);
+    x = cv("Conv2d_3b_1x1", x, 80, 1, 1, 1, 0, 0);
+    x = cv("Conv2d_4a_3x3", x, 192, 3, 3, 1, 0, 0);
+    x = g.pool("maxpool2", x, Op::MaxPool, 3, 2, 0);
+    int S = 35;
+    const int pool_features[3] = {32, 64, 64};
+    const char *a_names[3] = {"Mixed_5b", "Mixed_5c", "Mixed_5d"};
+    for (int b = 0; b < 3; ++b) {
+        const std::string p = a_names[b];
+        int buf = g.buffer(p, batch, 64 + 64 + 96 + pool_features[b], S, S);
+        g.place(cv(p + ".branch1x1", x, 64, 1, 1, 1, 0, 0), buf, 0);
+        int t = cv(p + ".branch5x5_1", x, 48, 1, 1, 1, 0, 0);
+        g.place(cv(p + ".branch5x5_2", t, 64, 5, 5, 1, 2, 2), buf, 64);
+        t = cv(p + ".branch3x3dbl_1", x, 64, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch3x3dbl_2", t, 96, 3, 3, 1, 1, 1);
+        g.place(cv(p + ".branch3x3dbl_3", t, 96, 3, 3, 1, 1, 1), buf, 128);
+        g.place(cv(p + ".branch_pool", avg3(p + ".pool", x), pool_features[b], 1, 1, 1, 0, 0), buf, 224);
+        x = buf;
+    }
+    {
+        const std::string p = "Mixed_6a";
+        S = 17;
+        int buf = g.buffer(p, batch, 384 + 96 + 288, S, S);
+        g.place(cv(p + ".branch3x3", x, 384, 3, 3, 2, 0, 0), buf, 0);
+        int t = cv(p + ".branch3x3dbl_1", x, 64, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch3x3dbl_2", t, 96, 3, 3, 1, 1, 1);
+        g.place(cv(p + ".branch3x3dbl_3", t, 96, 3, 3, 2, 0, 0), buf, 384);
+        g.place(g.pool(p + ".pool", x, Op::MaxPool, 3, 2, 0), buf, 480);
+        x = buf;
+    }
+    const int c7s[4] = {128, 160, 160, 192};
+    const char *c_names[4] = {"Mixed_6b", "Mixed_6c", "Mixed_6d", "Mixed_6e"};
+    for (int b = 0; b < 4; ++b) {
+        const std::string p = c_names[b];
+        const int c7 = c7s[b];
+        int buf = g.buffer(p, batch, 768, S, S);
+        g.place(cv(p + ".branch1x1", x, 192, 1, 1, 1, 0, 0), buf, 0);
+        int t = cv(p + ".branch7x7_1", x, c7, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch7x7_2", t, c7, 1, 7, 1, 0, 3);
+        g.place(cv(p + ".branch7x7_3", t, 192, 7, 1, 1, 3, 0), buf, 192);
+        t = cv(p + ".branch7x7dbl_1", x, c7, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch7x7dbl_2", t, c7, 7, 1, 1, 3, 0);
+        t = cv(p + ".branch7x7dbl_3", t, c7, 1, 7, 1, 0, 3);
+        t = cv(p + ".branch7x7dbl_4", t, c7, 7, 1, 1, 3, 0);
+        g.place(cv(p + ".branch7x7dbl_5", t, 192, 1, 7, 1, 0, 3), buf, 384);
+        g.place(cv(p + ".branch_pool", avg3(p + ".pool", x), 192, 1, 1, 1, 0, 0), buf, 576);
+        x = buf;
+    }
+    {
+        const std::string p = "Mixed_7a";
+        S = 8;
+        int buf = g.buffer(p, batch, 320 + 192 + 768, S, S);
+        int t = cv(p + ".branch3x3_1", x, 192, 1, 1, 1, 0, 0);
+        g.place(cv(p + ".branch3x3_2", t, 320, 3, 3, 2, 0, 0), buf, 0);
+        t = cv(p + ".branch7x7x3_1", x, 192, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch7x7x3_2", t, 192, 1, 7, 1, 0, 3);
+        t = cv(p + ".branch7x7x3_3", t, 192, 7, 1, 1, 3, 0);
+        g.place(cv(p + ".branch7x7x3_4", t, 192, 3, 3, 2, 0, 0), buf, 320);
+        g.place(g.pool(p + ".pool", x, Op::MaxPool, 3, 2, 0), buf, 512);
+        x = buf;
+    }
+    const char *e_names[2] = {"Mixed_7b", "Mixed_7c"};
+    for (int b = 0; b < 2; ++b) {
+        const std::string p = e_names[b];
+        int buf = g.buffer(p, batch, 2048, S, S);
+        g.place(cv(p + ".branch1x1", x, 320, 1, 1, 1, 0, 0), buf, 0);
+        int t = cv(p + ".branch3x3_1", x, 384, 1, 1, 1, 0, 0);
+        g.place(cv(p + ".branch3x3_2a", t, 384, 1, 3, 1, 0, 1), buf, 320);
+        g.place(cv(p + ".branch3x3_2b", t, 384, 3, 1, 1, 1, 0), buf, 704);
+        t = cv(p + ".branch3x3dbl_1", x, 448, 1, 1, 1, 0, 0);
+        t = cv(p + ".branch3x3dbl_2", t, 384, 3, 3, 1, 1, 1);
+        g.place(cv(p + ".branch3x3dbl_3a", t, 384, 1, 3, 1, 0, 1), buf, 1088);
+        g.place(cv(p + ".branch3x3dbl_3b", t, 384, 3, 1, 1, 1, 0), buf, 1472);
+        g.place(cv(p + ".branch_pool", avg3(p + ".pool", x), 192, 1, 1, 1, 0, 0), buf, 1856);
+        x = buf;
+    }
+    x = g.pool("avgpool", x, Op::AvgPool, S, 1, 0);
+    x = g.conv("heads", x, 1000, 1, 1, 0, false, -1, "fc", true);
+    m.head_node = x;
+}
+
 // DistilBERT (Sanh et al. 2019; the Hugging Face DistilBertModel layout and parameter names): the
 // BERT encoder without token-type embeddings, 6 layers for distilbert-base.  This is the sequence
 // model the reference compiles (scripts/compile/compile-bert.py:33-52, traced on a 6-token input);
@@ -277,6 +380,8 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         build_vgg(m, batch, cfg, (int)(sizeof(cfg) / sizeof(int)));
     } else if (name == "mobilenet_v2") {
         build_mobilenet_v2(m, batch);
+    } else if (name == "inception_v3" || name == "inception") {
+        build_inception_v3(m, batch);
     } else if (name == "densenet201" || name == "densenet") {
         const int cfg[4] = {6, 12, 48, 32};
         build_densenet(m, batch, cfg, 32, 64);
@@ -370,6 +475,7 @@ static bool full_map_dense(const Node &n, const Node &src) {
 
 static bool tensor_core_shape(const gpx_model &m, const Node &n, const Node &src) {
     if (n.op != Op::Conv) return false;
+    if ((n.kw && n.kw != n.k) || (n.pad_w >= 0 && n.pad_w != n.pad)) return false;  // one-sided filters: CUDA cores
     // Input channels in whole 64-wide K blocks; output channels in 16-byte vectors (the epilogue
     // masks the last column tile).
     if (stored_c(m, src) % 64 != 0 || stored_c(m, n) % 8 != 0) return false;
@@ -430,7 +536,8 @@ int finalize_model(gpx_model &m) {
             n.tensor_core = true;
         // Few input channels (the stem): build the patch matrix, then a 1x1 tensor-core GEMM.
         if (allow_tc && !n.tensor_core && out.kind == Storage::ActSplit && stored_c(m, n) % 64 == 0 &&
-            in.kind == Storage::InputF32 && n.k * n.k * src.C <= 1024) {
+            in.kind == Storage::InputF32 && n.k * n.k * src.C <= 1024 && (!n.kw || n.kw == n.k) &&
+            (n.pad_w < 0 || n.pad_w == n.pad)) {
             n.tensor_core = true;
             n.via_im2col = true;
         }
@@ -739,13 +846,14 @@ int finalize_model(gpx_model &m) {
         if (n.op != Op::Conv) {
             GPX_REQUIRE(m.storages[src.storage].kind == Storage::ActSplit, GPX_FAIL,
                         "%s: pooling the graph input is not supported", n.name.c_str());
-            add_pool(n.name, view_of(m, src), out, n.k, n.stride, n.pad, n.op == Op::MaxPool ? 0 : 1, -1,
-                     n.scale, n.shift, n.act);
+            add_pool(n.name, view_of(m, src), out, n.k, n.stride, n.pad,
+                     n.op == Op::MaxPool ? 0 : (n.count_pad ? 3 : 1), -1, n.scale, n.shift, n.act);
             continue;
         }
         const Storage &w = m.storages[n.weight];
-        const double flops = 2.0 * n.N * n.H * n.W * (double)n.k * n.k * src.C * n.C;
-        const double bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)n.k * n.k * src.C * n.C +
+        const int n_kw = n.kw ? n.kw : n.k;
+        const double flops = 2.0 * n.N * n.H * n.W * (double)n.k * n_kw * src.C * n.C;
+        const double bytes = 4.0 * ((double)src.N * src.H * src.W * src.C + (double)n.k * n_kw * src.C * n.C +
                                     (double)n.N * n.H * n.W * n.C * (n.residual >= 0 ? 2 : 1));
         if (!n.tensor_core) {
             Kernel kn;
@@ -771,11 +879,13 @@ int finalize_model(gpx_model &m) {
             p.Ho = n.H;
             p.Wo = n.W;
             p.Cout = n.C;
-            p.kh = p.kw = n.k;
+            p.kh = n.k;
+            p.kw = n_kw;
             p.stride = n.stride;
             p.pad = n.pad;
+            p.pad_w = n.pad_w >= 0 ? n.pad_w : n.pad;
             p.M = n.N * n.H * n.W;
-            p.K = n.k * n.k * src.C;
+            p.K = n.k * n_kw * src.C;
             p.relu = n.act;
             kn.tile = conv_pick_tile(p, m.sm_count);
             conv_set_tiles(p, kn.tile);
@@ -933,6 +1043,10 @@ int finalize_model(gpx_model &m) {
             if (atoi(e) == 1) p.dual = (m.fmt != PF_SPLIT || p.kb_per_split * 64 <= 1024) ? 1 : 0;
         }
         if (bn == 256) p.dual = 1;  // the only plan that fits 256-column tiles in tensor memory
+        {
+            const char *e = getenv("GPX_CGEMM_PACKED");
+            p.packed = (bn <= 128 && !(e && e[0] == '0')) ? 1 : 0;
+        }
         // The residual of a 1x1 stride-1 convolution on plain rows has the rows of the GEMM itself:
         // it is then added by the tensor core as identity K blocks instead of by the epilogue.
         p.res_kb = 0;

@@ -62,6 +62,9 @@ struct Node {
     int weight = -1, bias = -1;
     int N = 0, H = 0, W = 0, C = 0;  // output shape
     int k = 0, stride = 1, pad = 0;
+    int kw = 0;      // filter width when it differs from the height `k` (0 = square)
+    int pad_w = -1;  // horizontal padding when it differs from the vertical `pad` (-1 = same)
+    bool count_pad = false;  // average pooling that divides by the whole window (padding counts as zeros)
     int act = 0;  // ActKind applied after bias and residual
     int residual = -1;
     bool tensor_core = false;  // decided by finalize_model

@@ -25,6 +25,19 @@ DEFAULT = [
 ]
 
 
+def parse_specs(text: str) -> list[tuple[str, int, str, int]]:
+    """"model:batch:dtype[:seq_len]" entries separated by commas -> (model, batch, dtype, seq_len)."""
+    out = []
+    for item in text.split(","):
+        f = item.strip().split(":")
+        if len(f) < 3 or len(f) > 4:
+            raise ValueError(f"'{item}': expected model:batch:dtype[:seq_len]")
+        if f[2] not in ("float32", "bfloat16", "float16"):
+            raise ValueError(f"'{item}': dtype must be float32, bfloat16 or float16")
+        out.append((f[0], int(f[1]), f[2], int(f[3]) if len(f) > 3 else 0))
+    return out
+
+
 def run(model: str, batch: int, dtype: str, seq_len: int, iters: int, warmup: int, graph: bool) -> dict:
     ex = api.BaseExecutor()
     ex.init(model, batch=batch, seed=1, seq_len=seq_len, dtype=dtype)
@@ -110,15 +123,10 @@ def main() -> None:
     args = ap.parse_args()
     api.init_cuda(args.device)
     if args.kernels:
-        f = args.kernels.split(":")
-        per_kernel(f[0], int(f[1]), f[2], int(f[3]) if len(f) > 3 else 0, args.iters)
+        (model, batch, dtype, seq), = parse_specs(args.kernels)
+        per_kernel(model, batch, dtype, seq, args.iters)
         return
-    todo = DEFAULT
-    if args.only:
-        todo = []
-        for item in args.only.split(","):
-            f = item.split(":")
-            todo.append((f[0], int(f[1]), f[2], int(f[3]) if len(f) > 3 else 0))
+    todo = parse_specs(args.only) if args.only else DEFAULT
     for model, batch, dtype, seq in todo:
         print(json.dumps(run(model, batch, dtype, seq, args.iters, args.warmup, args.graph)), flush=True)
 

@@ -35,11 +35,23 @@ void orc_axpy_f32(float a, const float *x, float *y, size_t n) {
  * in  [N][Cin][H][W], w [Cout][Cin][kh][kw], bias [Cout] or NULL, res [N][Cout][Ho][Wo] or
  * NULL, out [N][Cout][Ho][Wo].  Each output is accumulated in fp64 over (ci, fh, fw) in
  * increasing order and rounded to fp32 once. */
+void orc_conv2d_nchw_hw(const float *in, const float *w, const float *bias, const float *res,
+                        float *out, int N, int Cin, int H, int W, int Cout, int kh, int kw,
+                        int stride, int pad_h, int pad_w, int relu);
+
 void orc_conv2d_nchw(const float *in, const float *w, const float *bias, const float *res,
                      float *out, int N, int Cin, int H, int W, int Cout, int kh, int kw,
                      int stride, int pad, int relu) {
-    const int Ho = (H + 2 * pad - kh) / stride + 1;
-    const int Wo = (W + 2 * pad - kw) / stride + 1;
+    orc_conv2d_nchw_hw(in, w, bias, res, out, N, Cin, H, W, Cout, kh, kw, stride, pad, pad, relu);
+}
+
+/* The same with separate vertical and horizontal padding (the 1x7 / 7x1 / 1x3 / 3x1 factorised
+ * convolutions of Inception-v3 pad one direction only). */
+void orc_conv2d_nchw_hw(const float *in, const float *w, const float *bias, const float *res,
+                        float *out, int N, int Cin, int H, int W, int Cout, int kh, int kw,
+                        int stride, int pad_h, int pad_w, int relu) {
+    const int Ho = (H + 2 * pad_h - kh) / stride + 1;
+    const int Wo = (W + 2 * pad_w - kw) / stride + 1;
 #pragma omp parallel
     {
         double *acc = (double *)malloc(sizeof(double) * (size_t)Ho * Wo);
@@ -54,16 +66,16 @@ void orc_conv2d_nchw(const float *in, const float *w, const float *bias, const f
                             const double wv = w[(((size_t)co * Cin + ci) * kh + fh) * kw + fw];
                             /* valid output range for this tap */
                             int ho_lo = 0, wo_lo = 0;
-                            while (ho_lo < Ho && ho_lo * stride - pad + fh < 0) ++ho_lo;
-                            while (wo_lo < Wo && wo_lo * stride - pad + fw < 0) ++wo_lo;
+                            while (ho_lo < Ho && ho_lo * stride - pad_h + fh < 0) ++ho_lo;
+                            while (wo_lo < Wo && wo_lo * stride - pad_w + fw < 0) ++wo_lo;
                             int ho_hi = Ho, wo_hi = Wo;
-                            while (ho_hi > ho_lo && (ho_hi - 1) * stride - pad + fh >= H) --ho_hi;
-                            while (wo_hi > wo_lo && (wo_hi - 1) * stride - pad + fw >= W) --wo_hi;
+                            while (ho_hi > ho_lo && (ho_hi - 1) * stride - pad_h + fh >= H) --ho_hi;
+                            while (wo_hi > wo_lo && (wo_hi - 1) * stride - pad_w + fw >= W) --wo_hi;
                             for (int ho = ho_lo; ho < ho_hi; ++ho) {
-                                const float *row = plane + (size_t)(ho * stride - pad + fh) * W;
+                                const float *row = plane + (size_t)(ho * stride - pad_h + fh) * W;
                                 double *arow = acc + (size_t)ho * Wo;
                                 for (int wo = wo_lo; wo < wo_hi; ++wo)
-                                    arow[wo] += wv * (double)row[wo * stride - pad + fw];
+                                    arow[wo] += wv * (double)row[wo * stride - pad_w + fw];
                             }
                         }
                     }
@@ -172,7 +184,8 @@ void orc_dwconv2d_nchw(const float *in, const float *w, const float *bias, float
     }
 }
 
-/* max (mode 0) / average over the valid taps (mode 1) pooling, NCHW. */
+/* max (mode 0) / average over the valid taps (mode 1) / average with the whole window as divisor,
+ * padding counted as zeros (mode 2, the default of torch.nn.functional.avg_pool2d) pooling, NCHW. */
 void orc_pool2d_nchw(const float *in, float *out, int N, int C, int H, int W, int k, int stride,
                      int pad, int mode) {
     const int Ho = (H + 2 * pad - k) / stride + 1;
@@ -201,6 +214,7 @@ void orc_pool2d_nchw(const float *in, float *out, int N, int C, int H, int W, in
                         }
                     }
                     if (mode == 1) acc /= (double)cnt;
+                    if (mode == 2) acc /= (double)(k * k);
                     o[(size_t)ho * Wo + wo] = (float)acc;
                 }
             }

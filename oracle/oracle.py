@@ -39,12 +39,12 @@ def build() -> str:
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        if not os.path.exists(_LIB_PATH):
-            build()
+        build()
         _lib = ctypes.CDLL(_LIB_PATH)
         conv_args = [_f32p, _f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 10
         _lib.orc_conv2d_nchw.argtypes = conv_args
         _lib.orc_conv2d_nchw_fast.argtypes = conv_args
+        _lib.orc_conv2d_nchw_hw.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 11
         _lib.orc_pool2d_nchw.argtypes = [_f32p, _f32p] + [ctypes.c_int] * 8
         _lib.orc_dwconv2d_nchw.argtypes = [_f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 9
         _lib.orc_axpy_f32.argtypes = [ctypes.c_float, _f32p, _f32p, ctypes.c_size_t]
@@ -76,16 +76,21 @@ def conv2d(x, w, bias=None, stride=1, pad=0, relu=False, residual=None, fast=Fal
     n, cin, h, wd = x.shape
     cout, cin2, kh, kw = w.shape
     assert cin == cin2
-    ho = (h + 2 * pad - kh) // stride + 1
-    wo = (wd + 2 * pad - kw) // stride + 1
+    ph, pw = (pad, pad) if np.isscalar(pad) else pad   # (vertical, horizontal) for one-sided kernels
+    ho = (h + 2 * ph - kh) // stride + 1
+    wo = (wd + 2 * pw - kw) // stride + 1
     out = np.empty((n, cout, ho, wo), np.float32)
     b = _c(bias) if bias is not None else None
     r = _c(residual) if residual is not None else None
     if r is not None:
         assert r.shape == out.shape
-    fn = lib().orc_conv2d_nchw_fast if fast else lib().orc_conv2d_nchw
-    fn(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(r, _f32p), _p(out, _f32p), n, cin, h, wd,
-       cout, kh, kw, stride, pad, 3 if relu == "relu6" else int(bool(relu)))
+    act = 3 if relu == "relu6" else int(bool(relu))
+    if fast and ph == pw:
+        lib().orc_conv2d_nchw_fast(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(r, _f32p), _p(out, _f32p), n, cin,
+                                   h, wd, cout, kh, kw, stride, ph, act)
+    else:
+        lib().orc_conv2d_nchw_hw(_p(x, _f32p), _p(w, _f32p), _p(b, _f32p), _p(r, _f32p), _p(out, _f32p), n, cin,
+                                 h, wd, cout, kh, kw, stride, ph, pw, act)
     return out
 
 
@@ -110,8 +115,9 @@ def pool2d(x, k, stride, pad, mode):
     ho = (h + 2 * pad - k) // stride + 1
     wo = (w + 2 * pad - k) // stride + 1
     out = np.empty((n, c, ho, wo), np.float32)
+    # "avg" divides by the number of taps inside the image, "avg_pad" by the whole window
     lib().orc_pool2d_nchw(_p(x, _f32p), _p(out, _f32p), n, c, h, w, k, stride, pad,
-                          0 if mode == "max" else 1)
+                          {"max": 0, "avg": 1, "avg_pad": 2}[mode])
     return out
 
 
@@ -394,7 +400,129 @@ MODELS = {
     "resnet_tiny": lambda p, d, **kw: resnet_forward(p, d, (1, 1, 1, 1), **kw),
     "vgg16": lambda p, d, **kw: vgg_forward(p, d, "vgg16", **kw),
     "vgg19": lambda p, d, **kw: vgg_forward(p, d, "vgg19", **kw),
+    "inception_v3": lambda p, d, **kw: inception_v3_forward(p, d, **kw),
 }
+
+
+# ---- Inception-v3 -------------------------------------------------------------------------------
+# Szegedy et al. 2016 in the torchvision layer schedule and parameter names (one of the models the
+# reference compiles, scripts/compile/compile.py:27-36, from relay.testing.inception_v3 with
+# 3x299x299 inputs; that definition uses max pooling in the last block's pooling branch where
+# torchvision, followed here, averages).  Every BasicConv2d is convolution + folded batch norm
+# (a bias) + ReLU.  INCEPTION_CONVS lists (name, cin, cout, (kh, kw), stride, (ph, pw)) in
+# execution order.
+
+def _inception_blocks():
+    convs = [("Conv2d_1a_3x3", 3, 32, (3, 3), 2, (0, 0)), ("Conv2d_2a_3x3", 32, 32, (3, 3), 1, (0, 0)),
+             ("Conv2d_2b_3x3", 32, 64, (3, 3), 1, (1, 1)), ("Conv2d_3b_1x1", 64, 80, (1, 1), 1, (0, 0)),
+             ("Conv2d_4a_3x3", 80, 192, (3, 3), 1, (0, 0))]
+
+    def a(p, cin, pf):
+        return [(f"{p}.branch1x1", cin, 64, (1, 1), 1, (0, 0)),
+                (f"{p}.branch5x5_1", cin, 48, (1, 1), 1, (0, 0)), (f"{p}.branch5x5_2", 48, 64, (5, 5), 1, (2, 2)),
+                (f"{p}.branch3x3dbl_1", cin, 64, (1, 1), 1, (0, 0)), (f"{p}.branch3x3dbl_2", 64, 96, (3, 3), 1, (1, 1)),
+                (f"{p}.branch3x3dbl_3", 96, 96, (3, 3), 1, (1, 1)), (f"{p}.branch_pool", cin, pf, (1, 1), 1, (0, 0))]
+
+    def b(p, cin):
+        return [(f"{p}.branch3x3", cin, 384, (3, 3), 2, (0, 0)),
+                (f"{p}.branch3x3dbl_1", cin, 64, (1, 1), 1, (0, 0)), (f"{p}.branch3x3dbl_2", 64, 96, (3, 3), 1, (1, 1)),
+                (f"{p}.branch3x3dbl_3", 96, 96, (3, 3), 2, (0, 0))]
+
+    def c(p, cin, c7):
+        return [(f"{p}.branch1x1", cin, 192, (1, 1), 1, (0, 0)),
+                (f"{p}.branch7x7_1", cin, c7, (1, 1), 1, (0, 0)), (f"{p}.branch7x7_2", c7, c7, (1, 7), 1, (0, 3)),
+                (f"{p}.branch7x7_3", c7, 192, (7, 1), 1, (3, 0)),
+                (f"{p}.branch7x7dbl_1", cin, c7, (1, 1), 1, (0, 0)), (f"{p}.branch7x7dbl_2", c7, c7, (7, 1), 1, (3, 0)),
+                (f"{p}.branch7x7dbl_3", c7, c7, (1, 7), 1, (0, 3)), (f"{p}.branch7x7dbl_4", c7, c7, (7, 1), 1, (3, 0)),
+                (f"{p}.branch7x7dbl_5", c7, 192, (1, 7), 1, (0, 3)), (f"{p}.branch_pool", cin, 192, (1, 1), 1, (0, 0))]
+
+    def d(p, cin):
+        return [(f"{p}.branch3x3_1", cin, 192, (1, 1), 1, (0, 0)), (f"{p}.branch3x3_2", 192, 320, (3, 3), 2, (0, 0)),
+                (f"{p}.branch7x7x3_1", cin, 192, (1, 1), 1, (0, 0)), (f"{p}.branch7x7x3_2", 192, 192, (1, 7), 1, (0, 3)),
+                (f"{p}.branch7x7x3_3", 192, 192, (7, 1), 1, (3, 0)), (f"{p}.branch7x7x3_4", 192, 192, (3, 3), 2, (0, 0))]
+
+    def e(p, cin):
+        return [(f"{p}.branch1x1", cin, 320, (1, 1), 1, (0, 0)),
+                (f"{p}.branch3x3_1", cin, 384, (1, 1), 1, (0, 0)), (f"{p}.branch3x3_2a", 384, 384, (1, 3), 1, (0, 1)),
+                (f"{p}.branch3x3_2b", 384, 384, (3, 1), 1, (1, 0)),
+                (f"{p}.branch3x3dbl_1", cin, 448, (1, 1), 1, (0, 0)), (f"{p}.branch3x3dbl_2", 448, 384, (3, 3), 1, (1, 1)),
+                (f"{p}.branch3x3dbl_3a", 384, 384, (1, 3), 1, (0, 1)), (f"{p}.branch3x3dbl_3b", 384, 384, (3, 1), 1, (1, 0)),
+                (f"{p}.branch_pool", cin, 192, (1, 1), 1, (0, 0))]
+
+    convs += a("Mixed_5b", 192, 32) + a("Mixed_5c", 256, 64) + a("Mixed_5d", 288, 64) + b("Mixed_6a", 288)
+    convs += c("Mixed_6b", 768, 128) + c("Mixed_6c", 768, 160) + c("Mixed_6d", 768, 160) + c("Mixed_6e", 768, 192)
+    convs += d("Mixed_7a", 768) + e("Mixed_7b", 1280) + e("Mixed_7c", 2048)
+    return convs
+
+
+INCEPTION_CONVS = _inception_blocks()
+
+
+def inception_v3_param_shapes(num_classes=1000):
+    s = {}
+    for name, cin, cout, (kh, kw), _, _ in INCEPTION_CONVS:
+        s[f"{name}.weight"] = (cout, cin, kh, kw)
+        s[f"{name}.bias"] = (cout,)
+    s["fc.weight"] = (num_classes, 2048, 1, 1)
+    s["fc.bias"] = (num_classes,)
+    return s
+
+
+def inception_v3_forward(params, data, fast=False, taps=None):
+    """Inception-v3 forward on [N][3][299][299]; returns the logits [N][1000]."""
+    spec = {c[0]: c for c in INCEPTION_CONVS}
+
+    def keep(name, v):
+        if taps is not None:
+            taps[name] = v
+        return v
+
+    def cv(name, x):
+        _, _, _, _, stride, pad = spec[name]
+        return keep(name, conv2d(x, params[f"{name}.weight"], params[f"{name}.bias"], stride, pad, True, fast=fast))
+
+    x = cv("Conv2d_1a_3x3", data)
+    x = cv("Conv2d_2a_3x3", x)
+    x = cv("Conv2d_2b_3x3", x)
+    x = keep("maxpool1", pool2d(x, 3, 2, 0, "max"))
+    x = cv("Conv2d_3b_1x1", x)
+    x = cv("Conv2d_4a_3x3", x)
+    x = keep("maxpool2", pool2d(x, 3, 2, 0, "max"))
+    for p in ("Mixed_5b", "Mixed_5c", "Mixed_5d"):
+        b1 = cv(f"{p}.branch1x1", x)
+        b5 = cv(f"{p}.branch5x5_2", cv(f"{p}.branch5x5_1", x))
+        b3 = cv(f"{p}.branch3x3dbl_3", cv(f"{p}.branch3x3dbl_2", cv(f"{p}.branch3x3dbl_1", x)))
+        bp = cv(f"{p}.branch_pool", pool2d(x, 3, 1, 1, "avg_pad"))
+        x = keep(p, np.concatenate([b1, b5, b3, bp], 1))
+    p = "Mixed_6a"
+    b3 = cv(f"{p}.branch3x3", x)
+    bd = cv(f"{p}.branch3x3dbl_3", cv(f"{p}.branch3x3dbl_2", cv(f"{p}.branch3x3dbl_1", x)))
+    x = keep(p, np.concatenate([b3, bd, pool2d(x, 3, 2, 0, "max")], 1))
+    for p in ("Mixed_6b", "Mixed_6c", "Mixed_6d", "Mixed_6e"):
+        b1 = cv(f"{p}.branch1x1", x)
+        b7 = cv(f"{p}.branch7x7_3", cv(f"{p}.branch7x7_2", cv(f"{p}.branch7x7_1", x)))
+        bd = x
+        for i in range(1, 6):
+            bd = cv(f"{p}.branch7x7dbl_{i}", bd)
+        bp = cv(f"{p}.branch_pool", pool2d(x, 3, 1, 1, "avg_pad"))
+        x = keep(p, np.concatenate([b1, b7, bd, bp], 1))
+    p = "Mixed_7a"
+    b3 = cv(f"{p}.branch3x3_2", cv(f"{p}.branch3x3_1", x))
+    b7 = x
+    for i in range(1, 5):
+        b7 = cv(f"{p}.branch7x7x3_{i}", b7)
+    x = keep(p, np.concatenate([b3, b7, pool2d(x, 3, 2, 0, "max")], 1))
+    for p in ("Mixed_7b", "Mixed_7c"):
+        b1 = cv(f"{p}.branch1x1", x)
+        t = cv(f"{p}.branch3x3_1", x)
+        b3 = np.concatenate([cv(f"{p}.branch3x3_2a", t), cv(f"{p}.branch3x3_2b", t)], 1)
+        t = cv(f"{p}.branch3x3dbl_2", cv(f"{p}.branch3x3dbl_1", x))
+        bd = np.concatenate([cv(f"{p}.branch3x3dbl_3a", t), cv(f"{p}.branch3x3dbl_3b", t)], 1)
+        bp = cv(f"{p}.branch_pool", pool2d(x, 3, 1, 1, "avg_pad"))
+        x = keep(p, np.concatenate([b1, b3, bd, bp], 1))
+    x = keep("avgpool", pool2d(x, x.shape[2], 1, 0, "avg"))
+    x = conv2d(x, params["fc.weight"].reshape(-1, 2048, 1, 1), params["fc.bias"], 1, 0, False, fast=fast)
+    return keep("heads", x.reshape(x.shape[0], -1))
 
 
 def forward(model, params, data, **kw):

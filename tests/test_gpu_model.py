@@ -642,3 +642,78 @@ def test_distilbert_matches_oracle(gpx, oracle, model, batch, seq, layers, heads
         assert _rel(ex.model.get(name).reshape(ref.shape), ref) <= RTOL_FP32, f"{model} node {name}"
     assert _rel(got, want) <= RTOL_FP32
     ex.clear()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_inception_v3_matches_oracle_layer_by_layer(gpx, oracle, batch):
+    """Inception-v3 on 3x299x299 inputs (scripts/compile/compile.py:27-36): one-sided and unpadded
+    filters on the CUDA-core kernel, 1x1 and padded 3x3 filters on the tensor cores, concatenation
+    by placement, padding-counting average pools; every convolution, pool and concatenation against
+    the float64 oracle with the fp32 bound."""
+    ex = gpx.BaseExecutor()
+    ex.init("inception_v3", batch=batch, seed=1)
+    threads = {ex.model.get_kernel_info(i)["launch_params"][3] for i in range(ex.get_kernel_num())}
+    assert max(threads) > 256, "no tensor-core kernel was selected"
+    data = gpx.synth_normal(batch * 3 * 299 * 299, 0, 0).reshape(batch, 3, 299, 299)
+    ex.set_input("data", data)
+    ex.execute()
+    assert ex.error() == (0, 0)
+    heads = ex.get_output("heads")
+    taps = {}
+    want = oracle.forward("inception_v3", ex.model.params(), data, taps=taps)
+    assert heads.shape == want.shape == (batch, 1000)
+    for name, ref in taps.items():
+        got = ex.model.get(name).reshape(ref.shape)
+        assert _rel(got, ref) <= RTOL_FP32, f"inception_v3 b{batch} node {name}: {_rel(got, ref):.2e}"
+    assert _rel(heads, want) <= RTOL_FP32
+    ex.clear()
+
+
+def test_inception_v3_bfloat16_and_preempt_resume(gpx, oracle):
+    base = gpx.BaseExecutor()
+    base.init("inception", batch=4, seed=1, dtype="bfloat16")   # the name the reference's configs use
+    data = gpx.synth_normal(4 * 3 * 299 * 299, 0, 0).reshape(4, 3, 299, 299)
+    base.set_input("data", data)
+    base.execute()
+    want = base.get_output("heads")
+    ref = oracle.forward("inception_v3", base.model.params(), data[:1])
+    assert _rel(want[:1], ref) <= RTOL_16BIT
+    word = gpx.PreemptWord(1)
+    ex = gpx.BLPExecutor()
+    ex.init("inception_v3", batch=4, dtype="bfloat16")
+    for k, v in base.model.params().items():
+        ex.model.set(k, v)
+    ex.set_word(word)
+    ex.set_input("data", data)
+    s = gpx.Stream(1)
+    t0 = time.perf_counter()
+    ex.execute(s)
+    s.sync()
+    run_us = (time.perf_counter() - t0) * 1e6
+    rng = np.random.default_rng(8)
+    stops = 0
+    for trial in range(5):
+        word.clear()
+        time.sleep(0.001)
+        ex.execute(s)
+        rounds = 0
+        while True:
+            if rounds < 4:
+                delay = float(rng.uniform(0, run_us / 2))
+                t0 = time.perf_counter()
+                while (time.perf_counter() - t0) * 1e6 < delay:
+                    pass
+                word.raise_()
+            s.sync()
+            word.clear()
+            time.sleep(0.0005)
+            stop = ex.resume(s)
+            rounds += 1
+            if stop == -1:
+                break
+            stops += 1
+            assert rounds < 60
+        s.sync()
+        assert np.array_equal(ex.get_output("heads"), want), f"trial {trial}"
+    assert stops > 0
+    base.clear(), ex.clear(), word.destroy(), s.destroy()

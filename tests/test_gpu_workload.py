@@ -153,7 +153,7 @@ def test_periodic_load_counts_dropped_arrivals_when_it_cannot_keep_up(gpx):
     rep = json.loads(gpx.run_workload("baseclient", json.dumps(fast)))
     t = rep["tasks"][0]
     assert t["droppedArrivals"] > t["requests"] > 50
-    assert 0.9 * 10000 <= t["requests"] + t["droppedArrivals"] <= 10001
+    assert 0.9 * 10000 <= t["requests"] + t["droppedArrivals"] <= 10100
 
 
 def test_load_coordinator_staggers_equal_frequency_periodic_loads(gpx):
@@ -286,3 +286,30 @@ def test_schedule_order_across_tenants_from_device_timestamps(gpx):
                 assert e[3] == 0, "a best-effort request did not run every tile exactly once"
                 be_done += 1
     assert hp_checked > 100 and stops > 20 and be_done > 20 and be_starts_checked > 20
+
+
+def test_reference_model_names_and_client_keys_run_unchanged(gpx):
+    """A task list written the way the reference's own configurations are (config/A.json,
+    config/C.json: model names vgg / resnet152 / densenet / inception / bert, batch 1, the
+    tfs_grpc_addr / triton_grpc_addr keys no client reads, periodic loads that carry their own
+    priority key): every task is served under the GP policy."""
+    def client(name, model, prio):
+        return {"name": name, "model_name": model, "priority": prio, "batch_size": 1,
+                "tfs_grpc_addr": "localhost:8500", "triton_grpc_addr": "localhost:8001",
+                "use_cuda_graph": True, "preprocess_time": 200}
+
+    tasks = []
+    for model in ("vgg", "resnet152", "densenet", "inception", "bert"):
+        tasks.append({"id": model + "_rt", "load": {"type": "periodic", "priority": 0, "frequency": 20},
+                      "client": client(model + "_rt", model, 0)})
+    tasks.append({"id": "resnet152_be", "load": {"type": "periodic", "priority": 0, "frequency": 100},
+                  "client": client("resnet152_be", "resnet152", 1)})
+    cfg = {"time": 1.5, "warmup": 2, "standalone": 2, "tasks": tasks}
+    rep = json.loads(gpx.run_workload("gpreemptclient", json.dumps(cfg)))
+    t = {x["id"]: x for x in rep["tasks"]}
+    assert set(t) == {x["id"] for x in tasks}
+    for x in t.values():
+        assert x["requests"] > 0 and x["avgPreprocessLatency(us)"] >= 200, x["id"]
+    # equal-frequency periodic latency-critical loads are staggered (builtinLoadCoordinator)
+    delays = sorted(t[m + "_rt"]["launchDelay(us)"] for m in ("vgg", "resnet152", "densenet", "inception", "bert"))
+    assert delays[0] == 0 and delays[1] > 0

@@ -318,3 +318,40 @@ def test_distilbert_restatement_matches_huggingface_distilbert(oracle):
     got = oracle.distilbert_forward(params, ids, layers=2, heads=4)
     assert got.shape == ref.shape
     assert _rel(got, ref) < 2e-6
+
+
+def test_inception_v3_restatement_matches_torchvision_topology(oracle):
+    """The oracle's Inception-v3 (one-sided 1x7 / 7x1 / 1x3 / 3x1 kernels, unpadded stride-2
+    convolutions, average pooling that counts the padding, four- and six-way concatenations)
+    against torchvision.models.inception_v3 with every batch norm replaced by the folded bias."""
+    import torchvision
+
+    rng = np.random.default_rng(8)
+    params = {}
+    for name, shape in oracle.inception_v3_param_shapes().items():
+        if name.endswith("weight"):
+            fan_in = int(np.prod(shape[1:]))
+            params[name] = (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        else:
+            params[name] = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    net = torchvision.models.inception_v3(weights=None, aux_logits=False, transform_input=False,
+                                          init_weights=False).double().eval()
+    seen = 0
+    for name, _, cout, _, _, _ in oracle.INCEPTION_CONVS:
+        block = net.get_submodule(name)          # a BasicConv2d: conv + bn (+ relu in forward)
+        assert tuple(block.conv.weight.shape) == params[name + ".weight"].shape, name
+        block.conv.weight.data = torch.from_numpy(params[name + ".weight"]).double()
+        block.bn = _Bias(torch.from_numpy(params[name + ".bias"]).double())
+        seen += 1
+    assert seen == sum(1 for m in net.modules() if isinstance(m, torch.nn.Conv2d))
+    net.fc.weight.data = torch.from_numpy(params["fc.weight"].reshape(1000, 2048)).double()
+    net.fc.bias.data = torch.from_numpy(params["fc.bias"]).double()
+    data = rng.standard_normal((1, 3, 299, 299)).astype(np.float32)
+    with torch.no_grad():
+        ref = net(torch.from_numpy(data).double()).numpy()
+    taps = {}
+    got = oracle.forward("inception_v3", params, data, taps=taps)
+    assert got.shape == (1, 1000)
+    assert taps["Mixed_5d"].shape == (1, 288, 35, 35) and taps["Mixed_6e"].shape == (1, 768, 17, 17)
+    assert taps["Mixed_7c"].shape == (1, 2048, 8, 8)
+    assert _rel(got, ref) < 5e-6
