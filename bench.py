@@ -383,7 +383,7 @@ def main() -> None:
             r = api.preempt_microbench(kind, size, args.triggers, seed=5)
             microbench[kind] = {k: r[k] for k in ("triggers", "preempted", "mismatches", "kernel_ms",
                                                   "drain_us_p50", "drain_us_p99", "drain_us_max",
-                                                  "seen_us_p50", "raise_call_us_max",
+                                                  "seen_us_p50", "late_starts", "raise_call_us_max",
                                                   "drain_after_return_us_max")}
         tflops = roof["conv_flops_per_step"] / (roof["conv_ms_per_step"] * 1e-3) / 1e12
         peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])

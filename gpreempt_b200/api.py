@@ -366,6 +366,13 @@ class Model:
         """Writes mod.json, host.json and mod.params into `path`; Model(path) loads them back."""
         check(B.load().gpx_model_export_dir(self.handle, path.encode()))
 
+    def reductions(self) -> tuple[float, float]:
+        """Domain mass and total energy of a miniweather model's state
+        (reductions, src/workloads/miniweather.cu:650-677)."""
+        mass, te = ctypes.c_double(), ctypes.c_double()
+        check(B.load().gpx_model_reductions(self.handle, ctypes.byref(mass), ctypes.byref(te)))
+        return mass.value, te.value
+
     def clear(self) -> None:
         if self.handle:
             B.load().gpx_model_close(self.handle)

@@ -41,7 +41,7 @@ class MicrobenchSummary(ctypes.Structure):
         ("seen_us_p50", ctypes.c_double), ("seen_us_p99", ctypes.c_double),
         ("clock_uncertainty_ns", ctypes.c_double),
         ("raise_call_us_p50", ctypes.c_double), ("raise_call_us_max", ctypes.c_double),
-        ("drain_after_return_us_max", ctypes.c_double),
+        ("drain_after_return_us_max", ctypes.c_double), ("late_starts", ctypes.c_int),
     ]
 
 
@@ -125,6 +125,7 @@ _SIGS = {
                               P(ctypes.c_double), P(ctypes.c_double)],
     "gpx_model_export_json": [vp, ctypes.c_char_p, sz, P(sz)],
     "gpx_model_export_dir": [vp, ctypes.c_char_p],
+    "gpx_model_reductions": [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)],
     "gpx_exec_create": [vp, ci, P(vp)],
     "gpx_exec_destroy": [vp],
     "gpx_exec_set_word": [vp, vp],

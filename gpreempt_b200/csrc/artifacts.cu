@@ -46,6 +46,7 @@ static const char *kernel_type_name(KernelType t) {
         case KernelType::DwConv: return "dwconv_kernel";
         case KernelType::AttentionTc: return "attention_tc_kernel";
         case KernelType::TransposeV: return "transpose_v_kernel";
+        case KernelType::Stencil: return "miniweather_step_kernel";
     }
     return "kernel";
 }
@@ -466,6 +467,7 @@ extern "C" {
 
 int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
     GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    GPX_REQUIRE(!m->sci, GPX_NOT_FOUND, "model '%s' has no graph to export", m->name.c_str());
     Json graph, host;
     render_graph(m, &graph, &host);
     std::string text = graph.dump(1);
@@ -477,6 +479,7 @@ int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed) {
 
 int gpx_model_export_dir(gpx_model *m, const char *dir) {
     GPX_REQUIRE(m && dir, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(!m->sci, GPX_NOT_FOUND, "model '%s' has no graph to export", m->name.c_str());
     if (::mkdir(dir, 0777) != 0 && errno != EEXIST) {
         set_error("cannot create %s", dir);
         return GPX_FAIL;

@@ -12,6 +12,13 @@
 // that transpose_v_kernel prepares; the per-block result is folded into fp32 registers.
 // Thread 0 issues TMA and MMA; every wait is bounded and its outcome is shared through a block
 // barrier, so all threads leave together when one gives up.
+//
+// A tile of 128 queries x 512 keys takes ~27 us, above the 20 us drain target, so the preempt word
+// is also polled once per block of 128 keys.  A CTA that sees it raised gives the tile up: nothing
+// has been written yet, the tile number goes into the CTA's slot, and the relaunched CTA computes
+// that tile from its first key block before it claims new ones (the reset-and-restart treatment of
+// REEF, src/reef-client/reef_scheduler.cpp:316-357, at tile granularity: at most one tile of work
+// per CTA is repeated, and the result is the same bits either way).
 #include "layers.cuh"
 #include "sm100.cuh"
 
@@ -31,6 +38,7 @@ struct FaControl {
     uint32_t tmem_base;
     int tile;
     int abort_flag;
+    int stop;  // the word was seen raised: leave at this key-block boundary
 };
 
 // 2^x, the hardware approximation (relative error ~2^-22; -inf gives 0).
@@ -92,9 +100,33 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
     const float scale_log2 = p.scale * 1.4426950408889634f;  // scores are exponentiated base 2
     uint32_t ph_q = 0, ph_k = 0, ph_v = 0, ph_m = 0;
     int iter = 0;
+    int tiles_done = 0;
     bool dead = false;
+    const bool resumable = blp.preempted != nullptr && p.slots != nullptr;
+    CgemmSlot *slot = resumable ? p.slots + blockIdx.x : nullptr;
+    // The tile this CTA gave up in the previous launch, if any (thread 0 only).
+    int pending = (resumable && tid == 0) ? slot->next_iter - 1 : -1;
     for (; !dead; ++iter) {
-        if (tid == 0) ctl->tile = blp_claim(blp, iter);
+        if (tid == 0) {
+            int t;
+            if (pending >= 0) {
+                // An interrupted tile comes first; a kernel relaunched while the word is still up
+                // keeps it for the next launch and reports itself as the stop point.
+                if (load_word(blp.preempted) != 0) {
+                    atomicCAS(blp.stop_index, -1, blp.kernel_id);
+                    if (blp.trace) atomicMin(blp.trace + 2, globaltimer_ns());
+                    t = -1;
+                } else {
+                    t = pending;
+                    pending = -1;
+                    slot->next_iter = 0;
+                }
+            } else {
+                t = blp_claim(blp, iter);
+            }
+            ctl->tile = t;
+            ctl->stop = 0;
+        }
         __syncthreads();
         const int tile = ctl->tile;
         if (tile < 0) break;
@@ -119,7 +151,12 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
         for (int d = 0; d < kFaD; ++d) o[d] = 0.f;
         leader_wait(&ctl->bar_q, ph_q, 401);
         ph_q ^= 1;
+        bool stopped = false;
         for (int kb = 0; kb < nkb; ++kb) {
+            // The word is read at the top of every key block; its value is needed only after the
+            // first product of the block, so the load's latency is hidden.
+            int word_now = 0;
+            if (resumable && tid == 0 && kb > 0) word_now = load_word(blp.preempted);
             // ---- S = Q K^T
             leader_wait(&ctl->bar_k, ph_k, 402);
             ph_k ^= 1;
@@ -132,9 +169,23 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
             }
             leader_wait(&ctl->bar_mma, ph_m, 403);
             ph_m ^= 1;
+            if (tid == 0 && word_now != 0) ctl->stop = 1;
             __syncthreads();
             if (*abort_flag) {
                 dead = true;
+                break;
+            }
+            if (ctl->stop) {
+                // Give the tile up.  The value tile of this block is the only copy still in flight.
+                leader_wait(&ctl->bar_v, ph_v, 406);
+                ph_v ^= 1;
+                if (tid == 0) {
+                    slot->next_iter = tile + 1;
+                    atomicCAS(blp.stop_index, -1, blp.kernel_id);
+                    if (blp.trace) atomicMin(blp.trace + 2, globaltimer_ns());
+                }
+                __syncthreads();
+                stopped = true;
                 break;
             }
             tc_fence_after_sync();
@@ -235,7 +286,8 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
             }
             tc_fence_before_sync();  // orders these TMEM reads before the next block's products
         }
-        if (dead) break;
+        if (dead || stopped) break;
+        ++tiles_done;
         if (q0 + tid < p.S) {
             const float inv = 1.0f / l;
             uint32_t w[kFaD / 2];
@@ -252,7 +304,7 @@ attention_tc_kernel(const __grid_constant__ AttnParams p, BlpArgs blp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, kFaTmemCols);
     }
-    if (tid == 0) trace_end(blp, iter);
+    if (tid == 0) trace_end(blp, tiles_done);
 }
 
 // Vt[(b*heads + h)*64 + d][key] = V[b*S + key][h*64 + d]: the value matrix with keys contiguous, the

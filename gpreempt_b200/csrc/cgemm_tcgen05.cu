@@ -84,6 +84,18 @@ struct CgemmControl {
 
 static_assert(sizeof(CgemmControl) <= sizeof(CgemmControlSize), "control block outgrew its shared-memory budget");
 
+// x / d for 0 <= x < 2^24 and d > 0 with `inv` = 1.0f / d: the float quotient is off by at most
+// one, which the remainder corrects.  An integer division by a run-time divisor is a chain of
+// ~30 dependent instructions; the epilogue decodes its tile and its row with six of them, about a
+// microsecond per tile for a lone warp, which is what bounded the layers with one or two K blocks.
+__device__ __forceinline__ int fast_div(int x, int d, float inv) {
+    int q = (int)((float)x * inv);
+    int r = x - q * d;
+    if (r < 0) --q;
+    if (r >= d) ++q;
+    return q;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&p);
@@ -531,6 +543,13 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         int seg_k0 = first_k;
         int tiles_done = 0;
         const int img = p.in_hs * p.in_ws;
+        float bias_next = 0.f;  // this thread's bias element of the next tile to drain
+        if (p.bias && !p.partial) {
+            const int t = (int)threadIdx.x - 64;
+            const int first_tile = blockIdx.x + first_iter * gridDim.x;
+            if (t < BN && first_tile < total_tiles)
+                bias_next = __ldg(p.bias + ((first_tile / p.k_splits) % p.tiles_n) * BN + t);
+        }
         TCK(t_epi0);
 #ifdef GPX_CGEMM_TIMING
         long long e_wait = 0, e_tmem = 0, e_math = 0, e_store = 0, e_bar = 0;
@@ -539,14 +558,18 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             const int buf = (int)(seg % nbuf);
             const uint32_t t_acc = t_lane + buf * buf_cols;
             TCK(t_wait0);
-            // The bias of the tile this buffer is being filled with goes to shared memory while
-            // the tile is still accumulating: read from global memory inside the drain loop, its
-            // latency (an L2 round trip under load) was paid once per 16-column piece.
+            // The bias of the tile this buffer holds goes to shared memory before the drain loop
+            // (read from global memory inside it, its latency - an L2 round trip under load - was
+            // paid once per 16-column piece).  The value stored now was requested one tile ago
+            // and the request for the tile after this one is issued here, so the round trip
+            // overlaps the drain of this tile instead of delaying its start.
             if (p.bias && !p.partial) {
-                const int next_tile = blockIdx.x + it * gridDim.x;
                 const int t = (int)threadIdx.x - 64;
-                if (next_tile < total_tiles && t < BN)
-                    ctl->bias_s[buf][t] = __ldg(p.bias + ((next_tile / p.k_splits) % p.tiles_n) * BN + t);
+                if (t < BN) {
+                    ctl->bias_s[buf][t] = bias_next;
+                    const int after = blockIdx.x + (it + 1) * gridDim.x;
+                    if (after < total_tiles) bias_next = __ldg(p.bias + ((after / p.k_splits) % p.tiles_n) * BN + t);
+                }
             }
             if (leader) {
                 bool ok = mbar_wait(smem_u32(&ctl->tmem_full[buf]), (seg / nbuf) & 1, abort_flag, kCWaitLimitNs);
@@ -571,27 +594,40 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             }
             if (kind == CEPI_COMPLETE) {
                 const int tile = blockIdx.x + it * gridDim.x;
-                const int n_blk = (tile / p.k_splits) % p.tiles_n;
-                const int m_blk = (tile / p.k_splits) / p.tiles_n;
-                const int split = tile % p.k_splits;
+                int otile = tile, split = 0;
+                if (p.k_splits > 1) {
+                    otile = fast_div(tile, p.k_splits, p.inv_k_splits);
+                    split = tile - otile * p.k_splits;
+                }
+                const int m_blk = p.tiles_n > 1 ? fast_div(otile, p.tiles_n, p.inv_tiles_n) : otile;
+                const int n_blk = otile - m_blk * p.tiles_n;
                 // Which output pixel, if any, does this GEMM row stand for?
                 const int vrow = m_blk * kCBM + row;
                 bool valid = vrow < p.m_rows;
-                int n_img = 0, h = 0, w = 0;
-                if (valid) {
-                    n_img = vrow / img;
-                    int r = vrow - n_img * img;
-                    int hs = r / p.in_ws;
-                    int ws = r - hs * p.in_ws;
-                    h = hs - p.in_off;
-                    w = ws - p.in_off;
-                    valid = h >= 0 && h < p.out.H && w >= 0 && w < p.out.W;
-                }
                 size_t out_off = 0, res_off = 0;
-                if (valid) {
-                    out_off = p.out_f32 ? ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid
-                                        : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
-                    if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
+                if (p.identity_rows) {
+                    // plain rows in, plain rows out (and a plain residual): row m of the GEMM is
+                    // row m of the output, no pixel arithmetic is needed
+                    if (valid) {
+                        out_off = (size_t)vrow * p.out.C + (size_t)n_blk * BN;
+                        if (p.res_hi) res_off = (size_t)vrow * p.res.C + (size_t)n_blk * BN;
+                    }
+                } else {
+                    int n_img = 0, h = 0, w = 0;
+                    if (valid) {
+                        n_img = fast_div(vrow, img, p.inv_img);
+                        int r = vrow - n_img * img;
+                        int hs = fast_div(r, p.in_ws, p.inv_in_ws);
+                        int ws = r - hs * p.in_ws;
+                        h = hs - p.in_off;
+                        w = ws - p.in_off;
+                        valid = h >= 0 && h < p.out.H && w >= 0 && w < p.out.W;
+                    }
+                    if (valid) {
+                        out_off = p.out_f32 ? ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid
+                                            : (size_t)layout_row(p.out, n_img, h, w) * p.out.C + (size_t)n_blk * BN;
+                        if (p.res_hi) res_off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + (size_t)n_blk * BN;
+                    }
                 }
                 // Every lane owns one row of the tile (its TMEM lane): 16 columns of a plane are 32
                 // contiguous bytes of that row, one 256-bit access, a whole sector.

@@ -54,11 +54,14 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
     } else if (k.type == KernelType::AttentionTc) {
         AttnParams p = k.attn;
         p.error = e->d_error;
+        p.slots = e->kind == GPX_EXEC_BLP ? e->d_slots + idx * kSlotsPerKernel : nullptr;
         err = attention_tc_launch(p, k.grid, b, s);
     } else if (k.type == KernelType::TransposeV) {
         err = transpose_v_launch(k.attn, k.grid, b, s);
     } else if (k.type == KernelType::Im2col) {
         err = im2col_launch(k.im2col, k.grid, b, s);
+    } else if (k.type == KernelType::Stencil) {
+        err = stencil_launch(k.stencil, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {
         err = conv_launch(k.conv, k.tile, k.grid, b, s);
     } else {

@@ -27,7 +27,7 @@ struct gpx_exec {
 };
 
 namespace gpx {
-constexpr size_t kSlotsPerKernel = 256;
+constexpr size_t kSlotsPerKernel = 320;  // >= the largest grid that keeps per-CTA state (2 CTAs per SM of attention)
 BlpArgs exec_blp_args(gpx_exec *e, size_t idx);
 int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s);
 // Re-arms cursors, progress slots and trace for a run from kernel 0 (what execute does first).

@@ -42,6 +42,10 @@ struct CgemmParams {
     int in_hs, in_ws;        // stored image dims of the input (decode of a GEMM row)
     int in_off;              // 1 when the input rows include a zero border, else 0
     int tiles_m, tiles_n;
+    // Reciprocals of the divisors the epilogue decodes a tile and a row with (fast_div), and whether
+    // GEMM row m is output row m (plain rows on both sides: no decode at all).
+    float inv_k_splits, inv_tiles_n, inv_img, inv_in_ws;
+    int identity_rows;
     int relu;
     const float *bias;       // [Cout] or null
     const bf16_bits *res_hi, *res_lo;  // residual planes or null
@@ -185,6 +189,9 @@ struct AttnParams {
     CUtensorMap tq, tk, tvt;
     bf16_bits *vt;
     int *error;
+    // One slot per CTA (this executor's): next_iter holds, plus one, the tile the CTA gave up when
+    // the word went up inside it; the relaunched CTA recomputes that tile before it claims new ones.
+    CgemmSlot *slots;
 };
 cudaError_t attention_launch(const AttnParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 cudaError_t attention_tc_prepare();

@@ -230,7 +230,7 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
     std::uniform_real_distribution<double> uni(0.0, 1.0);
     std::vector<double> drains, seens, raise_calls;
     double drain_after_return_max = 0;
-    int mismatches = 0, preempted = 0, resumes_total = 0;
+    int mismatches = 0, preempted = 0, resumes_total = 0, late_starts = 0;
     for (int t = 0; t < triggers; ++t) {
         GPX_TRY(prepare());
         GPX_TRY(gpx_word_clear(word));
@@ -250,7 +250,13 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
         uint64_t t_raised = now_ns();
         GPX_TRY(read());
         raise_calls.push_back((double)(t_raised - t_raise) / 1e3);
-        if (snap.stop != -1) {
+        // A launch that reached the GPU after the word was already up (a late launch on the host
+        // side: the kernel then leaves at its entry check) has nothing to drain; its "latency" would
+        // be the launch delay.  Such samples are counted, not mixed into the drain statistics.
+        const bool started_late = snap.stop != -1 && snap.trace[0] != ~0ull &&
+                                  (int64_t)snap.trace[0] + offset > (int64_t)t_raised + (int64_t)unc;
+        if (started_late) ++late_starts;
+        if (snap.stop != -1 && !started_late) {
             ++preempted;
             drain_after_return_max = std::max(
                 drain_after_return_max, ((double)((int64_t)snap.trace[1] + offset) - (double)t_raised) / 1e3);
@@ -308,6 +314,7 @@ extern "C" int gpx_preempt_microbench(int kind, size_t size, int triggers, uint6
     out->raise_call_us_p50 = pct(raise_calls, 0.5);
     out->raise_call_us_max = raise_calls.empty() ? 0 : *std::max_element(raise_calls.begin(), raise_calls.end());
     out->drain_after_return_us_max = drain_after_return_max;
+    out->late_starts = late_starts;
 
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);

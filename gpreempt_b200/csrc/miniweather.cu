@@ -1,0 +1,510 @@
+// miniWeather on the executor's kernel list: twelve preemptible semi-discrete steps per time step.
+// Follows src/workloads/miniweather.cu of the reference (initial state :395-507, time step
+// :182-200, kernels :222-372, reductions :650-677); arithmetic keeps the reference's types - the
+// horizontal flux evaluates density, winds, temperature and pressure in double, everything else
+// is float - so that results agree with it to rounding.
+#include "stencil.h"
+
+#include "model.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <thread>
+#include <vector>
+
+namespace gpx {
+
+namespace {
+
+// Physical constants of the reference (miniweather.cu:35-52), `real` = float.
+constexpr float kPi = 3.14159265358979323846264338327;
+constexpr float kGrav = 9.8;
+constexpr float kCp = 1004.;
+constexpr float kCv = 717.;
+constexpr float kRd = 287.;
+constexpr float kP0 = 1.e5;
+constexpr float kC0 = 27.5629410929725921310572974482;
+constexpr float kGamm = 1.40027894002789400278940027894;
+constexpr float kXlen = 2.e4;
+constexpr float kZlen = 1.e4;
+constexpr float kHvBeta = 0.05;
+constexpr float kCfl = 1.50;
+constexpr float kMaxSpeed = 450;
+constexpr int ID_DENS = 0, ID_UMOM = 1, ID_WMOM = 2, ID_RHOT = 3;
+
+struct Grid {
+    int nx, nz, W;     // W: row stride (nx + 4)
+    size_t plane;      // (nz + 4) * W
+};
+
+__device__ __forceinline__ Grid grid_of(const StencilParams &p) {
+    Grid g;
+    g.nx = p.nx;
+    g.nz = p.nz;
+    g.W = p.nx + 2 * kMwHalo;
+    g.plane = (size_t)(p.nz + 2 * kMwHalo) * g.W;
+    return g;
+}
+
+// Value of variable ll at array position (ka, ca) of the forcing state as the reference's flux
+// kernel would read it after set_halo_values_x (miniweather.cu:331-341): the two columns on each
+// side wrap around.  Only rows of the interior are read in this direction.
+__device__ __forceinline__ float load_x(const StencilParams &p, const Grid &g, int ll, int ka, int ca) {
+    int src = ca < kMwHalo ? ca + g.nx : (ca >= g.nx + kMwHalo ? ca - g.nx : ca);
+    return p.forcing[ll * g.plane + (size_t)ka * g.W + src];
+}
+
+// Value at (ka, ca) as read after set_halo_values_z (miniweather.cu:346-372): rows outside the
+// interior take the boundary row's value (scaled by the density ratio for the horizontal
+// momentum, zero for the vertical momentum) where the reference's launch covers them, and keep
+// what the array holds elsewhere.
+__device__ __forceinline__ float load_z(const StencilParams &p, const Grid &g, int ll, int ka, int ca) {
+    const size_t base = ll * g.plane;
+    if (ka >= kMwHalo && ka < g.nz + kMwHalo) return p.forcing[base + (size_t)ka * g.W + ca];
+    if (ll * g.W + ca >= p.halo_z_ids) return p.forcing[base + (size_t)ka * g.W + ca];
+    if (ll == ID_WMOM) return 0.f;
+    const bool low = ka < kMwHalo;
+    float v = p.forcing[base + (size_t)(low ? kMwHalo : g.nz + kMwHalo - 1) * g.W + ca];
+    if (ll == ID_UMOM) v = v * p.halo_ratio[low ? ka : ka - g.nz];
+    return v;
+}
+
+// Horizontal tile: cells [i0, i1) of row k.  compute_tendencies_x (:222-258) then
+// compute_tendencies_x_r (:260-272).
+__device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, int tile, float *sflux) {
+    const int k = tile / p.tiles_per_row;
+    const int i0 = (tile - k * p.tiles_per_row) * p.tile_x;
+    const int i1 = min(i0 + p.tile_x, g.nx);
+    const int n = i1 - i0;
+    const int ka = k + kMwHalo;
+    const int ld = kMwTileXMax + 1;
+    const float hv_coef = -kHvBeta * p.dx / (16 * p.dt);
+    const float hd = p.hy_dens_cell[ka], hdt = p.hy_dens_theta_cell[ka];
+    for (int f = threadIdx.x; f <= n; f += kMwThreads) {
+        const int i = i0 + f;  // interface between cells i-1 and i
+        float vals[kMwVars], d3_vals[kMwVars];
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) {
+            float s0 = load_x(p, g, ll, ka, i), s1 = load_x(p, g, ll, ka, i + 1);
+            float s2 = load_x(p, g, ll, ka, i + 2), s3 = load_x(p, g, ll, ka, i + 3);
+            vals[ll] = (-s0 + 7 * (s1 + s2) - s3) / 12;
+            d3_vals[ll] = (-s0 + 3 * (s1 - s2) + s3) * hv_coef;
+        }
+        double r = vals[ID_DENS] + hd;
+        double u = vals[ID_UMOM] / r;
+        double w = vals[ID_WMOM] / r;
+        double t = (vals[ID_RHOT] + hdt) / r;
+        double pr = kC0 * pow((r * t), (double)kGamm);
+        sflux[ID_DENS * ld + f] = r * u - d3_vals[ID_DENS];
+        sflux[ID_UMOM * ld + f] = r * u * u + pr - d3_vals[ID_UMOM];
+        sflux[ID_WMOM * ld + f] = r * u * w - d3_vals[ID_WMOM];
+        sflux[ID_RHOT * ld + f] = r * u * t - d3_vals[ID_RHOT];
+    }
+    // The tiles at the ends of a row store the halo columns they wrapped around for.
+    if (i0 == 0 && threadIdx.x < 2 * kMwVars) {
+        int ll = threadIdx.x >> 1, c = threadIdx.x & 1;
+        p.forcing[ll * g.plane + (size_t)ka * g.W + c] = load_x(p, g, ll, ka, c);
+    }
+    if (i1 == g.nx && threadIdx.x >= 32 && threadIdx.x < 32 + 2 * kMwVars) {
+        int ll = (threadIdx.x - 32) >> 1, c = g.nx + kMwHalo + ((threadIdx.x - 32) & 1);
+        p.forcing[ll * g.plane + (size_t)ka * g.W + c] = load_x(p, g, ll, ka, c);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * kMwVars; e += kMwThreads) {
+        const int ll = e / n, f = e - ll * n;
+        float tend = -(sflux[ll * ld + f + 1] - sflux[ll * ld + f]) / p.dx;
+        size_t inds = ll * g.plane + (size_t)ka * g.W + i0 + f + kMwHalo;
+        p.out[inds] = p.init[inds] + p.dt * tend;
+    }
+}
+
+// Vertical tile: cells [c0, c1) x [k0, k1).  compute_tendencies_z (:278-318) then
+// compute_tendencies_z_r (:320-336).
+__device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, int tile, float *sflux) {
+    const int tr = tile / p.tiles_cols;
+    const int c0 = (tile - tr * p.tiles_cols) * kMwTileZCols;
+    const int c1 = min(c0 + kMwTileZCols, g.nx);
+    const int k0 = tr * kMwTileZRows;
+    const int k1 = min(k0 + kMwTileZRows, g.nz);
+    const int nc = c1 - c0, nr = k1 - k0;
+    constexpr int ldv = (kMwTileZRows + 1) * kMwTileZCols;
+    const float hv_coef = -kHvBeta * p.dz / (16 * p.dt);
+    for (int e = threadIdx.x; e < (nr + 1) * kMwTileZCols; e += kMwThreads) {
+        const int fr = e / kMwTileZCols, fc = e - fr * kMwTileZCols;
+        if (fc >= nc) continue;
+        const int k = k0 + fr;         // interface below cell row k
+        const int ca = c0 + fc + kMwHalo;
+        float vals[kMwVars], d3_vals[kMwVars];
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) {
+            float s0 = load_z(p, g, ll, k, ca), s1 = load_z(p, g, ll, k + 1, ca);
+            float s2 = load_z(p, g, ll, k + 2, ca), s3 = load_z(p, g, ll, k + 3, ca);
+            vals[ll] = (-s0 + 7 * (s1 + s2) - s3) / 12;
+            d3_vals[ll] = (-s0 + 3 * (s1 - s2) + s3) * hv_coef;
+        }
+        float r = vals[ID_DENS] + p.hy_dens_int[k];
+        float u = vals[ID_UMOM] / r;
+        float w = vals[ID_WMOM] / r;
+        float t = (vals[ID_RHOT] + p.hy_dens_theta_int[k]) / r;
+        float pr = kC0 * powf((r * t), kGamm) - p.hy_pressure_int[k];
+        if (k == 0 || k == g.nz) {
+            w = 0;
+            d3_vals[ID_DENS] = 0;
+        }
+        sflux[ID_DENS * ldv + e] = r * w - d3_vals[ID_DENS];
+        sflux[ID_UMOM * ldv + e] = r * w * u - d3_vals[ID_UMOM];
+        sflux[ID_WMOM * ldv + e] = r * w * w + pr - d3_vals[ID_WMOM];
+        sflux[ID_RHOT * ldv + e] = r * w * t - d3_vals[ID_RHOT];
+    }
+    // Tiles on the bottom and top rows store the halo rows they derived, where the reference's
+    // halo launch covers them.
+    if (k0 == 0 || k1 == g.nz) {
+        for (int e = threadIdx.x; e < 2 * kMwVars * nc; e += kMwThreads) {
+            const int fc = e % nc, rest = e / nc;
+            const int ll = rest >> 1, h = rest & 1;
+            const int ca = c0 + fc + kMwHalo;
+            if (ll * g.W + ca >= p.halo_z_ids) continue;
+            if (k0 == 0) p.forcing[ll * g.plane + (size_t)h * g.W + ca] = load_z(p, g, ll, h, ca);
+            if (k1 == g.nz) {
+                const int ka = g.nz + kMwHalo + h;
+                p.forcing[ll * g.plane + (size_t)ka * g.W + ca] = load_z(p, g, ll, ka, ca);
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kMwVars * nr * kMwTileZCols; e += kMwThreads) {
+        const int ll = e / (nr * kMwTileZCols);
+        const int cell = e - ll * (nr * kMwTileZCols);
+        const int fr = cell / kMwTileZCols, fc = cell - fr * kMwTileZCols;
+        if (fc >= nc) continue;
+        float tend = -(sflux[ll * ldv + cell + kMwTileZCols] - sflux[ll * ldv + cell]) / p.dz;
+        const size_t at = (size_t)(k0 + fr + kMwHalo) * g.W + c0 + fc + kMwHalo;
+        if (ll == ID_WMOM) tend = tend - p.forcing[ID_DENS * g.plane + at] * kGrav;
+        const size_t inds = ll * g.plane + at;
+        p.out[inds] = p.init[inds] + p.dt * tend;
+    }
+}
+
+constexpr int kFluxFloats = kMwVars * (kMwTileZRows + 1) * kMwTileZCols;
+static_assert(kFluxFloats >= kMwVars * (kMwTileXMax + 1), "flux tile of the x direction must fit");
+
+}  // namespace
+
+__global__ void __launch_bounds__(kMwThreads)
+miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
+    pdl_enter();
+    __shared__ float sflux[kFluxFloats];
+    __shared__ int s_tile;
+    const bool dynamic = blp.preempted != nullptr;
+    if (threadIdx.x == 0) trace_begin(blp);
+    const Grid g = grid_of(p);
+    int iter = 0;
+    for (;;) {
+        int tile;
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = blp_claim(blp, iter);
+        }
+        if (tile < 0) break;
+        if (p.dir == 1)
+            tile_x(p, g, tile, sflux);
+        else
+            tile_z(p, g, tile, sflux);
+        ++iter;
+        __syncthreads();  // the flux tile and s_tile are reused
+    }
+    if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+namespace {
+
+// ---- initial state (sci_init, miniweather.cu:376-507) --------------------------------------
+
+// hydro_const_theta (:580-590): hydrostatic balance at constant potential temperature.
+void hydro_const_theta(float z, float &r, float &t) {
+    const float theta0 = 300.;
+    const float exner0 = 1.;
+    float p, exner, rt;
+    t = theta0;
+    exner = exner0 - kGrav * z / (kCp * theta0);
+    p = kP0 * std::pow(exner, (kCp / kRd));
+    rt = std::pow((p / kC0), (1. / kGamm));
+    r = rt / t;
+}
+
+// sample_ellipse_cosine (:612-622).
+float sample_ellipse_cosine(float x, float z, float amp, float x0, float z0, float xrad, float zrad) {
+    float dist = std::sqrt(((x - x0) / xrad) * ((x - x0) / xrad) + ((z - z0) / zrad) * ((z - z0) / zrad)) * kPi / 2.;
+    if (dist <= kPi / 2.) return amp * std::pow(std::cos(dist), 2.);
+    return 0.;
+}
+
+// collision (:566-575): two thermals of opposite sign on one vertical line.
+void collision(float x, float z, float &r, float &u, float &w, float &t, float &hr, float &ht) {
+    hydro_const_theta(z, hr, ht);
+    r = 0.;
+    t = 0.;
+    u = 0.;
+    w = 0.;
+    t = t + sample_ellipse_cosine(x, z, 20., kXlen / 2, 2000., 2000., 2000.);
+    t = t + sample_ellipse_cosine(x, z, -20., kXlen / 2, 8000., 2000., 2000.);
+}
+
+constexpr int kQ = 3;
+constexpr float kQPoints[kQ] = {0.112701665379258311482073460022E0, 0.500000000000000000000000000000E0,
+                                0.887298334620741688517926539980E0};
+constexpr float kQWeights[kQ] = {0.277777777777777777777777777779E0, 0.444444444444444444444444444444E0,
+                                 0.277777777777777777777777777779E0};
+
+struct HostFields {
+    std::vector<float> state, hy_dens_cell, hy_dens_theta_cell, hy_dens_int, hy_dens_theta_int, hy_pressure_int;
+};
+
+void init_rows(HostFields &h, int nx, int nz, float dx, float dz, int k_from, int k_to) {
+    const int W = nx + 2 * kMwHalo;
+    const size_t plane = (size_t)(nz + 2 * kMwHalo) * W;
+    for (int k = k_from; k < k_to; ++k)
+        for (int i = 0; i < W; ++i) {
+            float acc[kMwVars] = {0.f, 0.f, 0.f, 0.f};
+            for (int kk = 0; kk < kQ; ++kk)
+                for (int ii = 0; ii < kQ; ++ii) {
+                    float x = (0 + i - kMwHalo + 0.5) * dx + (kQPoints[ii] - 0.5) * dx;
+                    float z = (0 + k - kMwHalo + 0.5) * dz + (kQPoints[kk] - 0.5) * dz;
+                    float r, u, w, t, hr, ht;
+                    collision(x, z, r, u, w, t, hr, ht);
+                    acc[ID_DENS] = acc[ID_DENS] + r * kQWeights[ii] * kQWeights[kk];
+                    acc[ID_UMOM] = acc[ID_UMOM] + (r + hr) * u * kQWeights[ii] * kQWeights[kk];
+                    acc[ID_WMOM] = acc[ID_WMOM] + (r + hr) * w * kQWeights[ii] * kQWeights[kk];
+                    acc[ID_RHOT] = acc[ID_RHOT] + ((r + hr) * (t + ht) - hr * ht) * kQWeights[ii] * kQWeights[kk];
+                }
+            for (int ll = 0; ll < kMwVars; ++ll) h.state[ll * plane + (size_t)k * W + i] = acc[ll];
+        }
+}
+
+void init_fields(HostFields &h, int nx, int nz, float dx, float dz) {
+    const int W = nx + 2 * kMwHalo, R = nz + 2 * kMwHalo;
+    h.state.assign((size_t)kMwVars * R * W, 0.f);
+    unsigned nt = std::max(1u, std::min(16u, std::thread::hardware_concurrency()));
+    std::vector<std::thread> pool;
+    for (unsigned t = 0; t < nt; ++t) {
+        int a = (int)((long long)R * t / nt), b = (int)((long long)R * (t + 1) / nt);
+        pool.emplace_back([&h, nx, nz, dx, dz, a, b] { init_rows(h, nx, nz, dx, dz, a, b); });
+    }
+    for (auto &t : pool) t.join();
+    // Hydrostatic background over cells: every quadrature point samples the cell centre
+    // (miniweather.cu:461-475 omits the quadrature offset of z).
+    h.hy_dens_cell.assign(R, 0.f);
+    h.hy_dens_theta_cell.assign(R, 0.f);
+    for (int k = 0; k < R; ++k)
+        for (int kk = 0; kk < kQ; ++kk) {
+            float z = (0 + k - kMwHalo + 0.5) * dz;
+            float r, u, w, t, hr, ht;
+            collision(0., z, r, u, w, t, hr, ht);
+            h.hy_dens_cell[k] = h.hy_dens_cell[k] + hr * kQWeights[kk];
+            h.hy_dens_theta_cell[k] = h.hy_dens_theta_cell[k] + hr * ht * kQWeights[kk];
+        }
+    // ... and at the interfaces (:477-488).
+    h.hy_dens_int.assign(nz + 1, 0.f);
+    h.hy_dens_theta_int.assign(nz + 1, 0.f);
+    h.hy_pressure_int.assign(nz + 1, 0.f);
+    for (int k = 0; k < nz + 1; ++k) {
+        float z = (0 + k) * dz;
+        float r, u, w, t, hr, ht;
+        collision(0., z, r, u, w, t, hr, ht);
+        h.hy_dens_int[k] = hr;
+        h.hy_dens_theta_int[k] = hr * ht;
+        h.hy_pressure_int[k] = kC0 * std::pow((hr * ht), kGamm);
+    }
+}
+
+int add_field(gpx_model &m, const char *name, Storage::Kind kind, int rank, int64_t d0, int64_t d1, int64_t d2,
+              const float *host, bool hidden) {
+    Storage s;
+    s.name = name;
+    s.kind = kind;
+    s.rank = rank;
+    s.dims[0] = d0;
+    s.dims[1] = d1;
+    s.dims[2] = d2;
+    s.dims[3] = 1;
+    size_t n = (size_t)d0 * (rank > 1 ? d1 : 1) * (rank > 2 ? d2 : 1);
+    s.bytes = n * sizeof(float);
+    s.hidden = hidden;
+    GPX_CUDA(cudaMalloc((void **)&s.dptr, s.bytes));
+    GPX_CUDA(cudaMemcpy(s.dptr, host, s.bytes, cudaMemcpyHostToDevice));
+    m.add_storage(s);
+    return GPX_SUCC;
+}
+
+}  // namespace
+
+int stencil_grid(int total_tiles, int sm_count) {
+    int blocks = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, miniweather_step_kernel, kMwThreads, 0);
+    if (blocks < 1) blocks = 1;
+    long long grid = (long long)blocks * sm_count;
+    if (grid > total_tiles) grid = total_tiles;
+    return grid < 1 ? 1 : (int)grid;
+}
+
+cudaError_t stencil_launch(const StencilParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    launch_layer(miniweather_step_kernel, grid, kMwThreads, 0, s, p, blp);
+    return cudaGetLastError();
+}
+
+// "miniweather" is the reference's grid (3200 x 1600, miniweather.cu:21-22); "miniweather_tiny"
+// (320 x 160) and "miniweather_<nx>x<nz>" exist for tests.
+static bool parse_grid(const std::string &name, int &nx, int &nz) {
+    if (name == "miniweather") {
+        nx = 3200;
+        nz = 1600;
+        return true;
+    }
+    if (name == "miniweather_tiny") {
+        nx = 320;
+        nz = 160;
+        return true;
+    }
+    int a = 0, b = 0;
+    char tail = 0;
+    if (sscanf(name.c_str(), "miniweather_%dx%d%c", &a, &b, &tail) == 2) {
+        nx = a;
+        nz = b;
+        return true;
+    }
+    return false;
+}
+
+bool is_miniweather(const std::string &name) {
+    int nx, nz;
+    return parse_grid(name, nx, nz);
+}
+
+int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opts &) {
+    int nx = 0, nz = 0;
+    GPX_REQUIRE(parse_grid(name, nx, nz), GPX_NOT_FOUND, "unknown model '%s'", name.c_str());
+    GPX_REQUIRE(nx >= 8 && nz >= 8 && nx <= 32768 && nz <= 32768 && (long long)nx * nz <= (1ll << 27), GPX_OUT_OF_RANGE,
+                "%s: grid %d x %d is outside 8..32768 per side and 2^27 cells", name.c_str(), nx, nz);
+    const DeviceInfo &d = device_info();
+    GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
+    m.device = d.device;
+    m.sm_count = d.sm_count;
+    m.sci = true;
+    m.sci_nx = nx;
+    m.sci_nz = nz;
+    const float dx = kXlen / nx, dz = kZlen / nz;
+    const float dt = std::min(dx, dz) / kMaxSpeed * kCfl;
+    m.sci_dt = dt;
+    m.sci_dx = dx;
+    m.sci_dz = dz;
+
+    HostFields h;
+    init_fields(h, nx, nz, dx, dz);
+    const int W = nx + 2 * kMwHalo, R = nz + 2 * kMwHalo;
+    // state, state_tmp as the reference names them (:142-143); state_tmp2 receives the second
+    // Runge-Kutta stage.  All three start from the initial state, halo cells included.
+    GPX_TRY(add_field(m, "state", Storage::Table, 3, kMwVars, R, W, h.state.data(), false));
+    GPX_TRY(add_field(m, "state_tmp", Storage::Table, 3, kMwVars, R, W, h.state.data(), false));
+    GPX_TRY(add_field(m, "state_tmp2", Storage::Table, 3, kMwVars, R, W, h.state.data(), true));
+    GPX_TRY(add_field(m, "hy_dens_cell", Storage::Vec, 1, R, 1, 1, h.hy_dens_cell.data(), false));
+    GPX_TRY(add_field(m, "hy_dens_theta_cell", Storage::Vec, 1, R, 1, 1, h.hy_dens_theta_cell.data(), false));
+    GPX_TRY(add_field(m, "hy_dens_int", Storage::Vec, 1, nz + 1, 1, 1, h.hy_dens_int.data(), false));
+    GPX_TRY(add_field(m, "hy_dens_theta_int", Storage::Vec, 1, nz + 1, 1, 1, h.hy_dens_theta_int.data(), false));
+    GPX_TRY(add_field(m, "hy_pressure_int", Storage::Vec, 1, nz + 1, 1, 1, h.hy_pressure_int.data(), false));
+    m.sci_hy_dens_cell = h.hy_dens_cell;
+    m.sci_hy_dens_theta_cell = h.hy_dens_theta_cell;
+    m.sci_initial = std::move(h.state);
+
+    StencilParams base{};
+    base.hy_dens_cell = m.storages[m.find("hy_dens_cell")].dptr;
+    base.hy_dens_theta_cell = m.storages[m.find("hy_dens_theta_cell")].dptr;
+    base.hy_dens_int = m.storages[m.find("hy_dens_int")].dptr;
+    base.hy_dens_theta_int = m.storages[m.find("hy_dens_theta_int")].dptr;
+    base.hy_pressure_int = m.storages[m.find("hy_pressure_int")].dptr;
+    // hy_dens_cell_const (:501-506)
+    base.halo_ratio[0] = h.hy_dens_cell[0] / h.hy_dens_cell[kMwHalo];
+    base.halo_ratio[1] = h.hy_dens_cell[1] / h.hy_dens_cell[kMwHalo];
+    base.halo_ratio[2] = h.hy_dens_cell[nz + kMwHalo] / h.hy_dens_cell[nz + kMwHalo - 1];
+    base.halo_ratio[3] = h.hy_dens_cell[nz + kMwHalo + 1] / h.hy_dens_cell[nz + kMwHalo - 1];
+    base.dx = dx;
+    base.dz = dz;
+    base.nx = nx;
+    base.nz = nz;
+    const int row_tiles = (nx + kMwTileXMax - 1) / kMwTileXMax;
+    base.tile_x = ((nx + row_tiles - 1) / row_tiles + 31) / 32 * 32;
+    base.tiles_per_row = (nx + base.tile_x - 1) / base.tile_x;
+    base.tiles_cols = (nx + kMwTileZCols - 1) / kMwTileZCols;
+    const char *cover = getenv("GPX_MINIWEATHER_FULL_HALO");
+    base.halo_z_ids = (cover && cover[0] == '1') ? W * kMwVars
+                                                 : (nx + 2 * kMwHalo * kMwVars + 255) / 256 * 256;
+
+    float *state = m.storages[m.find("state")].dptr;
+    float *tmp = m.storages[m.find("state_tmp")].dptr;
+    float *tmp2 = m.storages[m.find("state_tmp2")].dptr;
+    // perform_timestep (:182-200): x, z, z, x, each a three-stage Runge-Kutta sweep.
+    const int dirs[4] = {1, 2, 2, 1};
+    for (int sweep = 0; sweep < 4; ++sweep)
+        for (int stage = 0; stage < 3; ++stage) {
+            Kernel k;
+            k.type = KernelType::Stencil;
+            k.name = std::string("miniweather_step_kernel.") + (dirs[sweep] == 1 ? "x" : "z") + std::to_string(sweep) +
+                     ".rk" + std::to_string(stage + 1);
+            StencilParams p = base;
+            p.dir = dirs[sweep];
+            p.init = state;
+            p.forcing = stage == 0 ? state : (stage == 1 ? tmp : tmp2);
+            p.out = stage == 0 ? tmp : (stage == 1 ? tmp2 : state);
+            p.dt = stage == 0 ? dt / 3 : (stage == 1 ? dt / 2 : dt / 1);
+            k.stencil = p;
+            k.threads = kMwThreads;
+            k.total_tiles = p.dir == 1 ? nz * p.tiles_per_row
+                                       : p.tiles_cols * ((nz + kMwTileZRows - 1) / kMwTileZRows);
+            k.grid = stencil_grid(k.total_tiles, m.sm_count);
+            const double cells = (double)nx * nz;
+            k.bytes = cells * kMwVars * 4.0 * 3.0;  // forcing and init read, out written
+            k.flops = cells * (p.dir == 1 ? 120.0 : 100.0);
+            m.kernels.push_back(k);
+        }
+    return GPX_SUCC;
+}
+
+}  // namespace gpx
+
+extern "C" {
+
+// reductions (miniweather.cu:650-677): domain mass and total energy in double from the float state.
+int gpx_model_reductions(gpx_model *m, double *mass, double *te) {
+    using namespace gpx;
+    GPX_REQUIRE(m && mass && te, GPX_FAIL, "NULL argument");
+    GPX_REQUIRE(m->sci, GPX_NOT_FOUND, "model '%s' has no reductions (miniweather only)", m->name.c_str());
+    const int nx = m->sci_nx, nz = m->sci_nz, W = nx + 2 * kMwHalo;
+    const size_t plane = (size_t)(nz + 2 * kMwHalo) * W;
+    std::vector<float> st(plane * kMwVars);
+    GPX_CUDA(cudaMemcpy(st.data(), m->storages[m->find("state")].dptr, st.size() * sizeof(float),
+                        cudaMemcpyDeviceToHost));
+    double ms = 0, en = 0;
+    const float dx = m->sci_dx, dz = m->sci_dz;
+    for (int k = 0; k < nz; ++k)
+        for (int i = 0; i < nx; ++i) {
+            size_t at = (size_t)(k + kMwHalo) * W + i + kMwHalo;
+            double r = st[ID_DENS * plane + at] + m->sci_hy_dens_cell[kMwHalo + k];
+            double u = st[ID_UMOM * plane + at] / r;
+            double w = st[ID_WMOM * plane + at] / r;
+            double th = (st[ID_RHOT * plane + at] + m->sci_hy_dens_theta_cell[kMwHalo + k]) / r;
+            double p = kC0 * pow(r * th, kGamm);
+            double t = th / pow(kP0 / p, kRd / kCp);
+            double ke = r * (u * u + w * w);
+            double ie = r * kCv * t;
+            ms += r * dx * dz;
+            en += (ke + ie) * dx * dz;
+        }
+    *mass = ms;
+    *te = en;
+    return GPX_SUCC;
+}
+
+}  // extern "C"

@@ -344,6 +344,11 @@ static void build_distilbert(gpx_model &m, int batch, int seq, int layers, int h
 int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_opts &opts) {
     int batch = opts.batch > 0 ? opts.batch : 1;
     m.batch = batch;
+    if (is_miniweather(name)) {
+        // The scientific workload (Executor::init, src/executor.cpp:35-38): no graph, no parameters.
+        m.name = name;
+        return build_miniweather(m, name, opts);
+    }
     // Storage and tensor-core operand format between layers; inputs, outputs, parameters and all
     // arithmetic outside the tensor-core products stay fp32.
     m.fmt = PF_SPLIT;
@@ -1061,6 +1066,20 @@ int finalize_model(gpx_model &m) {
                 p.res_hi = p.res_lo = nullptr;
             }
         }
+        p.inv_k_splits = 1.0f / (float)p.k_splits;
+        p.inv_tiles_n = 1.0f / (float)p.tiles_n;
+        p.inv_img = 1.0f / (float)(p.in_hs * p.in_ws);
+        p.inv_in_ws = 1.0f / (float)p.in_ws;
+        // (the float quotient of fast_div is exact to within one below 2^24)
+        GPX_REQUIRE((long long)p.tiles_m * 128 < (1 << 24) && (long long)out_tiles * p.k_splits < (1 << 24), GPX_OUT_OF_RANGE,
+                    "%s: %d rows exceed what the tensor-core kernel indexes", n.name.c_str(), p.m_rows);
+        {
+            const Storage *res_st = n.residual >= 0 ? &m.storages[m.nodes[n.residual].storage] : nullptr;
+            const bool res_plain = !res_st || (res_st->layout.order == ACT_PLAIN && res_st->layout.rows == il.rows);
+            p.identity_rows = (!head && il.order == ACT_PLAIN && out.layout.order == ACT_PLAIN &&
+                               out.layout.rows == il.rows && p.in_off == 0 && res_plain && !(full_map_dense(n, src) && !n.via_im2col))
+                                  ? 1 : 0;
+        }
         kn.total_tiles = out_tiles * p.k_splits;
         kn.grid = std::min(kn.total_tiles, m.sm_count);
         m.max_cgemm_grid = std::max(m.max_cgemm_grid, kn.grid);
@@ -1303,7 +1322,7 @@ int gpx_model_open(const char *name, const gpx_model_opts *opts, gpx_model **out
         if (nm == "resnet") nm = "resnet152";
         GPX_TRY(build_builtin_graph(*m, nm, o));
     }
-    int st = finalize_model(*m);
+    int st = m->sci ? GPX_SUCC : finalize_model(*m);
     if (st == GPX_SUCC && from_dir) st = check_host_json(*m, nm);
     if (st == GPX_SUCC && from_dir) {
         // Parameters travel with the directory (Executor::load_param, src/executor.cpp:115-117).
@@ -1408,6 +1427,13 @@ int gpx_model_shape(gpx_model *m, const char *name, int64_t dims[4], int *rank) 
 
 int gpx_model_init_random(gpx_model *m, uint64_t seed) {
     GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    if (m->sci) {
+        // No parameters: the call puts the simulation back to its initial state.
+        for (const char *name : {"state", "state_tmp", "state_tmp2"})
+            GPX_CUDA(cudaMemcpy(m->storages[m->find(name)].dptr, m->sci_initial.data(),
+                                m->sci_initial.size() * sizeof(float), cudaMemcpyHostToDevice));
+        return GPX_SUCC;
+    }
     std::vector<float> tmp;
     uint64_t stream = 0;
     for (auto &s : m->storages) {

@@ -6,6 +6,7 @@
 
 #include "common.h"
 #include "layers.cuh"
+#include "stencil.h"
 
 #include <string>
 #include <unordered_map>
@@ -78,7 +79,7 @@ struct Node {
     int scale = -1, shift = -1;    // Affine, or a pooling node that normalises its input: Vec storages
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV, Stencil };
 
 struct Kernel {
     std::string name;
@@ -92,6 +93,7 @@ struct Kernel {
     LayerNormParams ln{};
     AttnParams attn{};
     DwConvParams dw{};
+    StencilParams stencil{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     int grid = 1;
     int threads = 256;
@@ -120,6 +122,12 @@ struct gpx_model {
     std::vector<void *> scratch;         // device buffers owned by the model besides the storages
     gpx::bf16_bits *identity = nullptr;  // 128 x 128 identity matrix in the plane format
     int fmt = 0;                    // PlaneFmt of activations and tensor-core weights (dtype option)
+    // miniWeather (stencil.h): no graph nodes, no "data"/"heads"; one execute is one time step.
+    bool sci = false;
+    int sci_nx = 0, sci_nz = 0;
+    float sci_dt = 0.f, sci_dx = 0.f, sci_dz = 0.f;
+    std::vector<float> sci_hy_dens_cell, sci_hy_dens_theta_cell;  // host copies for the reductions
+    std::vector<float> sci_initial;                               // initial state, to start over
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;

@@ -813,7 +813,7 @@ struct Suite {
         }
         t->state.store(ST_IDLE, std::memory_order_release);
         uint64_t t4 = now_ns();
-        if (!resident) {
+        if (!resident && t->out_bytes) {
             int head = t->model->nodes[t->model->head_node].storage;
             GPX_CUDA(cudaMemcpyAsync(t->h_out, t->model->storages[head].dptr, t->out_bytes,
                                      cudaMemcpyDeviceToHost, t->stream));
@@ -981,6 +981,13 @@ static int init_tenant(Suite &s, Tenant *t) {
     for (auto &ev : t->seg_ev) GPX_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     GPX_CUDA(cudaEventCreate(&t->ev_first));
     GPX_CUDA(cudaEventCreate(&t->ev_last));
+    if (t->model->sci) {
+        // The scientific workload has no request data (Executor::set_input / get_output do nothing
+        // for it, src/executor.cpp:47-75): a request is one time step of the resident state.
+        t->in_bytes = t->out_bytes = 0;
+        if (t->use_graph) GPX_TRY(gpx_exec_capture_graph(t->exec, t->stream));
+        return GPX_SUCC;
+    }
     const Storage &in = t->model->storages[0];
     const Storage &out = t->model->storages[t->model->nodes[t->model->head_node].storage];
     t->in_bytes = in.bytes;

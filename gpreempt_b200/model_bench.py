@@ -38,14 +38,21 @@ def parse_specs(text: str) -> list[tuple[str, int, str, int]]:
     return out
 
 
+def synthetic_input(ex) -> np.ndarray:
+    """Seeded input of the shape and type the model's `data` tensor has: N(0,1) images, or token
+    ids uniform over the rows of the word-embedding table."""
+    shape = ex.model.shape("data")
+    info = ex.model.get_storage_info(ex.model.find_storage_idx("data"))
+    if info["stype"] == "int64":
+        vocab = ex.model.shape("embeddings.word_embeddings.weight")[0]
+        return np.random.default_rng(6).integers(0, vocab, shape).astype(np.int64)
+    return api.synth_normal(int(np.prod(shape)), 0, 0).reshape(shape)
+
+
 def run(model: str, batch: int, dtype: str, seq_len: int, iters: int, warmup: int, graph: bool) -> dict:
     ex = api.BaseExecutor()
     ex.init(model, batch=batch, seed=1, seq_len=seq_len, dtype=dtype)
-    if model.startswith("bert"):
-        vocab = 30522 if model == "bert_base" else 1000
-        ex.set_input("data", np.random.default_rng(6).integers(0, vocab, (batch, seq_len or 128)).astype(np.int64))
-    else:
-        ex.set_input("data", api.synth_normal(batch * 3 * 224 * 224, 0, 0).reshape(batch, 3, 224, 224))
+    ex.set_input("data", synthetic_input(ex))
     s = api.Stream(0)
     if graph:
         ex.capture_graph(s)
@@ -80,11 +87,7 @@ def per_kernel(model: str, batch: int, dtype: str, seq_len: int, reps: int) -> N
     word = api.PreemptWord(1)
     ex.set_word(word)
     s = api.Stream(1)
-    if model.startswith("bert"):
-        vocab = 30522 if model == "bert_base" else 1000
-        ex.set_input("data", np.random.default_rng(6).integers(0, vocab, (batch, seq_len or 128)).astype(np.int64))
-    else:
-        ex.set_input("data", api.synth_normal(batch * 3 * 224 * 224, 0, 0).reshape(batch, 3, 224, 224))
+    ex.set_input("data", synthetic_input(ex))
     nk = ex.get_kernel_num()
     infos = [ex.model.get_kernel_info(i) for i in range(nk)]
     for _ in range(3):

@@ -205,6 +205,10 @@ typedef struct gpx_microbench_summary {
      * a host thread that was delayed while issuing the write, not a kernel that was slow to leave. */
     double raise_call_us_p50, raise_call_us_max;
     double drain_after_return_us_max;
+    /* Launches whose first CTA started only after the word had been raised (the launch itself was
+     * late): they stop at their entry check, are resumed and verified like the others, and are
+     * left out of the drain statistics because no running kernel was interrupted. */
+    int late_starts;
 } gpx_microbench_summary;
 int gpx_preempt_microbench(int kind, size_t size, int triggers, uint64_t seed, int transport,
                            double *drain_us, double *seen_us, gpx_microbench_summary *out);
@@ -275,6 +279,14 @@ int gpx_model_export_json(gpx_model *m, char *buf, size_t cap, size_t *needed);
  * function, its kernels with launch_params[6] and argument indices; scripts/compile/compile.py:
  * 73-85 writes mod.params).  gpx_model_open(dir) loads it back. */
 int gpx_model_export_dir(gpx_model *m, const char *dir);
+/* The scientific workload, model name "miniweather" (3200 x 1600 cells as in
+ * src/workloads/miniweather.cu:21-22; "miniweather_tiny" and "miniweather_<nx>x<nz>" are smaller
+ * grids): Executor::init builds the initial state (src/executor.cpp:35-38), every execute is
+ * SciCompute{Raw,Blp}::perform_timestep (src/executor.cpp:131,229), set/get of "data" are not
+ * needed.  Storages "state" and "state_tmp" hold [4][nz+4][nx+4] floats in the reference's layout.
+ * gpx_model_reductions is reductions(mass, te) (miniweather.cu:650-677): domain mass and total
+ * energy of "state".  gpx_model_init_random puts the simulation back to its initial state. */
+int gpx_model_reductions(gpx_model *m, double *mass, double *te);
 
 /* ---- executor ----------------------------------------------------------------------- */
 

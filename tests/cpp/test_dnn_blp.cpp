@@ -4,7 +4,7 @@
 // output must equal an uninterrupted BaseExecutor run bit for bit.
 //
 //   test_dnn_blp <model> [batch] [delay_us] [out.bin]
-#include "gpx/executor.h"
+#include "executor.h"  // found in include/gpx, as the reference's sources find theirs in include/
 
 #include <chrono>
 #include <cstdio>

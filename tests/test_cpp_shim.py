@@ -18,7 +18,9 @@ LIBDIR = os.path.join(ROOT, "gpreempt_b200", "lib")
 def _compile(tmp_path, compiler, std, src, out):
     gpx_build.build()
     exe = str(tmp_path / out)
+    # include/ for the C header, include/gpx for the classes with the reference's header names
     cmd = [compiler, f"-std={std}", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+           "-I", os.path.join(ROOT, "include", "gpx"),
            os.path.join(ROOT, "tests", "cpp", src), "-o", exe, "-L", LIBDIR, "-lgpx",
            f"-Wl,-rpath,{LIBDIR}"]
     res = subprocess.run(cmd, capture_output=True, text=True)
