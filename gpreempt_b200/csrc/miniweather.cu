@@ -34,8 +34,8 @@ constexpr float kMaxSpeed = 450;
 constexpr int ID_DENS = 0, ID_UMOM = 1, ID_WMOM = 2, ID_RHOT = 3;
 
 struct Grid {
-    int nx, nz, W;     // W: row stride (nx + 4)
-    size_t plane;      // (nz + 4) * W
+    int nx, nz, W;   // W: row stride (nx + 4)
+    unsigned plane;  // (nz + 4) * W; four planes stay below 2^31 elements (checked when the model is built)
 };
 
 __device__ __forceinline__ Grid grid_of(const StencilParams &p) {
@@ -43,51 +43,43 @@ __device__ __forceinline__ Grid grid_of(const StencilParams &p) {
     g.nx = p.nx;
     g.nz = p.nz;
     g.W = p.nx + 2 * kMwHalo;
-    g.plane = (size_t)(p.nz + 2 * kMwHalo) * g.W;
+    g.plane = (unsigned)(p.nz + 2 * kMwHalo) * (unsigned)g.W;
     return g;
 }
 
-// Value of variable ll at array position (ka, ca) of the forcing state as the reference's flux
-// kernel would read it after set_halo_values_x (miniweather.cu:331-341): the two columns on each
-// side wrap around.  Only rows of the interior are read in this direction.
-__device__ __forceinline__ float load_x(const StencilParams &p, const Grid &g, int ll, int ka, int ca) {
-    int src = ca < kMwHalo ? ca + g.nx : (ca >= g.nx + kMwHalo ? ca - g.nx : ca);
-    return p.forcing[ll * g.plane + (size_t)ka * g.W + src];
-}
-
-// Value at (ka, ca) as read after set_halo_values_z (miniweather.cu:346-372): rows outside the
-// interior take the boundary row's value (scaled by the density ratio for the horizontal
-// momentum, zero for the vertical momentum) where the reference's launch covers them, and keep
-// what the array holds elsewhere.
-__device__ __forceinline__ float load_z(const StencilParams &p, const Grid &g, int ll, int ka, int ca) {
-    const size_t base = ll * g.plane;
-    if (ka >= kMwHalo && ka < g.nz + kMwHalo) return p.forcing[base + (size_t)ka * g.W + ca];
-    if (ll * g.W + ca >= p.halo_z_ids) return p.forcing[base + (size_t)ka * g.W + ca];
-    if (ll == ID_WMOM) return 0.f;
-    const bool low = ka < kMwHalo;
-    float v = p.forcing[base + (size_t)(low ? kMwHalo : g.nz + kMwHalo - 1) * g.W + ca];
-    if (ll == ID_UMOM) v = v * p.halo_ratio[low ? ka : ka - g.nz];
-    return v;
-}
-
 // Horizontal tile: cells [i0, i1) of row k.  compute_tendencies_x (:222-258) then
-// compute_tendencies_x_r (:260-272).
-__device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, int tile, float *sflux) {
+// compute_tendencies_x_r (:260-272).  The row segment with two cells on either side is staged in
+// shared memory; the cells beyond the ends of the row wrap around as set_halo_values_x (:331-341)
+// would have written them, and the tiles at the ends of the row store those halo cells.
+__device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, int tile, float *smem) {
+    constexpr int ldi = kMwTileXMax + 2 * kMwHalo;  // staged values per variable
+    constexpr int ldf = kMwTileXMax + 1;            // fluxes per variable
+    float *sin = smem, *sflux = smem + kMwVars * ldi;
     const int k = tile / p.tiles_per_row;
     const int i0 = (tile - k * p.tiles_per_row) * p.tile_x;
     const int i1 = min(i0 + p.tile_x, g.nx);
     const int n = i1 - i0;
-    const int ka = k + kMwHalo;
-    const int ld = kMwTileXMax + 1;
+    const unsigned row = (unsigned)(k + kMwHalo) * (unsigned)g.W;
+    const float *__restrict__ forcing = p.forcing;
+    for (int c = threadIdx.x; c < n + 2 * kMwHalo; c += kMwThreads) {
+        const int ca = i0 + c;  // array column
+        const int src = ca < kMwHalo ? ca + g.nx : (ca >= g.nx + kMwHalo ? ca - g.nx : ca);
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) {
+            const float v = forcing[ll * g.plane + row + src];
+            sin[ll * ldi + c] = v;
+            if (src != ca) p.forcing[ll * g.plane + row + ca] = v;
+        }
+    }
+    __syncthreads();
     const float hv_coef = -kHvBeta * p.dx / (16 * p.dt);
-    const float hd = p.hy_dens_cell[ka], hdt = p.hy_dens_theta_cell[ka];
-    for (int f = threadIdx.x; f <= n; f += kMwThreads) {
-        const int i = i0 + f;  // interface between cells i-1 and i
+    const float hd = p.hy_dens_cell[k + kMwHalo], hdt = p.hy_dens_theta_cell[k + kMwHalo];
+    for (int f = threadIdx.x; f <= n; f += kMwThreads) {  // interface between cells i0+f-1 and i0+f
         float vals[kMwVars], d3_vals[kMwVars];
 #pragma unroll
         for (int ll = 0; ll < kMwVars; ++ll) {
-            float s0 = load_x(p, g, ll, ka, i), s1 = load_x(p, g, ll, ka, i + 1);
-            float s2 = load_x(p, g, ll, ka, i + 2), s3 = load_x(p, g, ll, ka, i + 3);
+            const float s0 = sin[ll * ldi + f], s1 = sin[ll * ldi + f + 1];
+            const float s2 = sin[ll * ldi + f + 2], s3 = sin[ll * ldi + f + 3];
             vals[ll] = (-s0 + 7 * (s1 + s2) - s3) / 12;
             d3_vals[ll] = (-s0 + 3 * (s1 - s2) + s3) * hv_coef;
         }
@@ -96,52 +88,80 @@ __device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, in
         double w = vals[ID_WMOM] / r;
         double t = (vals[ID_RHOT] + hdt) / r;
         double pr = kC0 * pow((r * t), (double)kGamm);
-        sflux[ID_DENS * ld + f] = r * u - d3_vals[ID_DENS];
-        sflux[ID_UMOM * ld + f] = r * u * u + pr - d3_vals[ID_UMOM];
-        sflux[ID_WMOM * ld + f] = r * u * w - d3_vals[ID_WMOM];
-        sflux[ID_RHOT * ld + f] = r * u * t - d3_vals[ID_RHOT];
-    }
-    // The tiles at the ends of a row store the halo columns they wrapped around for.
-    if (i0 == 0 && threadIdx.x < 2 * kMwVars) {
-        int ll = threadIdx.x >> 1, c = threadIdx.x & 1;
-        p.forcing[ll * g.plane + (size_t)ka * g.W + c] = load_x(p, g, ll, ka, c);
-    }
-    if (i1 == g.nx && threadIdx.x >= 32 && threadIdx.x < 32 + 2 * kMwVars) {
-        int ll = (threadIdx.x - 32) >> 1, c = g.nx + kMwHalo + ((threadIdx.x - 32) & 1);
-        p.forcing[ll * g.plane + (size_t)ka * g.W + c] = load_x(p, g, ll, ka, c);
+        sflux[ID_DENS * ldf + f] = r * u - d3_vals[ID_DENS];
+        sflux[ID_UMOM * ldf + f] = r * u * u + pr - d3_vals[ID_UMOM];
+        sflux[ID_WMOM * ldf + f] = r * u * w - d3_vals[ID_WMOM];
+        sflux[ID_RHOT * ldf + f] = r * u * t - d3_vals[ID_RHOT];
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n * kMwVars; e += kMwThreads) {
-        const int ll = e / n, f = e - ll * n;
-        float tend = -(sflux[ll * ld + f + 1] - sflux[ll * ld + f]) / p.dx;
-        size_t inds = ll * g.plane + (size_t)ka * g.W + i0 + f + kMwHalo;
-        p.out[inds] = p.init[inds] + p.dt * tend;
+    for (int f = threadIdx.x; f < n; f += kMwThreads) {
+        const unsigned at = row + (unsigned)(i0 + f + kMwHalo);
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) {
+            float tend = -(sflux[ll * ldf + f + 1] - sflux[ll * ldf + f]) / p.dx;
+            const unsigned inds = ll * g.plane + at;
+            p.out[inds] = p.init[inds] + p.dt * tend;
+        }
     }
 }
 
-// Vertical tile: cells [c0, c1) x [k0, k1).  compute_tendencies_z (:278-318) then
-// compute_tendencies_z_r (:320-336).
-__device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, int tile, float *sflux) {
+// Value of variable ll in array row ka (a row outside the interior) of column ca as the
+// reference's flux kernel reads it after set_halo_values_z (:346-372): the boundary row's value
+// (scaled by the density ratio for the horizontal momentum, zero for the vertical momentum) where
+// the reference's launch covers the cell, else what the array holds.  A derived value is stored.
+__device__ __forceinline__ float halo_row_value(const StencilParams &p, const Grid &g, int ll, int ka, int ca) {
+    const unsigned at = ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca;
+    if (ll * g.W + ca >= p.halo_z_ids) return p.forcing[at];
+    float v = 0.f;
+    if (ll != ID_WMOM) {
+        const bool low = ka < kMwHalo;
+        v = p.forcing[ll * g.plane + (unsigned)(low ? kMwHalo : g.nz + kMwHalo - 1) * (unsigned)g.W + (unsigned)ca];
+        if (ll == ID_UMOM) v = v * p.halo_ratio[low ? ka : ka - g.nz];
+    }
+    p.forcing[at] = v;
+    return v;
+}
+
+// Vertical tile: kMwThreads columns x up to kMwTileZRows rows; one thread walks down one column
+// with the four stencil rows of every variable in registers.  compute_tendencies_z (:278-318)
+// then compute_tendencies_z_r (:320-336).
+__device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, int tile) {
     const int tr = tile / p.tiles_cols;
-    const int c0 = (tile - tr * p.tiles_cols) * kMwTileZCols;
-    const int c1 = min(c0 + kMwTileZCols, g.nx);
+    const int i = (tile - tr * p.tiles_cols) * kMwThreads + (int)threadIdx.x;  // cell column
+    if (i >= g.nx) return;
     const int k0 = tr * kMwTileZRows;
-    const int k1 = min(k0 + kMwTileZRows, g.nz);
-    const int nc = c1 - c0, nr = k1 - k0;
-    constexpr int ldv = (kMwTileZRows + 1) * kMwTileZCols;
+    const int nr = min(kMwTileZRows, g.nz - k0);
+    const int ca = i + kMwHalo;
     const float hv_coef = -kHvBeta * p.dz / (16 * p.dt);
-    for (int e = threadIdx.x; e < (nr + 1) * kMwTileZCols; e += kMwThreads) {
-        const int fr = e / kMwTileZCols, fc = e - fr * kMwTileZCols;
-        if (fc >= nc) continue;
-        const int k = k0 + fr;         // interface below cell row k
-        const int ca = c0 + fc + kMwHalo;
-        float vals[kMwVars], d3_vals[kMwVars];
+    const float *__restrict__ forcing = p.forcing;
+    float win[kMwVars][4];  // array rows k .. k+3 of interface k
+#pragma unroll
+    for (int ll = 0; ll < kMwVars; ++ll)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+            const int ka = k0 + s;
+            win[ll][s + 1] = ka >= kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
+                                           : halo_row_value(p, g, ll, ka, ca);
+        }
+    float below[kMwVars];  // flux through the interface under the cell about to be updated
+    for (int j = 0; j <= nr; ++j) {
+        const int k = k0 + j;  // interface below cell row k
+        const int ka = k + 3;
+        float vals[kMwVars], d3_vals[kMwVars], init_v[kMwVars];
+        const unsigned cell = (unsigned)(k - 1 + kMwHalo) * (unsigned)g.W + (unsigned)ca;  // cell above interface k-1
 #pragma unroll
         for (int ll = 0; ll < kMwVars; ++ll) {
-            float s0 = load_z(p, g, ll, k, ca), s1 = load_z(p, g, ll, k + 1, ca);
-            float s2 = load_z(p, g, ll, k + 2, ca), s3 = load_z(p, g, ll, k + 3, ca);
-            vals[ll] = (-s0 + 7 * (s1 + s2) - s3) / 12;
-            d3_vals[ll] = (-s0 + 3 * (s1 - s2) + s3) * hv_coef;
+            win[ll][0] = win[ll][1];
+            win[ll][1] = win[ll][2];
+            win[ll][2] = win[ll][3];
+            win[ll][3] = ka < g.nz + kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
+                                             : halo_row_value(p, g, ll, ka, ca);
+            if (j > 0) init_v[ll] = p.init[ll * g.plane + cell];
+        }
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) {
+            vals[ll] = (-win[ll][0] + 7 * (win[ll][1] + win[ll][2]) - win[ll][3]) / 12;
+            d3_vals[ll] = (-win[ll][0] + 3 * (win[ll][1] - win[ll][2]) + win[ll][3]) * hv_coef;
         }
         float r = vals[ID_DENS] + p.hy_dens_int[k];
         float u = vals[ID_UMOM] / r;
@@ -152,49 +172,41 @@ __device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, in
             w = 0;
             d3_vals[ID_DENS] = 0;
         }
-        sflux[ID_DENS * ldv + e] = r * w - d3_vals[ID_DENS];
-        sflux[ID_UMOM * ldv + e] = r * w * u - d3_vals[ID_UMOM];
-        sflux[ID_WMOM * ldv + e] = r * w * w + pr - d3_vals[ID_WMOM];
-        sflux[ID_RHOT * ldv + e] = r * w * t - d3_vals[ID_RHOT];
-    }
-    // Tiles on the bottom and top rows store the halo rows they derived, where the reference's
-    // halo launch covers them.
-    if (k0 == 0 || k1 == g.nz) {
-        for (int e = threadIdx.x; e < 2 * kMwVars * nc; e += kMwThreads) {
-            const int fc = e % nc, rest = e / nc;
-            const int ll = rest >> 1, h = rest & 1;
-            const int ca = c0 + fc + kMwHalo;
-            if (ll * g.W + ca >= p.halo_z_ids) continue;
-            if (k0 == 0) p.forcing[ll * g.plane + (size_t)h * g.W + ca] = load_z(p, g, ll, h, ca);
-            if (k1 == g.nz) {
-                const int ka = g.nz + kMwHalo + h;
-                p.forcing[ll * g.plane + (size_t)ka * g.W + ca] = load_z(p, g, ll, ka, ca);
+        float flux[kMwVars];
+        flux[ID_DENS] = r * w - d3_vals[ID_DENS];
+        flux[ID_UMOM] = r * w * u - d3_vals[ID_UMOM];
+        flux[ID_WMOM] = r * w * w + pr - d3_vals[ID_WMOM];
+        flux[ID_RHOT] = r * w * t - d3_vals[ID_RHOT];
+        if (j > 0) {
+            // Cell row k-1, whose forcing values are win[.][1] (array row k+1).  When the reference
+            // runs this stage with forcing and out in one array (the second Runge-Kutta stage) its
+            // gravity term reads the density the same launch has already updated: its threads are
+            // numbered variable-major (:322-324) and the density blocks run far ahead of the
+            // momentum blocks.  `gravity_from_out` selects that value here, where out is a
+            // separate array.
+            float dens_new = 0.f;
+#pragma unroll
+            for (int ll = 0; ll < kMwVars; ++ll) {
+                float tend = -(flux[ll] - below[ll]) / p.dz;
+                if (ll == ID_WMOM) tend = tend - (p.gravity_from_out ? dens_new : win[ID_DENS][1]) * kGrav;
+                const float v = init_v[ll] + p.dt * tend;
+                if (ll == ID_DENS) dens_new = v;
+                p.out[ll * g.plane + cell] = v;
             }
         }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < kMwVars * nr * kMwTileZCols; e += kMwThreads) {
-        const int ll = e / (nr * kMwTileZCols);
-        const int cell = e - ll * (nr * kMwTileZCols);
-        const int fr = cell / kMwTileZCols, fc = cell - fr * kMwTileZCols;
-        if (fc >= nc) continue;
-        float tend = -(sflux[ll * ldv + cell + kMwTileZCols] - sflux[ll * ldv + cell]) / p.dz;
-        const size_t at = (size_t)(k0 + fr + kMwHalo) * g.W + c0 + fc + kMwHalo;
-        if (ll == ID_WMOM) tend = tend - p.forcing[ID_DENS * g.plane + at] * kGrav;
-        const size_t inds = ll * g.plane + at;
-        p.out[inds] = p.init[inds] + p.dt * tend;
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll) below[ll] = flux[ll];
     }
 }
 
-constexpr int kFluxFloats = kMwVars * (kMwTileZRows + 1) * kMwTileZCols;
-static_assert(kFluxFloats >= kMwVars * (kMwTileXMax + 1), "flux tile of the x direction must fit");
+constexpr int kStageFloats = kMwVars * (kMwTileXMax + 2 * kMwHalo) + kMwVars * (kMwTileXMax + 1);
 
 }  // namespace
 
 __global__ void __launch_bounds__(kMwThreads)
 miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
     pdl_enter();
-    __shared__ float sflux[kFluxFloats];
+    __shared__ float smem[kStageFloats];
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -203,6 +215,7 @@ miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
     for (;;) {
         int tile;
         if (dynamic) {
+            __syncthreads();  // every thread has read the previous s_tile
             if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
             __syncthreads();
             tile = s_tile;
@@ -210,12 +223,13 @@ miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        if (p.dir == 1)
-            tile_x(p, g, tile, sflux);
-        else
-            tile_z(p, g, tile, sflux);
+        if (p.dir == 1) {
+            tile_x(p, g, tile, smem);
+            __syncthreads();  // the staging area is reused by the next tile
+        } else {
+            tile_z(p, g, tile);
+        }
         ++iter;
-        __syncthreads();  // the flux tile and s_tile are reused
     }
     if (threadIdx.x == 0) trace_end(blp, iter);
 }
@@ -437,7 +451,7 @@ int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opt
     const int row_tiles = (nx + kMwTileXMax - 1) / kMwTileXMax;
     base.tile_x = ((nx + row_tiles - 1) / row_tiles + 31) / 32 * 32;
     base.tiles_per_row = (nx + base.tile_x - 1) / base.tile_x;
-    base.tiles_cols = (nx + kMwTileZCols - 1) / kMwTileZCols;
+    base.tiles_cols = (nx + kMwThreads - 1) / kMwThreads;
     const char *cover = getenv("GPX_MINIWEATHER_FULL_HALO");
     base.halo_z_ids = (cover && cover[0] == '1') ? W * kMwVars
                                                  : (nx + 2 * kMwHalo * kMwVars + 255) / 256 * 256;
@@ -459,6 +473,7 @@ int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opt
             p.forcing = stage == 0 ? state : (stage == 1 ? tmp : tmp2);
             p.out = stage == 0 ? tmp : (stage == 1 ? tmp2 : state);
             p.dt = stage == 0 ? dt / 3 : (stage == 1 ? dt / 2 : dt / 1);
+            p.gravity_from_out = stage == 1 ? 1 : 0;
             k.stencil = p;
             k.threads = kMwThreads;
             k.total_tiles = p.dir == 1 ? nz * p.tiles_per_row

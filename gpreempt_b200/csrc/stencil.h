@@ -19,13 +19,13 @@ constexpr int kMwHalo = 2;       // hs
 constexpr int kMwVars = 4;       // rho', rho*u, rho*w, (rho*theta)'
 constexpr int kMwThreads = 256;
 constexpr int kMwTileXMax = 512; // cells of one row per x-direction tile (at most)
-constexpr int kMwTileZCols = 128, kMwTileZRows = 16;
+constexpr int kMwTileZRows = 16;  // rows of a z-direction tile; its columns are one per thread
 
 // One semi-discrete step out = init + dt * rhs(forcing) in one direction (semi_discrete_step,
 // src/workloads/miniweather.cu:204-216).  The reference runs it as three kernels (halo, flux,
-// update) with the flux array in global memory; here one kernel computes the fluxes of a tile into
-// shared memory and updates the tile, and the tiles on the domain edge produce (and store) the
-// halo cells they read.  `out` never aliases `forcing`: the second Runge-Kutta stage writes a
+// update) with the flux array in global memory; here one kernel computes the fluxes of a tile (in
+// shared memory along x, in registers while walking down a column along z) and updates the tile,
+// and the tiles on the domain edge produce (and store) the halo cells they read.  `out` never aliases `forcing`: the second Runge-Kutta stage writes a
 // third state buffer instead of updating its forcing array in place.
 struct StencilParams {
     const float *init;
@@ -43,13 +43,14 @@ struct StencilParams {
     int dir;              // 1 = x, 2 = z
     int tile_x;           // x direction: cells per tile; tiles_per_row = ceil(nx / tile_x)
     int tiles_per_row;
-    int tiles_cols;       // z direction: ceil(nx / kMwTileZCols)
+    int tiles_cols;       // z direction: ceil(nx / kMwThreads)
     // The reference launches its vertical halo kernel with (nx + 2*hs*NUM_VARS + 255) / 256 blocks
     // (miniweather.cu:213), so only flat indices below that many threads get halo values: all of
     // the density and the first columns of the horizontal momentum.  The other vertical halo cells
     // keep the values the initial state gave them.  `halo_z_ids` is that thread count; a value of
     // (nx + 4) * 4 would cover every variable.
     int halo_z_ids;
+    int gravity_from_out;  // vertical update: the gravity term reads the updated density (stage 2)
 };
 
 cudaError_t stencil_launch(const StencilParams &p, int grid, const BlpArgs &blp, cudaStream_t s);

@@ -38,10 +38,14 @@ def parse_specs(text: str) -> list[tuple[str, int, str, int]]:
     return out
 
 
-def synthetic_input(ex) -> np.ndarray:
+def synthetic_input(ex) -> np.ndarray | None:
     """Seeded input of the shape and type the model's `data` tensor has: N(0,1) images, or token
-    ids uniform over the rows of the word-embedding table."""
-    shape = ex.model.shape("data")
+    ids uniform over the rows of the word-embedding table.  None for a workload without request
+    data (miniweather: every execute advances the resident simulation)."""
+    try:
+        shape = ex.model.shape("data")
+    except api.GpxError:
+        return None
     info = ex.model.get_storage_info(ex.model.find_storage_idx("data"))
     if info["stype"] == "int64":
         vocab = ex.model.shape("embeddings.word_embeddings.weight")[0]
@@ -52,7 +56,9 @@ def synthetic_input(ex) -> np.ndarray:
 def run(model: str, batch: int, dtype: str, seq_len: int, iters: int, warmup: int, graph: bool) -> dict:
     ex = api.BaseExecutor()
     ex.init(model, batch=batch, seed=1, seq_len=seq_len, dtype=dtype)
-    ex.set_input("data", synthetic_input(ex))
+    data = synthetic_input(ex)
+    if data is not None:
+        ex.set_input("data", data)
     s = api.Stream(0)
     if graph:
         ex.capture_graph(s)
@@ -87,7 +93,9 @@ def per_kernel(model: str, batch: int, dtype: str, seq_len: int, reps: int) -> N
     word = api.PreemptWord(1)
     ex.set_word(word)
     s = api.Stream(1)
-    ex.set_input("data", synthetic_input(ex))
+    data = synthetic_input(ex)
+    if data is not None:
+        ex.set_input("data", data)
     nk = ex.get_kernel_num()
     infos = [ex.model.get_kernel_info(i) for i in range(nk)]
     for _ in range(3):

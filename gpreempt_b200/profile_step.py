@@ -56,14 +56,17 @@ def main() -> None:
         ex = api.BLPExecutor()
         ex.init(a.model, batch=a.batch, seed=1, dtype=a.dtype, seq_len=a.seq_len)
         ex.set_word(word)
-        if a.model.startswith("bert"):
+        if a.model.startswith("miniweather"):
+            data = None  # no request data: every execute advances the resident simulation
+        elif a.model.startswith("bert"):
             import numpy as np
 
             vocab = 30522 if a.model == "bert_base" else 1000
             data = np.random.default_rng(6).integers(0, vocab, (a.batch, a.seq_len or 128)).astype(np.int64)
         else:
             data = api.synth_normal(a.batch * 3 * 224 * 224, 0).reshape(a.batch, 3, 224, 224)
-        ex.set_input("data", data)
+        if data is not None:
+            ex.set_input("data", data)
         for _ in range(a.iters):
             ex.execute(s)
             assert ex.getStopPoint(s) == -1
