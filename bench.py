@@ -245,6 +245,16 @@ def cpu_baseline(seconds: float = 10.0) -> dict:
         others["axpy_2p26_gb_s"] = 12.0 * (1 << 26) / timed(lambda: orc.axpy(1.0009765625, x, y), 3) / 1e9
         a = orc.f32_to_bf16(rng.uniform(-1, 1, (1024, 1024)).astype(np.float32))
         others["gemm_bf16_1024_gflop_s"] = 2.0 * 1024 ** 3 / timed(lambda: orc.gemm_bf16_nt_fast(a, a), 2) / 1e9
+        from oracle import miniweather as mw
+
+        sim = mw.Oracle(3200, 1600)
+        others["miniweather_3200x1600_cpu_oracle_ms_per_time_step"] = timed(sim.timestep, 2) * 1e3
+        if mw.reference_available():
+            # the reference's own CUDA source for this workload, compiled unmodified (oracle/Makefile)
+            ref = mw.Reference(0)
+            ref.timestep(2)
+            others["miniweather_3200x1600_reference_kernels_ms_per_time_step"] = ref.time_steps(20) / 20
+            ref.close()
     except Exception as e:  # noqa: BLE001 - the side figures must not cost the run its line
         others["error"] = repr(e)
     return {"value": images / dt, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
@@ -288,6 +298,31 @@ def run_reference(args, rank: int) -> None:
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def miniweather_figures(api, hbm_gbs: float) -> dict:
+    """The scientific best-effort workload (the reference's config/Y.json tenant): device time of one
+    time step of the 3200 x 1600 grid, replayed from a CUDA graph, and its share of HBM bandwidth
+    (12 kernels, each reads two state arrays and writes one: 2.95 GB per time step)."""
+    ex = api.BaseExecutor()
+    ex.init("miniweather")
+    s = api.Stream(0)
+    ex.capture_graph(s)
+    for _ in range(3):
+        ex.execute(s)
+    s.sync()
+    e0, e1 = api.Event(), api.Event()
+    e0.record(s)
+    for _ in range(20):
+        ex.execute(s)
+    e1.record(s)
+    s.sync()
+    ms = e0.elapsed_ms(e1) / 20
+    nbytes = sum(ex.model.get_kernel_info(i)["bytes"] for i in range(ex.get_kernel_num()))
+    ex.clear()
+    s.destroy()
+    return {"ms_per_time_step": ms, "kernels": 12, "algorithmic_gb": nbytes / 1e9,
+            "achieved_gb_s": nbytes / (ms * 1e-3) / 1e9, "hbm_frac": nbytes / (ms * 1e-3) / 1e9 / hbm_gbs}
 
 
 def model_roofline_ms(layers, peak_tflops: float, hbm_gbs: float) -> float:
@@ -472,6 +507,8 @@ def main() -> None:
             "preempt_microbench": microbench,
             "wall_s_resident_run": t1 - t0,
         }
+        if world == 1:
+            line["other_workloads"] = {"miniweather_3200x1600": miniweather_figures(api, hbm)}
         if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)

@@ -47,6 +47,22 @@ __device__ __forceinline__ Grid grid_of(const StencilParams &p) {
     return g;
 }
 
+
+// Arithmetic with every rounding written out.  The reference is compiled with nvcc's default
+// -fmad=true, which leaves the choice between a fused multiply-add and a rounded product plus a
+// sum to the assembler; its choice depends on the surrounding code, so relying on it here would
+// tie the results to register pressure.  These are the operations the reference's kernels
+// execute (checked on a GPU against that code: all cells of all variables identical).
+__device__ __forceinline__ float interp4(float s0, float s1, float s2, float s3) {
+    // (-s0 + 7*(s1 + s2) - s3) / 12
+    return __fdiv_rn(__fsub_rn(__fmaf_rn(7.f, __fadd_rn(s1, s2), -s0), s3), 12.f);
+}
+__device__ __forceinline__ float third_derivative(float s0, float s1, float s2, float s3, float hv_coef) {
+    // (-s0 + 3*(s1 - s2) + s3) * hv_coef
+    return __fmul_rn(__fadd_rn(__fmaf_rn(3.f, __fsub_rn(s1, s2), -s0), s3), hv_coef);
+}
+__device__ __forceinline__ float advance(float init, float dt, float tend) { return __fmaf_rn(dt, tend, init); }
+
 // Horizontal tile: cells [i0, i1) of row k.  compute_tendencies_x (:222-258) then
 // compute_tendencies_x_r (:260-272).  The row segment with two cells on either side is staged in
 // shared memory; the cells beyond the ends of the row wrap around as set_halo_values_x (:331-341)
@@ -61,18 +77,43 @@ __device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, in
     const int n = i1 - i0;
     const unsigned row = (unsigned)(k + kMwHalo) * (unsigned)g.W;
     const float *__restrict__ forcing = p.forcing;
-    for (int c = threadIdx.x; c < n + 2 * kMwHalo; c += kMwThreads) {
+    // Every global load of the tile is issued up front: the row segment to stage (up to three
+    // values per variable and thread) and the cells' starting values, which are not needed until
+    // the update and so overlap the flux arithmetic.
+    constexpr int kStageIters = (kMwTileXMax + 2 * kMwHalo + kMwThreads - 1) / kMwThreads;
+    constexpr int kCellIters = kMwTileXMax / kMwThreads;
+    float staged[kStageIters][kMwVars], init_v[kCellIters][kMwVars];
+#pragma unroll
+    for (int it = 0; it < kStageIters; ++it) {
+        const int c = threadIdx.x + it * kMwThreads;
         const int ca = i0 + c;  // array column
         const int src = ca < kMwHalo ? ca + g.nx : (ca >= g.nx + kMwHalo ? ca - g.nx : ca);
 #pragma unroll
-        for (int ll = 0; ll < kMwVars; ++ll) {
-            const float v = forcing[ll * g.plane + row + src];
-            sin[ll * ldi + c] = v;
-            if (src != ca) p.forcing[ll * g.plane + row + ca] = v;
+        for (int ll = 0; ll < kMwVars; ++ll)
+            staged[it][ll] = c < n + 2 * kMwHalo ? forcing[ll * g.plane + row + src] : 0.f;
+    }
+#pragma unroll
+    for (int it = 0; it < kCellIters; ++it) {
+        const int f = threadIdx.x + it * kMwThreads;
+#pragma unroll
+        for (int ll = 0; ll < kMwVars; ++ll)
+            init_v[it][ll] = f < n ? p.init[ll * g.plane + row + (unsigned)(i0 + f + kMwHalo)] : 0.f;
+    }
+#pragma unroll
+    for (int it = 0; it < kStageIters; ++it) {
+        const int c = threadIdx.x + it * kMwThreads;
+        const int ca = i0 + c;
+        if (c < n + 2 * kMwHalo) {
+            const bool halo = ca < kMwHalo || ca >= g.nx + kMwHalo;
+#pragma unroll
+            for (int ll = 0; ll < kMwVars; ++ll) {
+                sin[ll * ldi + c] = staged[it][ll];
+                if (halo) p.forcing[ll * g.plane + row + ca] = staged[it][ll];
+            }
         }
     }
     __syncthreads();
-    const float hv_coef = -kHvBeta * p.dx / (16 * p.dt);
+    const float hv_coef = __fdiv_rn(__fmul_rn(-kHvBeta, p.dx), __fmul_rn(16.f, p.dt));
     const float hd = p.hy_dens_cell[k + kMwHalo], hdt = p.hy_dens_theta_cell[k + kMwHalo];
     for (int f = threadIdx.x; f <= n; f += kMwThreads) {  // interface between cells i0+f-1 and i0+f
         float vals[kMwVars], d3_vals[kMwVars];
@@ -80,27 +121,32 @@ __device__ __forceinline__ void tile_x(const StencilParams &p, const Grid &g, in
         for (int ll = 0; ll < kMwVars; ++ll) {
             const float s0 = sin[ll * ldi + f], s1 = sin[ll * ldi + f + 1];
             const float s2 = sin[ll * ldi + f + 2], s3 = sin[ll * ldi + f + 3];
-            vals[ll] = (-s0 + 7 * (s1 + s2) - s3) / 12;
-            d3_vals[ll] = (-s0 + 3 * (s1 - s2) + s3) * hv_coef;
+            vals[ll] = interp4(s0, s1, s2, s3);
+            d3_vals[ll] = third_derivative(s0, s1, s2, s3, hv_coef);
         }
-        double r = vals[ID_DENS] + hd;
-        double u = vals[ID_UMOM] / r;
-        double w = vals[ID_WMOM] / r;
-        double t = (vals[ID_RHOT] + hdt) / r;
-        double pr = kC0 * pow((r * t), (double)kGamm);
-        sflux[ID_DENS * ldf + f] = r * u - d3_vals[ID_DENS];
-        sflux[ID_UMOM * ldf + f] = r * u * u + pr - d3_vals[ID_UMOM];
-        sflux[ID_WMOM * ldf + f] = r * u * w - d3_vals[ID_WMOM];
-        sflux[ID_RHOT * ldf + f] = r * u * t - d3_vals[ID_RHOT];
+        const double r = (double)__fadd_rn(vals[ID_DENS], hd);
+        const double u = __ddiv_rn((double)vals[ID_UMOM], r);
+        const double w = __ddiv_rn((double)vals[ID_WMOM], r);
+        const double t = __ddiv_rn((double)__fadd_rn(vals[ID_RHOT], hdt), r);
+        const double pr = __dmul_rn((double)kC0, pow(__dmul_rn(r, t), (double)kGamm));
+        const double ru = __dmul_rn(r, u);
+        // r*u feeds four fluxes; the mass flux subtracts from the rounded product, the others fuse
+        sflux[ID_DENS * ldf + f] = (float)__dsub_rn(ru, (double)d3_vals[ID_DENS]);
+        sflux[ID_UMOM * ldf + f] = (float)__dsub_rn(__fma_rn(ru, u, pr), (double)d3_vals[ID_UMOM]);
+        sflux[ID_WMOM * ldf + f] = (float)__fma_rn(ru, w, -(double)d3_vals[ID_WMOM]);
+        sflux[ID_RHOT * ldf + f] = (float)__fma_rn(ru, t, -(double)d3_vals[ID_RHOT]);
     }
     __syncthreads();
-    for (int f = threadIdx.x; f < n; f += kMwThreads) {
-        const unsigned at = row + (unsigned)(i0 + f + kMwHalo);
 #pragma unroll
-        for (int ll = 0; ll < kMwVars; ++ll) {
-            float tend = -(sflux[ll * ldf + f + 1] - sflux[ll * ldf + f]) / p.dx;
-            const unsigned inds = ll * g.plane + at;
-            p.out[inds] = p.init[inds] + p.dt * tend;
+    for (int it = 0; it < kCellIters; ++it) {
+        const int f = threadIdx.x + it * kMwThreads;
+        if (f < n) {
+            const unsigned at = row + (unsigned)(i0 + f + kMwHalo);
+#pragma unroll
+            for (int ll = 0; ll < kMwVars; ++ll) {
+                const float tend = __fdiv_rn(-__fsub_rn(sflux[ll * ldf + f + 1], sflux[ll * ldf + f]), p.dx);
+                p.out[ll * g.plane + at] = advance(init_v[it][ll], p.dt, tend);
+            }
         }
     }
 }
@@ -129,10 +175,10 @@ __device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, in
     const int tr = tile / p.tiles_cols;
     const int i = (tile - tr * p.tiles_cols) * kMwThreads + (int)threadIdx.x;  // cell column
     if (i >= g.nx) return;
-    const int k0 = tr * kMwTileZRows;
-    const int nr = min(kMwTileZRows, g.nz - k0);
+    const int k0 = tr * p.tile_rows;
+    const int nr = min(p.tile_rows, g.nz - k0);
     const int ca = i + kMwHalo;
-    const float hv_coef = -kHvBeta * p.dz / (16 * p.dt);
+    const float hv_coef = __fdiv_rn(__fmul_rn(-kHvBeta, p.dz), __fmul_rn(16.f, p.dt));
     const float *__restrict__ forcing = p.forcing;
     float win[kMwVars][4];  // array rows k .. k+3 of interface k
 #pragma unroll
@@ -143,10 +189,19 @@ __device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, in
             win[ll][s + 1] = ka >= kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
                                            : halo_row_value(p, g, ll, ka, ca);
         }
-    float below[kMwVars];  // flux through the interface under the cell about to be updated
+    // Values of the next step are loaded one step ahead, before this step's stores (out may be
+    // the array init points to, so a load could not move above a store by itself).
+    float next_row[kMwVars], next_init[kMwVars];
+#pragma unroll
+    for (int ll = 0; ll < kMwVars; ++ll) {
+        const int ka = k0 + 3;
+        next_row[ll] = ka < g.nz + kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
+                                           : halo_row_value(p, g, ll, ka, ca);
+        next_init[ll] = 0.f;
+    }
+    float below[kMwVars] = {0.f, 0.f, 0.f, 0.f};  // flux through the interface under the cell about to be updated
     for (int j = 0; j <= nr; ++j) {
         const int k = k0 + j;  // interface below cell row k
-        const int ka = k + 3;
         float vals[kMwVars], d3_vals[kMwVars], init_v[kMwVars];
         const unsigned cell = (unsigned)(k - 1 + kMwHalo) * (unsigned)g.W + (unsigned)ca;  // cell above interface k-1
 #pragma unroll
@@ -154,29 +209,38 @@ __device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, in
             win[ll][0] = win[ll][1];
             win[ll][1] = win[ll][2];
             win[ll][2] = win[ll][3];
-            win[ll][3] = ka < g.nz + kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
-                                             : halo_row_value(p, g, ll, ka, ca);
-            if (j > 0) init_v[ll] = p.init[ll * g.plane + cell];
+            win[ll][3] = next_row[ll];
+            init_v[ll] = next_init[ll];
+        }
+        if (j < nr) {
+            const int ka = k + 4;  // last row of the next interface's stencil
+#pragma unroll
+            for (int ll = 0; ll < kMwVars; ++ll) {
+                next_row[ll] = ka < g.nz + kMwHalo ? forcing[ll * g.plane + (unsigned)ka * (unsigned)g.W + (unsigned)ca]
+                                                   : halo_row_value(p, g, ll, ka, ca);
+                next_init[ll] = p.init[ll * g.plane + cell + (unsigned)g.W];  // cell row k, updated next step
+            }
         }
 #pragma unroll
         for (int ll = 0; ll < kMwVars; ++ll) {
-            vals[ll] = (-win[ll][0] + 7 * (win[ll][1] + win[ll][2]) - win[ll][3]) / 12;
-            d3_vals[ll] = (-win[ll][0] + 3 * (win[ll][1] - win[ll][2]) + win[ll][3]) * hv_coef;
+            vals[ll] = interp4(win[ll][0], win[ll][1], win[ll][2], win[ll][3]);
+            d3_vals[ll] = third_derivative(win[ll][0], win[ll][1], win[ll][2], win[ll][3], hv_coef);
         }
-        float r = vals[ID_DENS] + p.hy_dens_int[k];
-        float u = vals[ID_UMOM] / r;
-        float w = vals[ID_WMOM] / r;
-        float t = (vals[ID_RHOT] + p.hy_dens_theta_int[k]) / r;
-        float pr = kC0 * powf((r * t), kGamm) - p.hy_pressure_int[k];
+        const float r = __fadd_rn(vals[ID_DENS], p.hy_dens_int[k]);
+        const float u = __fdiv_rn(vals[ID_UMOM], r);
+        float w = __fdiv_rn(vals[ID_WMOM], r);
+        const float t = __fdiv_rn(__fadd_rn(vals[ID_RHOT], p.hy_dens_theta_int[k]), r);
+        const float pr = __fmaf_rn(kC0, powf(__fmul_rn(r, t), kGamm), -p.hy_pressure_int[k]);
         if (k == 0 || k == g.nz) {
             w = 0;
             d3_vals[ID_DENS] = 0;
         }
+        const float rw = __fmul_rn(r, w);
         float flux[kMwVars];
-        flux[ID_DENS] = r * w - d3_vals[ID_DENS];
-        flux[ID_UMOM] = r * w * u - d3_vals[ID_UMOM];
-        flux[ID_WMOM] = r * w * w + pr - d3_vals[ID_WMOM];
-        flux[ID_RHOT] = r * w * t - d3_vals[ID_RHOT];
+        flux[ID_DENS] = __fsub_rn(rw, d3_vals[ID_DENS]);  // from the rounded product, as along x
+        flux[ID_UMOM] = __fmaf_rn(rw, u, -d3_vals[ID_UMOM]);
+        flux[ID_WMOM] = __fsub_rn(__fmaf_rn(rw, w, pr), d3_vals[ID_WMOM]);
+        flux[ID_RHOT] = __fmaf_rn(rw, t, -d3_vals[ID_RHOT]);
         if (j > 0) {
             // Cell row k-1, whose forcing values are win[.][1] (array row k+1).  When the reference
             // runs this stage with forcing and out in one array (the second Runge-Kutta stage) its
@@ -187,9 +251,9 @@ __device__ __forceinline__ void tile_z(const StencilParams &p, const Grid &g, in
             float dens_new = 0.f;
 #pragma unroll
             for (int ll = 0; ll < kMwVars; ++ll) {
-                float tend = -(flux[ll] - below[ll]) / p.dz;
-                if (ll == ID_WMOM) tend = tend - (p.gravity_from_out ? dens_new : win[ID_DENS][1]) * kGrav;
-                const float v = init_v[ll] + p.dt * tend;
+                float tend = __fdiv_rn(-__fsub_rn(flux[ll], below[ll]), p.dz);
+                if (ll == ID_WMOM) tend = __fmaf_rn(-(p.gravity_from_out ? dens_new : win[ID_DENS][1]), kGrav, tend);
+                const float v = advance(init_v[ll], p.dt, tend);
                 if (ll == ID_DENS) dens_new = v;
                 p.out[ll * g.plane + cell] = v;
             }
@@ -203,10 +267,13 @@ constexpr int kStageFloats = kMwVars * (kMwTileXMax + 2 * kMwHalo) + kMwVars * (
 
 }  // namespace
 
-__global__ void __launch_bounds__(kMwThreads)
+// One kernel per direction, so each gets its own register budget (the x direction holds doubles
+// and a staged row, the z direction a 4 x 4 stencil window and two prefetched rows).
+template <int DIR>
+__global__ void __launch_bounds__(kMwThreads, 4)
 miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
     pdl_enter();
-    __shared__ float smem[kStageFloats];
+    __shared__ float smem[DIR == 1 ? kStageFloats : 1];
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (threadIdx.x == 0) trace_begin(blp);
@@ -223,7 +290,7 @@ miniweather_step_kernel(const __grid_constant__ StencilParams p, BlpArgs blp) {
             tile = blp_claim(blp, iter);
         }
         if (tile < 0) break;
-        if (p.dir == 1) {
+        if (DIR == 1) {
             tile_x(p, g, tile, smem);
             __syncthreads();  // the staging area is reused by the next tile
         } else {
@@ -356,9 +423,12 @@ int add_field(gpx_model &m, const char *name, Storage::Kind kind, int rank, int6
 
 }  // namespace
 
-int stencil_grid(int total_tiles, int sm_count) {
+int stencil_grid(int dir, int total_tiles, int sm_count) {
     int blocks = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, miniweather_step_kernel, kMwThreads, 0);
+    if (dir == 1)
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, miniweather_step_kernel<1>, kMwThreads, 0);
+    else
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, miniweather_step_kernel<2>, kMwThreads, 0);
     if (blocks < 1) blocks = 1;
     long long grid = (long long)blocks * sm_count;
     if (grid > total_tiles) grid = total_tiles;
@@ -366,7 +436,10 @@ int stencil_grid(int total_tiles, int sm_count) {
 }
 
 cudaError_t stencil_launch(const StencilParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    launch_layer(miniweather_step_kernel, grid, kMwThreads, 0, s, p, blp);
+    if (p.dir == 1)
+        launch_layer(miniweather_step_kernel<1>, grid, kMwThreads, 0, s, p, blp);
+    else
+        launch_layer(miniweather_step_kernel<2>, grid, kMwThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 
@@ -452,6 +525,22 @@ int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opt
     base.tile_x = ((nx + row_tiles - 1) / row_tiles + 31) / 32 * 32;
     base.tiles_per_row = (nx + base.tile_x - 1) / base.tile_x;
     base.tiles_cols = (nx + kMwThreads - 1) / kMwThreads;
+    // Rows per vertical tile: every tile recomputes one flux row and re-reads three stencil rows,
+    // so taller is cheaper, but the static schedule of a non-preemptible executor gives each CTA
+    // ceil(tiles / grid) tiles; pick the height that wastes least of both.
+    {
+        const int grid_full = stencil_grid(2, 1 << 30, m.sm_count);
+        double best = -1.0;
+        for (int rows = 8; rows <= kMwTileZRowsMax; ++rows) {
+            const long long tiles = (long long)base.tiles_cols * ((nz + rows - 1) / rows);
+            const long long waves = (tiles + grid_full - 1) / grid_full;
+            const double eff = (double)tiles / (double)(waves * std::min<long long>(grid_full, tiles)) * rows / (rows + 1.5);
+            if (eff > best) {
+                best = eff;
+                base.tile_rows = rows;
+            }
+        }
+    }
     const char *cover = getenv("GPX_MINIWEATHER_FULL_HALO");
     base.halo_z_ids = (cover && cover[0] == '1') ? W * kMwVars
                                                  : (nx + 2 * kMwHalo * kMwVars + 255) / 256 * 256;
@@ -477,8 +566,8 @@ int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opt
             k.stencil = p;
             k.threads = kMwThreads;
             k.total_tiles = p.dir == 1 ? nz * p.tiles_per_row
-                                       : p.tiles_cols * ((nz + kMwTileZRows - 1) / kMwTileZRows);
-            k.grid = stencil_grid(k.total_tiles, m.sm_count);
+                                       : p.tiles_cols * ((nz + p.tile_rows - 1) / p.tile_rows);
+            k.grid = stencil_grid(p.dir, k.total_tiles, m.sm_count);
             const double cells = (double)nx * nz;
             k.bytes = cells * kMwVars * 4.0 * 3.0;  // forcing and init read, out written
             k.flops = cells * (p.dir == 1 ? 120.0 : 100.0);

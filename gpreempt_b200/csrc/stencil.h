@@ -19,7 +19,7 @@ constexpr int kMwHalo = 2;       // hs
 constexpr int kMwVars = 4;       // rho', rho*u, rho*w, (rho*theta)'
 constexpr int kMwThreads = 256;
 constexpr int kMwTileXMax = 512; // cells of one row per x-direction tile (at most)
-constexpr int kMwTileZRows = 16;  // rows of a z-direction tile; its columns are one per thread
+constexpr int kMwTileZRowsMax = 40;  // rows of a z-direction tile (chosen per grid); its columns are one per thread
 
 // One semi-discrete step out = init + dt * rhs(forcing) in one direction (semi_discrete_step,
 // src/workloads/miniweather.cu:204-216).  The reference runs it as three kernels (halo, flux,
@@ -44,6 +44,7 @@ struct StencilParams {
     int tile_x;           // x direction: cells per tile; tiles_per_row = ceil(nx / tile_x)
     int tiles_per_row;
     int tiles_cols;       // z direction: ceil(nx / kMwThreads)
+    int tile_rows;        // z direction: rows per tile
     // The reference launches its vertical halo kernel with (nx + 2*hs*NUM_VARS + 255) / 256 blocks
     // (miniweather.cu:213), so only flat indices below that many threads get halo values: all of
     // the density and the first columns of the horizontal momentum.  The other vertical halo cells
@@ -54,7 +55,7 @@ struct StencilParams {
 };
 
 cudaError_t stencil_launch(const StencilParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
-int stencil_grid(int total_tiles, int sm_count);
+int stencil_grid(int dir, int total_tiles, int sm_count);
 
 bool is_miniweather(const std::string &name);
 int build_miniweather(gpx_model &m, const std::string &name, const gpx_model_opts &opts);
