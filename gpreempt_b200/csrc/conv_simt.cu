@@ -284,6 +284,9 @@ __device__ __forceinline__ void pool_store8(const PoolParams &p, size_t off, con
 // Max / average pooling, or a strided copy, over split-plane activations; eight channels (one
 // 16-byte vector per plane) per thread-iteration.  A tile is tile_elems consecutive output
 // vectors in (n, ho, wo, c/8) order.
+// kMax3 selects the 3x3 max-pooling instance, which keeps nine taps in registers and so runs at a
+// lower occupancy than the other modes want.
+template <bool kMax3>
 __global__ void __launch_bounds__(kPoolThreads)
 pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
     pdl_enter();
@@ -363,6 +366,34 @@ pool_kernel(const __grid_constant__ PoolParams p, BlpArgs blp) {
             int n = (int)(t / Ho);
             float acc[8];
             const bool readable = c8 * 8 < p.in_valid;
+            if (kMax3 && readable) {
+                // 3x3 max pooling: the nine taps are fetched before any is converted, so a thread
+                // waits for memory once instead of nine times.
+                uint4 ra[9], rb[9];
+                bool ok[9];
+                const int fmt = p.in.l.fmt;
+#pragma unroll
+                for (int t9 = 0; t9 < 9; ++t9) {
+                    const int hi = ho * p.stride - p.pad + t9 / 3, wi = wo * p.stride - p.pad + t9 % 3;
+                    ok[t9] = hi >= 0 && hi < H && wi >= 0 && wi < W;
+                    ra[t9] = rb[t9] = make_uint4(0, 0, 0, 0);
+                    if (ok[t9])
+                        planes_fetch8(p.in.hi, p.in.lo, (size_t)layout_row(p.in.l, n, hi, wi) * Cin + c8 * 8, fmt,
+                                      ra[t9], rb[t9]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = -INFINITY;
+#pragma unroll
+                for (int t9 = 0; t9 < 9; ++t9) {
+                    if (!ok[t9]) continue;
+                    float x[8];
+                    planes_decode8(ra[t9], rb[t9], fmt, x);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = fmaxf(acc[j], x[j]);
+                }
+                pool_store8(p, (size_t)layout_row(p.out, n, ho, wo) * Cout + c8 * 8, acc);
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = (p.mode == 0 && readable) ? -INFINITY : 0.f;
             int cnt = 0;
@@ -427,6 +458,59 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
     }
     __syncthreads();
     int iter = 0;
+    if (p.win_w > 0) {
+        // Row-window mode.  The window of the tile - Cin x kh input rows, (win_w-1)*stride + kw
+        // wide, zeros outside the image - is staged with coalesced loads; a patch-matrix element
+        // is then one table lookup and one shared-memory read, and the stores stay row-contiguous.
+        __shared__ float s_win[kIm2colWindowFloats];
+        const int win_cols = (p.win_w - 1) * p.stride + p.kw;
+        const int seg = p.Cin * p.kh;  // window rows
+        for (int k = threadIdx.x; k < p.Kp; k += kPoolThreads)
+            s_off[k] = s_fh[k] == 255 ? -1 : ((int)s_ci[k] * p.kh + (int)s_fh[k]) * win_cols + (int)s_fw[k];
+        for (;;) {
+            int tile;
+            __syncthreads();  // the table is complete / the previous window has been consumed
+            if (dynamic) {
+                if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+                __syncthreads();
+                tile = s_tile;
+            } else {
+                tile = blp_claim(blp, iter);
+            }
+            if (tile < 0) break;
+            const int chunk = tile % p.win_chunks;
+            const int t = tile / p.win_chunks;
+            const int ho = t % p.Ho, n = t / p.Ho;
+            const int wo0 = chunk * p.win_w;
+            const int nw = min(p.win_w, p.Wo - wo0);
+            const int h0 = ho * p.stride - p.pad, w0 = wo0 * p.stride - p.pad;
+            for (int e = threadIdx.x; e < seg * win_cols; e += kPoolThreads) {
+                const int r = e / win_cols, c = e - r * win_cols;
+                const int ci = r / p.kh, fh = r - ci * p.kh;
+                const int hi = h0 + fh, wi = w0 + c;
+                float v = 0.f;
+                if (hi >= 0 && hi < H && wi >= 0 && wi < W)
+                    v = p.in.f32[(((size_t)n * p.Cin + ci) * H + hi) * W + wi];
+                s_win[e] = v;
+            }
+            __syncthreads();
+            const size_t m0 = ((size_t)n * p.Ho + ho) * p.Wo + wo0;
+            for (int e = threadIdx.x; e < nw * K8; e += kPoolThreads) {
+                const int wl = e / K8, k8 = e - wl * K8;
+                const int shift = wl * p.stride;
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int off = s_off[k8 * 8 + u];
+                    x[u] = off < 0 ? 0.f : s_win[off + shift];
+                }
+                planes_store8(p.out_hi, p.out_lo, (m0 + wl) * p.Kp + k8 * 8, p.fmt, x);
+            }
+            ++iter;
+        }
+        if (threadIdx.x == 0) trace_end(blp, iter);
+        return;
+    }
     for (;;) {
         int tile;
         if (dynamic) {
@@ -620,15 +704,25 @@ cudaError_t dwconv_launch(const DwConvParams &p, int grid, const BlpArgs &blp, c
     return cudaGetLastError();
 }
 
+static bool pool_is_max3(const PoolParams &p) { return p.mode == 0 && p.k == 3 && !p.scale; }
+
 int pool_grid(const PoolParams &p, int sm_count) {
-    long long grid = (long long)sm_count * 8;
+    int per_sm = 8;
+    if (pool_is_max3(p)) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pool_kernel<true>, kPoolThreads, 0);
+        if (per_sm < 1) per_sm = 1;
+    }
+    long long grid = (long long)sm_count * per_sm;
     if (grid > p.total_tiles) grid = p.total_tiles;
     if (grid < 1) grid = 1;
     return (int)grid;
 }
 
 cudaError_t pool_launch(const PoolParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
-    launch_layer(pool_kernel, grid, kPoolThreads, 0, s, p, blp);
+    if (pool_is_max3(p))
+        launch_layer(pool_kernel<true>, grid, kPoolThreads, 0, s, p, blp);
+    else
+        launch_layer(pool_kernel<false>, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();
 }
 

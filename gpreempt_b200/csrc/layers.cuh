@@ -155,7 +155,12 @@ struct Im2colParams {
     int fmt;                // PlaneFmt of the patch matrix
     int total_tiles;
     int tile_elems;         // 8-column vectors per tile
+    // Row-window mode (fp32 NCHW input): a tile is `win_w` consecutive output pixels of one
+    // output row; the input window they read is staged in shared memory with coalesced loads.
+    int win_w;              // 0 = off
+    int win_chunks;         // ceil(Wo / win_w)
 };
+constexpr int kIm2colWindowFloats = 4096;
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
 // LayerNorm over the channels of a [rows][H] matrix (H <= 1024, multiple of 8).  With `ids` set

@@ -928,6 +928,19 @@ int finalize_model(gpx_model &m) {
             // (twice the usual cap: a patch-matrix tile re-reads its lookup table, ~5 us per 256 vectors)
             q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2 * kMaxTileVectors, total / (8LL * m.sm_count) / 32 * 32));
             q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
+            {
+                // fp32 NCHW input: tiles of up to 64 output pixels of one output row, staged window
+                const char *off = getenv("GPX_IM2COL_WINDOW");
+                const int chunks = (n.W + 63) / 64;
+                const int win_w = (n.W + chunks - 1) / chunks;
+                const long long window = (long long)src.C * n.k * ((win_w - 1) * n.stride + n.k);
+                if (m.storages[src.storage].kind == Storage::InputF32 && window <= kIm2colWindowFloats &&
+                    !(off && off[0] == '0')) {
+                    q.win_w = win_w;
+                    q.win_chunks = chunks;
+                    q.total_tiles = n.N * n.H * chunks;
+                }
+            }
             ki.total_tiles = q.total_tiles;
             ki.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
             ki.flops = 0;
@@ -968,7 +981,8 @@ int finalize_model(gpx_model &m) {
             // accumulator buffer they give up (ResNet-50's 1x1 convolutions with K <= 512 lose 6 %,
             // BERT's dense layers and VGG's 3x3 convolutions gain 17-19 %).
             const char *wide = getenv("GPX_CGEMM_BN256");
-            if (m.fmt != PF_SPLIT && !head && cout_st % 256 == 0 && tiles128 / 2 >= m.sm_count &&
+            const bool try_split = wide && wide[0] == 's';  // experiment: 256-column tiles for two-plane operands
+            if ((m.fmt != PF_SPLIT || try_split) && !head && cout_st % 256 == 0 && tiles128 / 2 >= m.sm_count &&
                 (long long)eff_k * eff_k * eff_cin >= 768 &&
                 !(wide && wide[0] == '0'))
                 bn = 256;

@@ -65,6 +65,31 @@ __device__ __forceinline__ void planes_load8(const plane_bits *hi, const plane_b
     }
 }
 
+// The two halves of planes_load8: raw 16-byte vectors first, so that a caller can have many
+// loads in flight before it converts any of them.
+__device__ __forceinline__ void planes_fetch8(const plane_bits *hi, const plane_bits *lo, size_t off, int fmt,
+                                              uint4 &a, uint4 &b) {
+    a = *reinterpret_cast<const uint4 *>(hi + off);
+    if (fmt == PF_SPLIT) b = *reinterpret_cast<const uint4 *>(lo + off);
+}
+__device__ __forceinline__ void planes_decode8(const uint4 &a, const uint4 &b, int fmt, float (&x)[8]) {
+    const unsigned ah[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float2 v = pf_unpack2(ah[q], fmt);
+        x[2 * q] = v.x;
+        x[2 * q + 1] = v.y;
+    }
+    if (fmt == PF_SPLIT) {
+        const unsigned bl[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            x[2 * q] += __uint_as_float(bl[q] << 16);
+            x[2 * q + 1] += __uint_as_float(bl[q] & 0xffff0000u);
+        }
+    }
+}
+
 __device__ __forceinline__ void planes_store8(plane_bits *hi, plane_bits *lo, size_t off, int fmt,
                                               const float (&x)[8]) {
     unsigned h4[4];

@@ -202,3 +202,25 @@ def test_best_effort_tenant_under_a_latency_critical_model(gpx):
     assert 90 <= by_id["vgg_rt"]["requests"] <= 101
     assert rep["gpus"][0]["wordRaises"] > 0 and by_id["miniweather_be"]["resumes"] > 0
     assert by_id["miniweather_be"]["in_bytes"] == 0
+
+
+def test_mass_and_energy_drift_as_the_reference_prints_them(gpx):
+    """src/tests/test-sci.cpp:10-21: initialise, take the reductions, run one time step, print the
+    relative change of mass and total energy.  The figures of the reference's own kernels are in
+    tests/golden/miniweather_reference.json."""
+    import os
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "miniweather_reference.json")) as fp:
+        golden = json.load(fp)
+    ex = gpx.BaseExecutor()
+    ex.init("miniweather")
+    mass0, te0 = ex.model.reductions()
+    ex.execute()
+    mass, te = ex.model.reductions()
+    d_mass, d_te = (mass - mass0) / mass0, (te - te0) / te0
+    g0, g1 = golden["steps"]["0"], golden["steps"]["1"]
+    assert (mass0, te0) == (g0["mass"], g0["te"])
+    assert (mass, te) == (g1["mass"], g1["te"])          # same cells, same sum order: same doubles
+    assert d_mass == (g1["mass"] - g0["mass"]) / g0["mass"] and abs(d_mass) < 1e-9
+    assert d_te == (g1["te"] - g0["te"]) / g0["te"] and abs(d_te) < 1e-7
+    ex.clear()
