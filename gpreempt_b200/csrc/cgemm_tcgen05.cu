@@ -521,10 +521,13 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
         uint32_t v[32];
         if (first_k > 0) {
             for (int c = s_lo; c < s_hi; c += 32) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
+                // Spill layout: private to this kernel, so it is chosen for the stores: the j-th
+                // 16-byte piece of a 32-column chunk of all 128 rows is contiguous, one warp store
+                // writes 512 consecutive bytes (row-major rows 2 KB apart cost a line per thread).
+                const uint4 *src = reinterpret_cast<const uint4 *>(spill) + (size_t)(c / 32) * 8 * kCBM + row;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    uint4 q = src[j];
+                    uint4 q = src[j * kCBM];
                     v[4 * j + 0] = q.x;
                     v[4 * j + 1] = q.y;
                     v[4 * j + 2] = q.z;
@@ -756,10 +759,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 for (int c = s_lo; c < s_hi; c += 32) {
                     tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
-                    uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * Cfg::kTmemCols + c);
+                    uint4 *dst = reinterpret_cast<uint4 *>(spill) + (size_t)(c / 32) * 8 * kCBM + row;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        dst[j] = make_uint4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        dst[j * kCBM] = make_uint4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
             if (leader) {

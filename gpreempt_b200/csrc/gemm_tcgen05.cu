@@ -285,10 +285,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (first_k > 0) {
             // Resume: reload the spilled fp32 accumulator into tensor memory.
             for (int c = 0; c < kBN; c += 32) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(spill + (size_t)row * kBN + c);
+                // (layout of the spill area: see the store below)
+                const uint4 *src = reinterpret_cast<const uint4 *>(spill) + (size_t)(c / 32) * 8 * 128 + row;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    uint4 q = src[j];
+                    uint4 q = src[j * 128];
                     v[4 * j + 0] = q.x;
                     v[4 * j + 1] = q.y;
                     v[4 * j + 2] = q.z;
@@ -375,10 +376,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (int c = 0; c < kBN; c += 32) {
                     tmem_ld_32x32(t_acc + c, v);
                     tmem_ld_wait();
-                    uint4 *dst = reinterpret_cast<uint4 *>(spill + (size_t)row * kBN + c);
+                    // The spill area is private to this kernel, so its layout is chosen for the
+                    // stores: the j-th 16-byte piece of a 32-column chunk of all 128 rows is
+                    // contiguous and one warp store writes 512 consecutive bytes (with row-major
+                    // rows, 1 KB apart, every thread of a store touched its own line).
+                    uint4 *dst = reinterpret_cast<uint4 *>(spill) + (size_t)(c / 32) * 8 * 128 + row;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        dst[j] = make_uint4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        dst[j * 128] = make_uint4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
             if (leader) {
