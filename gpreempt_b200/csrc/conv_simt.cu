@@ -458,6 +458,62 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
     }
     __syncthreads();
     int iter = 0;
+    if (p.s2d) {
+        // Space-to-depth windows.  One thread-iteration gathers eight of the sixteen channels of one
+        // 2x2 block (hb, wb'), splits them once and stores them into the up to four pixels
+        // wb' - j (j = 0..3) whose window holds that block, at channel group j.  Blocks wb' >= Wo lie
+        // past the padded image and are zero; they fill the tail groups of a row's last pixels.
+        const int Wx = p.Wo + 3;
+        const unsigned vectors = (unsigned)p.in.l.N * p.Ho * Wx * 2;
+        // channel c of a block = (dy*2 + dx)*Cin + ci: the decomposition is tabulated once
+        for (int c = threadIdx.x; c < 16; c += kPoolThreads) {
+            const int q = c / p.Cin;
+            s_fh[c] = q < 4 ? (unsigned char)q : 255;
+            s_ci[c] = (unsigned char)(c - q * p.Cin);
+        }
+        for (;;) {
+            int tile;
+            __syncthreads();
+            if (dynamic) {
+                if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+                __syncthreads();
+                tile = s_tile;
+            } else {
+                tile = blp_claim(blp, iter);
+            }
+            if (tile < 0) break;
+            const unsigned begin = (unsigned)tile * p.tile_elems;
+            const unsigned end = begin + p.tile_elems < vectors ? begin + p.tile_elems : vectors;
+            for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+                const int half = (int)(e & 1);
+                const unsigned b = e >> 1;
+                const int wb = (int)(b % Wx);
+                const unsigned t = b / Wx;
+                const int hb = (int)(t % p.Ho), n = (int)(t / p.Ho);
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int c = half * 8 + u;
+                    const int q = s_fh[c];
+                    const int hi = 2 * hb + (q >> 1) - p.pad, wi = 2 * wb + (q & 1) - p.pad;
+                    float v = 0.f;
+                    if (q != 255 && hi >= 0 && hi < H && wi >= 0 && wi < W)
+                        v = p.in.f32[(((size_t)n * p.Cin + s_ci[c]) * H + hi) * W + wi];
+                    x[u] = v;
+                }
+                const size_t row0 = ((size_t)n * p.Ho + hb) * p.Wo;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int wp = wb - j;  // the pixel whose window has this block at position j
+                    if (wp >= 0 && wp < p.Wo)
+                        planes_store8(p.out_hi, p.out_lo, (row0 + wp) * 64 + j * 16 + half * 8, p.fmt, x);
+                }
+            }
+            ++iter;
+        }
+        if (threadIdx.x == 0) trace_end(blp, iter);
+        return;
+    }
     if (p.win_w > 0) {
         // Row-window mode.  The window of the tile - Cin x kh input rows, (win_w-1)*stride + kw
         // wide, zeros outside the image - is staged with coalesced loads; a patch-matrix element

@@ -159,6 +159,10 @@ struct Im2colParams {
     // output row; the input window they read is staged in shared memory with coalesced loads.
     int win_w;              // 0 = off
     int win_chunks;         // ceil(Wo / win_w)
+    // Space-to-depth window mode: the output is [N][Ho][Wo][64]; channel j*16 + (dy*2+dx)*Cin + ci
+    // of block (hb, wb) is input pixel (2*hb+dy-pad, 2*(wb+j)+dx-pad), j = 0..3, zero elsewhere;
+    // kh, kw, stride, K are unused.
+    int s2d;
 };
 constexpr int kIm2colWindowFloats = 4096;
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s);

@@ -545,6 +545,14 @@ int finalize_model(gpx_model &m) {
             (n.pad_w < 0 || n.pad_w == n.pad)) {
             n.tensor_core = true;
             n.via_im2col = true;
+            // A 7x7 stride-2 stem on at most four channels: instead of a patch matrix (308 MB at
+            // batch 32) the input is rearranged once into 2x2 blocks of 16 channels, and every
+            // block position stores the four consecutive blocks wb .. wb+3 (64 channels, 108 MB).
+            // An output pixel then reads four block rows, each one 64-channel row of that tensor:
+            // a four-tap row-shifted GEMM (K = 256) like the 3x3 convolutions.
+            const char *e = getenv("GPX_STEM_S2D");
+            if (n.k == 7 && !n.kw && n.stride == 2 && n.pad == 3 && src.C * 4 <= 16 && !(e && e[0] == '0'))
+                n.via_s2d = true;
         }
     }
     // 2. row order of every activation: what its 3x3 tensor-core consumers need, if they agree
@@ -591,7 +599,13 @@ int finalize_model(gpx_model &m) {
         s.dims[1] = n.via_im2col ? (n.k * n.k * src.C + 7) / 8 * 8 : src.C;
         s.dims[2] = n.H;
         s.dims[3] = n.W;
-        s.bytes = (size_t)n.N * s.dims[1] * n.H * n.W * sizeof(float);
+        if (n.via_s2d) {
+            s.name = n.name + ".s2d";
+            s.dims[1] = 64;
+            s.dims[2] = (src.H + 2 * n.pad + 1) / 2;
+            s.dims[3] = (src.W + 2 * n.pad + 1) / 2;
+        }
+        s.bytes = (size_t)n.N * s.dims[1] * s.dims[2] * s.dims[3] * sizeof(float);
         if (!n.via_im2col && stored_c(m, src) != src.C) s.cs = stored_c(m, src);
         n.sub_storage = m.add_storage(s);
         order.push_back(ACT_PLAIN);
@@ -607,6 +621,10 @@ int finalize_model(gpx_model &m) {
             w.cin_pad = n.via_im2col ? src.C : stored_c(m, src);
             w.cout_pad = m.storages[n.storage].kind == Storage::OutputF32 ? n.C : (stored_c(m, n) + 63) / 64 * 64;
             w.split_k = (int)((w.dims[2] * w.dims[3] * w.cin_pad + 63) / 64 * 64);
+            if (n.via_s2d) {
+                w.s2d = true;
+                w.split_k = 256;  // four block rows x four blocks x 16 channels
+            }
         }
 
     // 5. allocation: one buffer per storage, zero-filled, no sharing (src/model.cpp:101-113)
@@ -924,7 +942,16 @@ int finalize_model(gpx_model &m) {
             q.K = n.k * n.k * src.C;
             q.Kp = (int)pm.dims[1];
             q.M = n.N * n.H * n.W;
+            if (n.via_s2d) {
+                ki.name = n.name + ".s2d";
+                q.s2d = 1;
+                q.Ho = (int)pm.dims[2];
+                q.Wo = (int)pm.dims[3];
+                q.M = n.N * q.Ho * q.Wo;
+                q.Kp = 64;
+            }
             long long total = (long long)q.M * (q.Kp / 8);
+            if (n.via_s2d) total = (long long)n.N * q.Ho * (q.Wo + 3) * 2;  // half blocks, each stored up to four times
             // (twice the usual cap: a patch-matrix tile re-reads its lookup table, ~5 us per 256 vectors)
             q.tile_elems = (int)std::max<long long>(256, std::min<long long>(2 * kMaxTileVectors, total / (8LL * m.sm_count) / 32 * 32));
             q.total_tiles = (int)((total + q.tile_elems - 1) / q.tile_elems);
@@ -935,7 +962,7 @@ int finalize_model(gpx_model &m) {
                 const int win_w = (n.W + chunks - 1) / chunks;
                 const long long window = (long long)src.C * n.k * ((win_w - 1) * n.stride + n.k);
                 if (m.storages[src.storage].kind == Storage::InputF32 && window <= kIm2colWindowFloats &&
-                    !(off && off[0] == '0')) {
+                    !(off && off[0] == '0') && !n.via_s2d) {
                     q.win_w = win_w;
                     q.win_chunks = chunks;
                     q.total_tiles = n.N * n.H * chunks;
@@ -948,7 +975,7 @@ int finalize_model(gpx_model &m) {
             m.kernels.push_back(ki);
             in = &pm;
             eff_k = 1;
-            eff_cin = q.Kp;
+            eff_cin = n.via_s2d ? 64 : q.Kp;
         } else if (n.k == 1 && n.stride == 2) {
             const Storage &sub = m.storages[n.sub_storage];
             add_pool(n.name + ".subsample", view_of(m, src), sub, 1, 2, 0, 2);
@@ -992,6 +1019,11 @@ int finalize_model(gpx_model &m) {
         p.cin = eff_cin;
         p.cin_blocks = (eff_cin + 63) / 64;
         for (int t = 0; t < 9; ++t) p.tap_shift[t] = 0;
+        if (n.via_s2d) {
+            // four block rows; the four blocks of a row are the 64 channels of one stored pixel
+            p.taps = 4;
+            for (int t = 0; t < 4; ++t) p.tap_shift[t] = t * il.Ws;
+        }
         if (eff_k == 3) {
             for (int fh = 0; fh < 3; ++fh)
                 for (int fw = 0; fw < 3; ++fw) {
@@ -1202,6 +1234,8 @@ static int storage_set(gpx_model *m, Storage &s, const void *host, size_t len, c
                         for (int i = 0; i < I; ++i) {
                             float v = src[(((size_t)o * I + i) * KH + h) * KW + w];
                             size_t off = (size_t)o * K + ((size_t)h * KW + w) * s.cin_pad + i;
+                            // space-to-depth order: block row h/2, block w/2, channel ((h&1)*2 + (w&1))*I + i
+                            if (s.s2d) off = (size_t)o * K + (size_t)(h >> 1) * 64 + (size_t)(w >> 1) * 16 + (((h & 1) << 1) | (w & 1)) * I + i;
                             host_put(planes, s.plane_elems, off, v, fmt);
                         }
             GPX_CUDA(cudaMemcpyAsync(s.hi, planes.data(), planes.size() * sizeof(bf16_bits),

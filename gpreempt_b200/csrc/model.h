@@ -45,6 +45,7 @@ struct Storage {
     int cs = 0;                      // ActSplit: stored channels (logical channels padded to 64), 0 = dims[1]
     int cin_pad = 0, cout_pad = 0;   // Weight: padded channel counts of the tensor-core planes
     bool depthwise = false;          // Weight: [C][1][kh][kw] filter of a depthwise convolution
+    bool s2d = false;                // Weight: tensor-core planes in the space-to-depth order of the stem
     float init_mean = 0.f, init_std = 0.f;  // seeded initialiser; std 0 = He-normal / 0.01 default
     bool token_major = false;        // activations of sequence models: canonical [N][S][C]
     int parent = -1;                 // ActSplit: this tensor is a channel slice of that storage
@@ -72,6 +73,7 @@ struct Node {
     int sub_storage = -1;      // stride-2 1x1: compact copy of the sub-sampled input;
                                // few-channel input: patch matrix
     bool via_im2col = false;
+    bool via_s2d = false;      // 7x7 stride-2 stem on few channels: space-to-depth window tensor + four-tap GEMM
     int tables[3] = {-1, -1, -1};  // LayerNorm fed by embeddings: word, position, token-type tables
     int heads = 0;                 // Attention
     int Cs = 0;                    // stored output channels (C padded to 64 when the model pads)
