@@ -669,6 +669,17 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                     long long t_p1 = clock64();
                     e_tmem += t_p1 - t_p0;
 #endif
+                    if (p.cluster_reduce) {
+                        // Split K inside a cluster: the raw fp32 sum of this K range stays in this
+                        // CTA's shared memory (the ring is idle: a CTA of such a launch runs one
+                        // tile); rows are 16 bytes longer than BN floats so that the 32 rows of a
+                        // warp spread over the banks.
+                        float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(smem) + (size_t)row * (BN + 4) + c);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            dst[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                        continue;
+                    }
                     if (p.partial) {
                         // Split K: the raw fp32 sum of this K range goes to the workspace; the
                         // finishing kernel adds the ranges in split order and applies the rest.
@@ -789,6 +800,49 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
 
     tc_fence_before_sync();
     __syncthreads();
+    if (p.cluster_reduce) {
+        // Every CTA of the cluster has left its partial tile in shared memory (or has failed and set
+        // the error word: all waits above are bounded, so every thread gets here).  CTA r finishes
+        // rows [r, r+1) * 128/S of the output block: the S partial rows are read through distributed
+        // shared memory and added in split order from zero, exactly as splitk_finish_kernel adds the
+        // workspace rows, then bias, residual, activation and store by the same function.
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int S = p.k_splits;
+            const int rank = (int)cluster_ctarank();
+            const int otile = (int)blockIdx.x / S;
+            const int m_blk = otile / p.tiles_n, n_blk = otile - m_blk * p.tiles_n;
+            const int rows_per = kCBM / S;
+            const int img = p.fin.in_hs * p.fin.in_ws;
+            const uint32_t stage = smem_base;
+            for (int e = (int)threadIdx.x - 64; e < rows_per * (BN / 8); e += kCEpiThreads) {
+                const int lr = e / (BN / 8), c8 = e - lr * (BN / 8);
+                const int trow = rank * rows_per + lr;
+                const int vrow = m_blk * kCBM + trow;
+                const int col0 = n_blk * BN + c8 * 8;
+                if (vrow >= p.fin.m_rows || col0 >= p.fin.cout_padded) continue;
+                const int n_img = vrow / img;
+                const int r = vrow - n_img * img;
+                const int hs = r / p.fin.in_ws;
+                const int h = hs - p.fin.in_off;
+                const int w = r - hs * p.fin.in_ws - p.fin.in_off;
+                if (h < 0 || h >= p.fin.out.H || w < 0 || w >= p.fin.out.W) continue;
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = 0.f;
+                const uint32_t local = stage + (uint32_t)(((size_t)trow * (BN + 4) + c8 * 8) * sizeof(float));
+                for (int sidx = 0; sidx < S; ++sidx) {
+                    const uint32_t remote = cluster_map_shared(local, (uint32_t)sidx);
+                    const float4 a = ld_shared_cluster_f4(remote), b = ld_shared_cluster_f4(remote + 16);
+                    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+                    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+                }
+                splitk_apply(p.fin, n_img, h, w, col0, f);
+            }
+        }
+        // no CTA may exit (and release its shared memory) while a peer still reads it
+        cluster_sync_all();
+    }
     if (warp == 0 && lane == 0 && *abort_flag) {
         for (int spin = 0; spin < 64; ++spin) __nanosleep(1000);
     }
@@ -835,7 +889,59 @@ cudaError_t cgemm_prepare(int device) {
     return cudaSuccess;
 }
 
+template <int BN>
+static cudaError_t cgemm_launch_cluster(const CgemmParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)kCgemmThreads);
+    cfg.dynamicSmemBytes = CgemmCfg<BN>::kSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = (unsigned)p.k_splits;
+    at[1].val.clusterDim.y = 1;
+    at[1].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, cgemm_tcgen05_kernel<BN>, p, blp);
+}
+
+// CTAs of clusters of `cluster` CTAs of this kernel that the device keeps resident at once.
+int cgemm_max_cluster(int bn, int cluster) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)cluster);
+    cfg.blockDim = dim3((unsigned)kCgemmThreads);
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)cluster;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    cudaError_t err;
+    if (bn == 128) {
+        cfg.dynamicSmemBytes = CgemmCfg<128>::kSmem;
+        err = cudaOccupancyMaxActiveClusters(&clusters, cgemm_tcgen05_kernel<128>, &cfg);
+    } else {
+        cfg.dynamicSmemBytes = CgemmCfg<64>::kSmem;
+        err = cudaOccupancyMaxActiveClusters(&clusters, cgemm_tcgen05_kernel<64>, &cfg);
+    }
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return clusters * cluster;
+}
+
 cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s) {
+    if (p.cluster_reduce) {
+        // (256-column tiles are never split)
+        if (bn == 128) return cgemm_launch_cluster<128>(p, grid, blp, s);
+        return cgemm_launch_cluster<64>(p, grid, blp, s);
+    }
     if (bn == 256)
         launch_layer(cgemm_tcgen05_kernel<256>, grid, kCgemmThreads, CgemmCfg<256>::kSmem, s, p, blp);
     else if (bn == 128)

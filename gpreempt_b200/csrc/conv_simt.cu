@@ -656,28 +656,7 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
                 f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
                 f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
             }
-            const int col0 = c8 * 8;
-            if (p.bias) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += p.bias[col0 + j];  // bias buffers are padded
-            }
-            if (p.res_hi) {
-                size_t off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + col0;
-                float r[8];
-                planes_load8(p.res_hi, p.res_lo, off, p.res.fmt, r);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += r[j];
-            }
-            apply_act_n(f, p.relu);
-            if (p.out_f32) {
-                size_t off = ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid;
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (col0 + j < p.cout_valid) p.out_f32[off + col0 + j] = f[j];
-                continue;
-            }
-            planes_store8(p.out_hi, p.out_lo, (size_t)layout_row(p.out, n_img, h, w) * p.out.C + col0,
-                          p.out.fmt, f);
+            splitk_apply(p, n_img, h, w, c8 * 8, f);
         }
         ++iter;
         if (dynamic) __syncthreads();

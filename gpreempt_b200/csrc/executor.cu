@@ -40,8 +40,13 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         p.error = e->d_error;
         if (p.k_splits > 1) p.partial = e->d_partial;
         p.drop_on_stop = e->drop_tile_in_flight ? 1 : 0;
+        // The cluster reduction has no stop / resume form: preemptible executors keep the workspace
+        // and the finishing kernel.
+        if (e->kind != GPX_EXEC_BASE) p.cluster_reduce = 0;
         err = cgemm_launch(p, k.tile, k.grid, b, s);
     } else if (k.type == KernelType::SplitK) {
+        // The convolution kernel before it has already finished the tiles (cluster reduction).
+        if (k.fused_into_prev && e->kind == GPX_EXEC_BASE) return GPX_SUCC;
         SplitKParams p = k.splitk;
         p.partial = e->d_partial;
         err = splitk_launch(p, k.grid, b, s);

@@ -24,6 +24,25 @@ struct ActView {
 
 // ---- tensor-core convolution (cgemm_tcgen05.cu) ----------------------------------------------
 
+// Finishing pass of a split-K convolution (splitk_finish_kernel, or the cluster reduction inside
+// the convolution kernel): adds the per-split sums in split order, then bias, residual, activation.
+struct SplitKParams {
+    const float *partial;
+    int k_splits, partial_rows, partial_ld;
+    int m_rows, in_hs, in_ws, in_off;  // decode of a GEMM row, as in CgemmParams
+    int relu;
+    const float *bias;
+    const bf16_bits *res_hi, *res_lo;
+    ActLayout res;
+    bf16_bits *out_hi, *out_lo;
+    ActLayout out;
+    float *out_f32;
+    int cout_valid;
+    int cout_padded;       // multiple of 8 covered by the partial sums
+    int total_tiles;
+    int tile_elems;        // (row, 8-channel group) pairs per tile
+};
+
 struct CgemmSlot {
     int next_iter;  // first iteration of this CTA's static schedule that is not complete
     int k_done;     // K blocks already accumulated for it (spill area valid if > 0)
@@ -71,6 +90,12 @@ struct CgemmParams {
     int kb_per_split;        // K blocks per split (the last split may be shorter)
     float *partial;          // k_splits > 1: fp32 workspace [split][partial_rows][partial_ld]
     int partial_rows, partial_ld;
+    // Cluster reduction (non-preemptible launches only): the k_splits CTAs of one output block form
+    // a thread-block cluster, leave their partial tiles in shared memory and each finishes a share
+    // of the rows, reading its peers' tiles through distributed shared memory in split order - the
+    // additions of splitk_finish_kernel without the workspace round trip and the second launch.
+    int cluster_reduce;
+    SplitKParams fin;        // what the finishing pass needs (bias, residual, activation, output)
     CgemmSlot *slots;        // one per CTA of this kernel
     float *spill;            // [grid][128*BN] fp32, shared by the kernels of one executor
     int *error;              // {code, kernel*1000+cta}
@@ -78,6 +103,7 @@ struct CgemmParams {
 
 cudaError_t cgemm_prepare(int device);
 cudaError_t cgemm_launch(const CgemmParams &p, int bn, int grid, const BlpArgs &blp, cudaStream_t s);
+int cgemm_max_cluster(int bn, int cluster);  // CTAs of clusters of this size that can be resident at once
 size_t cgemm_spill_floats_per_cta();
 int cgemm_threads();
 
@@ -124,22 +150,33 @@ struct PoolParams {
 
 // Second half of a split-K tensor-core convolution: adds the per-split fp32 partial sums in
 // split order, then bias, residual and ReLU, and stores the result like the one-pass epilogue.
-struct SplitKParams {
-    const float *partial;
-    int k_splits, partial_rows, partial_ld;
-    int m_rows, in_hs, in_ws, in_off;  // decode of a GEMM row, as in CgemmParams
-    int relu;
-    const float *bias;
-    const bf16_bits *res_hi, *res_lo;
-    ActLayout res;
-    bf16_bits *out_hi, *out_lo;
-    ActLayout out;
-    float *out_f32;
-    int cout_valid;
-    int cout_padded;       // multiple of 8 covered by the partial sums
-    int total_tiles;
-    int tile_elems;        // (row, 8-channel group) pairs per tile
-};
+#if defined(__CUDACC__)
+// Tail of the finishing pass for eight channels (col0 .. col0+7) of output pixel (n_img, h, w):
+// f holds the sum of the splits.  One definition for both places that finish a split-K tile, so
+// they produce the same bits.
+__device__ __forceinline__ void splitk_apply(const SplitKParams &p, int n_img, int h, int w, int col0, float (&f)[8]) {
+    if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += p.bias[col0 + j];  // bias buffers are padded
+    }
+    if (p.res_hi) {
+        size_t off = (size_t)layout_row(p.res, n_img, h, w) * p.res.C + col0;
+        float r[8];
+        planes_load8(p.res_hi, p.res_lo, off, p.res.fmt, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += r[j];
+    }
+    apply_act_n(f, p.relu);
+    if (p.out_f32) {
+        size_t off = ((size_t)(n_img * p.out.H + h) * p.out.W + w) * p.cout_valid;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (col0 + j < p.cout_valid) p.out_f32[off + col0 + j] = f[j];
+        return;
+    }
+    planes_store8(p.out_hi, p.out_lo, (size_t)layout_row(p.out, n_img, h, w) * p.out.C + col0, p.out.fmt, f);
+}
+#endif
 cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
 // Patch matrix of a convolution whose input has too few channels for the tensor-core kernel

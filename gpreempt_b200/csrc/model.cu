@@ -1078,6 +1078,10 @@ int finalize_model(gpx_model &m) {
         const int split_from = e_all ? atoi(e_all) : 8;
         if (out_tiles * 2 <= m.sm_count && all_kb >= split_from) {
             int s_want = std::min(all_kb / min_kb, m.sm_count / out_tiles);
+            // Powers of two up to eight: the splits of an output block can then form a thread-block
+            // cluster and reduce through distributed shared memory (non-preemptible launches).
+            const char *e_cl = getenv("GPX_SPLITK_CLUSTER");
+            if (!(e_cl && e_cl[0] == '0')) s_want = s_want >= 8 ? 8 : (s_want >= 4 ? 4 : (s_want >= 2 ? 2 : 1));
             if (s_want >= 2) {
                 p.kb_per_split = (all_kb + s_want - 1) / s_want;
                 p.k_splits = (all_kb + p.kb_per_split - 1) / p.kb_per_split;
@@ -1173,6 +1177,18 @@ int finalize_model(gpx_model &m) {
         p.bias = nullptr;
         p.res_hi = p.res_lo = nullptr;
         p.relu = 0;
+        {
+            // Eligible for the cluster reduction (which executors use it: executor.cu): a power-of-two
+            // number of splits that divides the tile's rows, and every cluster resident at once.
+            const char *e_cl = getenv("GPX_SPLITK_CLUSTER");
+            const bool pow2 = p.k_splits == 2 || p.k_splits == 4 || p.k_splits == 8;
+            if (pow2 && bn <= 128 && !(e_cl && e_cl[0] == '0') && cgemm_max_cluster(bn, p.k_splits) >= kn.total_tiles &&
+                kn.grid == kn.total_tiles) {
+                p.cluster_reduce = 1;
+                p.fin = q;
+                kf.fused_into_prev = true;
+            }
+        }
         m.kernels.push_back(kn);
         m.kernels.push_back(kf);
     }

@@ -97,6 +97,7 @@ struct Kernel {
     DwConvParams dw{};
     StencilParams stencil{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
+    bool fused_into_prev = false;  // SplitK: a non-preemptible executor's convolution kernel finishes the tile itself
     int grid = 1;
     int threads = 256;
     int total_tiles = 0;

@@ -82,6 +82,33 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
         : "memory");
 }
 
+// ---- thread-block clusters: barrier and distributed shared memory -------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Every thread of every CTA of the cluster executes both halves; writes to shared memory made
+// before the arrive are visible to the peers after their wait.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `addr` in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+
 // 4-D tiled load (used for NHWC activations: coordinates c, w, h, n).
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void *tmap, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
