@@ -208,6 +208,34 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
 
+    // A non-preemptible launch knows its first tile without reading the cursor, and weights are
+    // never written by a kernel: its producer thread fetches the weight tiles of the first ring
+    // stages before it waits for the predecessor, so that their latency overlaps the
+    // predecessor's tail (batch-1 forwards are chains of such latencies).  Every other thread,
+    // and every thread of a preemptible launch, waits here.
+    const bool early_weights = !resumable && (int)blockIdx.x < total_tiles;
+    int prearmed = 0;  // ring stages whose barrier is armed and whose weight loads are in flight
+    if (early_weights && threadIdx.x == 0) {
+        const int tile = blockIdx.x;
+        const int n_blk = (tile / p.k_splits) % p.tiles_n;
+        const int main_kb = tile_kb_count(tile);
+        const int kb_base = tile_kb_begin(tile);
+        uint32_t ident_bytes = p.res_kb ? Cfg::kIdentBytes : 0u;
+        for (int kb = 0; kb < main_kb && kb < nst; ++kb) {
+            const int tap = (kb_base + kb) / p.cin_blocks;
+            const int cb = (kb_base + kb) - tap * p.cin_blocks;
+            const uint32_t bar = smem_u32(&ctl->full[kb]);
+            ctl->stage_msg[kb] = CMSG_DATA;
+            mbar_arrive_expect_tx(bar, (two_plane ? Cfg::kStageBytes : Cfg::kABytes + Cfg::kWBytes) + ident_bytes);
+            if (ident_bytes) tma_load_2d(smem_base + ident_off, &p.ident, bar, 0, 0);
+            ident_bytes = 0;
+            const uint32_t dst = smem_base + kb * stage_bytes;
+            const int w_col = tap * p.cin + cb * kCBK;
+            tma_load_2d(dst + w_off, &p.w_hi, bar, w_col, n_blk * BN);
+            if (two_plane) tma_load_2d(dst + 2 * Cfg::kABytes + Cfg::kWBytes, &p.w_lo, bar, w_col, n_blk * BN);
+            ++prearmed;
+        }
+    }
     pdl_wait();  // from here on the predecessor's results (and this executor's slots) are visible
     pdl_launch_dependents();
 
@@ -266,7 +294,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
             int msg = CMSG_EXIT;
             bool ok = true;
             // The identity tile travels with the first stage this CTA fills.
-            uint32_t ident_bytes = p.res_kb ? Cfg::kIdentBytes : 0u;
+            uint32_t ident_bytes = (p.res_kb && prearmed == 0) ? Cfg::kIdentBytes : 0u;
             TCK(t_prod0);
 #ifdef GPX_CGEMM_TIMING
             long long prod_wait = 0;
@@ -283,6 +311,22 @@ cgemm_tcgen05_kernel(const __grid_constant__ CgemmParams p, BlpArgs blp) {
                 const int kb_base = tile_kb_begin(tile);
                 for (int kb = kb0; kb < num_kb; ++kb) {
                     TCK(t_w0);
+                    if (it == first_iter && kb < prearmed) {
+                        // armed before the wait for the predecessor, weights already on their way:
+                        // only the activation tiles are missing
+                        const int tap = (kb_base + kb) / p.cin_blocks;
+                        const int cb = (kb_base + kb) - tap * p.cin_blocks;
+                        const uint32_t bar = smem_u32(&ctl->full[stage]);
+                        const uint32_t dst = smem_base + stage * stage_bytes;
+                        const int a_row = m_blk * kCBM + p.tap_shift[tap];
+                        tma_load_2d(dst, &p.a_hi, bar, cb * kCBK, a_row);
+                        if (two_plane) tma_load_2d(dst + Cfg::kABytes, &p.a_lo, bar, cb * kCBK, a_row);
+                        if (++stage == nst) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                        continue;
+                    }
                     if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, kCWaitLimitNs)) {
                         fail(101);
                         ok = false;
