@@ -4,6 +4,7 @@
 // getStopPoint (:269-278), resume (:280-298), init (:300-342).
 #include "executor.h"
 
+#include <algorithm>
 #include <atomic>
 #include <vector>
 
@@ -214,12 +215,95 @@ int gpx_exec_capture_graph(gpx_exec *e, gpx_stream stream) {
     GPX_REQUIRE(stream, GPX_FAIL, "graph capture needs a non-default stream");
     GPX_REQUIRE(!e->graph_exec, GPX_FAIL, "graph already captured");
     cudaStream_t s = as_stream(stream);
+    size_t nk = e->model->kernels.size();
+    // Projection shortcuts as a parallel branch (non-preemptible executors): the kernels of a
+    // convolution whose only consumer takes it as its residual, and whose input also feeds the main
+    // path, are captured on a second stream that forks after the block input and joins before the
+    // consumer.  At batch 1 every kernel is a few CTAs, so the branch runs beside the main path
+    // instead of in front of it.  A preemptible executor keeps one stream: its stop point is one
+    // index into the kernel list.  The split-K workspace is one per executor, so a branch that
+    // would use it while the main path does is left in line.
+    std::vector<char> side(nk, 0);
+    std::vector<int> join_before(nk, -1);  // kernel index -> first kernel of the branch it has to wait for
+    const gpx_model &m = *e->model;
+    const char *env_b = getenv("GPX_GRAPH_BRANCHES");
+    if (e->kind == GPX_EXEC_BASE && !m.sci && !(env_b && env_b[0] == '0')) {
+        auto uses_workspace = [&](size_t i) {
+            const Kernel &k = m.kernels[i];
+            return k.type == KernelType::Cgemm && k.cgemm.k_splits > 1 && !k.cgemm.cluster_reduce;
+        };
+        for (size_t c = 0; c < m.nodes.size(); ++c) {
+            const int d = m.nodes[c].residual;
+            if (d < 0 || m.nodes[d].op != Op::Conv || m.nodes[d].inputs.empty()) continue;
+            int users = 0, input_users = 0;
+            for (const Node &o : m.nodes) {  // consumer nodes (a residual is also listed among the inputs)
+                bool uses_d = o.residual == d, uses_in = o.residual == m.nodes[d].inputs[0];
+                for (int in : o.inputs) {
+                    uses_d = uses_d || in == d;
+                    uses_in = uses_in || in == m.nodes[d].inputs[0];
+                }
+                users += uses_d;
+                input_users += uses_in;
+            }
+            if (users != 1 || input_users < 2) continue;
+            // kernels of d (contiguous) and of the consumer c
+            size_t b0 = nk, b1 = 0, c0 = nk;
+            for (size_t i = 0; i < nk; ++i) {
+                if (m.kernels[i].node == d) {
+                    b0 = std::min(b0, i);
+                    b1 = std::max(b1, i + 1);
+                }
+                if (m.kernels[i].node == (int)c) c0 = std::min(c0, i);
+            }
+            if (b0 >= b1 || c0 == nk || b1 > c0) continue;
+            bool contiguous = true, clash = false, branch_ws = false, main_ws = false;
+            for (size_t i = b0; i < b1; ++i) {
+                contiguous = contiguous && m.kernels[i].node == d;
+                branch_ws = branch_ws || uses_workspace(i);
+            }
+            for (size_t i = b1; i < c0; ++i) {
+                main_ws = main_ws || uses_workspace(i);
+                clash = clash || side[i] || join_before[i] >= 0;
+            }
+            if (!contiguous || clash || (branch_ws && main_ws) || b1 == c0) continue;
+            for (size_t i = b0; i < b1; ++i) side[i] = 1;
+            join_before[c0] = (int)b0;
+        }
+    }
+    bool any_side = false;
+    for (char v : side) any_side = any_side || v;
+    cudaStream_t s2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    if (any_side) {
+        GPX_CUDA(cudaStreamCreateWithFlags(&s2, cudaStreamNonBlocking));
+        GPX_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        GPX_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+    }
     GPX_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     int st = exec_prologue(e, s);
-    size_t nk = e->model->kernels.size();
-    for (size_t i = 0; st == GPX_SUCC && i < nk; ++i) st = exec_launch(e, i, s);
+    cudaError_t cap = cudaSuccess;
+    for (size_t i = 0; st == GPX_SUCC && cap == cudaSuccess && i < nk; ++i) {
+        if (side[i] && (i == 0 || !side[i - 1])) {
+            cap = cudaEventRecord(ev_fork, s);
+            if (cap == cudaSuccess) cap = cudaStreamWaitEvent(s2, ev_fork, 0);
+        }
+        if (join_before[i] >= 0 && cap == cudaSuccess) {
+            cap = cudaEventRecord(ev_join, s2);
+            if (cap == cudaSuccess) cap = cudaStreamWaitEvent(s, ev_join, 0);
+        }
+        if (cap == cudaSuccess) st = exec_launch(e, i, side[i] ? s2 : s);
+    }
     g_kernel_launches.fetch_sub(st == GPX_SUCC ? nk : 0, std::memory_order_relaxed);  // captured, not run
     cudaError_t err = cudaStreamEndCapture(s, &e->graph);
+    if (s2) {
+        cudaStreamDestroy(s2);
+        cudaEventDestroy(ev_fork);
+        cudaEventDestroy(ev_join);
+    }
+    if (cap != cudaSuccess) {
+        set_error("graph capture with a parallel branch failed: %s", cudaGetErrorString(cap));
+        return GPX_FAIL;
+    }
     if (st != GPX_SUCC) return st;
     GPX_CUDA(err);
     GPX_CUDA(cudaGraphInstantiate(&e->graph_exec, e->graph, 0));
