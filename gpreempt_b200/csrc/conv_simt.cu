@@ -446,7 +446,7 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
     // once per CTA (K <= 1024).
     __shared__ int s_off[1024];
     __shared__ unsigned char s_fh[1024], s_fw[1024], s_ci[1024];
-    for (int k = threadIdx.x; k < p.Kp; k += kPoolThreads) {
+    for (int k = threadIdx.x; k < p.Kp && !p.planes_vec; k += kPoolThreads) {
         int tap = k / p.Cin;
         int ci = k - tap * p.Cin;
         int fh = tap / p.kw;
@@ -508,6 +508,45 @@ im2col_kernel(const __grid_constant__ Im2colParams p, BlpArgs blp) {
                     if (wp >= 0 && wp < p.Wo)
                         planes_store8(p.out_hi, p.out_lo, (row0 + wp) * 64 + j * 16 + half * 8, p.fmt, x);
                 }
+            }
+            ++iter;
+        }
+        if (threadIdx.x == 0) trace_end(blp, iter);
+        return;
+    }
+    if (p.planes_vec) {
+        const int Cs = p.in.l.C;            // stored channels of the input
+        const unsigned vectors = (unsigned)p.M * K8;
+        const int c8_per_tap = Cs / 8;
+        const int fmt = p.fmt;
+        for (;;) {
+            int tile;
+            __syncthreads();
+            if (dynamic) {
+                if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+                __syncthreads();
+                tile = s_tile;
+            } else {
+                tile = blp_claim(blp, iter);
+            }
+            if (tile < 0) break;
+            const unsigned begin = (unsigned)tile * p.tile_elems;
+            const unsigned end = begin + p.tile_elems < vectors ? begin + p.tile_elems : vectors;
+            for (unsigned e = begin + threadIdx.x; e < end; e += kPoolThreads) {
+                const int k8 = (int)(e % K8);
+                const unsigned m = e / K8;
+                const int wo = (int)(m % p.Wo);
+                const unsigned t = m / p.Wo;
+                const int ho = (int)(t % p.Ho), n = (int)(t / p.Ho);
+                const int tap = k8 / c8_per_tap, c8 = k8 - tap * c8_per_tap;
+                const int fh = tap / p.kw, fw = tap - fh * p.kw;
+                const int hi = ho * p.stride - p.pad + fh, wi = wo * p.stride - p.pad_w + fw;
+                uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+                if (fh < p.kh && hi >= 0 && hi < H && wi >= 0 && wi < W)
+                    planes_fetch8(p.in.hi, p.in.lo, (size_t)layout_row(p.in.l, n, hi, wi) * Cs + c8 * 8, fmt, a, b);
+                const size_t off = (size_t)m * p.Kp + k8 * 8;
+                *reinterpret_cast<uint4 *>(p.out_hi + off) = a;
+                if (fmt == PF_SPLIT) *reinterpret_cast<uint4 *>(p.out_lo + off) = b;
             }
             ++iter;
         }

@@ -200,6 +200,11 @@ struct Im2colParams {
     // of block (hb, wb) is input pixel (2*hb+dy-pad, 2*(wb+j)+dx-pad), j = 0..3, zero elsewhere;
     // kh, kw, stride, K are unused.
     int s2d;
+    // Plane mode (the input is an activation in planes with a multiple of eight stored channels):
+    // eight consecutive columns are eight channels of one tap, so a thread-iteration copies one
+    // 16-byte vector per plane, or writes zeros where the tap falls outside the image.
+    int planes_vec;
+    int pad_w;              // horizontal padding (plane mode; `pad` is the vertical one)
 };
 constexpr int kIm2colWindowFloats = 4096;
 cudaError_t im2col_launch(const Im2colParams &p, int grid, const BlpArgs &blp, cudaStream_t s);

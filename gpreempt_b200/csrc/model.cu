@@ -554,6 +554,15 @@ int finalize_model(gpx_model &m) {
             if (n.k == 7 && !n.kw && n.stride == 2 && n.pad == 3 && src.C * 4 <= 16 && !(e && e[0] == '0'))
                 n.via_s2d = true;
         }
+        // Shapes the row-shift scheme does not take (one-sided 1x7 / 7x1 / 1x3 / 3x1 filters, 5x5,
+        // unpadded or stride-2 3x3 on a plain input: Inception-v3): a patch matrix copied from the
+        // planes, 16 bytes per tap and eight channels, then a 1x1 tensor-core GEMM.
+        const char *e_pm = getenv("GPX_PATCH_GEMM");
+        if (allow_tc && !n.tensor_core && out.kind == Storage::ActSplit && in.kind == Storage::ActSplit &&
+            stored_c(m, n) % 64 == 0 && stored_c(m, src) % 8 == 0 && n.residual < 0 && !(e_pm && e_pm[0] == '0')) {
+            n.tensor_core = true;
+            n.via_im2col = true;
+        }
     }
     // 2. row order of every activation: what its 3x3 tensor-core consumers need, if they agree
     std::vector<int> order(m.storages.size(), ACT_PLAIN);
@@ -597,6 +606,8 @@ int finalize_model(gpx_model &m) {
         // the last 64-column K block, and the matrix (written once, read once) stays 21 % smaller
         // than with rows padded to 64 columns (7x7x3 = 147 -> 152 instead of 192).
         s.dims[1] = n.via_im2col ? (n.k * n.k * src.C + 7) / 8 * 8 : src.C;
+        if (n.via_im2col && m.storages[src.storage].kind == Storage::ActSplit)
+            s.dims[1] = (int64_t)n.k * (n.kw ? n.kw : n.k) * stored_c(m, src);
         s.dims[2] = n.H;
         s.dims[3] = n.W;
         if (n.via_s2d) {
@@ -618,7 +629,8 @@ int finalize_model(gpx_model &m) {
             Storage &w = m.storages[n.weight];
             w.wants_split = true;
             // rows of the planes: [tap][stored input channel], zero where the channel is padding
-            w.cin_pad = n.via_im2col ? src.C : stored_c(m, src);
+            // patch columns are [tap][channel]: the logical channels of an fp32 input, the stored ones of planes
+            w.cin_pad = (n.via_im2col && m.storages[src.storage].kind == Storage::InputF32) ? src.C : stored_c(m, src);
             w.cout_pad = m.storages[n.storage].kind == Storage::OutputF32 ? n.C : (stored_c(m, n) + 63) / 64 * 64;
             w.split_k = (int)((w.dims[2] * w.dims[3] * w.cin_pad + 63) / 64 * 64);
             if (n.via_s2d) {
@@ -942,6 +954,14 @@ int finalize_model(gpx_model &m) {
             q.K = n.k * n.k * src.C;
             q.Kp = (int)pm.dims[1];
             q.M = n.N * n.H * n.W;
+            if (m.storages[src.storage].kind == Storage::ActSplit) {
+                ki.name = n.name + ".patches";
+                q.planes_vec = 1;
+                q.kh = n.k;
+                q.kw = n.kw ? n.kw : n.k;
+                q.pad_w = n.pad_w >= 0 ? n.pad_w : n.pad;
+                q.K = q.Kp;
+            }
             if (n.via_s2d) {
                 ki.name = n.name + ".s2d";
                 q.s2d = 1;
