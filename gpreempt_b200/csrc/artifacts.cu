@@ -47,6 +47,7 @@ static const char *kernel_type_name(KernelType t) {
         case KernelType::AttentionTc: return "attention_tc_kernel";
         case KernelType::TransposeV: return "transpose_v_kernel";
         case KernelType::Stencil: return "miniweather_step_kernel";
+        case KernelType::DenseRows: return "dense_rows_kernel";
     }
     return "kernel";
 }

@@ -703,6 +703,93 @@ splitk_finish_kernel(const __grid_constant__ SplitKParams p, BlpArgs blp) {
     if (threadIdx.x == 0) trace_end(blp, iter);
 }
 
+__global__ void __launch_bounds__(kPoolThreads)
+dense_rows_kernel(const __grid_constant__ DenseRowsParams p, BlpArgs blp) {
+    pdl_enter();
+    __shared__ int s_tile;
+    __shared__ float s_part[kPoolThreads / 32][8];
+    const bool dynamic = blp.preempted != nullptr;
+    if (threadIdx.x == 0) trace_begin(blp);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int kStep = kPoolThreads * 8;  // elements of one row the CTA reads per step (4 KB per plane)
+    constexpr int kU = 4;
+    int iter = 0;
+    for (;;) {
+        int tile;
+        __syncthreads();
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = blp_claim(blp, iter);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = blp_claim(blp, iter);
+        }
+        if (tile < 0) break;
+        // A tile is eight output columns, one after the other; the whole CTA walks one weight row
+        // with consecutive threads on consecutive 16-byte vectors, so that DRAM sees long
+        // contiguous reads (one warp per row opened a new DRAM page with every 512 bytes and
+        // reached a quarter of the bandwidth).
+        for (int c = 0; c < 8; ++c) {
+            const int n = tile * 8 + c;
+            if (n >= p.cout) break;
+            float acc[8];
+#pragma unroll
+            for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+            const size_t w_row = (size_t)n * p.w_ld;
+            for (int k0 = threadIdx.x * 8; k0 < p.K; k0 += kStep * kU) {
+                uint4 wa[kU], wb[kU];
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    wa[u] = wb[u] = make_uint4(0, 0, 0, 0);
+                    if (k0 + u * kStep < p.K) planes_fetch8(p.w_hi, p.w_lo, w_row + k0 + u * kStep, p.fmt, wa[u], wb[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    if (k0 + u * kStep >= p.K) break;
+                    float w[8];
+                    planes_decode8(wa[u], wb[u], p.fmt, w);
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        if (m < p.M) {
+                            float a[8];
+                            planes_load8(p.a_hi, p.a_lo, (size_t)m * p.a_ld + k0 + u * kStep, p.fmt, a);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[m] = fmaf(a[j], w[j], acc[m]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int sh = 16; sh >= 1; sh >>= 1)
+#pragma unroll
+                for (int m = 0; m < 8; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], sh);
+            __syncthreads();  // the previous column's partial sums have been consumed
+            if (lane == 0)
+#pragma unroll
+                for (int m = 0; m < 8; ++m) s_part[wid][m] = acc[m];
+            __syncthreads();
+            if (threadIdx.x < p.M) {
+                const int m = threadIdx.x;
+                float v = 0.f;
+#pragma unroll
+                for (int w8 = 0; w8 < kPoolThreads / 32; ++w8) v += s_part[w8][m];  // fixed order
+                v = apply_act(v + (p.bias ? p.bias[n] : 0.f), p.relu);
+                if (p.out_f32)
+                    p.out_f32[(size_t)m * p.cout + n] = v;
+                else
+                    planes_store1(p.out_hi, p.out_lo, (size_t)m * p.out_ld + n, p.fmt, v);
+            }
+        }
+        ++iter;
+    }
+    if (threadIdx.x == 0) trace_end(blp, iter);
+}
+
+cudaError_t dense_rows_launch(const DenseRowsParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
+    launch_layer(dense_rows_kernel, grid, kPoolThreads, 0, s, p, blp);
+    return cudaGetLastError();
+}
+
 cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s) {
     launch_layer(splitk_finish_kernel, grid, kPoolThreads, 0, s, p, blp);
     return cudaGetLastError();

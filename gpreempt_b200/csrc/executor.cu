@@ -66,6 +66,8 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         err = transpose_v_launch(k.attn, k.grid, b, s);
     } else if (k.type == KernelType::Im2col) {
         err = im2col_launch(k.im2col, k.grid, b, s);
+    } else if (k.type == KernelType::DenseRows) {
+        err = dense_rows_launch(k.dense, k.grid, b, s);
     } else if (k.type == KernelType::Stencil) {
         err = stencil_launch(k.stencil, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {

@@ -179,6 +179,24 @@ __device__ __forceinline__ void splitk_apply(const SplitKParams &p, int n_img, i
 #endif
 cudaError_t splitk_launch(const SplitKParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
 
+// Dense layer on at most eight rows (batch <= 8 classifiers: VGG's 25088 -> 4096 -> 4096 -> 1000,
+// ResNet's 2048 -> 1000): a matrix-vector product streams the weights once and is bound by HBM,
+// where a 128-row tensor-core tile would idle.  One warp per output column; every lane walks the K
+// range in steps of 256 with eight elements per step, fp32 FMAs in a fixed order, a fixed shuffle
+// tree adds the lanes: the result does not depend on the grid.
+struct DenseRowsParams {
+    const bf16_bits *a_hi, *a_lo;  // input rows, planes
+    const bf16_bits *w_hi, *w_lo;  // weight planes [Cout][w_ld]
+    const float *bias;
+    bf16_bits *out_hi, *out_lo;    // output planes (row stride out_ld) or
+    float *out_f32;                // fp32 [M][cout] (graph heads)
+    int M, K, cout;
+    int a_ld, w_ld, out_ld;
+    int relu, fmt;
+    int total_tiles;               // eight output columns per tile
+};
+cudaError_t dense_rows_launch(const DenseRowsParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
+
 // Patch matrix of a convolution whose input has too few channels for the tensor-core kernel
 // (the stem): row m = output pixel, column k = (fh, fw, ci), zero-padded to a multiple of 64
 // columns, written as hi/lo planes so a 1x1 tensor-core GEMM can consume it.

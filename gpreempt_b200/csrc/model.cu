@@ -931,6 +931,51 @@ int finalize_model(gpx_model &m) {
             m.kernels.push_back(kn);
             continue;
         }
+        // A dense layer on at most eight rows: matrix-vector products on the CUDA cores, bound by
+        // reading the weights once (GPX_DENSE_ROWS=0 keeps the tensor-core tile).
+        {
+            const char *e_dr = getenv("GPX_DENSE_ROWS");
+            const bool one_pixel = n.k == 1 && n.stride == 1 && n.pad == 0 && src.H == 1 && src.W == 1;
+            const bool dense = one_pixel || full_map_dense(n, src);
+            const Storage &in0 = m.storages[src.storage];
+            const int k_len = (one_pixel ? 1 : n.k * n.k) * stored_c(m, src);
+            if (dense && !n.via_im2col && n.N <= 8 && n.residual < 0 && in0.kind == Storage::ActSplit &&
+                in0.layout.order == ACT_PLAIN && k_len % 8 == 0 && !(e_dr && e_dr[0] == '0')) {
+                const Storage &w = m.storages[n.weight];
+                const bool head = out.kind == Storage::OutputF32;
+                Kernel kd;
+                kd.name = n.name;
+                kd.node = (int)ni;
+                kd.type = KernelType::DenseRows;
+                DenseRowsParams &q = kd.dense;
+                q.a_hi = in0.hi;
+                q.a_lo = in0.lo;
+                q.a_ld = src.H * src.W * stored_c(m, src);
+                q.w_hi = w.hi;
+                q.w_lo = w.lo;
+                q.w_ld = w.split_k;
+                q.bias = m.storages[n.bias].dptr;
+                q.M = n.N;
+                q.K = k_len;
+                q.cout = head ? n.C : stored_c(m, n);
+                q.relu = n.act;
+                q.fmt = m.fmt;
+                if (head) {
+                    q.out_f32 = out.dptr;
+                } else {
+                    q.out_hi = out.hi;
+                    q.out_lo = out.lo;
+                    q.out_ld = out.layout.C;
+                }
+                q.total_tiles = (q.cout + 7) / 8;
+                kd.total_tiles = q.total_tiles;
+                kd.grid = (int)std::min<long long>((long long)m.sm_count * 8, q.total_tiles);
+                kd.flops = flops;
+                kd.bytes = bytes;
+                m.kernels.push_back(kd);
+                continue;
+            }
+        }
         // tensor-core convolution
         const Storage *in = &m.storages[src.storage];
         int eff_k = n.k, eff_cin = stored_c(m, src);

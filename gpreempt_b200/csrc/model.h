@@ -81,7 +81,7 @@ struct Node {
     int scale = -1, shift = -1;    // Affine, or a pooling node that normalises its input: Vec storages
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV, Stencil };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV, Stencil, DenseRows };
 
 struct Kernel {
     std::string name;
@@ -96,6 +96,7 @@ struct Kernel {
     AttnParams attn{};
     DwConvParams dw{};
     StencilParams stencil{};
+    DenseRowsParams dense{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     bool fused_into_prev = false;  // SplitK: a non-preemptible executor's convolution kernel finishes the tile itself
     int grid = 1;
