@@ -121,6 +121,15 @@ public:
         return Status::Succ;
     }
 
+    // "miniweather" (the reference's sciCompute workload, src/executor.cpp:14): a simulation state
+    // instead of "data" / "heads".
+    bool is_scientific() {
+        size_t idx;
+        return m_ && gpx_model_find(m_, "data", &idx) != GPX_SUCC && gpx_model_find(m_, "state", &idx) == GPX_SUCC;
+    }
+    // reductions(mass, te), src/workloads/miniweather.cu:650-677.
+    Status reductions(double &mass, double &te) { return (Status)gpx_model_reductions(m_, &mass, &te); }
+
     gpx_model *handle() const { return m_; }
 
 private:

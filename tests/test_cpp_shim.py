@@ -37,6 +37,17 @@ def test_c99_client_compiles_links_and_runs(tmp_path):
 
 def test_reference_named_classes_compile_and_link(tmp_path):
     _compile(tmp_path, "g++", "c++17", "test_dnn_blp.cpp", "test_dnn_blp")
+    _compile(tmp_path, "g++", "c++17", "test_sci.cpp", "test_sci")
+
+
+@pytest.mark.gpu
+def test_port_of_the_reference_sci_test(gpx, tmp_path):
+    """src/tests/test-sci.cpp through foo::BaseExecutor / foo::BLPExecutor: drift of mass and
+    energy after one miniWeather time step, and a preempted time step that ends in the same state."""
+    exe = _compile(tmp_path, "g++", "c++17", "test_sci.cpp", "test_sci")
+    res = subprocess.run([exe, "miniweather"], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, (res.stdout, res.stderr)
+    assert "d_mass:" in res.stdout and "d_te:" in res.stdout and "PASS" in res.stdout
 
 
 @pytest.mark.gpu
