@@ -39,15 +39,16 @@ int main(int argc, char **argv) {
     CHECK_STATUS(blp.execute(stream));
     blp.running = true;
     *(volatile int *)flag = 1;
-    CHECK_STATUS(blp.getStopPoint(stream));
+    GPUStreamSynchronize(stream);  // drained
     int stops = 0;
     for (int round = 0; round < 64; ++round) {
         *(volatile int *)flag = 0;
+        // resume reads the stop point itself (BLPExecutor::resume, src/executor.cpp:280-298)
         CHECK_STATUS(blp.resume(stream));
-        if (blp.stop_index() < 0) break;
+        if (blp.stop_index() < 0) break;  // nothing had been stopped: the time step is complete
         ++stops;
-        *(volatile int *)flag = 1;  // stop the next kernels too, a few times
-        if (round > 3) *(volatile int *)flag = 0;
+        if (round < 3) *(volatile int *)flag = 1;  // stop what was just relaunched, a few times
+        GPUStreamSynchronize(stream);
     }
     GPUStreamSynchronize(stream);
     double bm, bt;
