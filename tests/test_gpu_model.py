@@ -719,3 +719,20 @@ def test_inception_v3_bfloat16_and_preempt_resume(gpx, oracle):
         assert np.array_equal(ex.get_output("heads"), want), f"trial {trial}"
     assert stops > 0
     base.clear(), ex.clear(), word.destroy(), s.destroy()
+
+
+@pytest.mark.parametrize("name,model", [("vgg", "vgg19"), ("resnet152", "resnet152")])
+def test_reference_config_models_at_batch_one_match_oracle(gpx, oracle, name, model):
+    """The two models of the reference's config/A.json under the names that file uses (`vgg`,
+    `resnet152`), batch 1 fp32 as the reference compiles them (scripts/compile/compile.py:27-31):
+    logits against the CPU forward of the same graph."""
+    ex = gpx.BaseExecutor()
+    ex.init(name, batch=1, seed=3)
+    data = _data(gpx, 1, seed=4)
+    ex.set_input("data", data)
+    ex.execute()
+    got = ex.get_output("heads")
+    want = oracle.forward(model, ex.model.params(), data, fast=True)
+    assert got.shape == want.shape == (1, 1000)
+    assert _rel(got, want) <= RTOL_FP32
+    ex.clear()
