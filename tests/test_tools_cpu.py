@@ -2,6 +2,8 @@
 argument formats and the configurations they generate, checked without a GPU."""
 import json
 import os
+import subprocess
+import sys
 
 import pytest
 
@@ -69,3 +71,22 @@ def test_bench_workload_config_is_the_baseline_configuration():
     assert bench.MICROBENCH_AXPY_ELEMS * 4 == 4 << 30   # 4 GiB per vector
     # sum-of-layers roofline: a layer is bound by whichever of its two times is longer
     assert abs(bench.model_roofline_ms([(2e12, 1e9), (1e9, 6.5e9)], 1000.0, 6500.0) - (2.0 + 1.0)) < 1e-9
+
+
+def test_reference_workloads_tool_arguments_and_task_lists():
+    from gpreempt_b200 import reference_workloads as rw
+
+    assert set(rw.WORKLOADS) == {"A", "B", "C", "D", "E", "Y"}
+    for name, tasks in rw.WORKLOADS.items():
+        n_lc = 5 if name in "DE" else 1
+        assert all(t["client"]["priority"] == 0 and t["id"].endswith("_rt") for t in tasks[:n_lc])
+        assert all(t["client"]["priority"] == 1 for t in tasks[n_lc:])
+        kind = "poisson" if name == "E" else "periodic"
+        assert all(t["load"]["type"] == kind and t["client"]["batch_size"] == 1 for t in tasks)
+    assert [t["load"]["frequency"] for t in rw.WORKLOADS["D"]] == [20] * 5 + [100] * 5
+    assert [t["load"]["frequency"] for t in rw.WORKLOADS["B"]] == [220, 220]
+    assert len(rw.WORKLOADS["C"]) == 6
+    assert rw.WORKLOADS["Y"][1]["client"]["model_name"] == "miniweather"
+    res = subprocess.run([sys.executable, "-m", "gpreempt_b200.reference_workloads", "--only", "Q"],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert res.returncode != 0 and "unknown workload" in res.stderr
