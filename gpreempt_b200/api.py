@@ -318,7 +318,8 @@ class Model:
 
     def get(self, name: str, stream=None) -> np.ndarray:
         shape = self.shape(name)
-        out = np.empty(shape, np.float32)
+        stype = self.get_storage_info(self.find_storage_idx(name))["stype"]
+        out = np.empty(shape, np.uint32 if stype == "uint32" else np.float32)
         check(B.load().gpx_model_get(self.handle, name.encode(),
                                      out.ctypes.data_as(ctypes.c_void_p), out.nbytes, _h(stream)))
         check(B.load().gpx_stream_sync(_h(stream)))
@@ -373,6 +374,16 @@ class Model:
         check(B.load().gpx_model_reductions(self.handle, ctypes.byref(mass), ctypes.byref(te)))
         return mass.value, te.value
 
+    def graph_info(self) -> dict:
+        """Sizes and iteration counts of a graph-analytics model ("bfs:<prefix>", "sssp:...",
+        "cc:...", "pagerank:..."; the workloads of src/workloads/graphcompute.cu)."""
+        v, e = ctypes.c_uint64(), ctypes.c_uint64()
+        listed, live, conv = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        check(B.load().gpx_model_graph_info(self.handle, ctypes.byref(v), ctypes.byref(e), ctypes.byref(listed),
+                                            ctypes.byref(live), ctypes.byref(conv)))
+        return {"vertices": v.value, "edges": e.value, "listed_iterations": listed.value,
+                "live_iterations": live.value, "converged": bool(conv.value)}
+
     def clear(self) -> None:
         if self.handle:
             B.load().gpx_model_close(self.handle)
@@ -389,11 +400,19 @@ class Executor:
         self.handle = ctypes.c_void_p()
         self.batch = 1
         self.dtype = "float32"
+        self.graph_path = ""
+
+    def set_graph_path(self, path: str) -> None:
+        """Executor::set_graph_path (src/executor.cpp:18-21): the dataset of "cc", "bfs", "pagerank"
+        and "sssp", given before init."""
+        self.graph_path = path
 
     def init(self, workload: str, batch: int = 1, seed: int | None = None, seq_len: int = 0,
              dtype: str | None = None) -> None:
         if dtype is not None:
             self.dtype = dtype
+        if workload in ("cc", "bfs", "pagerank", "sssp"):
+            workload = workload + ":" + self.graph_path
         self.model = Model(workload, batch=batch, dtype=self.dtype, seq_len=seq_len)
         self.batch = batch
         if seed is not None:

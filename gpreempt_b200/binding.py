@@ -126,6 +126,8 @@ _SIGS = {
     "gpx_model_export_json": [vp, ctypes.c_char_p, sz, P(sz)],
     "gpx_model_export_dir": [vp, ctypes.c_char_p],
     "gpx_model_reductions": [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)],
+    "gpx_model_graph_info": [vp, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
+                             ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
     "gpx_exec_create": [vp, ci, P(vp)],
     "gpx_exec_destroy": [vp],
     "gpx_exec_set_word": [vp, vp],

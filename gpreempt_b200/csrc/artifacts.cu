@@ -48,6 +48,7 @@ static const char *kernel_type_name(KernelType t) {
         case KernelType::TransposeV: return "transpose_v_kernel";
         case KernelType::Stencil: return "miniweather_step_kernel";
         case KernelType::DenseRows: return "dense_rows_kernel";
+        case KernelType::GraphWl: return "graphwl_kernel";
     }
     return "kernel";
 }

@@ -70,6 +70,8 @@ int exec_launch(gpx_exec *e, size_t idx, cudaStream_t s) {
         err = dense_rows_launch(k.dense, k.grid, b, s);
     } else if (k.type == KernelType::Stencil) {
         err = stencil_launch(k.stencil, k.grid, b, s);
+    } else if (k.type == KernelType::GraphWl) {
+        err = graphwl_launch(k.graphwl, k.grid, b, s);
     } else if (k.type == KernelType::ConvSimt) {
         err = conv_launch(k.conv, k.tile, k.grid, b, s);
     } else {

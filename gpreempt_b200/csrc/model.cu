@@ -349,6 +349,11 @@ int build_builtin_graph(gpx_model &m, const std::string &name, const gpx_model_o
         m.name = name;
         return build_miniweather(m, name, opts);
     }
+    if (is_graph_workload(name)) {
+        // The graph-analytics workloads (Executor::init, src/executor.cpp:24-34).
+        m.name = name;
+        return build_graph_workload(m, name, opts);
+    }
     // Storage and tensor-core operand format between layers; inputs, outputs, parameters and all
     // arithmetic outside the tensor-core products stay fp32.
     m.fmt = PF_SPLIT;
@@ -1556,6 +1561,7 @@ int gpx_model_shape(gpx_model *m, const char *name, int64_t dims[4], int *rank) 
 
 int gpx_model_init_random(gpx_model *m, uint64_t seed) {
     GPX_REQUIRE(m, GPX_FAIL, "NULL model");
+    if (m->graph_algo >= 0) return GPX_SUCC;  // nothing to initialise: every run starts from its own init kernel
     if (m->sci) {
         // No parameters: the call puts the simulation back to its initial state.
         for (const char *name : {"state", "state_tmp", "state_tmp2"})

@@ -7,6 +7,7 @@
 #include "common.h"
 #include "layers.cuh"
 #include "stencil.h"
+#include "graphwl.h"
 
 #include <string>
 #include <unordered_map>
@@ -81,7 +82,7 @@ struct Node {
     int scale = -1, shift = -1;    // Affine, or a pooling node that normalises its input: Vec storages
 };
 
-enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV, Stencil, DenseRows };
+enum class KernelType { ConvSimt, Cgemm, Pool, Im2col, SplitK, LayerNorm, Attention, DwConv, AttentionTc, TransposeV, Stencil, DenseRows, GraphWl };
 
 struct Kernel {
     std::string name;
@@ -97,6 +98,7 @@ struct Kernel {
     DwConvParams dw{};
     StencilParams stencil{};
     DenseRowsParams dense{};
+    GraphWlParams graphwl{};
     int tile = 0;  // ConvSimt: ConvTile; Cgemm: BN
     bool fused_into_prev = false;  // SplitK: a non-preemptible executor's convolution kernel finishes the tile itself
     int grid = 1;
@@ -132,6 +134,12 @@ struct gpx_model {
     float sci_dt = 0.f, sci_dx = 0.f, sci_dz = 0.f;
     std::vector<float> sci_hy_dens_cell, sci_hy_dens_theta_cell;  // host copies for the reductions
     std::vector<float> sci_initial;                               // initial state, to start over
+    // Graph analytics (graphwl.h): `sci` is set as well (no graph nodes, no "data"/"heads"); one
+    // execute is one run of the algorithm to its fixed point.
+    int graph_algo = -1;
+    uint64_t graph_vertices = 0, graph_edges = 0;
+    int graph_iterations = 0;     // live iterations of the run that sized the kernel list
+    int *graph_active = nullptr;  // device: iteration flags (owned through `scratch`)
 
     int add_storage(const gpx::Storage &s);
     int find(const std::string &name) const;

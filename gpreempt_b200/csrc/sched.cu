@@ -915,6 +915,10 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         const Json &jc = jt["client"], &jl = jt["load"];
         t->name = jc["name"].as_string();
         t->model_name = jc["model_name"].as_string();
+        // The graph-analytics tenants name their dataset beside the model (config/Z.json:
+        // "model_name": "bfs", "graph_path": "crankseg_1/crankseg_1.bel").
+        if (jc.has("graph_path") && t->model_name.find(':') == std::string::npos)
+            t->model_name += ":" + jc["graph_path"].as_string();
         t->priority = (int)jc["priority"].as_int(1);
         t->batch = (int)jc["batch_size"].as_int(1);
         t->seq_len = (int)jc["seq_len"].as_int(0);

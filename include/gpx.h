@@ -287,6 +287,22 @@ int gpx_model_export_dir(gpx_model *m, const char *dir);
  * gpx_model_reductions is reductions(mass, te) (miniweather.cu:650-677): domain mass and total
  * energy of "state".  gpx_model_init_random puts the simulation back to its initial state. */
 int gpx_model_reductions(gpx_model *m, double *mass, double *te);
+/* The graph-analytics workloads, model names "bfs:<prefix>", "sssp:<prefix>", "cc:<prefix>" and
+ * "pagerank:<prefix>" (Executor::init with set_graph_path, src/executor.cpp:18-34): <prefix>.col,
+ * <prefix>.dst and, for sssp, <prefix>.val are the files GraphCompute*::read_graph reads
+ * (src/workloads/graphcompute.cu:15-45, 345-353); a relative prefix is taken under the directory in
+ * the environment variable GPX_GRAPH_BASE_PATH (the reference compiles one in, src/executor.cpp:12).
+ * Every execute is one GraphCompute::compute (src/executor.cpp:129,227): the algorithm from its
+ * initial state to its fixed point, from vertex 0 for bfs and sssp.  The result is the storage
+ * "label" (bfs: uint32 level, 0xFFFFFFFF = not reached), "cost" (sssp: uint32 distance), "comp" (cc:
+ * uint32, the smallest vertex id of the component; the reference keeps 64-bit ids) or "value"
+ * (pagerank: float32).  The reference has no call that returns these or the figures below.
+ * `listed_iterations` is the number of iterations in the kernel list (sized by one run when the model
+ * was opened), `live_iterations` how many of them the latest run needed, `converged` is 0 if that run
+ * used the whole list and still had work (pagerank: always 1, it stops after 100 iterations as
+ * in graphcompute.cu:281).  Any of the output pointers may be NULL. */
+int gpx_model_graph_info(gpx_model *m, uint64_t *vertices, uint64_t *edges, int *listed_iterations,
+                         int *live_iterations, int *converged);
 
 /* ---- executor ----------------------------------------------------------------------- */
 

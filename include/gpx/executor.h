@@ -27,8 +27,10 @@ namespace foo {
 
 class Executor {
 public:
-    // Executor::set_graph_path, src/executor.cpp:18-21 (the dataset of the graph-analytics
-    // workloads; kept for source compatibility, the DNN path does not use it).
+    // Executor::set_graph_path, src/executor.cpp:18-21: the dataset of the graph-analytics
+    // workloads ("cc", "bfs", "pagerank", "sssp"), called before init as the clients do
+    // (src/cuda-clients/blpclient.cpp:115-117).  A relative path is taken under the directory named by
+    // the environment variable GPX_GRAPH_BASE_PATH (GRAPH_BASE_PATH in the reference).
     Status set_graph_path(const std::string &path) {
         graph_path = path;
         return Status::Succ;
@@ -122,6 +124,13 @@ protected:
     }
 
     Status init_kind(const std::string &workload, int kind) {
+        if (workload == "cc" || workload == "bfs" || workload == "pagerank" || workload == "sssp") {
+            // src/executor.cpp:24-34
+            type = "graph";
+            Status st = load_model(workload + ":" + graph_path);
+            if (st != Status::Succ) return st;
+            return (Status)gpx_exec_create(model->handle(), kind, &exec_);
+        }
         type = "dnn";
         const std::string root = model_root();
         const std::string dir = root.empty() ? "" : root + "/" + workload;

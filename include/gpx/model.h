@@ -123,10 +123,13 @@ public:
 
     // "miniweather" (the reference's sciCompute workload, src/executor.cpp:14): a simulation state
     // instead of "data" / "heads".
+    // The graph-analytics workloads (graphCompute, src/executor.cpp:13) have none either.
     bool is_scientific() {
         size_t idx;
-        return m_ && gpx_model_find(m_, "data", &idx) != GPX_SUCC && gpx_model_find(m_, "state", &idx) == GPX_SUCC;
+        if (!m_ || gpx_model_find(m_, "data", &idx) == GPX_SUCC) return false;
+        return gpx_model_find(m_, "state", &idx) == GPX_SUCC || is_graph();
     }
+    bool is_graph() { return m_ && gpx_model_graph_info(m_, nullptr, nullptr, nullptr, nullptr, nullptr) == GPX_SUCC; }
     // reductions(mass, te), src/workloads/miniweather.cu:650-677.
     Status reductions(double &mass, double &te) { return (Status)gpx_model_reductions(m_, &mass, &te); }
 
