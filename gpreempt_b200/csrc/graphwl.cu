@@ -77,31 +77,32 @@ __device__ __forceinline__ void sssp_vertex(const GraphWlParams &p, unsigned u, 
     if (lane == 0) p.f0[u] = 0;
 }
 
-// Connected components, hooking (cc_kernel_coalesce, graphcompute.cu:57-93): along every edge of a
-// visited vertex the smaller component id is offered to the other end.  Ids are read from comp,
-// offers go to the new-comp array with atomicMin, the commit pass moves them over.
+// Connected components, hooking.  The reference (cc_kernel_coalesce, graphcompute.cu:57-93) offers the
+// smaller component id along every edge of the vertices that changed and repeats until nothing
+// moves, which takes as many launches as the graph is deep when ids are read from a stable copy.
+// Here every iteration hooks and then shortcuts (the scheme of Shiloach and Vishkin as in FastSV):
+// the smallest id m among u and its neighbours is offered to u and to the vertex u currently names,
+// X[u]; the vertex pass then replaces every id by the id that one names.  Ids are read from X and
+// offered to Y with atomicMin only, so the outcome of a pass does not depend on the order of its
+// warps, and the number of iterations is logarithmic in the depth.  Every id a vertex ever holds is
+// a vertex of its own component, ids only fall, and a pass that changes nothing leaves all ends of
+// every edge equal: the fixed point is the smallest vertex id of each component, as in the reference.
 __device__ __forceinline__ void cc_vertex(const GraphWlParams &p, unsigned u, int lane) {
-    const unsigned char *visit = (p.iter & 1) ? p.f1 : p.f0;
-    if (!visit[u]) return;
-    const unsigned cu = p.a[u];
-    unsigned mine = cu;
+    const unsigned xu = p.a[u];
+    unsigned m = xu;
     const unsigned long long beg = p.row[u], end = p.row[u + 1];
     for (unsigned long long i = beg + lane; i < end; i += 32 * kGwUnroll) {
-        unsigned v[kGwUnroll], c[kGwUnroll];
+        unsigned v[kGwUnroll];
 #pragma unroll
         for (int k = 0; k < kGwUnroll; ++k) v[k] = i + 32 * k < end ? p.adj[i + 32 * k] : u;
 #pragma unroll
-        for (int k = 0; k < kGwUnroll; ++k) c[k] = p.a[v[k]];
-#pragma unroll
-        for (int k = 0; k < kGwUnroll; ++k) {
-            if (c[k] > cu)
-                atomicMin(p.b + v[k], cu);
-            else
-                mine = min(mine, c[k]);
-        }
+        for (int k = 0; k < kGwUnroll; ++k) m = min(m, p.a[v[k]]);
     }
-    mine = warp_min(mine);
-    if (lane == 0 && mine < cu) atomicMin(p.b + u, mine);
+    m = warp_min(m);
+    if (lane == 0) {
+        atomicMin(p.b + u, m);
+        if (m < xu) atomicMin(p.b + xu, m);
+    }
 }
 
 // PageRank, one iteration (pr_kernel_coalesce + pr_update, graphcompute.cu:223-250) as a gather:
@@ -153,8 +154,8 @@ __device__ __forceinline__ void edge_tile(const GraphWlParams &p, int tile) {
     }
 }
 
-// sssp_update (graphcompute.cu:320-330) / the commit of the component ids: a vertex whose offered
-// value is below its own takes it and is in the next frontier.
+// sssp_update (graphcompute.cu:320-330): a vertex whose offered distance is below its own takes it and
+// is in the next frontier.  Components: the shortcut, X[v] = min(Y[v], Y[Y[v]]).
 template <int ALGO>
 __device__ __forceinline__ bool vertex_tile(const GraphWlParams &p, int tile) {
     bool found = false;
@@ -169,12 +170,10 @@ __device__ __forceinline__ bool vertex_tile(const GraphWlParams &p, int tile) {
                 found = true;
             }
         } else {
-            unsigned char *visit = (p.iter & 1) ? p.f1 : p.f0, *next = (p.iter & 1) ? p.f0 : p.f1;
-            visit[v] = 0;
-            const unsigned nb = p.b[v];
-            if (nb < p.a[v]) {
-                p.a[v] = nb;
-                next[v] = 1;
+            const unsigned y = p.b[v];
+            const unsigned nw = min(y, p.b[y]);
+            if (nw < p.a[v]) {
+                p.a[v] = nw;
                 found = true;
             }
         }
@@ -199,8 +198,6 @@ __device__ __forceinline__ void init_tile(const GraphWlParams &p, int tile) {
             p.f0[v] = v == p.src ? 1 : 0;
         } else if (p.algo == GW_CC) {
             p.a[v] = p.b[v] = v;
-            p.f0[v] = 1;
-            p.f1[v] = 0;
         } else {
             reinterpret_cast<float *>(p.a)[v] = 1.0f - p.alpha;
             reinterpret_cast<float *>(p.b)[v] = 0.0f;
@@ -217,18 +214,30 @@ graphwl_kernel(const __grid_constant__ GraphWlParams p, BlpArgs blp) {
     __shared__ int s_tile;
     const bool dynamic = blp.preempted != nullptr;
     if (PHASE != GW_INIT && p.active[p.iter] == 0) {
-        // Behind the last live iteration: nothing to do, the tiles count as run.
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            int had = 0;
-            if (dynamic) had = atomicMax(blp.executed, blp.total_tiles);
-            if (blp.trace && had < blp.total_tiles) {
-                const unsigned long long t = globaltimer_ns();
-                atomicMin(blp.trace + 0, t);
-                atomicMax(blp.trace + 1, t);
-                atomicAdd(blp.trace + 3, (unsigned long long)(blp.total_tiles - had));
-            }
+        // No flag for this iteration.  With the preempt word down that is final: every kernel before
+        // this one ran to its end (the word stays up from the moment a kernel stops until the stream
+        // is idle), so this one is behind the last live iteration, has nothing to do, and its tiles
+        // count as run.  With the word up a predecessor may have stopped before it raised the flag:
+        // the kernel then goes on to the claim below, which records it as a stop point, and it is
+        // judged again when the run is resumed.
+        if (dynamic) {
+            if (threadIdx.x == 0) s_tile = load_word(blp.preempted);
+            __syncthreads();
         }
-        return;
+        if (!dynamic || s_tile == 0) {
+            if (blockIdx.x == 0 && threadIdx.x == 0) {
+                int had = 0;
+                if (dynamic) had = atomicMax(blp.executed, blp.total_tiles);
+                if (blp.trace && had < blp.total_tiles) {
+                    const unsigned long long t = globaltimer_ns();
+                    atomicMin(blp.trace + 0, t);
+                    atomicMax(blp.trace + 1, t);
+                    atomicAdd(blp.trace + 3, (unsigned long long)(blp.total_tiles - had));
+                }
+            }
+            return;
+        }
+        __syncthreads();
     }
     if (threadIdx.x == 0) trace_begin(blp);
     int iter = 0;
@@ -476,8 +485,7 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
         GPX_TRY(device_zeroed(m, g.n, &base.d0));
         GPX_TRY(device_zeroed(m, g.n, &base.d1));
     }
-    if (algo == GW_SSSP || algo == GW_CC) GPX_TRY(device_zeroed(m, g.n, &base.f0));
-    if (algo == GW_CC) GPX_TRY(device_zeroed(m, g.n, &base.f1));
+    if (algo == GW_SSSP) GPX_TRY(device_zeroed(m, g.n, &base.f0));
     GPX_TRY(device_zeroed(m, (size_t)kGwMaxIters + 1, &base.active));
     m.graph_active = base.active;
 
@@ -537,7 +545,7 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
     m.graph_iterations = live;
     // Edge traffic of a whole run, spread over the live edge passes for the per-kernel figures.
     double edge_bytes = (double)g.e * (algo == GW_SSSP ? 12.0 : 8.0);
-    if (algo == GW_PAGERANK || algo == GW_CC) edge_bytes *= std::max(live, 1);
+    if (algo == GW_PAGERANK || algo == GW_CC) edge_bytes = (double)g.e * 4.0 * std::max(live, 1);
     for (Kernel &k : m.kernels)
         if (k.graphwl.phase == GW_EDGES && k.graphwl.iter < live) k.bytes += edge_bytes / std::max(live, 1);
     return GPX_SUCC;

@@ -13,7 +13,9 @@
 // found when the model is opened, by running the algorithm once.  For that to be exact the
 // iterations are race-free: every kernel reads values only an earlier kernel wrote (the reference's
 // kernels read distances and component ids other warps are lowering in the same launch, so its
-// iteration count depends on timing; the fixed points are the same).
+// iteration count depends on timing; the fixed points are the same).  Connected components use
+// hooking with shortcuts instead of the reference's plain label propagation, for the same fixed
+// point in a handful of iterations.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -30,7 +32,7 @@ enum GraphAlgo { GW_BFS = 0, GW_SSSP = 1, GW_CC = 2, GW_PAGERANK = 3 };
 enum GraphPhase {
     GW_INIT = 0,    // start of a request: result arrays, frontier and iteration flags
     GW_EDGES = 1,   // walks the edge lists of a tile of vertices (one warp per vertex)
-    GW_VERTICES = 2 // per-vertex pass after the edge pass (sssp: update; cc: commit)
+    GW_VERTICES = 2 // per-vertex pass after the edge pass (sssp: update; cc: shortcut)
 };
 
 constexpr int kGwThreads = 256;
@@ -50,9 +52,9 @@ struct GraphWlParams {
     const unsigned *wgt;            // sssp: edge weights
     const unsigned *outdeg;         // pagerank: out-degree of every vertex
     unsigned *a;          // bfs: label; sssp: cost; cc: comp; pagerank: value (float)
-    unsigned *b;          // sssp: new cost; cc: new comp; pagerank: residual (float)
+    unsigned *b;          // sssp: new cost; cc: offered ids; pagerank: residual (float)
     unsigned *d0, *d1;    // pagerank: delta, read from d<iter & 1>, written to the other
-    unsigned char *f0, *f1;  // sssp: f0 = label; cc: visit flags, read f<iter & 1>, written the other
+    unsigned char *f0;    // sssp: label (the frontier)
     int *active;          // [kGwMaxIters + 1]: active[i] != 0 <=> iteration i has work
     float alpha, tol;     // pagerank (0.85, 0.001: include/workloads/graphcompute.h:85-86)
 };

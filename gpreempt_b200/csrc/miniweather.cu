@@ -584,7 +584,7 @@ extern "C" {
 int gpx_model_reductions(gpx_model *m, double *mass, double *te) {
     using namespace gpx;
     GPX_REQUIRE(m && mass && te, GPX_FAIL, "NULL argument");
-    GPX_REQUIRE(m->sci, GPX_NOT_FOUND, "model '%s' has no reductions (miniweather only)", m->name.c_str());
+    GPX_REQUIRE(m->sci && m->graph_algo < 0, GPX_NOT_FOUND, "model '%s' has no reductions (miniweather only)", m->name.c_str());
     const int nx = m->sci_nx, nz = m->sci_nz, W = nx + 2 * kMwHalo;
     const size_t plane = (size_t)(nz + 2 * kMwHalo) * W;
     std::vector<float> st(plane * kMwVars);

@@ -231,4 +231,24 @@ def test_best_effort_tenants_under_a_latency_critical_model(gpx, graphs_on_disk)
         assert by_id[algo + "_be"]["requests"] > 30, algo
         assert by_id[algo + "_be"]["in_bytes"] == 0
     assert rep["gpus"][0]["wordRaises"] > 0
+    # closed-loop tenants keep the GPU busy, so latency-critical requests do interrupt them
+    for t in tasks[1:]:
+        t["load"] = {"type": "continuous"}
+    cfg["schedule_log"] = True
+    rep = json.loads(gpx.run_workload("gpreemptclient", json.dumps(cfg)))
+    by_id = {t["id"]: t for t in rep["tasks"]}
+    assert 130 <= by_id["vgg_rt"]["requests"] <= 151
     assert sum(by_id[a + "_be"]["resumes"] for a in ALGOS) > 0
+    assert all(by_id[a + "_be"]["requests"] > 100 for a in ALGOS)
+    # from the device time stamps: nothing behind a stop point ran, and every finished request ran
+    # each tile of each kernel once over its launches (the kernels behind the last live iteration count
+    # theirs without running them)
+    stops = done = 0
+    for e in rep["gpus"][0]["scheduleLog"]["events"]:
+        if e[0] == 4:
+            assert e[5] == 0, "a kernel behind the stop point ran a tile"
+            stops += 1
+        elif e[0] == 5:
+            assert e[3] == 0, "a best-effort request did not run every tile exactly once"
+            done += 1
+    assert stops > 0 and done > 400
