@@ -255,6 +255,7 @@ def cpu_baseline(seconds: float = 10.0) -> dict:
             ref.timestep(2)
             others["miniweather_3200x1600_reference_kernels_ms_per_time_step"] = ref.time_steps(20) / 20
             ref.close()
+        others.update(_graph_cpu_figures())
     except Exception as e:  # noqa: BLE001 - the side figures must not cost the run its line
         others["error"] = repr(e)
     return {"value": images / dt, "unit": "inf/s", "cores": os.cpu_count(), "kind": "port",
@@ -300,6 +301,34 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _graph_cpu_figures() -> dict:
+    """The graph workloads on the host: the sequential CPU oracle and, where it was built, the
+    reference's own CUDA source (compiled unmodified, oracle/Makefile) on the same synthetic graph."""
+    import tempfile
+    import time as _time
+
+    from gpreempt_b200 import graph_files
+    from oracle import graphs
+
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        prefix = os.path.join(tmp, "crank", "crank.bel")
+        graph_files.write_synthetic(prefix)
+        offsets, neighbours, weights = graph_files.read_bel(prefix)
+        runs = {"bfs": lambda: graphs.bfs(offsets, neighbours), "sssp": lambda: graphs.sssp(offsets, neighbours, weights),
+                "cc": lambda: graphs.cc(offsets, neighbours), "pagerank": lambda: graphs.pagerank(offsets, neighbours)}
+        for algo, run in runs.items():
+            t0 = _time.perf_counter()
+            run()
+            out[f"graph_{algo}_cpu_oracle_ms_per_run"] = (_time.perf_counter() - t0) * 1e3
+            if graphs.reference_available():
+                ref = graphs.Reference(algo, prefix)
+                ref.compute(2)
+                out[f"graph_{algo}_reference_kernels_ms_per_run"] = ref.compute(10) / 10
+                ref.close()
+    return out
+
+
 def miniweather_figures(api, hbm_gbs: float) -> dict:
     """The scientific best-effort workload (the reference's config/Y.json tenant): device time of one
     time step of the 3200 x 1600 grid, replayed from a CUDA graph, and its share of HBM bandwidth
@@ -323,6 +352,42 @@ def miniweather_figures(api, hbm_gbs: float) -> dict:
     s.destroy()
     return {"ms_per_time_step": ms, "kernels": 12, "algorithmic_gb": nbytes / 1e9,
             "achieved_gb_s": nbytes / (ms * 1e-3) / 1e9, "hbm_frac": nbytes / (ms * 1e-3) / 1e9 / hbm_gbs}
+
+
+def graph_workload_figures(api) -> dict:
+    """The graph-analytics best-effort workloads (the reference's config/Z.json tenants) on a seeded
+    synthetic graph of the size of the reference's dataset (52 804 vertices, ~10 million edges; the
+    dataset itself is not available): device time of one run to the fixed point, replayed from a CUDA
+    graph, with the number of iterations it took."""
+    import tempfile
+
+    from gpreempt_b200 import graph_files
+
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        prefix = os.path.join(tmp, "crank", "crank.bel")
+        info = graph_files.write_synthetic(prefix)
+        out["graph"] = {"vertices": info["vertices"], "edges": info["edges"], "data": "synthetic banded, seed 1"}
+        for algo in ("bfs", "sssp", "cc", "pagerank"):
+            ex = api.BaseExecutor()
+            ex.set_graph_path(prefix)
+            ex.init(algo)
+            s = api.Stream(0)
+            ex.capture_graph(s)
+            for _ in range(3):
+                ex.execute(s)
+            s.sync()
+            e0, e1 = api.Event(), api.Event()
+            e0.record(s)
+            for _ in range(20):
+                ex.execute(s)
+            e1.record(s)
+            s.sync()
+            out[algo] = {"ms_per_run": e0.elapsed_ms(e1) / 20, "iterations": ex.model.graph_info()["live_iterations"],
+                         "kernels": ex.get_kernel_num()}
+            ex.clear()
+            s.destroy()
+    return out
 
 
 def model_roofline_ms(layers, peak_tflops: float, hbm_gbs: float) -> float:
@@ -508,7 +573,8 @@ def main() -> None:
             "wall_s_resident_run": t1 - t0,
         }
         if world == 1:
-            line["other_workloads"] = {"miniweather_3200x1600": miniweather_figures(api, hbm)}
+            line["other_workloads"] = {"miniweather_3200x1600": miniweather_figures(api, hbm),
+                                       "graph_analytics": graph_workload_figures(api)}
         if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)

@@ -1,4 +1,4 @@
-"""The reference's own evaluation workloads A, B, C, D, E and Y (its Fig. 4-6) on this library.
+"""The reference's own evaluation workloads A, B, C, D, E, Y and Z (its Fig. 4-6) on this library.
 
     python -m gpreempt_b200.reference_workloads [--seconds 10] [--only A,B]
 
@@ -9,20 +9,28 @@ then with its best-effort tenants under `gpreemptclient` (GP); the line printed 
 gives the mean end-to-end latency of the latency-critical task in both runs (the figure the
 reference plots: DISB's avgTotalLatency, pre-processing included), what the contention adds, and
 the best-effort throughput in requests per second summed over the best-effort tasks.
+
+Z runs the graph-analytics tenants; its dataset (crankseg_1) ships with neither repository, so
+the files are written to a scratch directory from the seeded synthetic graph of the same size
+(gpreempt_b200.graph_files), unless --graph names the prefix of existing .col/.dst/.val files.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
+import tempfile
 
 from . import api
 
 
 def _task(tid: str, model: str, priority: int, hz: float, preprocess_us: int = 200,
-          load: str = "periodic") -> dict:
-    return {"id": tid, "load": {"type": load, "priority": 0, "frequency": hz},
-            "client": {"name": tid, "model_name": model, "priority": priority, "batch_size": 1,
-                       "use_cuda_graph": True, "preprocess_time": preprocess_us}}
+          load: str = "periodic", graph_path: str | None = None) -> dict:
+    client = {"name": tid, "model_name": model, "priority": priority, "batch_size": 1,
+              "use_cuda_graph": graph_path is None, "preprocess_time": preprocess_us}
+    if graph_path is not None:
+        client["graph_path"] = graph_path
+    return {"id": tid, "load": {"type": load, "priority": 0, "frequency": hz}, "client": client}
 
 
 _FIVE = ("resnet152", "densenet", "vgg", "inception", "bert")
@@ -40,11 +48,29 @@ WORKLOADS = {
          + [_task(m + "_be", m, 1, 100, load="poisson") for m in _FIVE],
     # config/Y.json: the scientific tenant (no pre-processing) at 150 Hz
     "Y": [_task("vgg_rt", "vgg", 0, 100), _task("miniweather_be", "miniweather", 1, 150, 0)],
+    # config/Z.json: bfs, sssp, pagerank and cc on one graph at 100 Hz each (no CUDA graph, as there)
+    "Z": [_task("vgg_rt", "vgg", 0, 100)] + [_task(a + "_be", a, 1, 100, graph_path="")
+                                             for a in ("bfs", "sssp", "pagerank", "cc")],
 }
 
 
-def run(name: str, seconds: float) -> dict:
-    tasks = WORKLOADS[name]
+def run(name: str, seconds: float, graph: str = "") -> dict:
+    tasks = json.loads(json.dumps(WORKLOADS[name]))
+    if any("graph_path" in t["client"] for t in tasks):
+        with tempfile.TemporaryDirectory() as tmp:
+            if not graph:
+                from . import graph_files
+
+                graph = os.path.join(tmp, "crank", "crank.bel")
+                graph_files.write_synthetic(graph)
+            for t in tasks:
+                if "graph_path" in t["client"]:
+                    t["client"]["graph_path"] = os.path.abspath(graph)
+            return _run(name, tasks, seconds)
+    return _run(name, tasks, seconds)
+
+
+def _run(name: str, tasks: list, seconds: float) -> dict:
     cfg = {"time": seconds, "seed": 1, "warmup": 3, "standalone": 3, "tasks": tasks}
     alone = json.loads(api.run_workload("rtonlyclient", json.dumps(cfg)))
     both = json.loads(api.run_workload("gpreemptclient", json.dumps(cfg)))
@@ -71,7 +97,8 @@ def run(name: str, seconds: float) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--seconds", type=float, default=10.0)
-    ap.add_argument("--only", default="A,B,C,D,E,Y")
+    ap.add_argument("--only", default="A,B,C,D,E,Y,Z")
+    ap.add_argument("--graph", default="", help="prefix of the graph files of workload Z")
     ap.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
     names = [n for n in a.only.split(",") if n]
@@ -80,7 +107,7 @@ def main() -> None:
             ap.error(f"unknown workload {n!r} (have {', '.join(WORKLOADS)})")
     api.init_cuda(a.device)
     for n in names:
-        print(json.dumps(run(n, a.seconds)), flush=True)
+        print(json.dumps(run(n, a.seconds, a.graph)), flush=True)
 
 
 if __name__ == "__main__":

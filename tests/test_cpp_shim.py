@@ -38,6 +38,7 @@ def test_c99_client_compiles_links_and_runs(tmp_path):
 def test_reference_named_classes_compile_and_link(tmp_path):
     _compile(tmp_path, "g++", "c++17", "test_dnn_blp.cpp", "test_dnn_blp")
     _compile(tmp_path, "g++", "c++17", "test_sci.cpp", "test_sci")
+    _compile(tmp_path, "g++", "c++17", "test_graph.cpp", "test_graph")
 
 
 @pytest.mark.gpu
@@ -48,6 +49,32 @@ def test_port_of_the_reference_sci_test(gpx, tmp_path):
     res = subprocess.run([exe, "miniweather"], capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, (res.stdout, res.stderr)
     assert "d_mass:" in res.stdout and "d_te:" in res.stdout and "PASS" in res.stdout
+
+
+@pytest.mark.gpu
+def test_port_of_the_reference_graph_tests(gpx, tmp_path):
+    """src/tests/test-graph.cpp and test-graph-blp.cpp through foo::BaseExecutor / foo::BLPExecutor
+    (set_graph_path, init, execute): the result equals the CPU oracle's, and a preempted and resumed
+    run ends with the same bytes."""
+    from gpreempt_b200 import graph_files
+    from oracle import graphs
+
+    exe = _compile(tmp_path, "g++", "c++17", "test_graph.cpp", "test_graph")
+    prefix = str(tmp_path / "g" / "g.bel")
+    graph_files.write_synthetic(prefix, 20000, 64, 400, 2)
+    offsets, neighbours, weights = graph_files.read_bel(prefix)
+    want = {"bfs": graphs.bfs(offsets, neighbours)[0], "sssp": graphs.sssp(offsets, neighbours, weights)[0],
+            "cc": graphs.cc(offsets, neighbours)[0].astype(np.uint32)}
+    for algo in ("bfs", "sssp", "cc", "pagerank"):
+        out = str(tmp_path / (algo + ".bin"))
+        res = subprocess.run([exe, algo, prefix, out], capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, (algo, res.stdout, res.stderr)
+        assert f"{algo} Compute:" in res.stdout and "PASS" in res.stdout
+        if algo in want:
+            assert np.array_equal(np.fromfile(out, np.uint32), want[algo]), algo
+        else:
+            rank = np.fromfile(out, np.float32)
+            assert np.max(np.abs(rank - graphs.pagerank(offsets, neighbours)[0])) <= 1.1e-3
 
 
 @pytest.mark.gpu

@@ -127,3 +127,39 @@ def test_graph_files_tool_writes_a_graph(tmp_path):
     assert res.returncode == 0, res.stderr
     o, d, w = graph_files.read_bel(prefix)
     assert len(o) == 301 and len(d) == len(w) > 1000
+
+
+def _golden():
+    import json
+
+    with open(os.path.join(ROOT, "tests", "golden", "graph_reference.json")) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("which", ["small", "crank"])
+def test_oracle_matches_results_of_the_reference_kernels(which):
+    """tests/golden/graph_reference.json holds what GraphComputeRaw::{BFS,SSSP,CC,PageRank} of the
+    reference computed on a GPU for two seeded graphs (tests/golden/make_graph_golden.py): labels,
+    distances and components must be identical, ranks within the tolerance of the float sums."""
+    import hashlib
+
+    entry = _golden()["graphs"][which]
+    offsets, neighbours = graph_files.synthetic_banded(**entry["spec"])
+    weights = graph_files.synthetic_weights(len(neighbours), entry["spec"]["seed"])
+    assert len(neighbours) == entry["edges"]
+    got = {"bfs": graphs.bfs(offsets, neighbours)[0], "sssp": graphs.sssp(offsets, neighbours, weights)[0],
+           "cc": graphs.cc(offsets, neighbours)[0], "pagerank": graphs.pagerank(offsets, neighbours)[0]}
+    for algo, want in entry["results"].items():
+        arr = got[algo]
+        picks = np.array(want["picks"])
+        if algo == "pagerank":
+            assert np.max(np.abs(arr[picks] - np.array(want["at_picks"]))) <= 1.1e-3
+            assert abs(float(arr.astype(np.float64).sum()) - want["sum"]) <= 2e-4 * len(arr)
+            if "values" in want:
+                err = np.abs(arr - np.array(want["values"], np.float32))
+                assert err.max() <= 1.1e-3 and err.mean() <= 1e-5
+        else:
+            assert arr[picks].astype(np.uint64).tolist() == want["at_picks"], algo
+            assert hashlib.sha256(arr.astype(np.uint64).tobytes()).hexdigest() == want["sha256"], algo
+            if "values" in want:
+                assert arr.astype(np.uint64).tolist() == want["values"], algo

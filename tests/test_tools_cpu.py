@@ -76,7 +76,7 @@ def test_bench_workload_config_is_the_baseline_configuration():
 def test_reference_workloads_tool_arguments_and_task_lists():
     from gpreempt_b200 import reference_workloads as rw
 
-    assert set(rw.WORKLOADS) == {"A", "B", "C", "D", "E", "Y"}
+    assert set(rw.WORKLOADS) == {"A", "B", "C", "D", "E", "Y", "Z"}
     for name, tasks in rw.WORKLOADS.items():
         n_lc = 5 if name in "DE" else 1
         assert all(t["client"]["priority"] == 0 and t["id"].endswith("_rt") for t in tasks[:n_lc])
@@ -84,6 +84,8 @@ def test_reference_workloads_tool_arguments_and_task_lists():
         kind = "poisson" if name == "E" else "periodic"
         assert all(t["load"]["type"] == kind and t["client"]["batch_size"] == 1 for t in tasks)
     assert [t["load"]["frequency"] for t in rw.WORKLOADS["D"]] == [20] * 5 + [100] * 5
+    assert [t["client"]["model_name"] for t in rw.WORKLOADS["Z"][1:]] == ["bfs", "sssp", "pagerank", "cc"]
+    assert all("graph_path" in t["client"] and not t["client"]["use_cuda_graph"] for t in rw.WORKLOADS["Z"][1:])
     assert [t["load"]["frequency"] for t in rw.WORKLOADS["B"]] == [220, 220]
     assert len(rw.WORKLOADS["C"]) == 6
     assert rw.WORKLOADS["Y"][1]["client"]["model_name"] == "miniweather"
