@@ -24,15 +24,14 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-constexpr int kGwUnroll = 4;  // neighbour ids a lane fetches before it follows any of them
+constexpr int kGwUnroll = 8;  // neighbour ids a lane fetches before it follows any of them: 256 edges a round
 
 // Breadth-first search, one level (bfs_kernel_coalesce, graphcompute.cu:149-170): every vertex of
 // the current level labels its unlabelled neighbours with the next one.  All writers of a label
 // store the same value.
-__device__ __forceinline__ void bfs_vertex(const GraphWlParams &p, unsigned u, int lane) {
+__device__ __forceinline__ void bfs_vertex(const GraphWlParams &p, unsigned u, unsigned long long beg,
+                                           unsigned long long end, int lane) {
     const unsigned level = (unsigned)p.iter;
-    if (p.a[u] != level) return;
-    const unsigned long long beg = p.row[u], end = p.row[u + 1];
     bool found = false;
     for (unsigned long long i = beg + lane; i < end; i += 32 * kGwUnroll) {
         unsigned v[kGwUnroll], l[kGwUnroll];
@@ -53,10 +52,9 @@ __device__ __forceinline__ void bfs_vertex(const GraphWlParams &p, unsigned u, i
 // Shortest paths, relaxation (sssp_kernel_coalesce, graphcompute.cu:297-318): every vertex whose
 // distance dropped in the last iteration offers it to its neighbours.  The distance offered is
 // cost[u], which only the update pass writes (the reference reads the array that is being lowered).
-__device__ __forceinline__ void sssp_vertex(const GraphWlParams &p, unsigned u, int lane) {
-    if (!p.f0[u]) return;
+__device__ __forceinline__ void sssp_vertex(const GraphWlParams &p, unsigned u, unsigned long long beg,
+                                            unsigned long long end, int lane) {
     const unsigned cu = p.a[u];
-    const unsigned long long beg = p.row[u], end = p.row[u + 1];
     for (unsigned long long i = beg + lane; i < end; i += 32 * kGwUnroll) {
         unsigned v[kGwUnroll], w[kGwUnroll], c[kGwUnroll];
 #pragma unroll
@@ -87,10 +85,10 @@ __device__ __forceinline__ void sssp_vertex(const GraphWlParams &p, unsigned u, 
 // warps, and the number of iterations is logarithmic in the depth.  Every id a vertex ever holds is
 // a vertex of its own component, ids only fall, and a pass that changes nothing leaves all ends of
 // every edge equal: the fixed point is the smallest vertex id of each component, as in the reference.
-__device__ __forceinline__ void cc_vertex(const GraphWlParams &p, unsigned u, int lane) {
+__device__ __forceinline__ void cc_vertex(const GraphWlParams &p, unsigned u, unsigned long long beg,
+                                          unsigned long long end, int lane) {
     const unsigned xu = p.a[u];
     unsigned m = xu;
-    const unsigned long long beg = p.row[u], end = p.row[u + 1];
     for (unsigned long long i = beg + lane; i < end; i += 32 * kGwUnroll) {
         unsigned v[kGwUnroll];
 #pragma unroll
@@ -108,10 +106,18 @@ __device__ __forceinline__ void cc_vertex(const GraphWlParams &p, unsigned u, in
 // PageRank, one iteration (pr_kernel_coalesce + pr_update, graphcompute.cu:223-250) as a gather:
 // the residual of v grows by the delta of every in-neighbour (0 for those that did not move last
 // time), summed in a fixed order instead of by atomicAdd, and v is updated in the same pass.
-__device__ __forceinline__ void pagerank_vertex(const GraphWlParams &p, unsigned v, int lane) {
+__device__ __forceinline__ void pagerank_vertex(const GraphWlParams &p, unsigned v, unsigned long long beg,
+                                                unsigned long long end, int lane) {
     const float *dold = reinterpret_cast<const float *>((p.iter & 1) ? p.d1 : p.d0);
     float *dnew = reinterpret_cast<float *>((p.iter & 1) ? p.d0 : p.d1);
-    const unsigned long long beg = p.row[v], end = p.row[v + 1];
+    float *value = reinterpret_cast<float *>(p.a), *residual = reinterpret_cast<float *>(p.b);
+    // what the update at the end needs, fetched while the edges are walked
+    float left = 0.f, val = 0.f, deg = 1.f;
+    if (lane == 0) {
+        left = residual[v];
+        val = value[v];
+        deg = (float)p.outdeg[v];
+    }
     float s = 0.f;
     for (unsigned long long i = beg + lane; i < end; i += 32 * kGwUnroll) {
         unsigned u[kGwUnroll];
@@ -125,11 +131,10 @@ __device__ __forceinline__ void pagerank_vertex(const GraphWlParams &p, unsigned
     }
     s = warp_sum(s);
     if (lane == 0) {
-        float *value = reinterpret_cast<float *>(p.a), *residual = reinterpret_cast<float *>(p.b);
-        const float r = residual[v] + s;
+        const float r = left + s;
         if (r > p.tol) {
-            value[v] += r;
-            dnew[v] = r * p.alpha / (float)p.outdeg[v];
+            value[v] = val + r;
+            dnew[v] = r * p.alpha / deg;
             residual[v] = 0.f;
             p.active[p.iter + 1] = 1;
         } else {
@@ -139,18 +144,38 @@ __device__ __forceinline__ void pagerank_vertex(const GraphWlParams &p, unsigned
     }
 }
 
+// One tile of an edge pass: p.tile_verts neighbouring vertices, an eighth of them per warp.  The
+// first lanes of a warp fetch, for its vertices at once, whether the vertex takes part and where its
+// edge list lies; the warp then walks the lists one after another.  Neighbouring vertices of a
+// graph with locality share neighbours, so their reads of labels, distances, ids and deltas hit the
+// same cache lines (tiles of vertices spread over the whole graph were tried: 1.8 to 2.7 times slower
+// on the searches).
 template <int ALGO>
 __device__ __forceinline__ void edge_tile(const GraphWlParams &p, int tile) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    constexpr int per_warp = kGwEdgeTileVerts / (kGwThreads / 32);
+    const int per_warp = p.tile_verts / (kGwThreads / 32);
+    const unsigned long long first = (unsigned long long)tile * p.tile_verts + wid * per_warp;
+    const unsigned long long mine = first + lane;
+    bool act = false;
+    unsigned long long beg = 0, end = 0;
+    if (lane < per_warp && mine < p.n) {
+        if (ALGO == GW_BFS) act = p.a[mine] == (unsigned)p.iter;
+        if (ALGO == GW_SSSP) act = p.f0[mine] != 0;
+        if (ALGO == GW_CC || ALGO == GW_PAGERANK) act = true;
+        if (act) {
+            beg = p.row[mine];
+            end = p.row[mine + 1];
+        }
+    }
 #pragma unroll 1
     for (int j = 0; j < per_warp; ++j) {
-        const unsigned long long u = (unsigned long long)tile * kGwEdgeTileVerts + wid * per_warp + j;
-        if (u >= p.n) break;
-        if (ALGO == GW_BFS) bfs_vertex(p, (unsigned)u, lane);
-        if (ALGO == GW_SSSP) sssp_vertex(p, (unsigned)u, lane);
-        if (ALGO == GW_CC) cc_vertex(p, (unsigned)u, lane);
-        if (ALGO == GW_PAGERANK) pagerank_vertex(p, (unsigned)u, lane);
+        if (!__shfl_sync(0xffffffffu, act ? 1 : 0, j)) continue;
+        const unsigned long long b = __shfl_sync(0xffffffffu, beg, j), e = __shfl_sync(0xffffffffu, end, j);
+        const unsigned u = (unsigned)(first + j);
+        if (ALGO == GW_BFS) bfs_vertex(p, u, b, e, lane);
+        if (ALGO == GW_SSSP) sssp_vertex(p, u, b, e, lane);
+        if (ALGO == GW_CC) cc_vertex(p, u, b, e, lane);
+        if (ALGO == GW_PAGERANK) pagerank_vertex(p, u, b, e, lane);
     }
 }
 
@@ -404,9 +429,9 @@ bool split_name(const std::string &name, int &algo, std::string &path) {
 
 }  // namespace
 
-int graphwl_grid(int total_tiles, int sm_count) {
+int graphwl_grid(const GraphWlParams &p, int total_tiles, int sm_count) {
     int blocks = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, graphwl_kernel<GW_SSSP, GW_EDGES>, kGwThreads, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, pick_kernel(p), kGwThreads, 0);
     if (blocks < 1) blocks = 1;
     long long grid = (long long)blocks * sm_count;
     if (grid > total_tiles) grid = total_tiles;
@@ -455,6 +480,16 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
     base.src = 0;
     base.alpha = 0.85f;
     base.tol = 0.001f;
+    // Vertices per tile of the edge passes.  The searches touch few vertices per pass, and what a
+    // CTA pays per tile is the latency of asking which: larger tiles, fewer rounds.  PageRank walks
+    // every edge list in every pass and balances better in small tiles.  (52 804 vertices with about
+    // 200 edges each: bfs 1.21 / 0.58 / 0.40 ms a run with 8 / 32 / 64, pagerank 1.60 / 2.08 / 2.09.)
+    {
+        const int by_algo[4] = {64, 32, 32, 8};
+        base.tile_verts = by_algo[algo];
+        const char *e = getenv("GPX_GRAPH_TILE");
+        if (e && atoi(e) >= 8) base.tile_verts = std::min(atoi(e) / 8 * 8, kGwEdgeTileVertsMax);
+    }
     unsigned long long *row = nullptr;
     unsigned *adj = nullptr;
     if (algo == GW_PAGERANK) {
@@ -489,7 +524,7 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
     GPX_TRY(device_zeroed(m, (size_t)kGwMaxIters + 1, &base.active));
     m.graph_active = base.active;
 
-    const int edge_tiles = (int)((g.n + kGwEdgeTileVerts - 1) / kGwEdgeTileVerts);
+    const int edge_tiles = (int)((g.n + base.tile_verts - 1) / base.tile_verts);
     const int vertex_tiles = (int)((g.n + kGwVertexTileVerts - 1) / kGwVertexTileVerts);
     auto make = [&](int phase, int iter) {
         Kernel k;
@@ -500,7 +535,7 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
         k.graphwl = p;
         k.threads = kGwThreads;
         k.total_tiles = phase == GW_EDGES ? edge_tiles : vertex_tiles;
-        k.grid = graphwl_grid(k.total_tiles, m.sm_count);
+        k.grid = graphwl_grid(p, k.total_tiles, m.sm_count);
         const char *what = phase == GW_INIT ? "init" : (phase == GW_EDGES ? "edges" : "vertices");
         k.name = std::string("graphwl_kernel.") + kAlgoNames[algo] + "." + what +
                  (phase == GW_INIT ? std::string() : "." + std::to_string(iter));

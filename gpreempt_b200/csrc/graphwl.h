@@ -36,7 +36,7 @@ enum GraphPhase {
 };
 
 constexpr int kGwThreads = 256;
-constexpr int kGwEdgeTileVerts = 32;      // vertices per tile of an edge pass (four per warp)
+constexpr int kGwEdgeTileVertsMax = 256;  // vertices per tile of an edge pass at most (32 per warp)
 constexpr int kGwVertexTileVerts = 1024;  // vertices per tile of a per-vertex pass
 constexpr int kGwMaxIters = 4096;         // iteration flags an executor of a graph workload has
 constexpr unsigned kGwInfinity = 0xFFFFFFFFu;  // MYINFINITY, include/workloads/graphcompute.h:14
@@ -45,6 +45,7 @@ struct GraphWlParams {
     int algo;
     int phase;
     int iter;             // iteration index; the BFS level
+    int tile_verts;       // edge passes: vertices per tile, a multiple of 8 (one warp takes an eighth of them in turn)
     unsigned n;           // vertices
     unsigned src;         // bfs, sssp: source vertex (0, graphcompute.cu:181,344)
     const unsigned long long *row;  // [n + 1] edge offsets (pagerank: of the in-edge lists)
@@ -60,7 +61,7 @@ struct GraphWlParams {
 };
 
 cudaError_t graphwl_launch(const GraphWlParams &p, int grid, const BlpArgs &blp, cudaStream_t s);
-int graphwl_grid(int total_tiles, int sm_count);
+int graphwl_grid(const GraphWlParams &p, int total_tiles, int sm_count);
 
 // "bfs:<prefix>", "sssp:<prefix>", "cc:<prefix>", "pagerank:<prefix>".
 bool is_graph_workload(const std::string &name);
