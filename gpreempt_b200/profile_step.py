@@ -4,6 +4,7 @@
     python -m gpreempt_b200.profile_step axpy  [--size 268435456] [--iters 2]
     python -m gpreempt_b200.profile_step model [--model resnet50] [--batch 32] [--dtype float32]
                                                [--seq-len 0] [--iters 2]
+    python -m gpreempt_b200.profile_step model --model pagerank:/tmp/g/g.bel   (graph files: gpreempt_b200.graph_files)
 
 Each run launches the kernels of interest `iters` times with preemption armed (the word stays
 clear) and exits; inputs are larger than L2 so DRAM counters are meaningful, and at most a few
@@ -54,10 +55,11 @@ def main() -> None:
             s.sync()
     else:
         ex = api.BLPExecutor()
-        ex.init(a.model, batch=a.batch, seed=1, dtype=a.dtype, seq_len=a.seq_len)
+        graph = a.model.split(":")[0] in ("bfs", "sssp", "cc", "pagerank")
+        ex.init(a.model, batch=a.batch, seed=None if graph else 1, dtype=a.dtype, seq_len=a.seq_len)
         ex.set_word(word)
-        if a.model.startswith("miniweather"):
-            data = None  # no request data: every execute advances the resident simulation
+        if a.model.startswith("miniweather") or graph:
+            data = None  # no request data: every execute advances the resident simulation / reruns the algorithm
         elif a.model.startswith("bert"):
             import numpy as np
 
