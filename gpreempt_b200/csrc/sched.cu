@@ -917,7 +917,8 @@ static int build_suite(Suite &s, const std::string &client, const Json &cfg) {
         t->model_name = jc["model_name"].as_string();
         // The graph-analytics tenants name their dataset beside the model (config/Z.json:
         // "model_name": "bfs", "graph_path": "crankseg_1/crankseg_1.bel").
-        if (jc.has("graph_path") && t->model_name.find(':') == std::string::npos)
+        // Other models ignore the key, as Executor::init does (src/executor.cpp:23-45).
+        if (jc.has("graph_path") && is_graph_workload(t->model_name) && t->model_name.find(':') == std::string::npos)
             t->model_name += ":" + jc["graph_path"].as_string();
         t->priority = (int)jc["priority"].as_int(1);
         t->batch = (int)jc["batch_size"].as_int(1);

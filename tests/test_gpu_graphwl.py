@@ -218,7 +218,8 @@ def test_best_effort_tenants_under_a_latency_critical_model(gpx, graphs_on_disk)
     prefix = graphs_on_disk["crank"]
     tasks = [{"id": "vgg_rt", "load": {"type": "periodic", "priority": 0, "frequency": 100},
               "client": {"name": "vgg_rt", "model_name": "vgg", "priority": 0, "batch_size": 1,
-                         "use_cuda_graph": True, "preprocess_time": 200}}]
+                         "use_cuda_graph": True, "preprocess_time": 200,
+                         "graph_path": prefix}}]  # ignored by a model that is not a graph workload
     for algo in ALGOS:
         tasks.append({"id": algo + "_be", "load": {"type": "periodic", "priority": 0, "frequency": 100},
                       "client": {"name": algo + "_be", "model_name": algo, "priority": 1, "batch_size": 1,
