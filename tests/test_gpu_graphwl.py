@@ -212,6 +212,44 @@ def test_names_paths_and_errors(gpx, graphs_on_disk, tmp_path, monkeypatch):
         gpx.Model("sssp:" + cut)
 
 
+def test_isolated_vertices_and_tiny_graphs(gpx, tmp_path):
+    """Vertices without edges, unreachable vertices, a graph of one vertex and one without any edge."""
+    g = _oracle()
+    cases = {
+        # 0-1-2 chain, 3 isolated, 4-5 pair
+        "six": (np.array([0, 1, 3, 4, 4, 5, 6], np.uint64), np.array([1, 0, 2, 1, 5, 4], np.uint64),
+                np.array([7, 7, 2, 2, 1, 1], np.uint32)),
+        "one": (np.array([0, 0], np.uint64), np.array([], np.uint64), np.array([], np.uint32)),
+        "no_edges": (np.zeros(41, np.uint64), np.array([], np.uint64), np.array([], np.uint32)),
+    }
+    for name, (offsets, neighbours, weights) in cases.items():
+        prefix = str(tmp_path / name / (name + ".bel"))
+        graph_files.write_bel(prefix, offsets, neighbours, weights)
+        want = {"bfs": g.bfs(offsets, neighbours)[0], "sssp": g.sssp(offsets, neighbours, weights)[0],
+                "cc": g.cc(offsets, neighbours)[0]}
+        for algo in ("bfs", "sssp", "cc"):
+            ex = gpx.BaseExecutor()
+            ex.set_graph_path(prefix)
+            ex.init(algo)
+            ex.execute()
+            _check(algo, ex.model.get(RESULT[algo]), want[algo], name)
+            assert ex.model.graph_info()["converged"]
+            ex.clear()
+        # pagerank: a vertex nobody points at keeps 1 - alpha (its own delta, infinite without
+        # out-edges as in the reference, is never read)
+        ex = gpx.BaseExecutor()
+        ex.set_graph_path(prefix)
+        ex.init("pagerank")
+        ex.execute()
+        rank = ex.model.get("value")
+        assert np.all(np.isfinite(rank))
+        if name != "six":
+            assert np.allclose(rank, 1 - g.ALPHA)
+        else:
+            _check("pagerank", rank, g.pagerank(offsets, neighbours)[0], name)
+        ex.clear()
+
+
 def test_best_effort_tenants_under_a_latency_critical_model(gpx, graphs_on_disk):
     """The shape of the reference's config/Z.json: the four graph workloads as periodic best-effort
     tenants (client key graph_path) under a latency-critical DNN."""
