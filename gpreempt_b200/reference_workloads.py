@@ -13,6 +13,10 @@ the best-effort throughput in requests per second summed over the best-effort ta
 Z runs the graph-analytics tenants; its dataset (crankseg_1) ships with neither repository, so
 the files are written to a scratch directory from the seeded synthetic graph of the same size
 (gpreempt_b200.graph_files), unless --graph names the prefix of existing .col/.dst/.val files.
+
+--config FILE runs a task file in the reference's schema as it is (its config/REAL.json with the
+recorded arrival traces, for instance) through the same two clients, for the file's own "time"
+unless --seconds is given.
 """
 from __future__ import annotations
 
@@ -94,9 +98,17 @@ def _run(name: str, tasks: list, seconds: float) -> dict:
     }
 
 
+def run_file(path: str, seconds: float | None) -> dict:
+    with open(path) as f:
+        cfg = json.load(f)
+    return _run(os.path.splitext(os.path.basename(path))[0], cfg["tasks"],
+                seconds if seconds is not None else float(cfg.get("time", 10.0)))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--seconds", type=float, default=10.0)
+    ap.add_argument("--seconds", type=float, default=None, help="length of each run (default 10, or the file's time)")
+    ap.add_argument("--config", default="", help="a task file in the reference's schema, run instead of --only")
     ap.add_argument("--only", default="A,B,C,D,E,Y,Z")
     ap.add_argument("--graph", default="", help="prefix of the graph files of workload Z")
     ap.add_argument("--device", type=int, default=0)
@@ -106,8 +118,11 @@ def main() -> None:
         if n not in WORKLOADS:
             ap.error(f"unknown workload {n!r} (have {', '.join(WORKLOADS)})")
     api.init_cuda(a.device)
+    if a.config:
+        print(json.dumps(run_file(a.config, a.seconds)), flush=True)
+        return
     for n in names:
-        print(json.dumps(run(n, a.seconds, a.graph)), flush=True)
+        print(json.dumps(run(n, a.seconds if a.seconds is not None else 10.0, a.graph)), flush=True)
 
 
 if __name__ == "__main__":
