@@ -31,14 +31,14 @@ namespace gpx {
 enum GraphAlgo { GW_BFS = 0, GW_SSSP = 1, GW_CC = 2, GW_PAGERANK = 3 };
 enum GraphPhase {
     GW_INIT = 0,    // start of a request: result arrays, frontier and iteration flags
-    GW_EDGES = 1,   // walks the edge lists of a tile of vertices (one warp per vertex)
+    GW_EDGES = 1,   // walks the edge lists of a tile of vertices (a warp takes one list at a time)
     GW_VERTICES = 2 // per-vertex pass after the edge pass (sssp: update; cc: shortcut)
 };
 
 constexpr int kGwThreads = 256;
 constexpr int kGwEdgeTileVertsMax = 256;  // vertices per tile of an edge pass at most (32 per warp)
 constexpr int kGwVertexTileVerts = 1024;  // vertices per tile of a per-vertex pass
-constexpr int kGwMaxIters = 4096;         // iteration flags an executor of a graph workload has
+constexpr int kGwMaxIters = 4096;         // iteration flags a graph workload has: no run may need more rounds
 constexpr unsigned kGwInfinity = 0xFFFFFFFFu;  // MYINFINITY, include/workloads/graphcompute.h:14
 
 struct GraphWlParams {
