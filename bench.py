@@ -573,8 +573,11 @@ def main() -> None:
             "wall_s_resident_run": t1 - t0,
         }
         if world == 1:
-            line["other_workloads"] = {"miniweather_3200x1600": miniweather_figures(api, hbm),
-                                       "graph_analytics": graph_workload_figures(api)}
+            line["other_workloads"] = {"miniweather_3200x1600": miniweather_figures(api, hbm)}
+            try:
+                line["other_workloads"]["graph_analytics"] = graph_workload_figures(api)
+            except Exception as e:  # noqa: BLE001 - a side figure must not cost the run its line
+                line["other_workloads"]["graph_analytics"] = {"error": repr(e)}
         if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
