@@ -174,6 +174,27 @@ def test_preempt_resume_bit_identical(gpx, graphs_on_disk):
             assert np.array_equal(ex.model.get(RESULT[algo]), want), f"{algo} trial {trial}"
             assert ex.model.graph_info()["converged"]
         assert stops_seen > 0, f"{algo}: no run was ever preempted"
+        # the same from a captured CUDA graph (a best-effort client with use_cuda_graph): the first
+        # launch is one graph launch, what a preemption leaves over is relaunched kernel by kernel
+        ex.capture_graph(s)
+        for trial in range(3):
+            word.clear()
+            time.sleep(0.001)
+            ex.execute(s)
+            delay = float(rng.uniform(0, run_us / 2))
+            t0 = time.perf_counter()
+            while (time.perf_counter() - t0) * 1e6 < delay:
+                pass
+            word.raise_()
+            s.sync()
+            word.clear()
+            time.sleep(0.0005)
+            rounds = 0
+            while ex.resume(s) != -1:
+                rounds += 1
+                assert rounds < 100
+            s.sync()
+            assert np.array_equal(ex.model.get(RESULT[algo]), want), f"{algo} graph launch, trial {trial}"
         ex.clear(), word.destroy(), s.destroy()
 
 
