@@ -38,7 +38,7 @@ enum GraphPhase {
 constexpr int kGwThreads = 256;
 constexpr int kGwEdgeTileVertsMax = 256;  // vertices per tile of an edge pass at most (32 per warp)
 constexpr int kGwVertexTileVerts = 1024;  // vertices per tile of a per-vertex pass
-constexpr int kGwMaxIters = 4096;         // iteration flags a graph workload has: no run may need more rounds
+constexpr int kGwMaxIters = 16384;        // iteration flags a graph workload has: no run may need more rounds
 constexpr unsigned kGwInfinity = 0xFFFFFFFFu;  // MYINFINITY, include/workloads/graphcompute.h:14
 
 struct GraphWlParams {

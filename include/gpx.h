@@ -300,7 +300,9 @@ int gpx_model_reductions(gpx_model *m, double *mass, double *te);
  * `listed_iterations` is the number of iterations in the kernel list (sized by one run when the model
  * was opened), `live_iterations` how many of them the latest run needed, `converged` is 0 if that run
  * used the whole list and still had work (pagerank: always 1, it stops after 100 iterations as
- * in graphcompute.cu:281).  Any of the output pointers may be NULL. */
+ * in graphcompute.cu:281).  Any of the output pointers may be NULL.  A graph on which an algorithm
+ * needs more than 16 382 rounds (a breadth-first search that deep) is refused when it is opened;
+ * the reference's host loop has no such limit. */
 int gpx_model_graph_info(gpx_model *m, uint64_t *vertices, uint64_t *edges, int *listed_iterations,
                          int *live_iterations, int *converged);
 

@@ -243,6 +243,15 @@ def test_isolated_vertices_and_tiny_graphs(gpx, tmp_path):
         "one": (np.array([0, 0], np.uint64), np.array([], np.uint64), np.array([], np.uint32)),
         "no_edges": (np.zeros(41, np.uint64), np.array([], np.uint64), np.array([], np.uint32)),
     }
+    # a path of 2 500 vertices: as many search levels as vertices, i.e. a kernel list of thousands
+    n = 2500
+    deg = np.full(n, 2, np.int64)
+    deg[[0, -1]] = 1
+    path_off = np.concatenate([[0], np.cumsum(deg)]).astype(np.uint64)
+    path_nb = np.empty(int(path_off[-1]), np.uint64)
+    for v in range(n):
+        path_nb[int(path_off[v]):int(path_off[v + 1])] = [u for u in (v - 1, v + 1) if 0 <= u < n]
+    cases["path"] = (path_off, path_nb, (np.arange(len(path_nb)) % 5 + 1).astype(np.uint32))
     for name, (offsets, neighbours, weights) in cases.items():
         prefix = str(tmp_path / name / (name + ".bel"))
         graph_files.write_bel(prefix, offsets, neighbours, weights)
@@ -255,6 +264,8 @@ def test_isolated_vertices_and_tiny_graphs(gpx, tmp_path):
             ex.execute()
             _check(algo, ex.model.get(RESULT[algo]), want[algo], name)
             assert ex.model.graph_info()["converged"]
+            if name == "path" and algo == "bfs":
+                assert ex.model.graph_info()["live_iterations"] == n and ex.get_kernel_num() == n + 3
             ex.clear()
         # pagerank: a vertex nobody points at keeps 1 - alpha (its own delta, infinite without
         # out-edges as in the reference, is never read)
@@ -264,7 +275,7 @@ def test_isolated_vertices_and_tiny_graphs(gpx, tmp_path):
         ex.execute()
         rank = ex.model.get("value")
         assert np.all(np.isfinite(rank))
-        if name != "six":
+        if name in ("one", "no_edges"):
             assert np.allclose(rank, 1 - g.ALPHA)
         else:
             _check("pagerank", rank, g.pagerank(offsets, neighbours)[0], name)
