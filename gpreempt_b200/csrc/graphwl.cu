@@ -144,6 +144,62 @@ __device__ __forceinline__ void pagerank_vertex(const GraphWlParams &p, unsigned
     }
 }
 
+// Two neighbouring vertices at once: their edge lists are walked in the same rounds, so twice as many
+// loads are in flight per lane and the pair costs the latency chain of one.  Each vertex's sum is
+// taken in the same order as pagerank_vertex takes it, so it does not matter which of the two
+// functions a vertex meets.
+__device__ __forceinline__ void pagerank_pair(const GraphWlParams &p, unsigned v0, unsigned long long b0,
+                                              unsigned long long e0, unsigned long long b1, unsigned long long e1,
+                                              int lane) {
+    const float *dold = reinterpret_cast<const float *>((p.iter & 1) ? p.d1 : p.d0);
+    float *dnew = reinterpret_cast<float *>((p.iter & 1) ? p.d0 : p.d1);
+    float *value = reinterpret_cast<float *>(p.a), *residual = reinterpret_cast<float *>(p.b);
+    float left = 0.f, val = 0.f, deg = 1.f;  // lane 0: v0, lane 1: v0 + 1
+    if (lane < 2) {
+        left = residual[v0 + lane];
+        val = value[v0 + lane];
+        deg = (float)p.outdeg[v0 + lane];
+    }
+    float s0 = 0.f, s1 = 0.f;
+    unsigned long long i0 = b0 + lane, i1 = b1 + lane;
+    while (i0 - lane < e0 || i1 - lane < e1) {
+        unsigned u0[kGwUnroll], u1[kGwUnroll];
+        float d0[kGwUnroll], d1[kGwUnroll];
+#pragma unroll
+        for (int k = 0; k < kGwUnroll; ++k) {
+            u0[k] = i0 + 32 * k < e0 ? p.adj[i0 + 32 * k] : kGwInfinity;
+            u1[k] = i1 + 32 * k < e1 ? p.adj[i1 + 32 * k] : kGwInfinity;
+        }
+#pragma unroll
+        for (int k = 0; k < kGwUnroll; ++k) {
+            d0[k] = u0[k] != kGwInfinity ? dold[u0[k]] : 0.f;
+            d1[k] = u1[k] != kGwInfinity ? dold[u1[k]] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < kGwUnroll; ++k) {
+            s0 += d0[k];
+            s1 += d1[k];
+        }
+        i0 += 32 * kGwUnroll;
+        i1 += 32 * kGwUnroll;
+    }
+    s0 = warp_sum(s0);
+    s1 = warp_sum(s1);
+    if (lane < 2) {
+        const unsigned v = v0 + lane;
+        const float r = left + (lane == 0 ? s0 : s1);
+        if (r > p.tol) {
+            value[v] = val + r;
+            dnew[v] = r * p.alpha / deg;
+            residual[v] = 0.f;
+            p.active[p.iter + 1] = 1;
+        } else {
+            residual[v] = r;
+            dnew[v] = 0.f;
+        }
+    }
+}
+
 // One tile of an edge pass: p.tile_verts neighbouring vertices, an eighth of them per warp.  The
 // first lanes of a warp fetch, for its vertices at once, whether the vertex takes part and where its
 // edge list lies; the warp then walks the lists one after another.  Neighbouring vertices of a
@@ -166,6 +222,17 @@ __device__ __forceinline__ void edge_tile(const GraphWlParams &p, int tile) {
             beg = p.row[mine];
             end = p.row[mine + 1];
         }
+    }
+    if (ALGO == GW_PAGERANK) {
+        // every vertex takes part: walk the lists two at a time
+        int j = 0;
+#pragma unroll 1
+        for (; j + 1 < per_warp && first + j + 1 < p.n; j += 2)
+            pagerank_pair(p, (unsigned)(first + j), __shfl_sync(0xffffffffu, beg, j), __shfl_sync(0xffffffffu, end, j),
+                          __shfl_sync(0xffffffffu, beg, j + 1), __shfl_sync(0xffffffffu, end, j + 1), lane);
+        if (j < per_warp && first + j < p.n)
+            pagerank_vertex(p, (unsigned)(first + j), __shfl_sync(0xffffffffu, beg, j), __shfl_sync(0xffffffffu, end, j), lane);
+        return;
     }
 #pragma unroll 1
     for (int j = 0; j < per_warp; ++j) {
@@ -482,10 +549,11 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
     base.tol = 0.001f;
     // Vertices per tile of the edge passes.  The searches touch few vertices per pass, and what a
     // CTA pays per tile is the latency of asking which: larger tiles, fewer rounds.  PageRank walks
-    // every edge list in every pass and balances better in small tiles.  (52 804 vertices with about
-    // 200 edges each: bfs 1.21 / 0.58 / 0.40 ms a run with 8 / 32 / 64, pagerank 1.60 / 2.08 / 2.09.)
+    // every edge list in every pass and balances better in small tiles: two vertices per warp, walked
+    // together.  (52 804 vertices with about 200 edges each: bfs 1.21 / 0.58 / 0.40 ms a run with 8 /
+    // 32 / 64; pagerank, one list at a time, 1.60 / 2.08 / 2.09.)
     {
-        const int by_algo[4] = {64, 32, 32, 8};
+        const int by_algo[4] = {64, 32, 32, 16};
         base.tile_verts = by_algo[algo];
         const char *e = getenv("GPX_GRAPH_TILE");
         if (e && atoi(e) >= 8) base.tile_verts = std::min(atoi(e) / 8 * 8, kGwEdgeTileVertsMax);
