@@ -282,19 +282,19 @@ def test_isolated_vertices_and_tiny_graphs(gpx, tmp_path):
         ex.clear()
 
 
-def test_best_effort_tenants_under_a_latency_critical_model(gpx, graphs_on_disk):
-    """The shape of the reference's config/Z.json: the four graph workloads as periodic best-effort
-    tenants (client key graph_path) under a latency-critical DNN."""
-    prefix = graphs_on_disk["crank"]
-    tasks = [{"id": "vgg_rt", "load": {"type": "periodic", "priority": 0, "frequency": 100},
-              "client": {"name": "vgg_rt", "model_name": "vgg", "priority": 0, "batch_size": 1,
-                         "use_cuda_graph": True, "preprocess_time": 200,
-                         "graph_path": prefix}}]  # ignored by a model that is not a graph workload
-    for algo in ALGOS:
-        tasks.append({"id": algo + "_be", "load": {"type": "periodic", "priority": 0, "frequency": 100},
-                      "client": {"name": algo + "_be", "model_name": algo, "priority": 1, "batch_size": 1,
-                                 "use_cuda_graph": False, "preprocess_time": 200, "graph_path": prefix}})
-    cfg = {"time": 1.5, "seed": 3, "warmup": 2, "standalone": 2, "tasks": tasks}
+def test_best_effort_tenants_under_a_latency_critical_model(gpx, graphs_on_disk, monkeypatch):
+    """config/Z_graph_analytics.json, the shape of the reference's config/Z.json: the four graph
+    workloads as periodic best-effort tenants (client key graph_path, relative to the dataset
+    directory) under a latency-critical DNN."""
+    prefix = graphs_on_disk["crank"]  # <root>/crank/crank.bel, as the shipped configuration names it
+    monkeypatch.setenv("GPX_GRAPH_BASE_PATH", os.path.dirname(os.path.dirname(prefix)))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "config", "Z_graph_analytics.json")) as f:
+        cfg = json.load(f)
+    tasks = cfg["tasks"]
+    assert [t["client"]["model_name"] for t in tasks] == ["vgg", "bfs", "sssp", "pagerank", "cc"]
+    tasks[0]["client"]["graph_path"] = prefix  # ignored by a model that is not a graph workload
+    cfg.update({"time": 1.5, "seed": 3, "warmup": 2, "standalone": 2})
     rep = json.loads(gpx.run_workload("gpreemptclient", json.dumps(cfg)))
     by_id = {t["id"]: t for t in rep["tasks"]}
     assert 130 <= by_id["vgg_rt"]["requests"] <= 151
