@@ -108,7 +108,7 @@ def write_from_mtx(prefix: str, mtx: str, seed: int = 1) -> dict:
     from scipy.io import mmread
     from scipy.sparse import csr_matrix
 
-    m = csr_matrix(mmread(mtx))
+    m = csr_matrix(mmread(mtx, spmatrix=False))
     m.sort_indices()
     write_bel(prefix, m.indptr, m.indices, synthetic_weights(m.nnz, seed))
     return {"prefix": prefix, "vertices": int(m.shape[0]), "edges": int(m.nnz)}

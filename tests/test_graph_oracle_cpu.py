@@ -163,3 +163,25 @@ def test_oracle_matches_results_of_the_reference_kernels(which):
             assert hashlib.sha256(arr.astype(np.uint64).tobytes()).hexdigest() == want["sha256"], algo
             if "values" in want:
                 assert arr.astype(np.uint64).tolist() == want["values"], algo
+
+
+def test_graph_files_from_a_matrix_market_file(tmp_path):
+    """--from-mtx: the route for a user who has the reference's dataset as SuiteSparse ships it."""
+    from scipy.io import mmwrite
+    from scipy.sparse import random as sparse_random
+
+    m = sparse_random(60, 60, density=0.08, random_state=3, format="coo")
+    m = ((m + m.T) > 0).astype(np.float64).tocoo()
+    mmwrite(str(tmp_path / "m.mtx"), m)
+    info = graph_files.write_from_mtx(str(tmp_path / "m.bel"), str(tmp_path / "m.mtx"))
+    offsets, neighbours, weights = graph_files.read_bel(str(tmp_path / "m.bel"))
+    csr = m.tocsr()
+    csr.sort_indices()
+    assert info == {"prefix": str(tmp_path / "m.bel"), "vertices": 60, "edges": int(csr.nnz)}
+    assert np.array_equal(offsets, csr.indptr.astype(np.uint64))
+    assert np.array_equal(neighbours, csr.indices.astype(np.uint64))
+    assert len(weights) == csr.nnz and weights.min() >= 1
+    comp, _ = graphs.cc(offsets, neighbours)
+    from scipy.sparse.csgraph import connected_components
+
+    assert len(np.unique(comp)) == connected_components(csr, directed=False)[0]
