@@ -202,7 +202,7 @@ __device__ __forceinline__ void pagerank_pair(const GraphWlParams &p, unsigned v
 
 // One tile of an edge pass: p.tile_verts neighbouring vertices, an eighth of them per warp.  The
 // first lanes of a warp fetch, for its vertices at once, whether the vertex takes part and where its
-// edge list lies; the warp then walks the lists one after another.  Neighbouring vertices of a
+// edge list lies; the warp then walks the lists one after another (PageRank: two at a time).  Neighbouring vertices of a
 // graph with locality share neighbours, so their reads of labels, distances, ids and deltas hit the
 // same cache lines (tiles of vertices spread over the whole graph were tried: 1.8 to 2.7 times slower
 // on the searches).
@@ -242,7 +242,6 @@ __device__ __forceinline__ void edge_tile(const GraphWlParams &p, int tile) {
         if (ALGO == GW_BFS) bfs_vertex(p, u, b, e, lane);
         if (ALGO == GW_SSSP) sssp_vertex(p, u, b, e, lane);
         if (ALGO == GW_CC) cc_vertex(p, u, b, e, lane);
-        if (ALGO == GW_PAGERANK) pagerank_vertex(p, u, b, e, lane);
     }
 }
 
