@@ -528,15 +528,15 @@ int build_graph_workload(gpx_model &m, const std::string &name, const gpx_model_
         const char *base = getenv("GPX_GRAPH_BASE_PATH");
         if (base && base[0]) path = std::string(base) + "/" + path;
     }
+    // The files first: what is wrong with them can be told without a GPU.
+    HostGraph g;
+    GPX_TRY(read_graph_files(path, algo == GW_SSSP, g));
     const DeviceInfo &d = device_info();
     GPX_REQUIRE(d.device >= 0, GPX_FAIL, "gpx_init was not called");
     m.device = d.device;
     m.sm_count = d.sm_count;
     m.sci = true;
     m.graph_algo = algo;
-
-    HostGraph g;
-    GPX_TRY(read_graph_files(path, algo == GW_SSSP, g));
     m.graph_vertices = g.n;
     m.graph_edges = g.e;
 

@@ -185,3 +185,50 @@ def test_graph_files_from_a_matrix_market_file(tmp_path):
     from scipy.sparse.csgraph import connected_components
 
     assert len(np.unique(comp)) == connected_components(csr, directed=False)[0]
+
+
+def test_library_refuses_broken_graph_files_before_it_needs_a_gpu(tmp_path):
+    """gpx_model_open("bfs:<prefix>") reads the files first, so their errors are reported where no GPU
+    is: a missing file is NotFound (3), a malformed one Fail (1), too many vertices OutOfRange (4);
+    a good one gets as far as asking for the device."""
+    from gpreempt_b200 import api
+
+    def status_of(name):
+        with pytest.raises(api.GpxError) as e:
+            api.Model(name)
+        return e.value.status, str(e.value)
+
+    assert status_of("bfs")[0] == 3 and "needs a graph" in status_of("bfs")[1]
+    assert status_of("bfs:" + str(tmp_path / "nothing.bel"))[0] == 3
+    offsets, neighbours = graph_files.synthetic_banded(200, 8, 12, 1)
+    weights = graph_files.synthetic_weights(len(neighbours), 1)
+    good = str(tmp_path / "good.bel")
+    graph_files.write_bel(good, offsets, neighbours, weights)
+    st, text = status_of("sssp:" + good)
+    assert st == 1 and "gpx_init" in text  # the files were accepted
+
+    def variant(name, offs=offsets, nbs=neighbours, wts=weights, cut=None):
+        prefix = str(tmp_path / name)
+        # written by hand: write_bel refuses these itself
+        for ext, head, arr in ((".col", len(offs), np.asarray(offs, np.uint64)), (".dst", len(nbs), np.asarray(nbs, np.uint64)),
+                               (".val", len(wts), np.asarray(wts, np.uint32))):
+            with open(prefix + ext, "wb") as f:
+                np.array([head, 8], np.uint64).tofile(f)
+                arr.tofile(f)
+        if cut:
+            with open(prefix + cut, "r+b") as f:
+                f.truncate(16 + 8)
+        return prefix
+
+    bad_id = neighbours.copy()
+    bad_id[5] = 200
+    assert "points at vertex" in status_of("cc:" + variant("bad_id.bel", nbs=bad_id))[1]
+    down = offsets.copy()
+    down[10], down[11] = down[11], down[10]
+    assert "offsets decrease" in status_of("cc:" + variant("down.bel", offs=down))[1]
+    assert "offsets run from" in status_of("cc:" + variant("short.bel", nbs=neighbours[:-3], wts=weights[:-3]))[1]
+    assert "shorter than its header" in status_of("cc:" + variant("cut.bel", cut=".dst"))[1]
+    assert "weights for" in status_of("sssp:" + variant("few_w.bel", wts=weights[:10]))[1]
+    os.remove(variant("no_w.bel") + ".val")
+    assert status_of("sssp:" + str(tmp_path / "no_w.bel"))[0] == 3
+    assert status_of("bfs:" + str(tmp_path / "no_w.bel"))[1].count("gpx_init") == 1  # bfs needs no weights
